@@ -1,0 +1,174 @@
+"""Python front end of the tcgen05 batched GEMM (``csrc/ns_gemm_sm100.cu``).
+
+``ns_gemm`` computes ``C = alpha * s^pa * A @ op(B) + beta * s^pb * D`` on bf16 batches, where
+``op(B)`` is ``B^T`` for ``B`` given as ``[N, K]`` and ``B`` itself for ``B`` given as ``[K, N]``.
+With ``sym=True`` only the upper-triangle tiles are computed and mirrored.  It stands in for the
+reference's three Triton kernels and its cuBLAS ``baddbmm`` call
+(dion/newton_schulz_triton.py:160-198, 290-333, 450-491, 557-563).
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Dict, Optional, Tuple
+
+import torch
+from torch import Tensor
+
+from . import _backend
+
+_BM = 128
+_tile_cache: Dict[Tuple, Tensor] = {}
+_status: Dict[int, Tensor] = {}
+_sm_count: Dict[int, int] = {}
+
+STATUS_MESSAGES = {
+    1: "MMA warp timed out waiting for a TMA stage",
+    2: "TMA producer timed out waiting for a free stage",
+    3: "epilogue timed out waiting for an accumulator",
+    4: "MMA warp timed out waiting for a drained accumulator",
+    5: "wait on a peer GPU's flag timed out",
+    6: "bad arguments",
+}
+
+
+def status_tensor(device: torch.device) -> Tensor:
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    t = _status.get(idx)
+    if t is None:
+        t = torch.zeros(4, dtype=torch.int32, device=torch.device("cuda", idx))
+        _status[idx] = t
+    return t
+
+
+def check_status(device: Optional[torch.device] = None) -> None:
+    """Read the device status word (synchronizes) and raise if a kernel reported a timeout."""
+    devs = list(_status) if device is None else [device.index or 0]
+    for idx in devs:
+        t = _status.get(idx)
+        if t is None:
+            continue
+        code = int(t[0].item())
+        if code != 0:
+            t.zero_()
+            raise RuntimeError(
+                f"dion_b200 kernel error on cuda:{idx}: {STATUS_MESSAGES.get(code, code)}"
+            )
+
+
+def sm_count(device: torch.device) -> int:
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    n = _sm_count.get(idx)
+    if n is None:
+        n = torch.cuda.get_device_properties(idx).multi_processor_count
+        _sm_count[idx] = n
+    return n
+
+
+def tile_table(M: int, N: int, bn: int, sym: bool, device: torch.device) -> Tensor:
+    """Device array of (tile_m, tile_n) pairs.  For ``sym`` only tiles that intersect the
+    upper triangle (column range reaching the tile's first row) are listed."""
+    key = (M, N, bn, sym, device.index)
+    t = _tile_cache.get(key)
+    if t is not None:
+        return t
+    tm_n = (M + _BM - 1) // _BM
+    tn_n = (N + bn - 1) // bn
+    pairs = []
+    for tm in range(tm_n):
+        for tn in range(tn_n):
+            if sym and (tn + 1) * bn - 1 < tm * _BM:
+                continue
+            pairs.append((tm, tn))
+    t = torch.tensor(pairs, dtype=torch.int32, device=device).contiguous()
+    _tile_cache[key] = t
+    return t
+
+
+def _p(t: Optional[Tensor]) -> ctypes.c_void_p:
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _as3d(t: Tensor) -> Tensor:
+    return t.unsqueeze(0) if t.ndim == 2 else t
+
+
+def _ld_stride(t: Tensor) -> Tuple[int, int]:
+    assert t.stride(-1) == 1, "innermost dimension must be contiguous"
+    ld = t.stride(-2)
+    bs = t.stride(0) if t.size(0) > 1 else t.size(-2) * ld
+    return ld, bs
+
+
+def supported(A: Tensor, B: Tensor) -> bool:
+    """True when the TMA constraints hold (16-byte aligned bases, strides multiples of 8)."""
+    for t in (A, B):
+        if t.dtype != torch.bfloat16 or not t.is_cuda or t.stride(-1) != 1:
+            return False
+        if t.data_ptr() % 16 or t.stride(-2) % 8:
+            return False
+        if t.ndim == 3 and t.size(0) > 1 and t.stride(0) % 8:
+            return False
+    return True
+
+
+def ns_gemm(
+    A: Tensor,
+    B: Tensor,
+    out: Optional[Tensor] = None,
+    *,
+    b_is_kn: bool = False,
+    D: Optional[Tensor] = None,
+    alpha: float = 1.0,
+    beta: float = 0.0,
+    scale: Optional[Tensor] = None,
+    alpha_pow: int = 0,
+    beta_pow: int = 0,
+    sym: bool = False,
+    out_t: Optional[Tensor] = None,
+    out_f32: Optional[Tensor] = None,
+    bn: Optional[int] = None,
+) -> Tensor:
+    A3, B3 = _as3d(A), _as3d(B)
+    batch, M, K = A3.shape
+    N = B3.size(-1) if b_is_kn else B3.size(-2)
+    assert (B3.size(-2) if b_is_kn else B3.size(-1)) == K and B3.size(0) == batch
+    if not supported(A3, B3):
+        raise ValueError("ns_gemm operands violate the TMA alignment rules; see supported()")
+    dev = A.device
+    if out is None and out_f32 is None:
+        out = torch.empty((batch, M, N), dtype=torch.bfloat16, device=dev)
+        if A.ndim == 2:
+            out = out[0]
+    C3 = _as3d(out) if out is not None else None
+    Cf3 = _as3d(out_f32) if out_f32 is not None else None
+    tgt = Cf3 if Cf3 is not None else C3
+    ldc, sc = _ld_stride(tgt)
+    D3 = _as3d(D) if D is not None else None
+    ldd, sd = _ld_stride(D3) if D3 is not None else (0, 0)
+    CT3 = _as3d(out_t) if out_t is not None else None
+    ldct, sct = _ld_stride(CT3) if CT3 is not None else (0, 0)
+    lda, sa = _ld_stride(A3)
+    ldb, sb = _ld_stride(B3)
+    if bn is None:
+        bn = 256 if N > 128 else 128
+    tiles = tile_table(M, N, bn, sym, dev)
+    if scale is not None:
+        assert scale.dtype == torch.float32 and scale.numel() >= batch
+    st = status_tensor(dev)
+    rc = _backend.lib("ns_gemm_sm100").dion_ns_gemm(
+        _p(A3), ctypes.c_longlong(lda), ctypes.c_longlong(sa),
+        _p(B3), ctypes.c_longlong(ldb), ctypes.c_longlong(sb), ctypes.c_int(1 if b_is_kn else 0),
+        _p(C3), ctypes.c_longlong(ldc), ctypes.c_longlong(sc),
+        _p(D3), ctypes.c_longlong(ldd), ctypes.c_longlong(sd),
+        _p(CT3), ctypes.c_longlong(ldct), ctypes.c_longlong(sct),
+        _p(Cf3),
+        ctypes.c_int(batch), ctypes.c_int(M), ctypes.c_int(N), ctypes.c_int(K),
+        ctypes.c_float(alpha), ctypes.c_float(beta), _p(scale),
+        ctypes.c_int(alpha_pow), ctypes.c_int(beta_pow), ctypes.c_int(1 if sym else 0),
+        _p(tiles), ctypes.c_int(tiles.size(0)), ctypes.c_int(bn),
+        ctypes.c_int(sm_count(dev)), _p(st),
+        ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream),
+    )
+    if rc != 0:
+        raise RuntimeError(f"dion_ns_gemm launch failed with code {rc}")
+    return out if out is not None else out_f32
