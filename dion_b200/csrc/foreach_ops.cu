@@ -101,14 +101,14 @@ __device__ __forceinline__ float block_sum(float v) {
 }
 
 // Iterates the 4-element groups of this block's chunk: f(i, count) with count in 1..4.
-#define DION_CHUNK_LOOP(tb, BODY)                                                       \
+#define DION_CHUNK_LOOP(tb, ...)                                                        \
   const int t = find_tensor(tb, blockIdx.x);                                            \
   const long long numel = tb.numel(t);                                                  \
   const long long base = ((long long)blockIdx.x - tb.prefix()[t]) * kChunk;             \
   const long long end = (base + kChunk < numel) ? base + kChunk : numel;                \
   for (long long i = base + (long long)threadIdx.x * 4; i < end; i += kThreads * 4) {   \
     const bool full = (i + 4 <= end);                                                   \
-    BODY                                                                                \
+    __VA_ARGS__                                                                         \
   }
 
 // ---------------------------------------------------------------------------------------------

@@ -1,0 +1,284 @@
+// Dion2 / NorDion2 sub-matrix selection on sm_100a.
+//
+//   1. slice_norms : M += G (optional) fused with the L1 norm of every row or column of M
+//   2. topk_select : exact top-k of the slice norms per matrix (radix select on the float bits,
+//                    ties broken by lowest index so the result is deterministic), writing the
+//                    selected indices and an inverse map (slice -> position or -1)
+//   3. gather_ef   : copy the selected slices to a dense bf16 matrix and scale them in M by the
+//                    error-feedback factor
+//
+// Together these replace the reference's compiled dion2_pre_orthogonalize
+// (dion/dion2.py:437-547: foreach add, stacked norm, torch.topk, gather, per-parameter scatter_).
+#include "common.cuh"
+
+namespace dion {
+
+enum : int { DT_F32 = 0, DT_BF16 = 1 };
+
+__device__ __forceinline__ float ldv(const void* p, int dt, long long i) {
+  return dt == DT_F32 ? reinterpret_cast<const float*>(p)[i]
+                      : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i]);
+}
+__device__ __forceinline__ void stv(void* p, int dt, long long i, float v) {
+  if (dt == DT_F32) reinterpret_cast<float*>(p)[i] = v;
+  else reinterpret_cast<__nv_bfloat16*>(p)[i] = __float2bfloat16_rn(v);
+}
+__device__ __forceinline__ float rnd(float v, int dt) {
+  return dt == DT_F32 ? v : __bfloat162float(__float2bfloat16_rn(v));
+}
+
+// ptrs: device array [2][n] of int64 = G pointers (may be 0) then M pointers.
+// Row selection: one warp per row.
+__global__ void __launch_bounds__(256)
+row_norms_kernel(const long long* ptrs, int n, int rows, int cols, int g_dt, int m_dt,
+                 float* norms) {
+  const long long wid = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (wid >= (long long)n * rows) return;
+  const int t = (int)(wid / rows), r = (int)(wid - (long long)t * rows);
+  const void* G = reinterpret_cast<const void*>(ptrs[t]);
+  void* M = reinterpret_cast<void*>(ptrs[n + t]);
+  const long long off = (long long)r * cols;
+  float s = 0.f;
+  for (int c = lane; c < cols; c += 32) {
+    float m = ldv(M, m_dt, off + c);
+    if (G) {
+      m = rnd(m + rnd(ldv(G, g_dt, off + c), m_dt), m_dt);
+      stv(M, m_dt, off + c, m);
+    }
+    s += fabsf(m);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+  if (lane == 0) norms[wid] = s;
+}
+
+// Column selection: thread = column, block covers 64 columns x a strip of rows; partial column
+// sums are accumulated with atomics into norms (zeroed by the caller).
+constexpr int kColStrip = 128;
+__global__ void __launch_bounds__(256)
+col_norms_kernel(const long long* ptrs, int n, int rows, int cols, int g_dt, int m_dt,
+                 float* norms) {
+  const int t = blockIdx.z;
+  const int c = blockIdx.x * 64 + (threadIdx.x & 63);
+  const int rlane = threadIdx.x >> 6;  // 0..3
+  const int r0 = blockIdx.y * kColStrip;
+  const int r1 = min(rows, r0 + kColStrip);
+  if (c >= cols) return;
+  const void* G = reinterpret_cast<const void*>(ptrs[t]);
+  void* M = reinterpret_cast<void*>(ptrs[n + t]);
+  float s = 0.f;
+  for (int r = r0 + rlane; r < r1; r += 4) {
+    const long long e = (long long)r * cols + c;
+    float m = ldv(M, m_dt, e);
+    if (G) {
+      m = rnd(m + rnd(ldv(G, g_dt, e), m_dt), m_dt);
+      stv(M, m_dt, e, m);
+    }
+    s += fabsf(m);
+  }
+  atomicAdd(&norms[(long long)t * cols + c], s);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Exact top-k per matrix.  One block of 1024 threads per matrix; norms are non-negative, so the
+// float bit pattern orders like an unsigned integer.
+// ---------------------------------------------------------------------------------------------
+constexpr int kSelThreads = 1024;
+
+__device__ __forceinline__ int block_exclusive_scan(int v, int* total, int* warp_sums) {
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  int x = v;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    int y = __shfl_up_sync(0xffffffffu, x, o);
+    if (lane >= o) x += y;
+  }
+  __syncthreads();
+  if (lane == 31) warp_sums[w] = x;
+  __syncthreads();
+  if (w == 0) {
+    int s = warp_sums[lane];
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      int y = __shfl_up_sync(0xffffffffu, s, o);
+      if (lane >= o) s += y;
+    }
+    warp_sums[lane] = s;
+  }
+  __syncthreads();
+  const int warp_off = (w == 0) ? 0 : warp_sums[w - 1];
+  *total = warp_sums[31];
+  return warp_off + x - v;
+}
+
+__global__ void __launch_bounds__(kSelThreads)
+topk_select_kernel(const float* norms, int num, int k, long long* idx_out, int* map_out) {
+  __shared__ int hist[256];
+  __shared__ int warp_sums[32];
+  __shared__ uint32_t s_prefix;
+  __shared__ int s_remaining;
+  const int t = blockIdx.x;
+  const uint32_t* keys = reinterpret_cast<const uint32_t*>(norms + (long long)t * num);
+  long long* idx = idx_out + (long long)t * k;
+  int* map = map_out + (long long)t * num;
+
+  if (threadIdx.x == 0) { s_prefix = 0; s_remaining = k; }
+  __syncthreads();
+  // Radix select: after the loop s_prefix is the key of the k-th largest element.
+  for (int shift = 24; shift >= 0; shift -= 8) {
+    if (threadIdx.x < 256) hist[threadIdx.x] = 0;
+    __syncthreads();
+    const uint32_t prefix = s_prefix;
+    const uint32_t hi_mask = (shift == 24) ? 0u : (0xFFFFFFFFu << (shift + 8));
+    for (int i = threadIdx.x; i < num; i += kSelThreads) {
+      const uint32_t key = keys[i];
+      if ((key & hi_mask) == prefix) atomicAdd(&hist[(key >> shift) & 255], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      int rem = s_remaining;
+      int b = 255;
+      for (; b > 0; --b) {
+        if (hist[b] >= rem) break;
+        rem -= hist[b];
+      }
+      s_prefix = prefix | ((uint32_t)b << shift);
+      s_remaining = rem;
+    }
+    __syncthreads();
+  }
+  const uint32_t thr = s_prefix;
+  // s_remaining = how many elements equal to thr are taken (lowest indices first).
+  const int take_eq = s_remaining;
+  const int n_gt = k - take_eq;
+  int run_gt = 0, run_eq = 0;
+  for (int base = 0; base < num; base += kSelThreads) {
+    const int i = base + threadIdx.x;
+    uint32_t key = 0;
+    const bool in = i < num;
+    if (in) key = keys[i];
+    const int f_gt = (in && key > thr) ? 1 : 0;
+    const int f_eq = (in && key == thr) ? 1 : 0;
+    int tot_gt, tot_eq;
+    const int p_gt = block_exclusive_scan(f_gt, &tot_gt, warp_sums);
+    __syncthreads();
+    const int p_eq = block_exclusive_scan(f_eq, &tot_eq, warp_sums);
+    __syncthreads();
+    if (in) {
+      int pos = -1;
+      if (f_gt) pos = run_gt + p_gt;
+      else if (f_eq && run_eq + p_eq < take_eq) pos = n_gt + run_eq + p_eq;
+      map[i] = pos;
+      if (pos >= 0) idx[pos] = i;
+    }
+    run_gt += tot_gt;
+    run_eq += tot_eq;
+  }
+}
+
+// Row gather + error feedback.  grid = (k, n); U[t][j][:] = bf16(M[t][idx[j]][:]);
+// M[t][idx[j]][:] *= ef (skipped when ef_apply == 0).  M pointers from ptrs[n + t].
+__global__ void __launch_bounds__(256)
+gather_rows_kernel(const long long* ptrs, int n, int cols, int m_dt, const long long* idx, int k,
+                   __nv_bfloat16* U, long long u_stride, float ef, int ef_apply) {
+  const int j = blockIdx.x, t = blockIdx.y;
+  void* M = reinterpret_cast<void*>(ptrs[n + t]);
+  const long long r = idx[(long long)t * k + j];
+  const long long off = r * cols;
+  __nv_bfloat16* u = U + (long long)t * u_stride + (long long)j * cols;
+  for (int c = threadIdx.x; c < cols; c += 256) {
+    const float m = ldv(M, m_dt, off + c);
+    u[c] = __float2bfloat16_rn(m);
+    if (ef_apply) stv(M, m_dt, off + c, m * ef);
+  }
+}
+
+// Column gather: U[t][r][j] = bf16(M[t][r][idx[j]]); M *= ef at the selected columns.
+// grid = (ceil(rows/8), n); 256 threads = 8 rows x 32 column lanes.
+__global__ void __launch_bounds__(256)
+gather_cols_kernel(const long long* ptrs, int n, int rows, int cols, int m_dt,
+                   const long long* idx, int k, __nv_bfloat16* U, long long u_stride, float ef,
+                   int ef_apply) {
+  const int t = blockIdx.y;
+  const int r = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (r >= rows) return;
+  void* M = reinterpret_cast<void*>(ptrs[n + t]);
+  const long long* id = idx + (long long)t * k;
+  __nv_bfloat16* u = U + (long long)t * u_stride + (long long)r * k;
+  for (int j = threadIdx.x & 31; j < k; j += 32) {
+    const long long e = (long long)r * cols + id[j];
+    const float m = ldv(M, m_dt, e);
+    u[j] = __float2bfloat16_rn(m);
+    if (ef_apply) stv(M, m_dt, e, m * ef);
+  }
+}
+
+// Scatter rows of a dense bf16 [n][k][cols] into zero-initialised [n][rows][cols] (global scope).
+__global__ void __launch_bounds__(256)
+scatter_rows_kernel(const __nv_bfloat16* src, const long long* idx, int k, int cols,
+                    __nv_bfloat16* dst, int rows) {
+  const int j = blockIdx.x, t = blockIdx.y;
+  const long long r = idx[(long long)t * k + j];
+  const __nv_bfloat16* s = src + ((long long)t * k + j) * cols;
+  __nv_bfloat16* d = dst + ((long long)t * rows + r) * cols;
+  for (int c = threadIdx.x; c < cols; c += 256) d[c] = s[c];
+}
+
+}  // namespace dion
+
+using namespace dion;
+static inline cudaStream_t S(void* s) { return static_cast<cudaStream_t>(s); }
+static inline int rc() { return cudaGetLastError() == cudaSuccess ? 0 : -1; }
+
+// norms must hold n*rows (select_rows) or n*cols floats; for column selection it must be zeroed.
+DION_EXPORT int dion_slice_norms(const void* ptrs, int n, int rows, int cols, int g_dt, int m_dt,
+                                 int select_rows, float* norms, void* stream) {
+  if (n <= 0 || rows <= 0 || cols <= 0) return 0;
+  if (select_rows) {
+    const long long warps = (long long)n * rows;
+    row_norms_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, S(stream)>>>(
+        static_cast<const long long*>(ptrs), n, rows, cols, g_dt, m_dt, norms);
+  } else {
+    dim3 grid((cols + 63) / 64, (rows + kColStrip - 1) / kColStrip, n);
+    col_norms_kernel<<<grid, 256, 0, S(stream)>>>(static_cast<const long long*>(ptrs), n, rows,
+                                                  cols, g_dt, m_dt, norms);
+  }
+  return rc();
+}
+
+DION_EXPORT int dion_topk_select(const float* norms, int n, int num, int k, long long* idx,
+                                 int* map, void* stream) {
+  if (n <= 0 || num <= 0) return 0;
+  if (k <= 0 || k > num) return -2;
+  topk_select_kernel<<<n, kSelThreads, 0, S(stream)>>>(norms, num, k, idx, map);
+  return rc();
+}
+
+DION_EXPORT int dion_gather_ef(const void* ptrs, int n, int rows, int cols, int m_dt,
+                               const long long* idx, int k, int select_rows, void* U,
+                               long long u_stride, float ef, int ef_apply, void* stream) {
+  if (n <= 0 || k <= 0) return 0;
+  if (select_rows) {
+    dim3 grid(k, n);
+    gather_rows_kernel<<<grid, 256, 0, S(stream)>>>(static_cast<const long long*>(ptrs), n, cols,
+                                                    m_dt, idx, k, static_cast<__nv_bfloat16*>(U),
+                                                    u_stride, ef, ef_apply);
+  } else {
+    dim3 grid((rows + 7) / 8, n);
+    gather_cols_kernel<<<grid, 256, 0, S(stream)>>>(static_cast<const long long*>(ptrs), n, rows,
+                                                    cols, m_dt, idx, k,
+                                                    static_cast<__nv_bfloat16*>(U), u_stride, ef,
+                                                    ef_apply);
+  }
+  return rc();
+}
+
+DION_EXPORT int dion_scatter_rows(const void* src, const long long* idx, int n, int k, int cols,
+                                  void* dst, int rows, void* stream) {
+  if (n <= 0 || k <= 0) return 0;
+  dim3 grid(k, n);
+  scatter_rows_kernel<<<grid, 256, 0, S(stream)>>>(static_cast<const __nv_bfloat16*>(src), idx, k,
+                                                   cols, static_cast<__nv_bfloat16*>(dst), rows);
+  return rc();
+}

@@ -25,7 +25,7 @@ LIBDIR = _PKG / "_lib"
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
-    "-lineinfo", "-O3", "-std=c++17", "--use_fast_math",
+    "-lineinfo", "-O3", "-std=c++17",
     "--shared", "-Xcompiler", "-fPIC",
 ]
 
