@@ -1,0 +1,111 @@
+"""Low-rank building blocks of the Dion optimizer: power-iteration GEMMs, randomized
+Cholesky-QR orthogonalization, column normalization and the rank-r in-place updates
+(reference: dion/dion.py:1197-1558).
+
+All functions work on local (already un-wrapped) tensors; the callers own the collectives.
+Batched operands are ``[B, rows, cols]``.
+"""
+from __future__ import annotations
+
+import math
+from typing import Callable, List, Optional, Tuple
+
+import torch
+from torch import Tensor
+
+
+def sketch_rows(r: int, oversample: float) -> int:
+    """Number of sketch rows: ``oversample * r`` rounded up to a multiple of 128."""
+    return int(math.ceil(oversample * r / 128.0) * 128)
+
+
+def random_sketch(batch: int, k: int, m: int, dtype: torch.dtype, device: torch.device,
+                  generator: Optional[torch.Generator] = None) -> Tensor:
+    """Gaussian sketch ``S ~ N(0, 1/k)`` of shape ``[batch, k, m]``."""
+    S = torch.empty((batch, k, m), dtype=dtype, device=device)
+    S.normal_(std=math.sqrt(1.0 / k), generator=generator)
+    return S
+
+
+def householder_q(P: Tensor) -> Tensor:
+    """Orthonormal factor of a reduced QR in fp32 (used when rows <= cols)."""
+    Q, _ = torch.linalg.qr(P.to(torch.float32), mode="reduced")
+    return Q
+
+
+def qr_r_factor(A: Tensor) -> Tensor:
+    """Upper-triangular factor of ``A`` (fp32)."""
+    return torch.linalg.qr(A.to(torch.float32), mode="r")[1]
+
+
+def cholesky_upper(G: Tensor) -> Tensor:
+    """Upper Cholesky factor without raising on failure (NaNs propagate and are handled by
+    :func:`fix_all_zero_or_nan`)."""
+    return torch.linalg.cholesky_ex(G, upper=True)[0]
+
+
+def right_solve_upper(R: Tensor, P: Tensor) -> Tensor:
+    """``P @ R^-1`` for upper-triangular ``R``."""
+    return torch.linalg.solve_triangular(R, P, upper=True, left=False)
+
+
+def orthogonalize(P: Tensor, oversample: float = 1.25,
+                  generator: Optional[torch.Generator] = None,
+                  sketch: Optional[Tensor] = None) -> Tensor:
+    """Orthonormalize the columns of every ``P[b]`` (``[B, m, r]``), result in ``P.dtype``.
+
+    ``m <= r``: Householder QR.  Otherwise randomized Cholesky-QR: ``R1 = qr(S P).R``,
+    ``P <- P R1^-1`` (well conditioned), then ``R2 = chol(P^T P)``, ``P <- P R2^-1``."""
+    assert P.ndim >= 3, "expected a batch dimension"
+    dtype = P.dtype
+    m, r = P.shape[-2], P.shape[-1]
+    if m <= r:
+        return householder_q(P).to(dtype).contiguous()
+    if sketch is None:
+        sketch = random_sketch(P.size(0), sketch_rows(r, oversample), m, dtype, P.device, generator)
+    R1 = qr_r_factor(sketch @ P)
+    P32 = right_solve_upper(R1, P.to(torch.float32))
+    R2 = cholesky_upper(P32.mT @ P32)
+    return right_solve_upper(R2, P32).to(dtype).contiguous()
+
+
+def fix_all_zero_or_nan(P: Tensor, R: Tensor, Q_init: Tensor, B: Tensor) -> Tuple[Tensor, Tensor]:
+    """Branch-free guard: where the (local) momentum ``B[b]`` is entirely zero, return ``P = 0``
+    and ``R = Q_init``; elsewhere replace NaNs by zero.  Shards are judged independently so no
+    communication is needed."""
+    zero = (B == 0).all(dim=(-2, -1), keepdim=True)
+    keep = ~zero
+    return P.nan_to_num() * keep, R.nan_to_num() * keep + Q_init * zero
+
+
+def local_column_sum_sq(X: Tensor) -> Tensor:
+    """Per-column sum of squares in fp32, shape ``[..., 1, cols]``."""
+    return X.to(torch.float32).square().sum(dim=-2, keepdim=True)
+
+
+def column_normalize(X: Tensor, full_column_sum_sq: Optional[Tensor] = None,
+                     epsilon: float = 1e-8) -> Tensor:
+    """``X / (||X||_col + eps)`` computed in fp32; a row-sharded ``X`` passes the all-reduced
+    column sums of squares."""
+    X32 = X.to(torch.float32)
+    ss = X32.square().sum(dim=-2, keepdim=True) if full_column_sum_sq is None \
+        else full_column_sum_sq.to(torch.float32)
+    return (X32 / (ss.sqrt() + epsilon)).to(X.dtype)
+
+
+def foreach_baddbmm_(X: List[Tensor], A: Tensor, B: Tensor, alpha=1.0, beta=1.0,
+                     transpose: bool = False) -> None:
+    """``X[i] = beta*X[i] + alpha*(A[i] @ B[i]^T)`` (or ``B[i] @ A[i]^T`` when ``transpose``)."""
+    assert A.size(0) == B.size(0) == len(X)
+    upd = (B @ A.mT) if transpose else (A @ B.mT)
+    upd = torch._foreach_mul(list(upd.unbind(0)), alpha)
+    if not (isinstance(beta, float) and beta == 1.0):
+        torch._foreach_mul_(X, beta)
+    torch._foreach_add_(X, [u.to(x.dtype) for u, x in zip(upd, X)])
+
+
+def stack_for_power_iteration(M: List[Tensor], Q: List[Tensor], transposed: bool):
+    """``(M_batch, Q_batch)`` with ``M_batch[i] = M[i]^T`` when ``transposed``; ``Q`` is cast to
+    the momentum dtype."""
+    Mb = torch.stack([m.mT for m in M]) if transposed else torch.stack(M)
+    return Mb, torch.stack(Q).to(Mb.dtype)
