@@ -1,0 +1,402 @@
+#!/usr/bin/env python
+"""Headline benchmark: GPT-160M (12 layers, d_model 768, 12 heads, vocab 50304, seq 1024) trained
+with Dion2 (fraction 0.25, ef_decay 0.95, AdamW for embedding/head) under DDP, bf16 autocast with
+fp32 master weights, 32x1024 uniform-random tokens per GPU per step, random init at seed 0.
+
+    python bench.py --gpus N --steps K --warmup W [--impl reference]
+
+For N > 1 launch with ``python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N``.
+Rank 0 prints one JSON line.  ``value`` is whole-job tokens/s of the device-timed loop (inputs
+already on the GPU); ``e2e.value`` is tokens/s of the loop a user runs: every step copies its
+batch from pinned host memory, runs forward/backward/optimizer through the public API and reads
+the loss back to the host.  ``--impl reference`` runs the unmodified reference package from
+``baseline/_ref`` (its GPT model, its Dion2 with its Triton kernels, torch DDP) on the same
+configuration and prints the same line with ``"impl": "reference"``.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+
+MODEL = dict(n_layer=12, n_embd=768, n_head=12, vocab_size=50304, sequence_len=1024)
+DEVICE_BATCH = 32
+SEQ = 1024
+LR, FRACTION, MU, WD = 0.02, 0.25, 0.95, 0.01
+
+
+def parse() -> argparse.Namespace:
+    p = argparse.ArgumentParser()
+    p.add_argument("--gpus", type=int, default=1)
+    p.add_argument("--steps", type=int, default=20)
+    p.add_argument("--warmup", type=int, default=5)
+    p.add_argument("--impl", type=str, default="ours", choices=["ours", "reference"])
+    p.add_argument("--optimizer", type=str, default="dion2",
+                   choices=["dion2", "muon", "normuon", "nordion2", "dion"])
+    p.add_argument("--no-e2e", action="store_true")
+    return p.parse_args()
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.path = tempfile.mktemp(prefix="clocks_", suffix=".csv")
+        self.proc = None
+        self.gpu_index = gpu_index
+
+    def start(self) -> None:
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "200", "-i", str(self.gpu_index)],
+                stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, power, reasons = [], [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        try:
+            for line in open(self.path):
+                f = [c.strip() for c in line.split(",")]
+                if len(f) < 9:
+                    continue
+                try:
+                    sm.append(float(f[1])); mx.append(float(f[2])); power.append(float(f[3]))
+                except ValueError:
+                    continue
+                for name, val in zip(names, f[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+        finally:
+            try:
+                os.unlink(self.path)
+            except OSError:
+                pass
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": max(mx) if mx else None,
+                "power_w_max": max(power) if power else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def setup_dist(n_gpus: int):
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world != n_gpus:
+        raise SystemExit(f"--gpus {n_gpus} but WORLD_SIZE={world}; launch with torch.distributed.run")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    return rank, local_rank, world
+
+
+def time_loop(step_fn, steps: int, warmup: int, world: int, device, sampler=None,
+              on_start=None):
+    """Runs ``warmup`` untimed and ``steps`` timed calls of ``step_fn`` bracketed by
+    barrier + synchronize; returns the device time in ms (max over ranks)."""
+    import torch
+    import torch.distributed as dist
+
+    for _ in range(warmup):
+        step_fn()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    if sampler is not None:
+        sampler.start()
+    if on_start is not None:
+        on_start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step_fn()
+    e1.record()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    clocks = sampler.stop() if sampler is not None else None
+    if world > 1:
+        t = torch.tensor([ms], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    return ms, clocks
+
+
+def synthetic_batches(n: int, rank: int, device):
+    """``n`` (x, y) batches of uniform-random token ids in pinned host memory."""
+    import numpy as np
+    import torch
+
+    out = []
+    for i in range(n):
+        rng = np.random.default_rng([0, rank, i])
+        w = torch.from_numpy(rng.integers(0, MODEL["vocab_size"], size=DEVICE_BATCH * SEQ + 1,
+                                          dtype=np.int64))
+        host = torch.empty((2, DEVICE_BATCH, SEQ), dtype=torch.int64).pin_memory()
+        host[0].copy_(w[:-1].view(DEVICE_BATCH, SEQ))
+        host[1].copy_(w[1:].view(DEVICE_BATCH, SEQ))
+        out.append(host)
+    return out
+
+
+def emit(args, impl, ms, e2e_ms, clocks, launches, world, extra=None):
+    tokens = world * DEVICE_BATCH * SEQ * args.steps
+    value = tokens / (ms / 1e3)
+    line = {
+        "metric": "training throughput, GPT-160M Dion2 DDP (tokens/sec, whole job)",
+        "impl": impl,
+        "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic uniform-random token ids, random-init weights (seed 0)",
+        "config": {"model": "GPT-160M (12L, d768, 12 heads, vocab 50304)",
+                   "optimizer": f"{args.optimizer} fraction={FRACTION} ef_decay={MU} lr={LR} "
+                                f"wd={WD} + AdamW(embedding, head)",
+                   "global_batch": world * DEVICE_BATCH, "seq_len": SEQ,
+                   "parallelism": f"ddp{world}",
+                   "precision": "bf16 autocast, fp32 master weights and optimizer state",
+                   "l2": "working set per step (weights, activations, logits) is several GB, "
+                         "far larger than the 126 MB L2; no explicit flush"},
+        "clocks": clocks,
+        "gpu_launches": launches,
+    }
+    if e2e_ms is not None:
+        line["e2e"] = {"value": tokens / (e2e_ms / 1e3), "unit": "tokens/s",
+                       "ms_per_step": e2e_ms / args.steps,
+                       "h2d_bytes_per_step": 2 * DEVICE_BATCH * SEQ * 8,
+                       "d2h_bytes_per_step": 4}
+    if extra:
+        line.update(extra)
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------
+# our arm
+# ------------------------------------------------------------------------------------------------
+def run_ours(args) -> None:
+    import torch
+    import torch.distributed as dist
+    from torch.nn.parallel import DistributedDataParallel as DDP
+
+    sys.path.insert(0, ROOT)
+    import dion_b200
+    from dion_b200.models.gpt import GPT, GPTConfig
+    from dion_b200.ops import _backend
+
+    rank, local_rank, world = setup_dist(args.gpus)
+    device = torch.device("cuda", local_rank)
+    torch.manual_seed(0)
+    model = GPT(GPTConfig(**MODEL)).to(device)
+    model.init_weights()
+    call = DDP(model, device_ids=[local_rank]) if world > 1 else model
+    pg = call.process_group if world > 1 else None
+
+    groups = [dict(params=list(model.transformer.h.parameters())),
+              dict(params=list(model.transformer.wte.parameters()), algorithm="adamw", lr=LR,
+                   weight_decay=0),
+              dict(params=list(model.lm_head.parameters()), algorithm="adamw", lr=LR,
+                   weight_decay=0)]
+    name = args.optimizer
+    if name == "dion2":
+        opt = dion_b200.Dion2(groups, distributed_mesh=pg, lr=LR, fraction=FRACTION, ef_decay=MU,
+                              weight_decay=WD, use_polar_express=False)
+    elif name == "muon":
+        opt = dion_b200.Muon(groups, distributed_mesh=pg, lr=LR, mu=MU, weight_decay=WD,
+                             nesterov=True, use_polar_express=False)
+    elif name == "normuon":
+        opt = dion_b200.NorMuon(groups, distributed_mesh=pg, lr=LR, mu=MU, weight_decay=WD,
+                                nesterov=True, use_polar_express=False)
+    elif name == "nordion2":
+        opt = dion_b200.NorDion2(groups, distributed_mesh=pg, lr=LR, fraction=FRACTION, mu=MU,
+                                 weight_decay=WD, use_polar_express=False)
+    else:
+        opt = dion_b200.Dion(groups, replicate_mesh=pg, replicate_mesh_grad_sync=False,
+                             rank_fraction=FRACTION, lr=LR, mu=MU, weight_decay=WD)
+
+    autocast = torch.autocast(device_type="cuda", dtype=torch.bfloat16)
+    host = synthetic_batches(4, rank, device)
+    dev_batches = [h.to(device) for h in host]
+    state = {"i": 0, "loss": None}
+
+    def step_device():
+        xy = dev_batches[state["i"] % len(dev_batches)]
+        state["i"] += 1
+        with autocast:
+            loss = call(xy[0], xy[1])
+        loss.backward()
+        opt.step()
+        call.zero_grad(set_to_none=True)
+        state["loss"] = loss.detach()
+
+    def step_e2e():
+        xy = host[state["i"] % len(host)].to(device, non_blocking=True)
+        state["i"] += 1
+        with autocast:
+            loss = call(xy[0], xy[1])
+        loss.backward()
+        opt.step()
+        call.zero_grad(set_to_none=True)
+        state["loss_host"] = loss.item()
+
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    ms, clocks = time_loop(step_device, args.steps, args.warmup, world, device, sampler,
+                           on_start=_backend.reset_launch_count)
+    launches = _backend.launch_count()
+    from dion_b200.ops.gemm import check_status
+
+    check_status()
+    e2e_ms = None
+    if not args.no_e2e:
+        e2e_ms, _ = time_loop(step_e2e, args.steps, 2, world, device, None)
+    if rank == 0:
+        emit(args, "ours", ms, e2e_ms, clocks, launches, world,
+             {"final_loss": float(state["loss"].item())})
+    if world > 1:
+        dist.destroy_process_group()
+
+
+# ------------------------------------------------------------------------------------------------
+# reference arm
+# ------------------------------------------------------------------------------------------------
+def run_reference(args) -> None:
+    ref_root = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref_root, "dion")):
+        print(json.dumps({"impl": "reference",
+                          "unavailable": "baseline/_ref is missing (reference not installed)"}))
+        return
+    sys.path.insert(0, ref_root)
+    try:
+        import torch
+        import torch.distributed as dist
+        from torch.nn.parallel import DistributedDataParallel as DDP
+
+        import dion as ref_dion                      # the reference package
+        from models.gpt_model import GPT, GPTConfig  # the reference model (baseline/_ref/models)
+    except Exception as exc:  # noqa: BLE001
+        print(json.dumps({"impl": "reference",
+                          "unavailable": f"reference import failed: {type(exc).__name__}: {exc}"}))
+        return
+    if not ref_dion.__file__.startswith(ref_root):
+        print(json.dumps({"impl": "reference",
+                          "unavailable": "import dion did not resolve to baseline/_ref"}))
+        return
+
+    rank, local_rank, world = setup_dist(args.gpus)
+    device = torch.device("cuda", local_rank)
+    torch.manual_seed(0)
+    model = GPT(GPTConfig(**MODEL)).to(device)
+    model.init_weights()
+    compiled = True
+    try:
+        model.compile()  # the reference trainer's stock path (train.py:815-816)
+    except Exception:  # noqa: BLE001
+        compiled = False
+    call = DDP(model, device_ids=[local_rank]) if world > 1 else model
+    pg = call.process_group if world > 1 else None
+    groups = [dict(params=list(model.transformer.h.parameters())),
+              dict(params=list(model.transformer.wte.parameters()), algorithm="adamw", lr=LR,
+                   betas=(0.95, 0.98), weight_decay=0),
+              dict(params=list(model.lm_head.parameters()), algorithm="adamw", lr=LR,
+                   betas=(0.95, 0.98), weight_decay=0)]
+    # Arguments as the reference trainer builds them (train.py:448-470): Triton Newton-Schulz and
+    # the Triton post-update on, Polar-Express off.
+    name = args.optimizer
+    if name == "dion2":
+        opt = ref_dion.Dion2(groups, distributed_mesh=pg, lr=LR, fraction=FRACTION, ef_decay=MU,
+                             weight_decay=WD, adjust_lr="spectral_norm", use_triton=True,
+                             use_polar_express=False, verbose=False, triton_post_ortho=True)
+    elif name == "muon":
+        opt = ref_dion.Muon(groups, distributed_mesh=pg, lr=LR, mu=MU, weight_decay=WD,
+                            nesterov=True, use_triton=True, use_polar_express=False)
+    elif name == "normuon":
+        opt = ref_dion.NorMuon(groups, distributed_mesh=pg, lr=LR, mu=MU, weight_decay=WD,
+                               nesterov=True, use_triton=True, use_polar_express=False)
+    elif name == "nordion2":
+        opt = ref_dion.NorDion2(groups, distributed_mesh=pg, lr=LR, fraction=FRACTION, mu=MU,
+                                weight_decay=WD, use_triton=True, use_polar_express=False,
+                                triton_post_ortho=True)
+    else:
+        opt = ref_dion.Dion(groups, replicate_mesh=pg, replicate_mesh_grad_sync=False,
+                            rank_fraction=FRACTION, lr=LR, mu=MU, weight_decay=WD)
+
+    autocast = torch.autocast(device_type="cuda", dtype=torch.bfloat16)
+    host = synthetic_batches(4, rank, device)
+    dev_batches = [h.to(device) for h in host]
+    state = {"i": 0, "loss": None}
+
+    def step_device():
+        xy = dev_batches[state["i"] % len(dev_batches)]
+        state["i"] += 1
+        with autocast:
+            loss = call(xy[0], xy[1])
+        loss.backward()
+        opt.step()
+        call.zero_grad(set_to_none=True)
+        state["loss"] = loss.detach()
+
+    def step_e2e():
+        xy = host[state["i"] % len(host)].to(device, non_blocking=True)
+        state["i"] += 1
+        with autocast:
+            loss = call(xy[0], xy[1])
+        loss.backward()
+        opt.step()
+        call.zero_grad(set_to_none=True)
+        state["loss_host"] = loss.item()
+
+    try:
+        step_device()  # first call compiles / autotunes; failures here fall back to eager
+    except Exception as exc:  # noqa: BLE001
+        if rank == 0:
+            print(json.dumps({"impl": "reference",
+                              "unavailable": f"reference step failed: {type(exc).__name__}: "
+                                             f"{str(exc)[:300]}"}))
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    ms, clocks = time_loop(step_device, args.steps, args.warmup, world, device, sampler)
+    e2e_ms = None
+    if not args.no_e2e:
+        e2e_ms, _ = time_loop(step_e2e, args.steps, 2, world, device, None)
+    if rank == 0:
+        emit(args, "reference", ms, e2e_ms, clocks, 0, world,
+             {"final_loss": float(state["loss"].item()), "model_compiled": compiled})
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    a = parse()
+    if a.impl == "reference":
+        run_reference(a)
+    else:
+        run_ours(a)

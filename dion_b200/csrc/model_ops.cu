@@ -1,0 +1,416 @@
+// Fused element-wise kernels of the GPT block and the loss, forward and backward, for sm_100a.
+// They take the place of what the reference gets from tracing its model with a compiler
+// (models/gpt_model.py:82-111, 171-179, 195-200): RMS norm, rotary embedding + QK norm, ReLU^2
+// and a cross entropy that reads bf16 logits once and leaves its gradient in their place.
+// All of them are bandwidth-bound: 128-bit accesses, fp32 arithmetic, one pass over the data.
+#include "common.cuh"
+
+namespace dion {
+
+enum : int { DT_F32 = 0, DT_BF16 = 1 };
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// 8 consecutive elements as floats (D % 8 == 0 and 16/32-byte aligned rows are guaranteed by the
+// callers).
+__device__ __forceinline__ void load8(const void* p, int dt, long long i, float (&v)[8]) {
+  if (dt == DT_F32) {
+    const float4* q = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p) + i);
+    float4 a = q[0], b = q[1];
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+  } else {
+    uint4 u = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p) + i);
+    float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z),
+           d = unpack_bf16x2(u.w);
+    v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y; v[4] = c.x; v[5] = c.y; v[6] = d.x; v[7] = d.y;
+  }
+}
+__device__ __forceinline__ void store8(void* p, int dt, long long i, const float (&v)[8]) {
+  if (dt == DT_F32) {
+    float4* q = reinterpret_cast<float4*>(reinterpret_cast<float*>(p) + i);
+    q[0] = make_float4(v[0], v[1], v[2], v[3]);
+    q[1] = make_float4(v[4], v[5], v[6], v[7]);
+  } else {
+    *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p) + i) =
+        make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]),
+                   pack_bf16x2(v[6], v[7]));
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// RMS norm: one warp per row, the row is kept in registers between the two passes (D <= 8192).
+// ---------------------------------------------------------------------------------------------
+constexpr int kMaxVecPerLane = 32;  // 32 lanes * 8 elems * 32 = 8192 columns
+
+__global__ void __launch_bounds__(256)
+rmsnorm_fwd_kernel(const void* X, int x_dt, void* Y, int y_dt, float* rstd, long long rows, int D,
+                   float eps) {
+  const long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  const long long base = row * D;
+  const int nvec = D / 8;
+  float ss = 0.f;
+  for (int j = lane; j < nvec; j += 32) {
+    float v[8];
+    load8(X, x_dt, base + j * 8, v);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) ss += v[e] * v[e];
+  }
+  ss = warp_sum(ss);
+  const float r = rsqrtf(ss / (float)D + eps);
+  if (lane == 0) rstd[row] = r;
+  for (int j = lane; j < nvec; j += 32) {
+    float v[8];
+    load8(X, x_dt, base + j * 8, v);  // second read hits L1/L2
+#pragma unroll
+    for (int e = 0; e < 8; ++e) v[e] *= r;
+    store8(Y, y_dt, base + j * 8, v);
+  }
+}
+
+// dx = r * (dy - xhat * mean(dy * xhat)),  xhat = x * r
+__global__ void __launch_bounds__(256)
+rmsnorm_bwd_kernel(const void* X, int x_dt, const void* DY, int dy_dt, const float* rstd, void* DX,
+                   long long rows, int D) {
+  const long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  const long long base = row * D;
+  const int nvec = D / 8;
+  const float r = rstd[row];
+  float dot = 0.f;
+  for (int j = lane; j < nvec; j += 32) {
+    float x[8], g[8];
+    load8(X, x_dt, base + j * 8, x);
+    load8(DY, dy_dt, base + j * 8, g);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) dot += g[e] * x[e];
+  }
+  dot = warp_sum(dot) * r / (float)D;  // mean(dy * xhat)
+  for (int j = lane; j < nvec; j += 32) {
+    float x[8], g[8], o[8];
+    load8(X, x_dt, base + j * 8, x);
+    load8(DY, dy_dt, base + j * 8, g);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) o[e] = r * (g[e] - x[e] * r * dot);
+    store8(DX, x_dt, base + j * 8, o);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// RoPE + RMS norm over head_dim for q and k ([B,T,H,D] bf16, cos/sin [T, D/2] bf16).
+// One warp per (tensor, b, t, h) vector; lane l owns the rotation pairs p = l, l+32, ...
+// ---------------------------------------------------------------------------------------------
+template <int D>
+__global__ void __launch_bounds__(256)
+rope_qknorm_fwd_kernel(const __nv_bfloat16* Q, const __nv_bfloat16* K, const __nv_bfloat16* COS,
+                       const __nv_bfloat16* SIN, __nv_bfloat16* QO, __nv_bfloat16* KO, float* rstd,
+                       long long n_vec, int T, int H, float eps) {
+  constexpr int HALF = D / 2, PAIRS = HALF / 32;
+  const long long w = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (w >= 2 * n_vec) return;
+  const bool is_k = w >= n_vec;
+  const long long vec = is_k ? w - n_vec : w;
+  const int t = (int)((vec / H) % T);
+  const __nv_bfloat16* x = (is_k ? K : Q) + vec * D;
+  __nv_bfloat16* y = (is_k ? KO : QO) + vec * D;
+  float y1[PAIRS], y2[PAIRS];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < PAIRS; ++i) {
+    const int p = lane + 32 * i;
+    const float c = __bfloat162float(COS[(long long)t * HALF + p]);
+    const float s = __bfloat162float(SIN[(long long)t * HALF + p]);
+    const float x1 = __bfloat162float(x[p]), x2 = __bfloat162float(x[p + HALF]);
+    y1[i] = x1 * c + x2 * s;
+    y2[i] = x2 * c - x1 * s;
+    ss += y1[i] * y1[i] + y2[i] * y2[i];
+  }
+  ss = warp_sum(ss);
+  const float r = rsqrtf(ss / (float)D + eps);
+  if (lane == 0) rstd[w] = r;
+#pragma unroll
+  for (int i = 0; i < PAIRS; ++i) {
+    const int p = lane + 32 * i;
+    y[p] = __float2bfloat16_rn(y1[i] * r);
+    y[p + HALF] = __float2bfloat16_rn(y2[i] * r);
+  }
+}
+
+template <int D>
+__global__ void __launch_bounds__(256)
+rope_qknorm_bwd_kernel(const __nv_bfloat16* Q, const __nv_bfloat16* K, const __nv_bfloat16* COS,
+                       const __nv_bfloat16* SIN, const __nv_bfloat16* DQO,
+                       const __nv_bfloat16* DKO, const float* rstd, __nv_bfloat16* DQ,
+                       __nv_bfloat16* DK, long long n_vec, int T, int H) {
+  constexpr int HALF = D / 2, PAIRS = HALF / 32;
+  const long long w = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (w >= 2 * n_vec) return;
+  const bool is_k = w >= n_vec;
+  const long long vec = is_k ? w - n_vec : w;
+  const int t = (int)((vec / H) % T);
+  const __nv_bfloat16* x = (is_k ? K : Q) + vec * D;
+  const __nv_bfloat16* g = (is_k ? DKO : DQO) + vec * D;
+  __nv_bfloat16* dx = (is_k ? DK : DQ) + vec * D;
+  const float r = rstd[w];
+  float y1[PAIRS], y2[PAIRS], g1[PAIRS], g2[PAIRS], cs[PAIRS], sn[PAIRS];
+  float dot = 0.f;
+#pragma unroll
+  for (int i = 0; i < PAIRS; ++i) {
+    const int p = lane + 32 * i;
+    cs[i] = __bfloat162float(COS[(long long)t * HALF + p]);
+    sn[i] = __bfloat162float(SIN[(long long)t * HALF + p]);
+    const float x1 = __bfloat162float(x[p]), x2 = __bfloat162float(x[p + HALF]);
+    y1[i] = x1 * cs[i] + x2 * sn[i];
+    y2[i] = x2 * cs[i] - x1 * sn[i];
+    g1[i] = __bfloat162float(g[p]);
+    g2[i] = __bfloat162float(g[p + HALF]);
+    dot += g1[i] * y1[i] + g2[i] * y2[i];
+  }
+  dot = warp_sum(dot) * r / (float)D;
+#pragma unroll
+  for (int i = 0; i < PAIRS; ++i) {
+    const int p = lane + 32 * i;
+    const float d1 = r * (g1[i] - y1[i] * r * dot);  // grad w.r.t. the rotated vector
+    const float d2 = r * (g2[i] - y2[i] * r * dot);
+    dx[p] = __float2bfloat16_rn(d1 * cs[i] - d2 * sn[i]);
+    dx[p + HALF] = __float2bfloat16_rn(d1 * sn[i] + d2 * cs[i]);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// ReLU^2
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+relu2_fwd_kernel(const void* X, void* Y, int dt, long long n8) {
+  for (long long i = (long long)blockIdx.x * 256 + threadIdx.x; i < n8;
+       i += (long long)gridDim.x * 256) {
+    float v[8];
+    load8(X, dt, i * 8, v);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) { const float r = fmaxf(v[e], 0.f); v[e] = r * r; }
+    store8(Y, dt, i * 8, v);
+  }
+}
+__global__ void __launch_bounds__(256)
+relu2_bwd_kernel(const void* X, const void* DY, void* DX, int dt, long long n8) {
+  for (long long i = (long long)blockIdx.x * 256 + threadIdx.x; i < n8;
+       i += (long long)gridDim.x * 256) {
+    float x[8], g[8];
+    load8(X, dt, i * 8, x);
+    load8(DY, dt, i * 8, g);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) g[e] = 2.f * fmaxf(x[e], 0.f) * g[e];
+    store8(DX, dt, i * 8, g);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Cross entropy.  One block per row: online max / sum-of-exponentials in one read, then the
+// gradient (softmax - onehot) / count is written over the logits in a second sweep that is served
+// from L2.
+// ---------------------------------------------------------------------------------------------
+__global__ void ce_count_kernel(const long long* tgt, long long n, int ignore_index, float* count) {
+  float c = 0.f;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (long long)gridDim.x * blockDim.x)
+    c += (tgt[i] != ignore_index) ? 1.f : 0.f;
+  c = warp_sum(c);
+  if ((threadIdx.x & 31) == 0 && c != 0.f) atomicAdd(count, c);
+}
+
+constexpr int kCeThreads = 512;
+
+__global__ void __launch_bounds__(kCeThreads)
+ce_fwd_bwd_kernel(void* L, int dt, const long long* tgt, long long n, int V, long long ld,
+                  int ignore_index, float* losses, const float* count, int write_grad) {
+  __shared__ float s_m[kCeThreads / 32], s_s[kCeThreads / 32];
+  __shared__ float s_max, s_lse;
+  const long long row = blockIdx.x;
+  const long long base = row * ld;
+  const long long target = tgt[row];
+  const int nvec = V / 8;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (target == ignore_index) {
+    if (threadIdx.x == 0) losses[row] = 0.f;
+    if (write_grad) {
+      float z[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+      for (int j = threadIdx.x; j < nvec; j += kCeThreads) store8(L, dt, base + j * 8, z);
+    }
+    return;
+  }
+  float m = -INFINITY, s = 0.f;
+  for (int j = threadIdx.x; j < nvec; j += kCeThreads) {
+    float v[8];
+    load8(L, dt, base + j * 8, v);
+    float vm = v[0];
+#pragma unroll
+    for (int e = 1; e < 8; ++e) vm = fmaxf(vm, v[e]);
+    const float nm = fmaxf(m, vm);
+    float acc = 0.f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc += __expf(v[e] - nm);
+    s = s * __expf(m - nm) + acc;
+    m = nm;
+  }
+  // combine (m, s) pairs across the block
+  const float wm = warp_max(m);
+  s = warp_sum(m == -INFINITY ? 0.f : s * __expf(m - wm));
+  if (lane == 0) { s_m[warp] = wm; s_s[warp] = s; }
+  __syncthreads();
+  if (warp == 0) {
+    float mm = lane < kCeThreads / 32 ? s_m[lane] : -INFINITY;
+    float ssum = lane < kCeThreads / 32 ? s_s[lane] : 0.f;
+    const float bm = warp_max(mm);
+    ssum = warp_sum(mm == -INFINITY ? 0.f : ssum * __expf(mm - bm));
+    if (lane == 0) { s_max = bm; s_lse = bm + logf(ssum); }
+  }
+  __syncthreads();
+  const float lse = s_lse;
+  if (threadIdx.x == 0) {
+    const float xt = dt == DT_F32
+                         ? reinterpret_cast<const float*>(L)[base + target]
+                         : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(L)[base + target]);
+    losses[row] = lse - xt;
+  }
+  if (!write_grad) return;
+  __syncthreads();  // the target logit has been read before it is overwritten
+  const float inv = 1.f / fmaxf(*count, 1.f);
+  for (int j = threadIdx.x; j < nvec; j += kCeThreads) {
+    float v[8];
+    load8(L, dt, base + j * 8, v);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      float g = __expf(v[e] - lse);
+      if ((long long)j * 8 + e == target) g -= 1.f;
+      v[e] = g * inv;
+    }
+    store8(L, dt, base + j * 8, v);
+  }
+}
+
+// x *= *scale unless *scale == 1 (every block exits at once in the common case).
+__global__ void __launch_bounds__(256)
+scale_unless_one_kernel(void* X, int dt, long long n8, const float* scale) {
+  const float s = *scale;
+  if (s == 1.f) return;
+  for (long long i = (long long)blockIdx.x * 256 + threadIdx.x; i < n8;
+       i += (long long)gridDim.x * 256) {
+    float v[8];
+    load8(X, dt, i * 8, v);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) v[e] *= s;
+    store8(X, dt, i * 8, v);
+  }
+}
+
+}  // namespace dion
+
+using namespace dion;
+static inline cudaStream_t S(void* s) { return static_cast<cudaStream_t>(s); }
+static inline int rc() { return cudaGetLastError() == cudaSuccess ? 0 : -1; }
+static inline unsigned grid_for(long long n8) {
+  long long b = (n8 + 255) / 256;
+  return (unsigned)(b < 148 * 16 ? (b > 0 ? b : 1) : 148 * 16);
+}
+
+DION_EXPORT int dion_rmsnorm_fwd(const void* X, int x_dt, void* Y, int y_dt, float* rstd,
+                                 long long rows, int D, float eps, void* stream) {
+  if (rows <= 0) return 0;
+  if (D % 8) return -2;
+  rmsnorm_fwd_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, S(stream)>>>(X, x_dt, Y, y_dt, rstd,
+                                                                       rows, D, eps);
+  return rc();
+}
+DION_EXPORT int dion_rmsnorm_bwd(const void* X, int x_dt, const void* DY, int dy_dt,
+                                 const float* rstd, void* DX, long long rows, int D,
+                                 void* stream) {
+  if (rows <= 0) return 0;
+  if (D % 8) return -2;
+  rmsnorm_bwd_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, S(stream)>>>(X, x_dt, DY, dy_dt, rstd,
+                                                                       DX, rows, D);
+  return rc();
+}
+
+#define DION_ROPE_DISPATCH(D_, CALL) \
+  switch (D_) {                      \
+    case 64: { constexpr int DD = 64; CALL; break; }   \
+    case 128: { constexpr int DD = 128; CALL; break; } \
+    case 192: { constexpr int DD = 192; CALL; break; } \
+    case 256: { constexpr int DD = 256; CALL; break; } \
+    default: return -2;              \
+  }
+
+DION_EXPORT int dion_rope_qknorm_fwd(const void* Q, const void* K, const void* COS,
+                                     const void* SIN, void* QO, void* KO, float* rstd, int B,
+                                     int T, int H, int D, float eps, void* stream) {
+  const long long n_vec = (long long)B * T * H;
+  if (n_vec <= 0) return 0;
+  const unsigned grid = (unsigned)((2 * n_vec + 7) / 8);
+  typedef const __nv_bfloat16* CP;
+  typedef __nv_bfloat16* P;
+  DION_ROPE_DISPATCH(D, (rope_qknorm_fwd_kernel<DD><<<grid, 256, 0, S(stream)>>>(
+                            (CP)Q, (CP)K, (CP)COS, (CP)SIN, (P)QO, (P)KO, rstd, n_vec, T, H, eps)))
+  return rc();
+}
+DION_EXPORT int dion_rope_qknorm_bwd(const void* Q, const void* K, const void* COS,
+                                     const void* SIN, const void* DQO, const void* DKO,
+                                     const float* rstd, void* DQ, void* DK, int B, int T, int H,
+                                     int D, void* stream) {
+  const long long n_vec = (long long)B * T * H;
+  if (n_vec <= 0) return 0;
+  const unsigned grid = (unsigned)((2 * n_vec + 7) / 8);
+  typedef const __nv_bfloat16* CP;
+  typedef __nv_bfloat16* P;
+  DION_ROPE_DISPATCH(D, (rope_qknorm_bwd_kernel<DD><<<grid, 256, 0, S(stream)>>>(
+                            (CP)Q, (CP)K, (CP)COS, (CP)SIN, (CP)DQO, (CP)DKO, rstd, (P)DQ, (P)DK,
+                            n_vec, T, H)))
+  return rc();
+}
+
+DION_EXPORT int dion_relu2_fwd(const void* X, void* Y, int dt, long long n, void* stream) {
+  if (n <= 0) return 0;
+  relu2_fwd_kernel<<<grid_for(n / 8), 256, 0, S(stream)>>>(X, Y, dt, n / 8);
+  return rc();
+}
+DION_EXPORT int dion_relu2_bwd(const void* X, const void* DY, void* DX, int dt, long long n,
+                               void* stream) {
+  if (n <= 0) return 0;
+  relu2_bwd_kernel<<<grid_for(n / 8), 256, 0, S(stream)>>>(X, DY, DX, dt, n / 8);
+  return rc();
+}
+
+DION_EXPORT int dion_ce_count(const void* tgt, long long n, int ignore_index, float* count,
+                              void* stream) {
+  if (n <= 0) return 0;
+  ce_count_kernel<<<(unsigned)((n + 1023) / 1024 < 256 ? (n + 1023) / 1024 : 256), 1024, 0,
+                    S(stream)>>>(static_cast<const long long*>(tgt), n, ignore_index, count);
+  return rc();
+}
+DION_EXPORT int dion_ce_fwd_bwd(void* L, int dt, const void* tgt, long long n, int V, long long ld,
+                                int ignore_index, float* losses, const float* count,
+                                int write_grad, void* stream) {
+  if (n <= 0) return 0;
+  if (V % 8 || ld % 8) return -2;
+  ce_fwd_bwd_kernel<<<(unsigned)n, kCeThreads, 0, S(stream)>>>(
+      L, dt, static_cast<const long long*>(tgt), n, V, ld, ignore_index, losses, count, write_grad);
+  return rc();
+}
+DION_EXPORT int dion_scale_unless_one(void* X, int dt, long long n, const float* scale,
+                                      void* stream) {
+  if (n <= 0) return 0;
+  scale_unless_one_kernel<<<grid_for(n / 8), 256, 0, S(stream)>>>(X, dt, n / 8, scale);
+  return rc();
+}

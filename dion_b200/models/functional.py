@@ -1,0 +1,219 @@
+"""Fused element-wise pieces of the GPT block and the loss.
+
+Each function is an autograd ``Function`` whose forward and backward are single CUDA kernels from
+``csrc/model_ops.cu`` when the input lives on a GPU, and the equivalent PyTorch expression
+otherwise (CPU tests, unsupported dtypes).  They replace what the reference obtains by tracing
+its model with ``torch.compile`` (models/gpt_model.py:195-200).
+
+* ``rms_norm(x)``            RMS normalisation over the last dim, no weight; under bf16 autocast
+                             the result is emitted in bf16 for the GEMM that consumes it.
+* ``rope_qknorm(q, k, ...)`` rotary embedding followed by RMS-norm over ``head_dim`` for q and k.
+* ``relu2(x)``               ``relu(x)**2``.
+* ``cross_entropy(...)``     mean token loss from bf16/fp32 logits with fp32 softmax arithmetic;
+                             the backward pass is computed together with the forward and stored
+                             in place of the logits.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional, Tuple
+
+import torch
+import torch.nn.functional as tF
+from torch import Tensor
+
+from ..ops import _backend
+
+_DT = {torch.float32: 0, torch.bfloat16: 1}
+
+
+def _c(t: Optional[Tensor]):
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _stream(dev):
+    return ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+
+
+def _lib():
+    return _backend.lib("model_ops")
+
+
+def _check(rc, name):
+    if rc != 0:
+        raise RuntimeError(f"{name} launch failed (code {rc})")
+
+
+def _autocast_bf16(x: Tensor) -> bool:
+    return x.is_cuda and torch.is_autocast_enabled() and torch.get_autocast_gpu_dtype() == torch.bfloat16
+
+
+def _eps_for(dtype: torch.dtype) -> float:
+    return float(torch.finfo(dtype).eps)
+
+
+# ------------------------------------------------------------------------------------------------
+# RMS norm
+# ------------------------------------------------------------------------------------------------
+class _RMSNorm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x: Tensor, eps: float, out_dtype: torch.dtype):
+        D = x.size(-1)
+        x2 = x.reshape(-1, D)
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        rows = x2.size(0)
+        y = torch.empty((rows, D), dtype=out_dtype, device=x.device)
+        rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
+        _check(_lib().dion_rmsnorm_fwd(_c(x2), _DT[x2.dtype], _c(y), _DT[out_dtype], _c(rstd),
+                                       ctypes.c_longlong(rows), D, ctypes.c_float(eps),
+                                       _stream(x.device)), "dion_rmsnorm_fwd")
+        ctx.save_for_backward(x2, rstd)
+        ctx.shape = x.shape
+        return y.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, dy: Tensor):
+        x2, rstd = ctx.saved_tensors
+        rows, D = x2.shape
+        dy2 = dy.reshape(rows, D)
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        dx = torch.empty_like(x2)
+        _check(_lib().dion_rmsnorm_bwd(_c(x2), _DT[x2.dtype], _c(dy2), _DT[dy2.dtype], _c(rstd),
+                                       _c(dx), ctypes.c_longlong(rows), D, _stream(x2.device)),
+               "dion_rmsnorm_bwd")
+        return dx.view(ctx.shape), None, None
+
+
+def rms_norm(x: Tensor, eps: Optional[float] = None) -> Tensor:
+    """``x * rsqrt(mean(x**2, -1) + eps)``; ``eps`` defaults to the machine epsilon of ``x``'s
+    dtype, as in ``torch.nn.functional.rms_norm``."""
+    if x.is_cuda and x.dtype in _DT and x.size(-1) % 8 == 0:
+        out_dtype = torch.bfloat16 if _autocast_bf16(x) else x.dtype
+        return _RMSNorm.apply(x, _eps_for(x.dtype) if eps is None else eps, out_dtype)
+    return tF.rms_norm(x, (x.size(-1),), eps=eps)
+
+
+# ------------------------------------------------------------------------------------------------
+# RoPE + QK norm
+# ------------------------------------------------------------------------------------------------
+def _rope_torch(x: Tensor, cos: Tensor, sin: Tensor) -> Tensor:
+    d = x.shape[3] // 2
+    c, s = cos[None, :, None, :], sin[None, :, None, :]
+    x1, x2 = x[..., :d], x[..., d:]
+    return torch.cat([x1 * c + x2 * s, x2 * c - x1 * s], 3).type_as(x)
+
+
+class _RopeQKNorm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q: Tensor, k: Tensor, cos: Tensor, sin: Tensor, eps: float):
+        B, T, H, D = q.shape
+        q = q.contiguous()
+        k = k.contiguous()
+        qo, ko = torch.empty_like(q), torch.empty_like(k)
+        n = B * T * H
+        rstd = torch.empty((2, n), dtype=torch.float32, device=q.device)
+        _check(_lib().dion_rope_qknorm_fwd(_c(q), _c(k), _c(cos), _c(sin), _c(qo), _c(ko),
+                                           _c(rstd), B, T, H, D, ctypes.c_float(eps),
+                                           _stream(q.device)), "dion_rope_qknorm_fwd")
+        ctx.save_for_backward(q, k, cos, sin, rstd)
+        return qo, ko
+
+    @staticmethod
+    def backward(ctx, dqo: Tensor, dko: Tensor):
+        q, k, cos, sin, rstd = ctx.saved_tensors
+        B, T, H, D = q.shape
+        dqo, dko = dqo.contiguous(), dko.contiguous()
+        dq, dk = torch.empty_like(q), torch.empty_like(k)
+        _check(_lib().dion_rope_qknorm_bwd(_c(q), _c(k), _c(cos), _c(sin), _c(dqo), _c(dko),
+                                           _c(rstd), _c(dq), _c(dk), B, T, H, D,
+                                           _stream(q.device)), "dion_rope_qknorm_bwd")
+        return dq, dk, None, None, None
+
+
+def rope_qknorm(q: Tensor, k: Tensor, cos: Tensor, sin: Tensor) -> Tuple[Tensor, Tensor]:
+    """Rotary embedding (``cos/sin``: ``[T, D/2]``) then RMS-norm over the last dim, for ``q``
+    and ``k`` of shape ``[B, T, H, D]``."""
+    D = q.size(-1)
+    if (q.is_cuda and q.dtype == torch.bfloat16 and k.dtype == torch.bfloat16 and D % 64 == 0
+            and D <= 256 and cos.dtype == torch.bfloat16 and q.shape == k.shape):
+        return _RopeQKNorm.apply(q, k, cos, sin, _eps_for(torch.bfloat16))
+    q, k = _rope_torch(q, cos, sin), _rope_torch(k, cos, sin)
+    return tF.rms_norm(q, (D,)), tF.rms_norm(k, (D,))
+
+
+# ------------------------------------------------------------------------------------------------
+# ReLU^2
+# ------------------------------------------------------------------------------------------------
+class _Relu2(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x: Tensor):
+        x = x.contiguous()
+        y = torch.empty_like(x)
+        _check(_lib().dion_relu2_fwd(_c(x), _c(y), _DT[x.dtype], ctypes.c_longlong(x.numel()),
+                                     _stream(x.device)), "dion_relu2_fwd")
+        ctx.save_for_backward(x)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy: Tensor):
+        (x,) = ctx.saved_tensors
+        dy = dy.contiguous()
+        dx = torch.empty_like(x)
+        _check(_lib().dion_relu2_bwd(_c(x), _c(dy), _c(dx), _DT[x.dtype],
+                                     ctypes.c_longlong(x.numel()), _stream(x.device)),
+               "dion_relu2_bwd")
+        return dx
+
+
+def relu2(x: Tensor) -> Tensor:
+    if x.is_cuda and x.dtype in _DT and x.numel() % 8 == 0:
+        return _Relu2.apply(x)
+    return tF.relu(x).square()
+
+
+# ------------------------------------------------------------------------------------------------
+# Cross entropy
+# ------------------------------------------------------------------------------------------------
+class _CrossEntropy(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, logits: Tensor, targets: Tensor, ignore_index: int):
+        N, V = logits.shape
+        need_grad = logits.requires_grad and torch.is_grad_enabled()
+        losses = torch.empty(N, dtype=torch.float32, device=logits.device)
+        count = torch.zeros(1, dtype=torch.float32, device=logits.device)
+        tgt = targets if targets.dtype == torch.int64 else targets.long()
+        lib = _lib()
+        _check(lib.dion_ce_count(_c(tgt), ctypes.c_longlong(N), ignore_index, _c(count),
+                                 _stream(logits.device)), "dion_ce_count")
+        # Loss per row and, when a backward pass will follow, d(mean loss)/d(logits) written
+        # over the logits themselves (nothing else reads them afterwards).
+        _check(lib.dion_ce_fwd_bwd(_c(logits), _DT[logits.dtype], _c(tgt), ctypes.c_longlong(N), V,
+                                   ctypes.c_longlong(logits.stride(0)), ignore_index, _c(losses),
+                                   _c(count), int(need_grad), _stream(logits.device)),
+               "dion_ce_fwd_bwd")
+        loss = losses.sum() / count.clamp(min=1.0)
+        if need_grad:
+            ctx.save_for_backward(logits)
+        return loss.reshape(())
+
+    @staticmethod
+    def backward(ctx, dloss: Tensor):
+        (grad,) = ctx.saved_tensors
+        # The upstream gradient is 1 for a plain ``loss.backward()``: the kernel reads it on the
+        # device and returns at once in that case, otherwise it rescales the stored gradient.
+        scale = dloss.detach().reshape(1).to(torch.float32)
+        _check(_lib().dion_scale_unless_one(_c(grad), _DT[grad.dtype],
+                                            ctypes.c_longlong(grad.numel()), _c(scale),
+                                            _stream(grad.device)), "dion_scale_unless_one")
+        return grad, None, None
+
+
+def cross_entropy(logits: Tensor, targets: Tensor, ignore_index: int = -1) -> Tensor:
+    """Mean cross entropy over the rows whose target is not ``ignore_index``; softmax
+    arithmetic in fp32 regardless of the logits' dtype."""
+    if (logits.is_cuda and logits.dtype in _DT and logits.ndim == 2 and logits.stride(1) == 1
+            and logits.size(1) % 8 == 0):
+        return _CrossEntropy.apply(logits, targets, ignore_index)
+    return tF.cross_entropy(logits.float(), targets, ignore_index=ignore_index)

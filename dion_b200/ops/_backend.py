@@ -40,7 +40,7 @@ SOURCES = {
     "no_alloc": "libdion_noalloc.so",
 }
 
-_loaded: Dict[str, ctypes.CDLL] = {}
+_loaded: Dict[str, "_CountingLib"] = {}
 _lock = threading.Lock()
 
 
@@ -84,7 +84,44 @@ def build(force: bool = False, verbose: bool = False) -> List[str]:
     return logs
 
 
-def lib(stem: str) -> ctypes.CDLL:
+# Kernels launched per exported entry point (default 1); used for the launch counter.
+_KERNELS_PER_CALL = {"dion_adamw": 2}
+_launches = 0
+
+
+class _CountingLib:
+    """Proxy over a ``ctypes.CDLL`` that counts kernel launches made through it."""
+
+    def __init__(self, dll: ctypes.CDLL):
+        self._dll = dll
+        self._cache = {}
+
+    def __getattr__(self, name: str):
+        fn = self._cache.get(name)
+        if fn is None:
+            raw = getattr(self._dll, name)
+            per_call = _KERNELS_PER_CALL.get(name, 1)
+
+            def fn(*args, _raw=raw, _n=per_call):
+                global _launches
+                _launches += _n
+                return _raw(*args)
+
+            self._cache[name] = fn
+        return fn
+
+
+def launch_count() -> int:
+    """Kernel launches issued through this package since the last reset."""
+    return _launches
+
+
+def reset_launch_count() -> None:
+    global _launches
+    _launches = 0
+
+
+def lib(stem: str) -> "_CountingLib":
     """Load (building first if a compiler is present and the source is newer) one library."""
     with _lock:
         h = _loaded.get(stem)
@@ -100,7 +137,7 @@ def lib(stem: str) -> ctypes.CDLL:
                 f"kernel library {out} is missing; run `python -c 'import __graft_entry__ as g; "
                 f"g.build()'` (needs nvcc)"
             )
-        h = ctypes.CDLL(str(out))
+        h = _CountingLib(ctypes.CDLL(str(out)))
         _loaded[stem] = h
         return h
 

@@ -1,0 +1,117 @@
+"""Fused model kernels (forward and backward) against PyTorch autograd in fp32."""
+import pytest
+import torch
+import torch.nn.functional as tF
+
+from dion_b200.models import functional as Fn
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_rms_norm(dtype):
+    torch.manual_seed(0)
+    x = torch.randn(4, 37, 768, device="cuda").to(dtype).requires_grad_()
+    xr = x.detach().float().requires_grad_()
+    y = Fn.rms_norm(x)
+    yr = tF.rms_norm(xr, (768,), eps=torch.finfo(dtype).eps)
+    g = torch.randn_like(yr)
+    y.backward(g.to(y.dtype))
+    yr.backward(g)
+    tol = 1e-5 if dtype == torch.float32 else 3e-2
+    assert (y.float() - yr).abs().max().item() < tol
+    assert (x.grad.float() - xr.grad).abs().max().item() < tol
+
+
+def test_rms_norm_autocast_emits_bf16():
+    x = torch.randn(8, 768, device="cuda", requires_grad=True)
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        y = Fn.rms_norm(x)
+    assert y.dtype == torch.bfloat16
+    y.float().sum().backward()
+    assert x.grad.dtype == torch.float32
+
+
+@pytest.mark.parametrize("D", [64, 128])
+def test_rope_qknorm(D):
+    torch.manual_seed(0)
+    B, T, H = 2, 50, 6
+    q = torch.randn(B, T, H, D, device="cuda").bfloat16().requires_grad_()
+    k = torch.randn(B, T, H, D, device="cuda").bfloat16().requires_grad_()
+    inv = 1.0 / (10000 ** (torch.arange(0, D, 2, device="cuda").float() / D))
+    fr = torch.outer(torch.arange(T, device="cuda").float(), inv)
+    cos, sin = fr.cos().bfloat16(), fr.sin().bfloat16()
+    qo, ko = Fn.rope_qknorm(q, k, cos, sin)
+    qr, kr = q.detach().float().requires_grad_(), k.detach().float().requires_grad_()
+
+    def ref(x):
+        d = D // 2
+        c, s = cos.float()[None, :, None, :], sin.float()[None, :, None, :]
+        y = torch.cat([x[..., :d] * c + x[..., d:] * s, x[..., d:] * c - x[..., :d] * s], 3)
+        return tF.rms_norm(y, (D,), eps=torch.finfo(torch.bfloat16).eps)
+
+    qro, kro = ref(qr), ref(kr)
+    gq, gk = torch.randn_like(qro), torch.randn_like(kro)
+    (qo.float() * gq + ko.float() * gk).sum().backward()
+    (qro * gq + kro * gk).sum().backward()
+    assert (qo.float() - qro).abs().max().item() < 3e-2
+    assert (ko.float() - kro).abs().max().item() < 3e-2
+    assert (q.grad.float() - qr.grad).abs().max().item() < 5e-2
+    assert (k.grad.float() - kr.grad).abs().max().item() < 5e-2
+
+
+def test_relu2():
+    x = torch.randn(16, 3072, device="cuda").bfloat16().requires_grad_()
+    xr = x.detach().float().requires_grad_()
+    y = Fn.relu2(x)
+    yr = tF.relu(xr).square()
+    g = torch.randn_like(yr)
+    y.backward(g.bfloat16())
+    yr.backward(g)
+    assert (y.float() - yr).abs().max().item() < 0.1
+    assert (x.grad.float() - xr.grad).abs().max().item() < 0.1
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("V", [64, 50304])
+def test_cross_entropy(dtype, V):
+    torch.manual_seed(0)
+    N = 300
+    logits = (torch.randn(N, V, device="cuda") * 2).to(dtype)
+    tgt = torch.randint(0, V, (N,), device="cuda")
+    tgt[::7] = -1
+    lr = logits.detach().float().requires_grad_()
+    ref = tF.cross_entropy(lr, tgt, ignore_index=-1)
+    ref.backward()
+    lg = logits.clone().requires_grad_()
+    loss = Fn.cross_entropy(lg, tgt, ignore_index=-1)
+    (loss * 0.5).backward()
+    assert abs(float(loss) - float(ref)) < (1e-4 if dtype == torch.float32 else 2e-2)
+    tol = 1e-6 if dtype == torch.float32 else 2e-4
+    assert (lg.grad.float() - 0.5 * lr.grad).abs().max().item() < tol
+
+
+def test_gpt_forward_backward_matches_torch_path():
+    from dion_b200.models.gpt import GPT, GPTConfig
+    torch.manual_seed(0)
+    cfg = GPTConfig(sequence_len=64, vocab_size=512, n_layer=2, n_head=2, n_embd=128)
+    m = GPT(cfg).cuda()
+    m.init_weights()
+    x = torch.randint(0, 512, (3, 64), device="cuda")
+    y = torch.randint(0, 512, (3, 64), device="cuda")
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        loss = m(x, y)
+    loss.backward()
+    g_fused = [p.grad.clone() for p in m.parameters()]
+    m.zero_grad()
+    mc = GPT(cfg)
+    mc.load_state_dict({k: v.cpu() for k, v in m.state_dict().items()})
+    for mod in mc.modules():
+        if hasattr(mod, "init_inv_freq"):
+            mod.init_inv_freq()
+    lc = mc(x.cpu(), y.cpu())
+    lc.backward()
+    assert abs(float(loss) - float(lc)) < 5e-2
+    for g, p in zip(g_fused, mc.parameters()):
+        denom = p.grad.abs().max().item() + 1e-6
+        assert (g.cpu() - p.grad).abs().max().item() / denom < 0.1
