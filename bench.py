@@ -293,6 +293,11 @@ def run_reference(args) -> None:
                           "unavailable": "baseline/_ref is missing (reference not installed)"}))
         return
     sys.path.insert(0, ref_root)
+    # The image's default g++ (/opt/gcc) cannot link OpenMP (no libgomp.spec), which breaks every
+    # torch.compile call of the reference; the system compiler works.
+    if os.path.exists("/usr/bin/g++"):
+        os.environ["CXX"] = "/usr/bin/g++"
+        os.environ["CC"] = "/usr/bin/gcc"
     try:
         import torch
         import torch.distributed as dist

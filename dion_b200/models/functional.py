@@ -45,7 +45,8 @@ def _check(rc, name):
 
 
 def _autocast_bf16(x: Tensor) -> bool:
-    return x.is_cuda and torch.is_autocast_enabled() and torch.get_autocast_gpu_dtype() == torch.bfloat16
+    return (x.is_cuda and torch.is_autocast_enabled("cuda")
+            and torch.get_autocast_dtype("cuda") == torch.bfloat16)
 
 
 def _eps_for(dtype: torch.dtype) -> float:
@@ -180,7 +181,7 @@ class _CrossEntropy(torch.autograd.Function):
     @staticmethod
     def forward(ctx, logits: Tensor, targets: Tensor, ignore_index: int):
         N, V = logits.shape
-        need_grad = logits.requires_grad and torch.is_grad_enabled()
+        need_grad = bool(ctx.needs_input_grad[0])
         losses = torch.empty(N, dtype=torch.float32, device=logits.device)
         count = torch.zeros(1, dtype=torch.float32, device=logits.device)
         tgt = targets if targets.dtype == torch.int64 else targets.long()

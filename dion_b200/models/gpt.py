@@ -53,8 +53,8 @@ class Rotary(nn.Module):
         T = x.shape[1]
         if T != self.seq_len_cached or self.cos_cached.device != x.device:
             self.seq_len_cached = T
-            t = torch.arange(T, device=x.device).type_as(self.inv_freq)
-            freqs = torch.outer(t, self.inv_freq.to(x.device))
+            inv = self.inv_freq.to(x.device)
+            freqs = torch.outer(torch.arange(T, device=x.device, dtype=inv.dtype), inv)
             self.cos_cached = freqs.cos().bfloat16().contiguous()
             self.sin_cached = freqs.sin().bfloat16().contiguous()
         return self.cos_cached, self.sin_cached

@@ -217,10 +217,10 @@ def test_cuda_matches_cpu(name, kw):
     a, _ = _run(getattr(dion_b200, name), kw, "cpu", shapes=shapes, pre=pre)
     if name == "Dion":
         def pre(opt, ps):  # identical Q on both devices
-            torch.manual_seed(5)
+            gen = torch.Generator().manual_seed(5)
             for p in ps:
                 st = opt._get_or_initialize_state(p, opt.param_groups[0])
-                st["Q"].copy_(torch.randn(st["Q"].shape).to(st["Q"].device))
+                st["Q"].copy_(torch.randn(st["Q"].shape, generator=gen).to(st["Q"].device))
         a, _ = _run(getattr(dion_b200, name), kw, "cpu", shapes=shapes, pre=pre)
     b, _ = _run(getattr(dion_b200, name), kw, "cuda", shapes=shapes, pre=pre)
     torch.cuda.synchronize()
