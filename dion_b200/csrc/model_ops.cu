@@ -1,8 +1,13 @@
 // Fused element-wise kernels of the GPT block and the loss, forward and backward, for sm_100a.
 // They take the place of what the reference gets from tracing its model with a compiler
-// (models/gpt_model.py:82-111, 171-179, 195-200): RMS norm, rotary embedding + QK norm, ReLU^2
-// and a cross entropy that reads bf16 logits once and leaves its gradient in their place.
-// All of them are bandwidth-bound: 128-bit accesses, fp32 arithmetic, one pass over the data.
+// (models/gpt_model.py:82-124, 171-179, 195-200):
+//   * residual add + RMS norm (fp32 residual stream in, bf16 normalised activations out) and its
+//     backward, which also folds in the residual-gradient accumulation and the bf16 cast;
+//   * rotary embedding + QK RMS norm;
+//   * ReLU^2;
+//   * cross entropy that reads bf16 logits once and leaves its gradient in their place.
+// All of them are bandwidth-bound: 128-bit accesses, fp32 arithmetic, one pass over the data
+// (rows are held in registers between the reduction and the write).
 #include "common.cuh"
 
 namespace dion {
@@ -20,8 +25,7 @@ __device__ __forceinline__ float warp_max(float v) {
   return v;
 }
 
-// 8 consecutive elements as floats (D % 8 == 0 and 16/32-byte aligned rows are guaranteed by the
-// callers).
+// 8 consecutive elements as floats (callers guarantee 8-element alignment).
 __device__ __forceinline__ void load8(const void* p, int dt, long long i, float (&v)[8]) {
   if (dt == DT_F32) {
     const float4* q = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p) + i);
@@ -47,147 +51,194 @@ __device__ __forceinline__ void store8(void* p, int dt, long long i, const float
 }
 
 // ---------------------------------------------------------------------------------------------
-// RMS norm: one warp per row, the row is kept in registers between the two passes (D <= 8192).
+// (residual add +) RMS norm.  One warp per row.  VPL = 8-element vectors per lane; rows with
+// D <= 256*VPL columns stay in registers between the reduction and the store.
+//   x_new = X + DELTA (DELTA optional);  Y = x_new * rsqrt(mean(x_new^2) + eps)
+// XOUT (optional) receives x_new in X's dtype.
 // ---------------------------------------------------------------------------------------------
-constexpr int kMaxVecPerLane = 32;  // 32 lanes * 8 elems * 32 = 8192 columns
-
+template <int VPL>
 __global__ void __launch_bounds__(256)
-rmsnorm_fwd_kernel(const void* X, int x_dt, void* Y, int y_dt, float* rstd, long long rows, int D,
-                   float eps) {
+rmsnorm_fwd_kernel(const void* X, int x_dt, const void* DELTA, int d_dt, void* XOUT, void* Y,
+                   int y_dt, float* rstd, long long rows, int D, float eps) {
   const long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (row >= rows) return;
   const long long base = row * D;
   const int nvec = D / 8;
+  float v[VPL][8];
   float ss = 0.f;
-  for (int j = lane; j < nvec; j += 32) {
-    float v[8];
-    load8(X, x_dt, base + j * 8, v);
 #pragma unroll
-    for (int e = 0; e < 8; ++e) ss += v[e] * v[e];
+  for (int i = 0; i < VPL; ++i) {
+    const int j = lane + 32 * i;
+    if (j < nvec) {
+      load8(X, x_dt, base + j * 8, v[i]);
+      if (DELTA) {
+        float d[8];
+        load8(DELTA, d_dt, base + j * 8, d);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[i][e] += d[e];
+        if (XOUT) store8(XOUT, x_dt, base + j * 8, v[i]);
+      }
+#pragma unroll
+      for (int e = 0; e < 8; ++e) ss += v[i][e] * v[i][e];
+    }
   }
   ss = warp_sum(ss);
   const float r = rsqrtf(ss / (float)D + eps);
   if (lane == 0) rstd[row] = r;
-  for (int j = lane; j < nvec; j += 32) {
-    float v[8];
-    load8(X, x_dt, base + j * 8, v);  // second read hits L1/L2
 #pragma unroll
-    for (int e = 0; e < 8; ++e) v[e] *= r;
-    store8(Y, y_dt, base + j * 8, v);
+  for (int i = 0; i < VPL; ++i) {
+    const int j = lane + 32 * i;
+    if (j < nvec) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v[i][e] *= r;
+      store8(Y, y_dt, base + j * 8, v[i]);
+    }
   }
 }
 
-// dx = r * (dy - xhat * mean(dy * xhat)),  xhat = x * r
+// dx = (GX) + r * (dy - xhat * mean(dy * xhat)),  xhat = x * r.
+// GX (optional, X's dtype) is the gradient arriving through the residual connection; DX2
+// (optional, bf16) receives a second copy of dx for the bf16 branch that produced DELTA.
+template <int VPL>
 __global__ void __launch_bounds__(256)
-rmsnorm_bwd_kernel(const void* X, int x_dt, const void* DY, int dy_dt, const float* rstd, void* DX,
-                   long long rows, int D) {
+rmsnorm_bwd_kernel(const void* X, int x_dt, const void* DY, int dy_dt, const float* rstd,
+                   const void* GX, void* DX, void* DX2, long long rows, int D) {
   const long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (row >= rows) return;
   const long long base = row * D;
   const int nvec = D / 8;
   const float r = rstd[row];
+  float x[VPL][8], g[VPL][8];
   float dot = 0.f;
-  for (int j = lane; j < nvec; j += 32) {
-    float x[8], g[8];
-    load8(X, x_dt, base + j * 8, x);
-    load8(DY, dy_dt, base + j * 8, g);
 #pragma unroll
-    for (int e = 0; e < 8; ++e) dot += g[e] * x[e];
+  for (int i = 0; i < VPL; ++i) {
+    const int j = lane + 32 * i;
+    if (j < nvec) {
+      load8(X, x_dt, base + j * 8, x[i]);
+      load8(DY, dy_dt, base + j * 8, g[i]);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) dot += g[i][e] * x[i][e];
+    }
   }
   dot = warp_sum(dot) * r / (float)D;  // mean(dy * xhat)
-  for (int j = lane; j < nvec; j += 32) {
-    float x[8], g[8], o[8];
-    load8(X, x_dt, base + j * 8, x);
-    load8(DY, dy_dt, base + j * 8, g);
 #pragma unroll
-    for (int e = 0; e < 8; ++e) o[e] = r * (g[e] - x[e] * r * dot);
-    store8(DX, x_dt, base + j * 8, o);
+  for (int i = 0; i < VPL; ++i) {
+    const int j = lane + 32 * i;
+    if (j < nvec) {
+      float o[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) o[e] = r * (g[i][e] - x[i][e] * r * dot);
+      if (GX) {
+        float gx[8];
+        load8(GX, x_dt, base + j * 8, gx);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] += gx[e];
+      }
+      store8(DX, x_dt, base + j * 8, o);
+      if (DX2) store8(DX2, DT_BF16, base + j * 8, o);
+    }
   }
 }
 
 // ---------------------------------------------------------------------------------------------
-// RoPE + RMS norm over head_dim for q and k ([B,T,H,D] bf16, cos/sin [T, D/2] bf16).
-// One warp per (tensor, b, t, h) vector; lane l owns the rotation pairs p = l, l+32, ...
+// RoPE + RMS norm over head_dim for q and k.  Inputs are [B*T, H, D] bf16 with a row stride (so
+// slices of a fused projection can be read in place), cos/sin are [T, D/2] bf16, outputs are
+// contiguous.  D/16 threads share one head vector: each holds 8 elements of the first half and
+// the 8 elements they are rotated with.
 // ---------------------------------------------------------------------------------------------
 template <int D>
 __global__ void __launch_bounds__(256)
-rope_qknorm_fwd_kernel(const __nv_bfloat16* Q, const __nv_bfloat16* K, const __nv_bfloat16* COS,
-                       const __nv_bfloat16* SIN, __nv_bfloat16* QO, __nv_bfloat16* KO, float* rstd,
-                       long long n_vec, int T, int H, float eps) {
-  constexpr int HALF = D / 2, PAIRS = HALF / 32;
-  const long long w = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
-  const int lane = threadIdx.x & 31;
-  if (w >= 2 * n_vec) return;
+rope_qknorm_fwd_kernel(const __nv_bfloat16* Q, const __nv_bfloat16* K, long long in_row_stride,
+                       const __nv_bfloat16* COS, const __nv_bfloat16* SIN, __nv_bfloat16* QO,
+                       __nv_bfloat16* KO, float* rstd, long long n_vec, int T, int H, float eps) {
+  constexpr int HALF = D / 2, TPV = D / 16;
+  const long long gid = (long long)blockIdx.x * 256 + threadIdx.x;
+  const long long w_raw = gid / TPV;
+  const int sub = (int)(gid % TPV);
+  const bool valid = w_raw < 2 * n_vec;  // no early exit: the shuffles below need whole warps
+  const long long w = valid ? w_raw : 0;
   const bool is_k = w >= n_vec;
   const long long vec = is_k ? w - n_vec : w;
-  const int t = (int)((vec / H) % T);
-  const __nv_bfloat16* x = (is_k ? K : Q) + vec * D;
+  const long long bt = vec / H;
+  const int h = (int)(vec - bt * H);
+  const int t = (int)(bt % T);
+  const __nv_bfloat16* x = (is_k ? K : Q) + bt * in_row_stride + (long long)h * D;
   __nv_bfloat16* y = (is_k ? KO : QO) + vec * D;
-  float y1[PAIRS], y2[PAIRS];
+  float x1[8], x2[8], c[8], s[8], y1[8], y2[8];
+  load8(x, DT_BF16, sub * 8, x1);
+  load8(x, DT_BF16, HALF + sub * 8, x2);
+  load8(COS, DT_BF16, (long long)t * HALF + sub * 8, c);
+  load8(SIN, DT_BF16, (long long)t * HALF + sub * 8, s);
   float ss = 0.f;
 #pragma unroll
-  for (int i = 0; i < PAIRS; ++i) {
-    const int p = lane + 32 * i;
-    const float c = __bfloat162float(COS[(long long)t * HALF + p]);
-    const float s = __bfloat162float(SIN[(long long)t * HALF + p]);
-    const float x1 = __bfloat162float(x[p]), x2 = __bfloat162float(x[p + HALF]);
-    y1[i] = x1 * c + x2 * s;
-    y2[i] = x2 * c - x1 * s;
-    ss += y1[i] * y1[i] + y2[i] * y2[i];
+  for (int e = 0; e < 8; ++e) {
+    y1[e] = x1[e] * c[e] + x2[e] * s[e];
+    y2[e] = x2[e] * c[e] - x1[e] * s[e];
+    ss += y1[e] * y1[e] + y2[e] * y2[e];
   }
-  ss = warp_sum(ss);
-  const float r = rsqrtf(ss / (float)D + eps);
-  if (lane == 0) rstd[w] = r;
 #pragma unroll
-  for (int i = 0; i < PAIRS; ++i) {
-    const int p = lane + 32 * i;
-    y[p] = __float2bfloat16_rn(y1[i] * r);
-    y[p + HALF] = __float2bfloat16_rn(y2[i] * r);
-  }
+  for (int o = TPV / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  const float r = rsqrtf(ss / (float)D + eps);
+  if (!valid) return;
+  if (sub == 0) rstd[w] = r;
+#pragma unroll
+  for (int e = 0; e < 8; ++e) { y1[e] *= r; y2[e] *= r; }
+  store8(y, DT_BF16, sub * 8, y1);
+  store8(y, DT_BF16, HALF + sub * 8, y2);
 }
 
 template <int D>
 __global__ void __launch_bounds__(256)
-rope_qknorm_bwd_kernel(const __nv_bfloat16* Q, const __nv_bfloat16* K, const __nv_bfloat16* COS,
-                       const __nv_bfloat16* SIN, const __nv_bfloat16* DQO,
-                       const __nv_bfloat16* DKO, const float* rstd, __nv_bfloat16* DQ,
-                       __nv_bfloat16* DK, long long n_vec, int T, int H) {
-  constexpr int HALF = D / 2, PAIRS = HALF / 32;
-  const long long w = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
-  const int lane = threadIdx.x & 31;
-  if (w >= 2 * n_vec) return;
+rope_qknorm_bwd_kernel(const __nv_bfloat16* Q, const __nv_bfloat16* K, long long in_row_stride,
+                       const __nv_bfloat16* COS, const __nv_bfloat16* SIN,
+                       const __nv_bfloat16* DQO, const __nv_bfloat16* DKO, const float* rstd,
+                       __nv_bfloat16* DQ, __nv_bfloat16* DK, long long out_row_stride,
+                       long long n_vec, int T, int H) {
+  constexpr int HALF = D / 2, TPV = D / 16;
+  const long long gid = (long long)blockIdx.x * 256 + threadIdx.x;
+  const long long w_raw = gid / TPV;
+  const int sub = (int)(gid % TPV);
+  const bool valid = w_raw < 2 * n_vec;  // no early exit: the shuffles below need whole warps
+  const long long w = valid ? w_raw : 0;
   const bool is_k = w >= n_vec;
   const long long vec = is_k ? w - n_vec : w;
-  const int t = (int)((vec / H) % T);
-  const __nv_bfloat16* x = (is_k ? K : Q) + vec * D;
+  const long long bt = vec / H;
+  const int h = (int)(vec - bt * H);
+  const int t = (int)(bt % T);
+  const __nv_bfloat16* x = (is_k ? K : Q) + bt * in_row_stride + (long long)h * D;
   const __nv_bfloat16* g = (is_k ? DKO : DQO) + vec * D;
-  __nv_bfloat16* dx = (is_k ? DK : DQ) + vec * D;
+  __nv_bfloat16* dx = (is_k ? DK : DQ) + bt * out_row_stride + (long long)h * D;
   const float r = rstd[w];
-  float y1[PAIRS], y2[PAIRS], g1[PAIRS], g2[PAIRS], cs[PAIRS], sn[PAIRS];
+  float x1[8], x2[8], c[8], s[8], y1[8], y2[8], g1[8], g2[8];
+  load8(x, DT_BF16, sub * 8, x1);
+  load8(x, DT_BF16, HALF + sub * 8, x2);
+  load8(COS, DT_BF16, (long long)t * HALF + sub * 8, c);
+  load8(SIN, DT_BF16, (long long)t * HALF + sub * 8, s);
+  load8(g, DT_BF16, sub * 8, g1);
+  load8(g, DT_BF16, HALF + sub * 8, g2);
   float dot = 0.f;
 #pragma unroll
-  for (int i = 0; i < PAIRS; ++i) {
-    const int p = lane + 32 * i;
-    cs[i] = __bfloat162float(COS[(long long)t * HALF + p]);
-    sn[i] = __bfloat162float(SIN[(long long)t * HALF + p]);
-    const float x1 = __bfloat162float(x[p]), x2 = __bfloat162float(x[p + HALF]);
-    y1[i] = x1 * cs[i] + x2 * sn[i];
-    y2[i] = x2 * cs[i] - x1 * sn[i];
-    g1[i] = __bfloat162float(g[p]);
-    g2[i] = __bfloat162float(g[p + HALF]);
-    dot += g1[i] * y1[i] + g2[i] * y2[i];
+  for (int e = 0; e < 8; ++e) {
+    y1[e] = x1[e] * c[e] + x2[e] * s[e];
+    y2[e] = x2[e] * c[e] - x1[e] * s[e];
+    dot += g1[e] * y1[e] + g2[e] * y2[e];
   }
-  dot = warp_sum(dot) * r / (float)D;
 #pragma unroll
-  for (int i = 0; i < PAIRS; ++i) {
-    const int p = lane + 32 * i;
-    const float d1 = r * (g1[i] - y1[i] * r * dot);  // grad w.r.t. the rotated vector
-    const float d2 = r * (g2[i] - y2[i] * r * dot);
-    dx[p] = __float2bfloat16_rn(d1 * cs[i] - d2 * sn[i]);
-    dx[p + HALF] = __float2bfloat16_rn(d1 * sn[i] + d2 * cs[i]);
+  for (int o = TPV / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+  if (!valid) return;
+  dot = dot * r / (float)D;
+  float o1[8], o2[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    const float d1 = r * (g1[e] - y1[e] * r * dot);  // gradient w.r.t. the rotated vector
+    const float d2 = r * (g2[e] - y2[e] * r * dot);
+    o1[e] = d1 * c[e] - d2 * s[e];
+    o2[e] = d1 * s[e] + d2 * c[e];
   }
+  store8(dx, DT_BF16, sub * 8, o1);
+  store8(dx, DT_BF16, HALF + sub * 8, o2);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -237,7 +288,7 @@ __global__ void __launch_bounds__(kCeThreads)
 ce_fwd_bwd_kernel(void* L, int dt, const long long* tgt, long long n, int V, long long ld,
                   int ignore_index, float* losses, const float* count, int write_grad) {
   __shared__ float s_m[kCeThreads / 32], s_s[kCeThreads / 32];
-  __shared__ float s_max, s_lse;
+  __shared__ float s_lse;
   const long long row = blockIdx.x;
   const long long base = row * ld;
   const long long target = tgt[row];
@@ -275,7 +326,7 @@ ce_fwd_bwd_kernel(void* L, int dt, const long long* tgt, long long n, int V, lon
     float ssum = lane < kCeThreads / 32 ? s_s[lane] : 0.f;
     const float bm = warp_max(mm);
     ssum = warp_sum(mm == -INFINITY ? 0.f : ssum * __expf(mm - bm));
-    if (lane == 0) { s_max = bm; s_lse = bm + logf(ssum); }
+    if (lane == 0) s_lse = bm + logf(ssum);
   }
   __syncthreads();
   const float lse = s_lse;
@@ -326,57 +377,77 @@ static inline unsigned grid_for(long long n8) {
   return (unsigned)(b < 148 * 16 ? (b > 0 ? b : 1) : 148 * 16);
 }
 
-DION_EXPORT int dion_rmsnorm_fwd(const void* X, int x_dt, void* Y, int y_dt, float* rstd,
-                                 long long rows, int D, float eps, void* stream) {
-  if (rows <= 0) return 0;
-  if (D % 8) return -2;
-  rmsnorm_fwd_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, S(stream)>>>(X, x_dt, Y, y_dt, rstd,
-                                                                       rows, D, eps);
-  return rc();
-}
-DION_EXPORT int dion_rmsnorm_bwd(const void* X, int x_dt, const void* DY, int dy_dt,
-                                 const float* rstd, void* DX, long long rows, int D,
+#define DION_VPL_DISPATCH(D_, CALL)                              \
+  if ((D_) <= 256) { constexpr int VPL = 1; CALL; }              \
+  else if ((D_) <= 512) { constexpr int VPL = 2; CALL; }         \
+  else if ((D_) <= 1024) { constexpr int VPL = 4; CALL; }        \
+  else if ((D_) <= 2048) { constexpr int VPL = 8; CALL; }        \
+  else if ((D_) <= 4096) { constexpr int VPL = 16; CALL; }       \
+  else return -3;
+
+// Y = rmsnorm(X + DELTA); DELTA and XOUT may be null (plain RMS norm).  D % 8 == 0, D <= 4096.
+DION_EXPORT int dion_rmsnorm_fwd(const void* X, int x_dt, const void* DELTA, int d_dt, void* XOUT,
+                                 void* Y, int y_dt, float* rstd, long long rows, int D, float eps,
                                  void* stream) {
   if (rows <= 0) return 0;
   if (D % 8) return -2;
-  rmsnorm_bwd_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, S(stream)>>>(X, x_dt, DY, dy_dt, rstd,
-                                                                       DX, rows, D);
+  const unsigned grid = (unsigned)((rows + 7) / 8);
+  DION_VPL_DISPATCH(D, (rmsnorm_fwd_kernel<VPL><<<grid, 256, 0, S(stream)>>>(
+                           X, x_dt, DELTA, d_dt, XOUT, Y, y_dt, rstd, rows, D, eps)))
+  return rc();
+}
+// DX = GX + rmsnorm_backward(DY); GX and DX2 (bf16 copy of DX) may be null.
+DION_EXPORT int dion_rmsnorm_bwd(const void* X, int x_dt, const void* DY, int dy_dt,
+                                 const float* rstd, const void* GX, void* DX, void* DX2,
+                                 long long rows, int D, void* stream) {
+  if (rows <= 0) return 0;
+  if (D % 8) return -2;
+  const unsigned grid = (unsigned)((rows + 7) / 8);
+  DION_VPL_DISPATCH(D, (rmsnorm_bwd_kernel<VPL><<<grid, 256, 0, S(stream)>>>(
+                           X, x_dt, DY, dy_dt, rstd, GX, DX, DX2, rows, D)))
   return rc();
 }
 
 #define DION_ROPE_DISPATCH(D_, CALL) \
   switch (D_) {                      \
+    case 32: { constexpr int DD = 32; CALL; break; }   \
     case 64: { constexpr int DD = 64; CALL; break; }   \
     case 128: { constexpr int DD = 128; CALL; break; } \
-    case 192: { constexpr int DD = 192; CALL; break; } \
     case 256: { constexpr int DD = 256; CALL; break; } \
     default: return -2;              \
   }
 
-DION_EXPORT int dion_rope_qknorm_fwd(const void* Q, const void* K, const void* COS,
-                                     const void* SIN, void* QO, void* KO, float* rstd, int B,
-                                     int T, int H, int D, float eps, void* stream) {
+DION_EXPORT int dion_rope_qknorm_fwd(const void* Q, const void* K, long long in_row_stride,
+                                     const void* COS, const void* SIN, void* QO, void* KO,
+                                     float* rstd, int B, int T, int H, int D, float eps,
+                                     void* stream) {
   const long long n_vec = (long long)B * T * H;
   if (n_vec <= 0) return 0;
-  const unsigned grid = (unsigned)((2 * n_vec + 7) / 8);
+  if (in_row_stride % 8) return -2;
+  const long long threads = 2 * n_vec * (D / 16);
+  const unsigned grid = (unsigned)((threads + 255) / 256);
   typedef const __nv_bfloat16* CP;
   typedef __nv_bfloat16* P;
   DION_ROPE_DISPATCH(D, (rope_qknorm_fwd_kernel<DD><<<grid, 256, 0, S(stream)>>>(
-                            (CP)Q, (CP)K, (CP)COS, (CP)SIN, (P)QO, (P)KO, rstd, n_vec, T, H, eps)))
+                            (CP)Q, (CP)K, in_row_stride, (CP)COS, (CP)SIN, (P)QO, (P)KO, rstd,
+                            n_vec, T, H, eps)))
   return rc();
 }
-DION_EXPORT int dion_rope_qknorm_bwd(const void* Q, const void* K, const void* COS,
-                                     const void* SIN, const void* DQO, const void* DKO,
-                                     const float* rstd, void* DQ, void* DK, int B, int T, int H,
-                                     int D, void* stream) {
+DION_EXPORT int dion_rope_qknorm_bwd(const void* Q, const void* K, long long in_row_stride,
+                                     const void* COS, const void* SIN, const void* DQO,
+                                     const void* DKO, const float* rstd, void* DQ, void* DK,
+                                     long long out_row_stride, int B, int T, int H, int D,
+                                     void* stream) {
   const long long n_vec = (long long)B * T * H;
   if (n_vec <= 0) return 0;
-  const unsigned grid = (unsigned)((2 * n_vec + 7) / 8);
+  if (in_row_stride % 8 || out_row_stride % 8) return -2;
+  const long long threads = 2 * n_vec * (D / 16);
+  const unsigned grid = (unsigned)((threads + 255) / 256);
   typedef const __nv_bfloat16* CP;
   typedef __nv_bfloat16* P;
   DION_ROPE_DISPATCH(D, (rope_qknorm_bwd_kernel<DD><<<grid, 256, 0, S(stream)>>>(
-                            (CP)Q, (CP)K, (CP)COS, (CP)SIN, (CP)DQO, (CP)DKO, rstd, (P)DQ, (P)DK,
-                            n_vec, T, H)))
+                            (CP)Q, (CP)K, in_row_stride, (CP)COS, (CP)SIN, (CP)DQO, (CP)DKO, rstd,
+                            (P)DQ, (P)DK, out_row_stride, n_vec, T, H)))
   return rc();
 }
 
@@ -395,8 +466,9 @@ DION_EXPORT int dion_relu2_bwd(const void* X, const void* DY, void* DX, int dt, 
 DION_EXPORT int dion_ce_count(const void* tgt, long long n, int ignore_index, float* count,
                               void* stream) {
   if (n <= 0) return 0;
-  ce_count_kernel<<<(unsigned)((n + 1023) / 1024 < 256 ? (n + 1023) / 1024 : 256), 1024, 0,
-                    S(stream)>>>(static_cast<const long long*>(tgt), n, ignore_index, count);
+  const long long blocks = (n + 1023) / 1024;
+  ce_count_kernel<<<(unsigned)(blocks < 256 ? blocks : 256), 1024, 0, S(stream)>>>(
+      static_cast<const long long*>(tgt), n, ignore_index, count);
   return rc();
 }
 DION_EXPORT int dion_ce_fwd_bwd(void* L, int dt, const void* tgt, long long n, int V, long long ld,

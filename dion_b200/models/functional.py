@@ -54,21 +54,23 @@ def _eps_for(dtype: torch.dtype) -> float:
 
 
 # ------------------------------------------------------------------------------------------------
-# RMS norm
+# RMS norm (optionally fused with the residual add that precedes it)
 # ------------------------------------------------------------------------------------------------
+def _rows(x: Tensor) -> Tensor:
+    x2 = x.reshape(-1, x.size(-1))
+    return x2 if x2.is_contiguous() else x2.contiguous()
+
+
 class _RMSNorm(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x: Tensor, eps: float, out_dtype: torch.dtype):
-        D = x.size(-1)
-        x2 = x.reshape(-1, D)
-        if not x2.is_contiguous():
-            x2 = x2.contiguous()
-        rows = x2.size(0)
+        x2 = _rows(x)
+        rows, D = x2.shape
         y = torch.empty((rows, D), dtype=out_dtype, device=x.device)
         rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
-        _check(_lib().dion_rmsnorm_fwd(_c(x2), _DT[x2.dtype], _c(y), _DT[out_dtype], _c(rstd),
-                                       ctypes.c_longlong(rows), D, ctypes.c_float(eps),
-                                       _stream(x.device)), "dion_rmsnorm_fwd")
+        _check(_lib().dion_rmsnorm_fwd(_c(x2), _DT[x2.dtype], _c(None), 0, _c(None), _c(y),
+                                       _DT[out_dtype], _c(rstd), ctypes.c_longlong(rows), D,
+                                       ctypes.c_float(eps), _stream(x.device)), "dion_rmsnorm_fwd")
         ctx.save_for_backward(x2, rstd)
         ctx.shape = x.shape
         return y.view(x.shape)
@@ -77,23 +79,75 @@ class _RMSNorm(torch.autograd.Function):
     def backward(ctx, dy: Tensor):
         x2, rstd = ctx.saved_tensors
         rows, D = x2.shape
-        dy2 = dy.reshape(rows, D)
-        if not dy2.is_contiguous():
-            dy2 = dy2.contiguous()
+        dy2 = _rows(dy)
         dx = torch.empty_like(x2)
         _check(_lib().dion_rmsnorm_bwd(_c(x2), _DT[x2.dtype], _c(dy2), _DT[dy2.dtype], _c(rstd),
-                                       _c(dx), ctypes.c_longlong(rows), D, _stream(x2.device)),
-               "dion_rmsnorm_bwd")
+                                       _c(None), _c(dx), _c(None), ctypes.c_longlong(rows), D,
+                                       _stream(x2.device)), "dion_rmsnorm_bwd")
         return dx.view(ctx.shape), None, None
+
+
+class _AddRMSNorm(torch.autograd.Function):
+    """``x_new = x + delta; h = rms_norm(x_new)`` in one pass; the backward pass adds the
+    gradient that reaches ``x_new`` through the residual path to the norm's gradient and emits
+    it twice: in ``x``'s dtype for the residual stream and in bf16 for the branch behind
+    ``delta``."""
+
+    @staticmethod
+    def forward(ctx, x: Tensor, delta: Tensor, eps: float, out_dtype: torch.dtype):
+        x2, d2 = _rows(x), _rows(delta)
+        rows, D = x2.shape
+        x_new = torch.empty_like(x2)
+        h = torch.empty((rows, D), dtype=out_dtype, device=x.device)
+        rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
+        _check(_lib().dion_rmsnorm_fwd(_c(x2), _DT[x2.dtype], _c(d2), _DT[d2.dtype], _c(x_new),
+                                       _c(h), _DT[out_dtype], _c(rstd), ctypes.c_longlong(rows),
+                                       D, ctypes.c_float(eps), _stream(x.device)),
+               "dion_rmsnorm_fwd")
+        ctx.save_for_backward(x_new, rstd)
+        ctx.shape = x.shape
+        ctx.delta_dtype = delta.dtype
+        return x_new.view(x.shape), h.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, g_x: Tensor, g_h: Tensor):
+        x_new, rstd = ctx.saved_tensors
+        rows, D = x_new.shape
+        gx2 = _rows(g_x) if g_x is not None else None
+        gh2 = _rows(g_h)
+        dx = torch.empty_like(x_new)
+        want_bf16 = ctx.delta_dtype == torch.bfloat16 and x_new.dtype != torch.bfloat16
+        dx2 = torch.empty((rows, D), dtype=torch.bfloat16, device=x_new.device) if want_bf16 else None
+        _check(_lib().dion_rmsnorm_bwd(_c(x_new), _DT[x_new.dtype], _c(gh2), _DT[gh2.dtype],
+                                       _c(rstd), _c(gx2), _c(dx), _c(dx2),
+                                       ctypes.c_longlong(rows), D, _stream(x_new.device)),
+               "dion_rmsnorm_bwd")
+        dx = dx.view(ctx.shape)
+        ddelta = dx2.view(ctx.shape) if want_bf16 else dx.to(ctx.delta_dtype)
+        return dx, ddelta, None, None
+
+
+def _norm_kernel_ok(x: Tensor) -> bool:
+    return x.is_cuda and x.dtype in _DT and x.size(-1) % 8 == 0 and x.size(-1) <= 4096
 
 
 def rms_norm(x: Tensor, eps: Optional[float] = None) -> Tensor:
     """``x * rsqrt(mean(x**2, -1) + eps)``; ``eps`` defaults to the machine epsilon of ``x``'s
     dtype, as in ``torch.nn.functional.rms_norm``."""
-    if x.is_cuda and x.dtype in _DT and x.size(-1) % 8 == 0:
+    if _norm_kernel_ok(x):
         out_dtype = torch.bfloat16 if _autocast_bf16(x) else x.dtype
         return _RMSNorm.apply(x, _eps_for(x.dtype) if eps is None else eps, out_dtype)
     return tF.rms_norm(x, (x.size(-1),), eps=eps)
+
+
+def add_rms_norm(x: Tensor, delta: Tensor, eps: Optional[float] = None) -> Tuple[Tensor, Tensor]:
+    """``(x + delta, rms_norm(x + delta))``: the residual update of a transformer block together
+    with the normalisation that feeds the next sub-layer."""
+    if _norm_kernel_ok(x) and delta.is_cuda and delta.dtype in _DT and delta.shape == x.shape:
+        out_dtype = torch.bfloat16 if _autocast_bf16(x) else x.dtype
+        return _AddRMSNorm.apply(x, delta, _eps_for(x.dtype) if eps is None else eps, out_dtype)
+    x = x + delta
+    return x, tF.rms_norm(x, (x.size(-1),), eps=eps)
 
 
 # ------------------------------------------------------------------------------------------------
@@ -106,19 +160,35 @@ def _rope_torch(x: Tensor, cos: Tensor, sin: Tensor) -> Tensor:
     return torch.cat([x1 * c + x2 * s, x2 * c - x1 * s], 3).type_as(x)
 
 
+def _row_stride(t: Tensor) -> Optional[int]:
+    """Row stride of a ``[B, T, H, D]`` tensor whose (H, D) block is dense and whose (B, T)
+    dims collapse to one row index, or None."""
+    B, T, H, D = t.shape
+    if t.stride(3) != 1 or t.stride(2) != D:
+        return None
+    rs = t.stride(1)
+    if B > 1 and t.stride(0) != T * rs:
+        return None
+    return rs
+
+
 class _RopeQKNorm(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q: Tensor, k: Tensor, cos: Tensor, sin: Tensor, eps: float):
         B, T, H, D = q.shape
-        q = q.contiguous()
-        k = k.contiguous()
-        qo, ko = torch.empty_like(q), torch.empty_like(k)
-        n = B * T * H
-        rstd = torch.empty((2, n), dtype=torch.float32, device=q.device)
-        _check(_lib().dion_rope_qknorm_fwd(_c(q), _c(k), _c(cos), _c(sin), _c(qo), _c(ko),
-                                           _c(rstd), B, T, H, D, ctypes.c_float(eps),
-                                           _stream(q.device)), "dion_rope_qknorm_fwd")
+        rs_q, rs_k = _row_stride(q), _row_stride(k)
+        if rs_q is None or rs_k != rs_q or rs_q % 8 or q.data_ptr() % 16 or k.data_ptr() % 16:
+            q, k = q.contiguous(), k.contiguous()
+            rs_q = H * D
+        qo = torch.empty((B, T, H, D), dtype=q.dtype, device=q.device)
+        ko = torch.empty_like(qo)
+        rstd = torch.empty((2, B * T * H), dtype=torch.float32, device=q.device)
+        _check(_lib().dion_rope_qknorm_fwd(_c(q), _c(k), ctypes.c_longlong(rs_q), _c(cos), _c(sin),
+                                           _c(qo), _c(ko), _c(rstd), B, T, H, D,
+                                           ctypes.c_float(eps), _stream(q.device)),
+               "dion_rope_qknorm_fwd")
         ctx.save_for_backward(q, k, cos, sin, rstd)
+        ctx.rs = rs_q
         return qo, ko
 
     @staticmethod
@@ -126,9 +196,11 @@ class _RopeQKNorm(torch.autograd.Function):
         q, k, cos, sin, rstd = ctx.saved_tensors
         B, T, H, D = q.shape
         dqo, dko = dqo.contiguous(), dko.contiguous()
-        dq, dk = torch.empty_like(q), torch.empty_like(k)
-        _check(_lib().dion_rope_qknorm_bwd(_c(q), _c(k), _c(cos), _c(sin), _c(dqo), _c(dko),
-                                           _c(rstd), _c(dq), _c(dk), B, T, H, D,
+        dq = torch.empty((B, T, H, D), dtype=q.dtype, device=q.device)
+        dk = torch.empty_like(dq)
+        _check(_lib().dion_rope_qknorm_bwd(_c(q), _c(k), ctypes.c_longlong(ctx.rs), _c(cos),
+                                           _c(sin), _c(dqo), _c(dko), _c(rstd), _c(dq), _c(dk),
+                                           ctypes.c_longlong(H * D), B, T, H, D,
                                            _stream(q.device)), "dion_rope_qknorm_bwd")
         return dq, dk, None, None, None
 
@@ -137,8 +209,9 @@ def rope_qknorm(q: Tensor, k: Tensor, cos: Tensor, sin: Tensor) -> Tuple[Tensor,
     """Rotary embedding (``cos/sin``: ``[T, D/2]``) then RMS-norm over the last dim, for ``q``
     and ``k`` of shape ``[B, T, H, D]``."""
     D = q.size(-1)
-    if (q.is_cuda and q.dtype == torch.bfloat16 and k.dtype == torch.bfloat16 and D % 64 == 0
-            and D <= 256 and cos.dtype == torch.bfloat16 and q.shape == k.shape):
+    if (q.is_cuda and q.dtype == torch.bfloat16 and k.dtype == torch.bfloat16
+            and D in (32, 64, 128, 256) and cos.dtype == torch.bfloat16 and q.shape == k.shape
+            and cos.is_contiguous() and sin.is_contiguous()):
         return _RopeQKNorm.apply(q, k, cos, sin, _eps_for(torch.bfloat16))
     q, k = _rope_torch(q, cos, sin), _rope_torch(k, cos, sin)
     return tF.rms_norm(q, (D,)), tF.rms_norm(k, (D,))

@@ -110,10 +110,15 @@ class Block(nn.Module):
         self.attn = CausalSelfAttention(config)
         self.mlp = MLP(config)
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
-        x = x + self.attn(Fn.rms_norm(x))
-        x = x + self.mlp(Fn.rms_norm(x))
-        return x
+    def forward(self, x: torch.Tensor, h: Optional[torch.Tensor] = None):
+        """``x`` is the residual stream; ``h = rms_norm(x)`` may be passed in by the caller that
+        already computed it.  Returns the new residual stream and its normalisation, so that the
+        next block (or the output head) does not have to read ``x`` again."""
+        if h is None:
+            h = Fn.rms_norm(x)
+        x, h = Fn.add_rms_norm(x, self.attn(h))
+        x, h = Fn.add_rms_norm(x, self.mlp(h))
+        return x, h
 
 
 class GPT(nn.Module):
@@ -144,9 +149,10 @@ class GPT(nn.Module):
     def forward(self, idx: torch.Tensor, targets: Optional[torch.Tensor] = None,
                 return_logits: bool = False):
         x = self.transformer.wte(idx)
+        h = None
         for block in self.transformer.h:
-            x = block(x)
-        x = Fn.rms_norm(x)
+            x, h = block(x, h)
+        x = h if h is not None else Fn.rms_norm(x)  # final norm rides on the last residual add
         if targets is not None:
             logits = self.lm_head(x)
             if return_logits:

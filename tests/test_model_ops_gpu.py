@@ -115,3 +115,25 @@ def test_gpt_forward_backward_matches_torch_path():
     for g, p in zip(g_fused, mc.parameters()):
         denom = p.grad.abs().max().item() + 1e-6
         assert (g.cpu() - p.grad).abs().max().item() / denom < 0.1
+
+
+@pytest.mark.parametrize("D", [768, 2048, 3072])
+def test_add_rms_norm(D):
+    torch.manual_seed(0)
+    x = torch.randn(3, 21, D, device="cuda", requires_grad=True)
+    d = torch.randn(3, 21, D, device="cuda").bfloat16().requires_grad_()
+    xr = x.detach().clone().requires_grad_()
+    dr = d.detach().float().requires_grad_()
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        xn, h = Fn.add_rms_norm(x, d)
+    assert xn.dtype == torch.float32 and h.dtype == torch.bfloat16
+    xnr = xr + dr
+    hr = tF.rms_norm(xnr, (D,), eps=torch.finfo(torch.float32).eps)
+    g1, g2 = torch.randn_like(xnr), torch.randn_like(hr)
+    (xn * g1).sum().backward(retain_graph=True)
+    (h.float() * g2).sum().backward()
+    ((xnr * g1).sum() + (hr * g2).sum()).backward()
+    assert (xn - xnr).abs().max().item() < 1e-5
+    assert (h.float() - hr).abs().max().item() < 3e-2
+    assert (x.grad - xr.grad).abs().max().item() < 2e-2  # g2 passed through bf16 h
+    assert (d.grad.float() - dr.grad).abs().max().item() < 5e-2
