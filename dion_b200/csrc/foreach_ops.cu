@@ -118,7 +118,7 @@ __device__ __forceinline__ float block_sum(float v) {
 // ---------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(kThreads)
 muon_pre_kernel(const long long* raw, int g_dt, int m_dt, float mu, int nesterov, int add_only,
-                float* sumsq) {
+                float* sumsq, int sumsq_in_table) {
   Table tb{raw};
   float acc = 0.f;
   const void* G;
@@ -164,6 +164,11 @@ muon_pre_kernel(const long long* raw, int g_dt, int m_dt, float mu, int nesterov
   if (sumsq) {
     const float s = block_sum(acc);
     if (threadIdx.x == 0) atomicAdd(&sumsq[t], s);
+  } else if (sumsq_in_table) {
+    // table pointer 3: where this tensor's partial sum is accumulated (may be peer memory)
+    float* target = reinterpret_cast<float*>(tb.ptr(3, t));
+    const float s = block_sum(acc);
+    if (threadIdx.x == 0 && target != nullptr) atomicAdd(target, s);
   }
 }
 
@@ -182,11 +187,40 @@ struct ApplyArgs {
   int cols;         // row length (for rowscale); 0 = unused
   const float* normU2;    // NorMuon: per-tensor ||U||^2 and ||U/denom||^2
   const float* normNew2;
+  // U of tensor t was stored into this GPU's memory by rank t / per_rank, which then raised
+  // wait_flags[t / per_rank] to *seq_ptr (optional).
+  const int* wait_flags;
+  const int* seq_ptr;
+  int per_rank;
+  int* status;
 };
+
+__device__ __forceinline__ bool wait_flag_block(const int* flag, int want) {
+  __shared__ int ok;
+  if (threadIdx.x == 0) {
+    int good = 0;
+    for (unsigned k = 0; k < (1u << 22); ++k) {
+      int v;
+      asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+      if (v >= want) { good = 1; break; }
+      __nanosleep(64);
+    }
+    ok = good;
+  }
+  __syncthreads();
+  return ok != 0;
+}
 
 __global__ void __launch_bounds__(kThreads)
 muon_post_kernel(const long long* raw, const ApplyArgs a) {
   Table tb{raw};
+  if (a.wait_flags) {
+    const int t0 = find_tensor(tb, blockIdx.x);
+    if (!wait_flag_block(a.wait_flags + t0 / a.per_rank, *a.seq_ptr)) {
+      if (threadIdx.x == 0) atomicExch(a.status, kStatusTimeoutPeer);
+      return;
+    }
+  }
   const float lr = *a.lr;
   const float wd = a.wd_ptr ? *a.wd_ptr : a.wd;
   const float decay = 1.f - lr * wd;
@@ -509,19 +543,23 @@ static inline cudaStream_t S(void* s) { return static_cast<cudaStream_t>(s); }
 static inline int rc() { return cudaGetLastError() == cudaSuccess ? 0 : -1; }
 
 DION_EXPORT int dion_muon_pre(const void* table, long long n_chunks, int g_dt, int m_dt, float mu,
-                              int nesterov, int add_only, float* sumsq, void* stream) {
+                              int nesterov, int add_only, float* sumsq, int sumsq_in_table,
+                              void* stream) {
   if (n_chunks <= 0) return 0;
   muon_pre_kernel<<<(unsigned)n_chunks, kThreads, 0, S(stream)>>>(
-      static_cast<const long long*>(table), g_dt, m_dt, mu, nesterov, add_only, sumsq);
+      static_cast<const long long*>(table), g_dt, m_dt, mu, nesterov, add_only, sumsq,
+      sumsq_in_table);
   return rc();
 }
 
 DION_EXPORT int dion_muon_post(const void* table, long long n_chunks, const float* lr,
                                const float* wd_ptr, float wd, float ratio, int cautious, int x_dt,
                                int cols, const float* normU2, const float* normNew2,
-                               void* stream) {
+                               const int* wait_flags, const int* seq_ptr, int per_rank,
+                               int* status, void* stream) {
   if (n_chunks <= 0) return 0;
-  ApplyArgs a{lr, wd_ptr, wd, ratio, cautious, x_dt, cols, normU2, normNew2};
+  ApplyArgs a{lr, wd_ptr, wd, ratio, cautious, x_dt, cols, normU2, normNew2,
+              wait_flags, seq_ptr, per_rank > 0 ? per_rank : 1, status};
   muon_post_kernel<<<(unsigned)n_chunks, kThreads, 0, S(stream)>>>(
       static_cast<const long long*>(table), a);
   return rc();

@@ -41,7 +41,46 @@ struct GemmArgs {
   int tiles_per_mat;
   int total_tiles;
   int* status;
+  // ---- optional coupling to other GPUs (all-to-all fused into the kernel) ----
+  // Rows [s*rows_per_src, (s+1)*rows_per_src) of the gated operands were written into this GPU's
+  // memory by rank s, which then set wait_flags[s] to the current sequence number.  The TMA
+  // producer polls the flags of the sources a tile needs before it loads the tile.
+  const int* wait_flags;
+  const int* seq_ptr;
+  int n_src;
+  int rows_per_src;
+  int wait_a, wait_b, wait_k;
+  // scale = 1 / (sqrt(sum_s scale_partials[b*n_src + s]) * scale_mult + scale_eps): the
+  // Frobenius norm assembled from per-source partial sums that travel with the data.
+  const float* scale_partials;
+  float scale_mult, scale_eps;
+  // Output rows scattered to their owners: row r of batch b is stored at
+  // remote_c[r / rows_per_dst] + ((remote_slot + b) * rows_per_dst + r % rows_per_dst) * ldc.
+  long long remote_c[8];
+  int rows_per_dst;
+  int remote_slot;
 };
+
+__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ float ld_volatile_f32(const float* p) {
+  float v;
+  asm volatile("ld.volatile.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
+  return v;
+}
+constexpr uint32_t kMaxFlagPolls = 1u << 22;  // ~ a second or two of polling a local flag
+
+// Waits until flag >= seq; false after kMaxFlagPolls polls.
+__device__ __forceinline__ bool wait_flag_bounded(const int* flag, int seq) {
+  for (uint32_t i = 0; i < kMaxFlagPolls; ++i) {
+    if (ld_acquire_sys(flag) >= seq) return true;
+    __nanosleep(64);
+  }
+  return false;
+}
 
 template <int BN>
 struct SmemLayout {
@@ -58,7 +97,7 @@ __device__ __forceinline__ float ipow(float s, int p) {
   return r;
 }
 
-template <int BN, bool B_MN>
+template <int BN, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(kNumThreads, 1)
 ns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const GemmArgs p) {
@@ -109,9 +148,35 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (lane == 0) {
       uint32_t stage = 0, phase = 0;
       bool ok = true;
+      uint32_t ready_mask = 0;
+      const int seq = p.wait_flags ? *p.seq_ptr : 0;
       for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
         const int b = t / p.tiles_per_mat;
         const int2 tt = p.tiles[t - b * p.tiles_per_mat];
+        if (p.wait_flags) {
+          // Gate this tile on the arrival of the source ranks that own its operand rows.
+          for (int op = 0; op < 2 && ok; ++op) {
+            if (op == 0 ? !p.wait_a : !p.wait_b) continue;
+            const int lim = op == 0 ? p.M : p.N;
+            const int r0 = op == 0 ? tt.x * BM : tt.y * BN;
+            int r1 = r0 + (op == 0 ? BM : BN) - 1;
+            if (r1 > lim - 1) r1 = lim - 1;
+            if (r0 > r1) continue;
+            for (int src = r0 / p.rows_per_src; src <= r1 / p.rows_per_src && src < p.n_src; ++src) {
+              if (ready_mask & (1u << src)) continue;
+              if (!wait_flag_bounded(p.wait_flags + src, seq)) {
+                atomicExch(p.status, kStatusTimeoutPeer);
+                abort_flag = 1;
+                ok = false;
+                break;
+              }
+              ready_mask |= 1u << src;
+            }
+          }
+          if (!ok) break;
+          // peer stores (generic proxy) must be visible to the TMA reads (async proxy)
+          asm volatile("fence.proxy.async;" ::: "memory");
+        }
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1)) {
             atomicExch(p.status, kStatusTimeoutEmpty);
@@ -122,7 +187,32 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           uint8_t* sa = smem + stage * L::kStageBytes;
           uint8_t* sb = sa + L::kABytes;
           mbar_expect_tx(&full_bar[stage], L::kStageBytes);
-          tma_load_3d(sa, &map_a, &full_bar[stage], kb * BK, tt.x * BM, b);
+          if (p.wait_flags && p.wait_k) {
+            // K-slab gating: rows [kb*BK, +BK) of the MN-major operands come from these sources.
+            int k1 = kb * BK + BK - 1;
+            if (k1 > p.K - 1) k1 = p.K - 1;
+            for (int src = (kb * BK) / p.rows_per_src; src <= k1 / p.rows_per_src && src < p.n_src;
+                 ++src) {
+              if (ready_mask & (1u << src)) continue;
+              if (!wait_flag_bounded(p.wait_flags + src, seq)) {
+                atomicExch(p.status, kStatusTimeoutPeer);
+                abort_flag = 1;
+                ok = false;
+                break;
+              }
+              ready_mask |= 1u << src;
+              asm volatile("fence.proxy.async;" ::: "memory");
+            }
+            if (!ok) break;
+          }
+          if (!A_MN) {
+            tma_load_3d(sa, &map_a, &full_bar[stage], kb * BK, tt.x * BM, b);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BM / 64; ++c)
+              tma_load_3d(sa + c * (BK * 128), &map_a, &full_bar[stage], tt.x * BM + c * 64,
+                          kb * BK, b);
+          }
           if (!B_MN) {
             tma_load_3d(sb, &map_b, &full_bar[stage], kb * BK, tt.y * BN, b);
           } else {
@@ -141,7 +231,7 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   } else if (warp == 1) {
     // ------------------------------ MMA issuer --------------------------------
     if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc_bf16(BM, BN, 0, B_MN ? 1 : 0);
+      constexpr uint32_t idesc = make_idesc_bf16(BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
       uint32_t stage = 0, phase = 0;
       uint32_t aslot = 0, aphase = 0;
       bool ok = true;
@@ -165,7 +255,8 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           const uint32_t sb = sa + L::kABytes;
 #pragma unroll
           for (int k = 0; k < BK / 16; ++k) {
-            const uint64_t da = make_smem_desc(sa + k * 32, 16, 1024);
+            const uint64_t da = A_MN ? make_smem_desc(sa + k * 2048, BK * 128, 1024)
+                                     : make_smem_desc(sa + k * 32, 16, 1024);
             const uint64_t db = B_MN ? make_smem_desc(sb + k * 2048, BK * 128, 1024)
                                      : make_smem_desc(sb + k * 32, 16, 1024);
             tc_mma_bf16(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
@@ -187,6 +278,7 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int lane_grp = warp & 3;  // TMEM lanes [32*lane_grp, +32) belong to this warp
     const int row_in_tile = lane_grp * 32 + lane;
     uint32_t aslot = 0, aphase = 0;
+    bool all_sources_ready = false;
     for (int t = blockIdx.x; t < p.total_tiles; t += gridDim.x) {
       const int b = t / p.tiles_per_mat;
       const int2 tt = p.tiles[t - b * p.tiles_per_mat];
@@ -197,6 +289,25 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       tc_fence_after();
       float sc = 1.f;
       if (p.scale != nullptr) sc = p.scale[b];
+      if (p.scale_partials != nullptr) {
+        // The norm needs every source's partial sum: wait for all of them once.
+        if (!all_sources_ready) {
+          bool fine = true;
+          if (lane == 0) {
+            const int seq = *p.seq_ptr;
+            for (int src = 0; src < p.n_src && fine; ++src)
+              fine = wait_flag_bounded(p.wait_flags + src, seq);
+            if (!fine) atomicExch(p.status, kStatusTimeoutPeer);
+          }
+          fine = __shfl_sync(0xffffffffu, fine ? 1 : 0, 0) != 0;
+          if (!fine) break;
+          all_sources_ready = true;
+        }
+        float ss = 0.f;
+        for (int src = 0; src < p.n_src; ++src)
+          ss += ld_volatile_f32(p.scale_partials + (long long)b * p.n_src + src);
+        sc = 1.f / (sqrtf(ss) * p.scale_mult + p.scale_eps);
+      }
       const float alpha = p.alpha * ipow(sc, p.alpha_pow);
       const float beta = p.beta * ipow(sc, p.beta_pow);
       const int r = tt.x * BM + row_in_tile;
@@ -205,12 +316,21 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       const __nv_bfloat16* Drow =
           p.D ? p.D + (long long)b * p.strideD + (long long)r * p.ldd : nullptr;
       __nv_bfloat16* Crow = p.C ? p.C + (long long)b * p.strideC + (long long)r * p.ldc : nullptr;
+      if (p.remote_c[0] != 0 && row_ok) {
+        const int dst = r / p.rows_per_dst;
+        Crow = reinterpret_cast<__nv_bfloat16*>(p.remote_c[dst]) +
+               ((long long)(p.remote_slot + b) * p.rows_per_dst + (r - dst * p.rows_per_dst)) *
+                   p.ldc;
+      }
       float* Cfrow = p.Cf ? p.Cf + (long long)b * p.strideC + (long long)r * p.ldc : nullptr;
       __nv_bfloat16* Cb = p.C ? p.C + (long long)b * p.strideC : nullptr;
       float* Cfb = p.Cf ? p.Cf + (long long)b * p.strideC : nullptr;
       __nv_bfloat16* CTb = p.CT ? p.CT + (long long)b * p.strideCT : nullptr;
-      const bool vec_ok = ((p.ldc & 7) == 0) && ((p.strideC & 7) == 0) &&
-                          ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0) && p.Cf == nullptr;
+      const bool vec_ok = ((p.ldc & 7) == 0) && p.Cf == nullptr &&
+                          (p.remote_c[0] != 0
+                               ? true
+                               : (((p.strideC & 7) == 0) &&
+                                  ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0)));
       const bool dvec_ok = p.D && ((p.ldd & 7) == 0) && ((p.strideD & 7) == 0) &&
                            ((reinterpret_cast<uintptr_t>(p.D) & 15) == 0);
 
@@ -364,20 +484,20 @@ static int make_map_3d(CUtensorMap* map, const void* ptr, int batch, int rows, i
   return r == CUDA_SUCCESS ? 0 : -2;
 }
 
-template <int BN, bool B_MN>
+template <int BN, bool A_MN, bool B_MN>
 static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& args, int num_sms,
                   cudaStream_t stream) {
   using L = SmemLayout<BN>;
   static bool configured = false;
   if (!configured) {
-    if (cudaFuncSetAttribute(ns_gemm_kernel<BN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (cudaFuncSetAttribute(ns_gemm_kernel<BN, A_MN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              L::kDynBytes) != cudaSuccess)
       return -3;
     configured = true;
   }
   int grid = args.total_tiles < num_sms ? args.total_tiles : num_sms;
   if (grid <= 0) return 0;
-  ns_gemm_kernel<BN, B_MN><<<grid, kNumThreads, L::kDynBytes, stream>>>(ma, mb, args);
+  ns_gemm_kernel<BN, A_MN, B_MN><<<grid, kNumThreads, L::kDynBytes, stream>>>(ma, mb, args);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
@@ -388,13 +508,26 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& 
 // `tiles` is a device array of (tile_m, tile_n) pairs in units of (128, bn).  Returns 0 on a
 // successful launch.  Requirements: K-contiguous leading dimensions and batch strides that are
 // multiples of 8 elements and 16-byte aligned base pointers for A and B.
-DION_EXPORT int dion_ns_gemm(const void* A, long long lda, long long strideA, const void* B,
-                             long long ldb, long long strideB, int b_mn, void* C, long long ldc,
-                             long long strideC, const void* D, long long ldd, long long strideD,
-                             void* CT, long long ldct, long long strideCT, void* Cf, int batch,
-                             int M, int N, int K, float alpha, float beta, const float* scale,
-                             int alpha_pow, int beta_pow, int sym, const void* tiles,
-                             int tiles_per_mat, int bn, int num_sms, int* status, void* stream) {
+// Optional cross-GPU coupling of one launch; see the matching fields of GemmArgs.
+struct DionGemmExtra {
+  const int* wait_flags;
+  const int* seq_ptr;
+  int n_src, rows_per_src, wait_a, wait_b, wait_k;
+  const float* scale_partials;
+  float scale_mult, scale_eps;
+  long long remote_c[8];
+  int rows_per_dst, remote_slot;
+};
+
+DION_EXPORT int dion_ns_gemm_ex(const void* A, long long lda, long long strideA, int a_mn,
+                                const void* B, long long ldb, long long strideB, int b_mn, void* C,
+                                long long ldc,
+                                long long strideC, const void* D, long long ldd, long long strideD,
+                                void* CT, long long ldct, long long strideCT, void* Cf, int batch,
+                                int M, int N, int K, float alpha, float beta, const float* scale,
+                                int alpha_pow, int beta_pow, int sym, const void* tiles,
+                                int tiles_per_mat, int bn, int num_sms, int* status, void* stream,
+                                const DionGemmExtra* ex) {
   using namespace dion;
   if (batch <= 0 || M <= 0 || N <= 0 || K <= 0) return 0;
   if ((lda & 7) || (ldb & 7) || (strideA & 7) || (strideB & 7) ||
@@ -402,7 +535,11 @@ DION_EXPORT int dion_ns_gemm(const void* A, long long lda, long long strideA, co
     return -10;
   if (bn != 128 && bn != 256) return -11;
   CUtensorMap ma, mb;
-  if (make_map_3d(&ma, A, batch, M, K, lda, strideA, BK, BM) != 0) return -12;
+  if (!a_mn) {
+    if (make_map_3d(&ma, A, batch, M, K, lda, strideA, BK, BM) != 0) return -12;
+  } else {
+    if (make_map_3d(&ma, A, batch, K, M, lda, strideA, 64, BK) != 0) return -12;
+  }
   if (!b_mn) {
     if (make_map_3d(&mb, B, batch, N, K, ldb, strideB, BK, bn) != 0) return -13;
   } else {
@@ -420,9 +557,52 @@ DION_EXPORT int dion_ns_gemm(const void* A, long long lda, long long strideA, co
   a.tiles = static_cast<const int2*>(tiles); a.tiles_per_mat = tiles_per_mat;
   a.total_tiles = tiles_per_mat * batch;
   a.status = status;
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (bn == 256) {
-    return b_mn ? launch<256, true>(ma, mb, a, num_sms, s) : launch<256, false>(ma, mb, a, num_sms, s);
+  a.wait_flags = nullptr; a.seq_ptr = nullptr; a.n_src = 0; a.rows_per_src = 1;
+  a.wait_a = a.wait_b = a.wait_k = 0;
+  a.scale_partials = nullptr; a.scale_mult = 1.f; a.scale_eps = 0.f;
+  for (int i = 0; i < 8; ++i) a.remote_c[i] = 0;
+  a.rows_per_dst = 1; a.remote_slot = 0;
+  if (ex != nullptr) {
+    if (ex->n_src > 8 || ex->n_src < 0) return -14;
+    if (ex->remote_c[0] != 0 && (sym || CT != nullptr || Cf != nullptr)) return -15;
+    if ((ex->wait_flags != nullptr || ex->scale_partials != nullptr) &&
+        (ex->seq_ptr == nullptr || ex->rows_per_src <= 0))
+      return -16;
+    a.wait_flags = ex->wait_flags; a.seq_ptr = ex->seq_ptr; a.n_src = ex->n_src;
+    a.rows_per_src = ex->rows_per_src; a.wait_a = ex->wait_a; a.wait_b = ex->wait_b;
+    a.wait_k = ex->wait_k;
+    a.scale_partials = ex->scale_partials; a.scale_mult = ex->scale_mult;
+    a.scale_eps = ex->scale_eps;
+    for (int i = 0; i < 8; ++i) a.remote_c[i] = ex->remote_c[i];
+    a.rows_per_dst = ex->rows_per_dst > 0 ? ex->rows_per_dst : 1;
+    a.remote_slot = ex->remote_slot;
   }
-  return b_mn ? launch<128, true>(ma, mb, a, num_sms, s) : launch<128, false>(ma, mb, a, num_sms, s);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int mode = (a_mn ? 2 : 0) | (b_mn ? 1 : 0);
+  if (bn == 256) {
+    switch (mode) {
+      case 0: return launch<256, false, false>(ma, mb, a, num_sms, s);
+      case 1: return launch<256, false, true>(ma, mb, a, num_sms, s);
+      case 2: return launch<256, true, false>(ma, mb, a, num_sms, s);
+      default: return launch<256, true, true>(ma, mb, a, num_sms, s);
+    }
+  }
+  switch (mode) {
+    case 0: return launch<128, false, false>(ma, mb, a, num_sms, s);
+    case 1: return launch<128, false, true>(ma, mb, a, num_sms, s);
+    case 2: return launch<128, true, false>(ma, mb, a, num_sms, s);
+    default: return launch<128, true, true>(ma, mb, a, num_sms, s);
+  }
+}
+
+DION_EXPORT int dion_ns_gemm(const void* A, long long lda, long long strideA, const void* B,
+                             long long ldb, long long strideB, int b_mn, void* C, long long ldc,
+                             long long strideC, const void* D, long long ldd, long long strideD,
+                             void* CT, long long ldct, long long strideCT, void* Cf, int batch,
+                             int M, int N, int K, float alpha, float beta, const float* scale,
+                             int alpha_pow, int beta_pow, int sym, const void* tiles,
+                             int tiles_per_mat, int bn, int num_sms, int* status, void* stream) {
+  return dion_ns_gemm_ex(A, lda, strideA, 0, B, ldb, strideB, b_mn, C, ldc, strideC, D, ldd, strideD,
+                         CT, ldct, strideCT, Cf, batch, M, N, K, alpha, beta, scale, alpha_pow,
+                         beta_pow, sym, tiles, tiles_per_mat, bn, num_sms, status, stream, nullptr);
 }

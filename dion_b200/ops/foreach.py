@@ -20,7 +20,7 @@ import torch
 from torch import Tensor
 
 from . import _backend
-from .tables import build_table
+from .tables import RawPointer, build_table
 
 Scalar = Union[float, Tensor]
 _DT = {torch.float32: 0, torch.bfloat16: 1}
@@ -41,7 +41,7 @@ def _kernel_ok(*lists: Sequence[Tensor]) -> bool:
         return False
     for lst in lists:
         for t in lst:
-            if t is None:
+            if t is None or isinstance(t, RawPointer):
                 continue
             if t.dtype not in _DT or not t.is_contiguous():
                 return False
@@ -86,23 +86,30 @@ def muon_pre(
     out: Optional[List[Tensor]] = None,
     sumsq: Optional[Tensor] = None,
     add_only: bool = False,
+    sumsq_targets: Optional[List[int]] = None,
 ) -> List[Tensor]:
     """``M = mu*M + G`` (or ``M += G`` with ``add_only``); returns the bf16 orthogonalization
     input ``U`` (``mu*M + G`` with Nesterov, else ``M``), written into ``out`` when given.
-    ``sumsq[i]`` (optional, fp32, pre-zeroed) receives ``sum(U_i**2)``."""
+    ``sumsq[i]`` (optional, fp32, pre-zeroed) receives ``sum(U_i**2)``.  ``out`` entries may be
+    :class:`RawPointer` addresses of peer-GPU memory; ``sumsq_targets[i]`` (raw addresses of fp32
+    accumulators, possibly on a peer) then receive the sums instead of ``sumsq``."""
     if not G:
         return []
     if out is None:
         out = [torch.empty_like(m, dtype=torch.bfloat16) for m in M]
     if _kernel_ok(G, M, out) and _same_dtype(G) and _same_dtype(M) and M[0].numel():
         dev = M[0].device
-        tb = build_table([G, M, out], [m.numel() for m in M], tag="pre")
+        lists = [G, M, out]
+        if sumsq_targets is not None:
+            lists.append([RawPointer(a) for a in sumsq_targets])
+        tb = build_table(lists, [m.numel() for m in M], tag="pre")
         _check(
             _backend.lib("foreach_ops").dion_muon_pre(
                 _c(tb.device_tensor.data_ptr()), ctypes.c_longlong(tb.n_chunks),
                 _DT[G[0].dtype], _DT[M[0].dtype], ctypes.c_float(float(mu)),
                 int(bool(nesterov)), int(bool(add_only)),
-                _c(sumsq.data_ptr() if sumsq is not None else 0), _stream(dev)),
+                _c(sumsq.data_ptr() if sumsq is not None else 0),
+                int(sumsq_targets is not None), _stream(dev)),
             "dion_muon_pre")
         return out
     # PyTorch path
@@ -140,8 +147,12 @@ def muon_post(
     rowscale: Optional[List[Tensor]] = None,
     normU2: Optional[Tensor] = None,
     normNew2: Optional[Tensor] = None,
+    wait: Optional[tuple] = None,
 ) -> None:
     """``X = X*(1 - lr*wd) - lr*ratio*U`` (cautious: decay only where ``X*U >= 0``).
+
+    ``wait = (flags, seq, per_rank, status)`` makes every block first wait (bounded) until the
+    rank that produced its ``U`` has raised its flag to the current sequence number.
 
     ``rowscale[i]`` (fp32, one value per row of ``U[i]``) and the pair ``normU2/normNew2``
     (per-tensor squared Frobenius norms before/after the row scaling) carry NorMuon's
@@ -162,7 +173,10 @@ def muon_post(
                 ctypes.c_float(wd_f), ctypes.c_float(float(ratio)), int(bool(cautious_wd)),
                 _DT[X[0].dtype], int(cols),
                 _c(normU2.data_ptr() if normU2 is not None else 0),
-                _c(normNew2.data_ptr() if normNew2 is not None else 0), _stream(dev)),
+                _c(normNew2.data_ptr() if normNew2 is not None else 0),
+                _c(wait[0].data_ptr() if wait else 0), _c(wait[1].data_ptr() if wait else 0),
+                int(wait[2]) if wait else 1, _c(wait[3].data_ptr() if wait else 0),
+                _stream(dev)),
             "dion_muon_post")
         return
     # PyTorch path

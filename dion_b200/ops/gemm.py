@@ -94,7 +94,7 @@ def _as3d(t: Tensor) -> Tensor:
 
 def _ld_stride(t: Tensor) -> Tuple[int, int]:
     assert t.stride(-1) == 1, "innermost dimension must be contiguous"
-    ld = t.stride(-2)
+    ld = t.stride(-2) if t.size(-2) > 1 else max(t.stride(-2), t.size(-1))
     bs = t.stride(0) if t.size(0) > 1 else t.size(-2) * ld
     return ld, bs
 
@@ -111,12 +111,29 @@ def supported(A: Tensor, B: Tensor) -> bool:
     return True
 
 
+class GemmExtra(ctypes.Structure):
+    """Cross-GPU coupling of one launch (mirrors ``DionGemmExtra`` in csrc/ns_gemm_sm100.cu)."""
+
+    _fields_ = [
+        ("wait_flags", ctypes.c_void_p), ("seq_ptr", ctypes.c_void_p),
+        ("n_src", ctypes.c_int), ("rows_per_src", ctypes.c_int),
+        ("wait_a", ctypes.c_int), ("wait_b", ctypes.c_int), ("wait_k", ctypes.c_int),
+        ("scale_partials", ctypes.c_void_p),
+        ("scale_mult", ctypes.c_float), ("scale_eps", ctypes.c_float),
+        ("remote_c", ctypes.c_longlong * 8),
+        ("rows_per_dst", ctypes.c_int), ("remote_slot", ctypes.c_int),
+    ]
+
+
 def ns_gemm(
     A: Tensor,
     B: Tensor,
     out: Optional[Tensor] = None,
     *,
+    a_is_km: bool = False,
     b_is_kn: bool = False,
+    extra: Optional[GemmExtra] = None,
+    out_shape: Optional[Tuple[int, int, int]] = None,
     D: Optional[Tensor] = None,
     alpha: float = 1.0,
     beta: float = 0.0,
@@ -129,20 +146,22 @@ def ns_gemm(
     bn: Optional[int] = None,
 ) -> Tensor:
     A3, B3 = _as3d(A), _as3d(B)
-    batch, M, K = A3.shape
+    batch = A3.size(0)
+    M, K = (A3.size(-1), A3.size(-2)) if a_is_km else (A3.size(-2), A3.size(-1))
     N = B3.size(-1) if b_is_kn else B3.size(-2)
     assert (B3.size(-2) if b_is_kn else B3.size(-1)) == K and B3.size(0) == batch
     if not supported(A3, B3):
         raise ValueError("ns_gemm operands violate the TMA alignment rules; see supported()")
     dev = A.device
-    if out is None and out_f32 is None:
+    remote = extra is not None and extra.remote_c[0] != 0
+    if out is None and out_f32 is None and not remote:
         out = torch.empty((batch, M, N), dtype=torch.bfloat16, device=dev)
         if A.ndim == 2:
             out = out[0]
     C3 = _as3d(out) if out is not None else None
     Cf3 = _as3d(out_f32) if out_f32 is not None else None
     tgt = Cf3 if Cf3 is not None else C3
-    ldc, sc = _ld_stride(tgt)
+    ldc, sc = _ld_stride(tgt) if tgt is not None else (N, M * N)
     D3 = _as3d(D) if D is not None else None
     ldd, sd = _ld_stride(D3) if D3 is not None else (0, 0)
     CT3 = _as3d(out_t) if out_t is not None else None
@@ -155,8 +174,8 @@ def ns_gemm(
     if scale is not None:
         assert scale.dtype == torch.float32 and scale.numel() >= batch
     st = status_tensor(dev)
-    rc = _backend.lib("ns_gemm_sm100").dion_ns_gemm(
-        _p(A3), ctypes.c_longlong(lda), ctypes.c_longlong(sa),
+    rc = _backend.lib("ns_gemm_sm100").dion_ns_gemm_ex(
+        _p(A3), ctypes.c_longlong(lda), ctypes.c_longlong(sa), ctypes.c_int(1 if a_is_km else 0),
         _p(B3), ctypes.c_longlong(ldb), ctypes.c_longlong(sb), ctypes.c_int(1 if b_is_kn else 0),
         _p(C3), ctypes.c_longlong(ldc), ctypes.c_longlong(sc),
         _p(D3), ctypes.c_longlong(ldd), ctypes.c_longlong(sd),
@@ -168,6 +187,7 @@ def ns_gemm(
         _p(tiles), ctypes.c_int(tiles.size(0)), ctypes.c_int(bn),
         ctypes.c_int(sm_count(dev)), _p(st),
         ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream),
+        ctypes.byref(extra) if extra is not None else None,
     )
     if rc != 0:
         raise RuntimeError(f"dion_ns_gemm launch failed with code {rc}")

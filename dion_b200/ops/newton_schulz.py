@@ -129,15 +129,16 @@ def _gram_torch(G: Tensor, coeffs: Coeffs, norm_mult: float, epsilon: float,
 # ------------------------------------------------------------------------------------------------
 # CUDA implementations on the tcgen05 GEMM
 # ------------------------------------------------------------------------------------------------
-def _prepare_cuda(G: Tensor):
-    """-> (X [B, m, n] bf16 contiguous with m <= n and m, n multiples of 8, restore)"""
+def _prepare_cuda(G: Tensor, allow_tall: bool = False):
+    """-> (X [B, m, n] bf16 contiguous with m, n multiples of 8, restore).  Tall inputs are
+    transposed to wide unless ``allow_tall`` (the caller then iterates in right-multiply form)."""
     shape = G.shape
     X = G.to(torch.bfloat16)
     if X.ndim == 2:
         X = X.unsqueeze(0)
     elif X.ndim > 3:
         X = X.reshape(-1, shape[-2], shape[-1])
-    tall = X.size(-2) > X.size(-1)
+    tall = X.size(-2) > X.size(-1) and not allow_tall
     if tall:
         X = X.mT
     m, n = X.size(-2), X.size(-1)
@@ -167,23 +168,51 @@ def _norm_scale(X: Tensor, norm_mult: float, epsilon: float) -> Tensor:
     return F.finalize_scale(ss, norm_mult, epsilon, out=ss)
 
 
-def _iterate_cuda(X: Tensor, coeffs: Coeffs, scale: Optional[Tensor]) -> Tensor:
+def _iterate_cuda(X: Tensor, coeffs: Coeffs, scale: Optional[Tensor], hooks=None) -> Tensor:
+    """Newton-Schulz iterations on ``X [B, m, n]``.  Wide or square matrices use the left form
+    ``A = X X^T, X' = aX + (bA + cA^2) X``; tall ones the right form ``A = X^T X,
+    X' = aX + X (bA + cA^2)``, reading ``X`` as an MN-major operand so that neither needs a
+    transposed copy.  ``hooks`` (fused exchange) may supply per-launch coupling to other GPUs:
+    ``hooks.first_gram()``, ``hooks.after_first_iteration()``, ``hooks.last_update()``."""
     B_, m, n = X.shape
-    A = torch.empty((B_, m, m), dtype=torch.bfloat16, device=X.device)
+    tall = m > n
+    g = n if tall else m
+    A = torch.empty((B_, g, g), dtype=torch.bfloat16, device=X.device)
     Bm = torch.empty_like(A)
     C = torch.empty_like(X)
+    last = len(coeffs) - 1
     for it, (a, b, c) in enumerate(coeffs):
         sc = scale if it == 0 else None
-        gemm.ns_gemm(X, X, out=A, sym=True, scale=sc, alpha_pow=2 if sc is not None else 0)
+        ex_first = hooks.first_gram(tall) if (hooks is not None and it == 0) else None
+        if ex_first is not None:
+            gemm.ns_gemm(X, X, out=A, sym=True, a_is_km=tall, b_is_kn=tall, alpha_pow=2,
+                         extra=ex_first)
+            sc = hooks.scale_after_first_gram()
+        else:
+            gemm.ns_gemm(X, X, out=A, sym=True, a_is_km=tall, b_is_kn=tall, scale=sc,
+                         alpha_pow=2 if sc is not None else 0)
         gemm.ns_gemm(A, A, out=Bm, sym=True, D=A, alpha=c, beta=b)
-        gemm.ns_gemm(Bm, X, out=C, b_is_kn=True, D=X, alpha=1.0, beta=a, scale=sc,
-                     alpha_pow=1 if sc is not None else 0, beta_pow=1 if sc is not None else 0)
-        X, C = C, X
-    return X
+        pw = 1 if sc is not None else 0
+        ex_last = hooks.last_update() if (hooks is not None and it == last) else None
+        out = None if ex_last is not None else C
+        if tall:   # X' = a X + X B   (B symmetric: its rows are its columns)
+            gemm.ns_gemm(X, Bm, out=out, D=X, alpha=1.0, beta=a, scale=sc, alpha_pow=pw,
+                         beta_pow=pw, extra=ex_last)
+        else:      # X' = a X + B X
+            gemm.ns_gemm(Bm, X, out=out, b_is_kn=True, D=X, alpha=1.0, beta=a, scale=sc,
+                         alpha_pow=pw, beta_pow=pw, extra=ex_last)
+        if hooks is not None and it == 0:
+            hooks.after_first_iteration()
+            # the input belongs to the exchange and is handed back to the peers: from here on
+            # ping-pong between private buffers only
+            X, C = C, torch.empty_like(C)
+        else:
+            X, C = C, X
+    return None if (hooks is not None) else X
 
 
 def _ns_cuda(G: Tensor, coeffs: Coeffs, norm_mult: float, epsilon: float) -> Tensor:
-    X, restore = _prepare_cuda(G)
+    X, restore = _prepare_cuda(G, allow_tall=True)
     scale = _norm_scale(X, norm_mult, epsilon)
     return restore(_iterate_cuda(X, coeffs, scale))
 
@@ -282,6 +311,20 @@ def gram_newton_schulz(G: Tensor, epsilon=1e-6, reset_iterations: Sequence[int] 
     if _use_cuda(G):
         return _gram_cuda(G, coeffs, norm_mult, eps, tuple(reset_iterations))
     return _gram_torch(G, coeffs, norm_mult, eps, tuple(reset_iterations))
+
+
+# (coefficients, norm multiplier) of the drivers whose iteration the fused exchange can run itself
+newton_schulz_quintic.ns_spec = (QUINTIC_COEFFS, 1.0)
+polar_express.ns_spec = (POLAR_EXPRESS_COEFFS, 1.02)
+newton_schulz_classic.ns_spec = ((CLASSIC_COEFF,) * 5, 1.0)
+
+
+def iterate_with_exchange(X: Tensor, ns_func: Callable, epsilon, hooks) -> None:
+    """Run ``ns_func``'s iteration on the exchange's receive buffer ``X`` with the cross-GPU
+    hooks attached (see ``parallel/fused_exchange.py``); results leave through the hooks."""
+    coeffs, mult = ns_func.ns_spec
+    hooks.norm_mult, hooks.eps = float(mult), _eps(epsilon)
+    _iterate_cuda(X, coeffs, None, hooks=hooks)
 
 
 def torch_reference(name: str) -> Callable:

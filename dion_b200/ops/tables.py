@@ -72,7 +72,20 @@ class TensorTable:
         self.keepalive = keepalive
 
 
-def _ptr(t: Optional[Tensor]) -> int:
+class RawPointer:
+    """A bare device address standing in for a tensor in a pointer table (e.g. a location in
+    another GPU's peer-mapped buffer)."""
+
+    __slots__ = ("address",)
+
+    def __init__(self, address: int):
+        self.address = int(address)
+
+    def data_ptr(self) -> int:
+        return self.address
+
+
+def _ptr(t) -> int:
     return 0 if t is None else t.data_ptr()
 
 
@@ -90,7 +103,7 @@ def build_table(
     hit = _cache.get(key)
     if hit is not None:
         return hit
-    device = next(t.device for lst in lists for t in lst if t is not None)
+    device = next(t.device for lst in lists for t in lst if isinstance(t, Tensor))
     prefix = [0]
     for ne in numels:
         prefix.append(prefix[-1] + (ne + chunk - 1) // chunk)

@@ -124,6 +124,7 @@ class DistributedOrthoBase(Optimizer):
         # State for every parameter up front, including ones that never get a gradient, so the
         # key set of state_dict() is the same on every rank and before/after a resume.
         self._arena = StepArena()
+        self._fused_exchanges: dict = {}  # symmetric workspaces of the fused megabatch exchange
         self._hyperparam_tensors: Dict[Tuple[int, str], Tensor] = {}
         self._live_hyperparams_by_group: Dict[int, Tuple[str, ...]] = {}
         self._state_prepopulated = False

@@ -1,0 +1,170 @@
+"""Multi-process CPU (gloo) runs of the distributed code paths, compared with single-process
+runs of the same optimizers."""
+import pytest
+import torch
+import torch.distributed as dist
+
+import dion_b200
+from tests.dist_utils import run_ranks
+
+SHAPES = ((16, 32), (16, 32), (16, 32), (32, 16), (32, 16))
+
+
+def _grads(step, shapes):
+    g = torch.Generator().manual_seed(100 + step)
+    return [torch.randn(*s, generator=g) for s in shapes]
+
+
+def _weights(shapes):
+    g = torch.Generator().manual_seed(7)
+    return [torch.randn(*s, generator=g) for s in shapes]
+
+
+def _single(name, kw, shapes=SHAPES, steps=2):
+    ps = [torch.nn.Parameter(w) for w in _weights(shapes)]
+    opt = getattr(dion_b200, name)([dict(params=ps)], lr=0.1, **kw)
+    for s in range(steps):
+        for p, g in zip(ps, _grads(s, shapes)):
+            p.grad = g
+        opt.step()
+    return [p.detach().clone() for p in ps]
+
+
+def _sharded_worker(rank, world, name, kw, shapes, steps, shard_dim):
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.tensor import Shard, distribute_tensor
+    mesh = init_device_mesh("cpu", (world,))
+    ps = [torch.nn.Parameter(distribute_tensor(w, mesh, [Shard(shard_dim)])) for w in _weights(shapes)]
+    opt = getattr(dion_b200, name)([dict(params=ps)], distributed_mesh=mesh, lr=0.1, **kw)
+    for s in range(steps):
+        for p, g in zip(ps, _grads(s, shapes)):
+            p.grad = distribute_tensor(g, mesh, [Shard(shard_dim)])
+        opt.step()
+    full = [p.detach().full_tensor().clone() for p in ps]
+    return full if rank == 0 else None
+
+
+def _replicated_worker(rank, world, name, kw, shapes, steps):
+    ps = [torch.nn.Parameter(w) for w in _weights(shapes)]
+    opt = getattr(dion_b200, name)([dict(params=ps)], distributed_mesh=dist.group.WORLD, lr=0.1, **kw)
+    for s in range(steps):
+        for p, g in zip(ps, _grads(s, shapes)):
+            p.grad = g
+        opt.step()
+    return [p.detach().clone() for p in ps] if rank == 0 else None
+
+
+SHARDED_CASES = [
+    ("Muon", dict(nesterov=True), 0, 1e-6),               # layout-invariant
+    ("Muon", dict(nesterov=True), 1, 1e-6),
+    ("NorMuon", dict(), 0, 2e-2),                          # per-shard Frobenius norms
+    ("Dion2", dict(selection_scope="global"), 0, 5e-4),    # exact whole-matrix top-k
+    ("Dion2", dict(selection_scope="global"), 1, 5e-4),
+    ("NorDion2", dict(selection_scope="global", fraction=1.0), 0, 2e-2),
+]
+
+
+WIDE, TALL = ((16, 32),) * 3, ((32, 16),) * 3
+
+
+def _case_shapes(name, sd):
+    # Dion2 selects along the sharded dim when sharded and along the shorter dim otherwise; the
+    # two agree for wide matrices sharded by rows and tall matrices sharded by columns.
+    if name == "Dion2":
+        return WIDE if sd == 0 else TALL
+    return SHAPES
+
+
+def _many_sharded(rank, world, cases, shapes, steps):
+    return [_sharded_worker(rank, world, n, kw, _case_shapes(n, sd), steps, sd)
+            for n, kw, sd, _ in cases]
+
+
+def _many_replicated(rank, world, names, shapes, steps):
+    return [_replicated_worker(rank, world, n, {}, shapes, steps) for n in names]
+
+
+def test_sharded_matches_single_process(tmp_path):
+    outs = run_ranks(_many_sharded, 2, "gloo", (SHARDED_CASES, SHAPES, 2), str(tmp_path))[0]
+    for (name, kw, sd, tol), out in zip(SHARDED_CASES, outs):
+        for a, b in zip(_single(name, kw, _case_shapes(name, sd)), out):
+            assert (a - b).abs().max().item() <= tol, (name, sd)
+
+
+def test_replicated_matches_single_process(tmp_path):
+    names = ["Muon", "NorMuon", "Dion2", "NorDion2"]
+    outs = run_ranks(_many_replicated, 2, "gloo", (names, SHAPES, 2), str(tmp_path))[0]
+    for name, out in zip(names, outs):
+        for a, b in zip(_single(name, {}), out):
+            assert (a - b).abs().max().item() <= 1e-6, name
+
+
+def _uneven_worker(rank, world):
+    shapes = ((3, 8), (3, 8), (3, 8))  # 3 rows over 4 ranks: one rank holds nothing
+    a = _sharded_worker(rank, world, "Muon", {}, shapes, 2, 0)
+    b = _sharded_worker(rank, world, "Dion2", dict(selection_scope="global"), shapes, 2, 0)
+    c = _sharded_worker(rank, world, "Dion2", dict(fraction=0.5), ((6, 8), (6, 8)), 2, 0)
+    return (a, b, c) if rank == 0 else None
+
+
+def test_uneven_and_empty_shards_do_not_hang(tmp_path):
+    shapes = ((3, 8), (3, 8), (3, 8))
+    a, b, c = run_ranks(_uneven_worker, 4, "gloo", (), str(tmp_path))[0]
+    for ref, out in ((_single("Muon", {}, shapes), a),
+                     (_single("Dion2", dict(selection_scope="global"), shapes), b)):
+        for x, y in zip(ref, out):
+            assert x.shape == y.shape and (x - y).abs().max().item() <= 5e-4
+    assert all(torch.isfinite(t).all() for t in c)  # local scope with short shards
+
+
+def _dion_worker(rank, world, mode, steps):
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.tensor import Replicate, Shard, distribute_tensor
+    shapes = ((32, 64), (32, 64), (64, 32), (64, 32))
+    torch.manual_seed(0)
+    if mode == "ddp":
+        ps = [torch.nn.Parameter(w) for w in _weights(shapes)]
+        opt = dion_b200.Dion([dict(params=ps)], replicate_mesh=dist.group.WORLD,
+                             replicate_mesh_grad_sync=True, rank_fraction=0.25, lr=0.1)
+        mk = lambda g: g  # noqa: E731
+    else:
+        if mode == "fsdp":
+            mesh = init_device_mesh("cpu", (world,), mesh_dim_names=("fs",))
+            opt_kw = dict(outer_shard_mesh=mesh["fs"])
+            place = lambda i: [Shard(0)]  # noqa: E731
+        elif mode == "tp":
+            mesh = init_device_mesh("cpu", (world,), mesh_dim_names=("tp",))
+            opt_kw = dict(inner_shard_mesh=mesh["tp"])
+            place = lambda i: [Shard(0)] if i < 2 else [Shard(1)]  # noqa: E731
+        else:  # fsdp x tp on a 2x2 mesh
+            mesh = init_device_mesh("cpu", (2, 2), mesh_dim_names=("fs", "tp"))
+            opt_kw = dict(outer_shard_mesh=mesh["fs"], inner_shard_mesh=mesh["tp"])
+            place = lambda i: [Shard(1), Shard(0)] if i < 2 else [Shard(0), Shard(1)]  # noqa: E731
+        ps = [torch.nn.Parameter(distribute_tensor(w, mesh, place(i)))
+              for i, w in enumerate(_weights(shapes))]
+        opt = dion_b200.Dion([dict(params=ps)], rank_fraction=0.25, lr=0.1, **opt_kw)
+        mk = lambda g, i=None: g  # noqa: E731
+    for s in range(steps):
+        for i, (p, g) in enumerate(zip(ps, _grads(s, shapes))):
+            p.grad = g if mode == "ddp" else distribute_tensor(g, p.device_mesh, p.placements)
+        opt.step()
+    if hasattr(opt, "synchronize_for_checkpoint"):
+        opt.synchronize_for_checkpoint()
+    out = [p.detach().full_tensor().clone() if mode != "ddp" else p.detach().clone() for p in ps]
+    qs = [tuple(opt.state[p]["Q"].shape) for p in ps]
+    return (out, qs) if rank == 0 else None
+
+
+def _dion_modes_worker(rank, world, modes):
+    return [_dion_worker(rank, world, m, 3) for m in modes]
+
+
+@pytest.mark.parametrize("modes,world", [(("ddp", "fsdp", "tp"), 2), (("fsdp_tp",), 4)])
+def test_dion_distributed_modes_run_and_descend(tmp_path, modes, world):
+    results = run_ranks(_dion_modes_worker, world, "gloo", (modes,), str(tmp_path))[0]
+    start = _weights(((32, 64), (32, 64), (64, 32), (64, 32)))
+    for mode, (out, qs) in zip(modes, results):
+        for a, b in zip(start, out):
+            assert a.shape == b.shape and torch.isfinite(b).all(), mode
+            assert (a - b).abs().max().item() > 0, mode
+        assert qs[0][1] == 8, mode  # r = ceil(0.25 * 32)
