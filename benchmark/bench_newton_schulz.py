@@ -1,0 +1,168 @@
+#!/usr/bin/env python
+"""Newton-Schulz sweep: time and TFLOP/s of the orthogonalization drivers on batched bf16
+matrices, against PyTorch (cuBLAS) and, when ``baseline/_ref`` is installed, the reference's
+Triton kernels.
+
+    python benchmark/bench_newton_schulz.py --grid            # shapes x batch sizes
+    python benchmark/bench_newton_schulz.py --single 4096 4096 --batch 8
+    python benchmark/bench_newton_schulz.py --gemms 2048 2048 --batch 24   # per-GEMM breakdown
+
+FLOP model (the reference's, benchmark/benchmark_newton_shultz.py:40-48): ``4 m^2 n + 2 m^3``
+per iteration with ``m <= n``, i.e. without crediting the symmetric half-work, so the numbers
+are directly comparable; the fraction of the measured cuBLAS bf16 peak is reported alongside.
+Entries are N(0,1), timed with CUDA events after warm-up; between timed runs a buffer larger
+than L2 is overwritten.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+from dion_b200.ops import gemm  # noqa: E402
+from dion_b200.ops import newton_schulz as NS  # noqa: E402
+
+GRID_SHAPES = [(768, 768), (768, 3072), (2048, 8192), (4096, 4096), (8192, 8192)]
+GRID_BATCH = [1, 4, 16, 64]
+
+
+def peak_tflops() -> float:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        return float(json.load(open(path))["bf16_tflops"])
+    except Exception:
+        return 1590.0  # fallback: earlier measurement on this pool
+
+
+def ns_flops(b: int, m: int, n: int, iters: int = 5) -> float:
+    m, n = min(m, n), max(m, n)
+    return b * iters * (4.0 * m * m * n + 2.0 * m ** 3)
+
+
+_flush = None
+
+
+def flush_l2() -> None:
+    global _flush
+    if _flush is None:
+        _flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    _flush.zero_()
+
+
+def bench(fn, iters: int = 10, warmup: int = 3) -> float:
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    total = 0.0
+    for _ in range(iters):
+        flush_l2()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        total += e0.elapsed_time(e1)
+    return total / iters
+
+
+def reference_drivers():
+    ref_root = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref_root, "dion")):
+        return {}
+    if os.path.exists("/usr/bin/g++"):
+        os.environ["CXX"], os.environ["CC"] = "/usr/bin/g++", "/usr/bin/gcc"
+    sys.path.insert(1, ref_root)
+    try:
+        from dion.newton_schulz_triton import newton_schulz_triton
+        from dion.polar_express import polar_express_triton
+        return {"ref_triton_quintic": newton_schulz_triton, "ref_triton_pe": polar_express_triton}
+    except Exception as exc:  # noqa: BLE001
+        print(f"# reference kernels unavailable: {exc}", file=sys.stderr)
+        return {}
+
+
+def run_case(b: int, m: int, n: int, drivers, peak: float, max_bytes: float = 6e9):
+    if b * m * n * 2 * 4 > max_bytes:
+        return None
+    G = torch.randn(b, m, n, device="cuda", dtype=torch.bfloat16)
+    G = G / G.float().norm(dim=(-2, -1), keepdim=True).to(G.dtype)
+    row = {"batch": b, "m": m, "n": n}
+    fl = ns_flops(b, m, n)
+    for name, fn in drivers.items():
+        try:
+            ms = bench(lambda: fn(G))
+        except Exception as exc:  # noqa: BLE001
+            row[name] = {"error": str(exc)[:120]}
+            continue
+        tf = fl / (ms * 1e-3) / 1e12
+        row[name] = {"ms": round(ms, 4), "tflops": round(tf, 1),
+                     "frac_of_measured_cublas_peak": round(tf / peak, 3)}
+    gemm.check_status()
+    return row
+
+
+def gemm_breakdown(b: int, m: int, n: int):
+    X = torch.randn(b, m, n, device="cuda").bfloat16()
+    A = torch.empty(b, m, m, device="cuda", dtype=torch.bfloat16)
+    Bm = torch.empty_like(A)
+    C = torch.empty_like(X)
+    out = {}
+    cases = {
+        "gram  A=XX^T (sym)": (lambda: gemm.ns_gemm(X, X, out=A, sym=True), 2.0 * b * m * m * n),
+        "poly  B=bA+cA^2 (sym)": (lambda: gemm.ns_gemm(A, A, out=Bm, sym=True, D=A, alpha=1.0, beta=1.0), 2.0 * b * m ** 3),
+        "upd   X'=aX+BX": (lambda: gemm.ns_gemm(Bm, X, out=C, b_is_kn=True, D=X, alpha=1.0, beta=1.0), 2.0 * b * m * m * n),
+        "gram  cuBLAS bmm": (lambda: torch.bmm(X, X.mT, out=A), 2.0 * b * m * m * n),
+        "upd   cuBLAS baddbmm": (lambda: torch.baddbmm(X, Bm, X, out=C), 2.0 * b * m * m * n),
+    }
+    for name, (fn, fl) in cases.items():
+        ms = bench(fn)
+        out[name] = {"ms": round(ms, 4), "nominal_tflops": round(fl / (ms * 1e-3) / 1e12, 1)}
+    gemm.check_status()
+    return out
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--grid", action="store_true")
+    ap.add_argument("--single", nargs=2, type=int, metavar=("M", "N"))
+    ap.add_argument("--gemms", nargs=2, type=int, metavar=("M", "N"))
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--no-reference", action="store_true")
+    ap.add_argument("--out", type=str, default=None)
+    args = ap.parse_args()
+    peak = peak_tflops()
+    drivers = {
+        "ours_quintic": NS.newton_schulz_quintic,
+        "ours_polar_express": NS.polar_express,
+        "ours_gram_ns": NS.gram_newton_schulz,
+        "ours_aol4": NS.newton_schulz_aol,
+        "torch_quintic": NS.torch_reference("quintic"),
+    }
+    if not args.no_reference:
+        drivers.update(reference_drivers())
+    results = []
+    if args.gemms:
+        r = gemm_breakdown(args.batch, *args.gemms)
+        print(json.dumps({"gemm_breakdown": r, "batch": args.batch, "shape": args.gemms}, indent=1))
+        return
+    cases = ([(b, m, n) for (m, n) in GRID_SHAPES for b in GRID_BATCH] if args.grid
+             else [(args.batch, *(args.single or (4096, 4096)))])
+    for b, m, n in cases:
+        row = run_case(b, m, n, drivers, peak)
+        if row is None:
+            continue
+        results.append(row)
+        print(json.dumps(row), flush=True)
+    if args.out:
+        json.dump({"measured_cublas_bf16_peak_tflops": peak, "rows": results},
+                  open(args.out, "w"), indent=1)
+
+
+if __name__ == "__main__":
+    main()
