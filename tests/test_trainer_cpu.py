@@ -1,0 +1,109 @@
+"""End-to-end checks on CPU: loss-curve parity of (our GPT + our Muon) with (reference GPT +
+reference Muon) on the small configuration, the data loaders, and the trainer under torchrun with
+gloo (DDP and FSDP2 + checkpoint resume)."""
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import dion_b200
+from dion_b200.models.data import (DistributedDataLoader, SyntheticDataLoader, write_datafile)
+from dion_b200.models.gpt import GPT, GPTConfig
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+TINY = dict(sequence_len=64, vocab_size=512, n_layer=2, n_head=4, n_embd=128)
+
+
+def _loss_curve(gpt_cls, cfg_cls, muon_cls, steps=6):
+    torch.manual_seed(0)
+    model = gpt_cls(cfg_cls(**TINY))
+    model.init_weights()
+    opt = muon_cls(
+        [dict(params=list(model.transformer.h.parameters())),
+         dict(params=list(model.transformer.wte.parameters()) + list(model.lm_head.parameters()),
+              algorithm="adamw", lr=3e-3)],
+        lr=0.02, mu=0.95, nesterov=True, weight_decay=0.01, use_polar_express=False)
+    g = torch.Generator().manual_seed(0)
+    losses = []
+    for _ in range(steps):
+        x = torch.randint(0, TINY["vocab_size"], (8, TINY["sequence_len"]), generator=g)
+        y = torch.randint(0, TINY["vocab_size"], (8, TINY["sequence_len"]), generator=g)
+        loss = model(x, y)
+        loss.backward()
+        opt.step()
+        model.zero_grad(set_to_none=True)
+        losses.append(float(loss.detach()))
+    return losses
+
+
+def test_loss_curve_matches_reference(ref_dion):
+    from models.gpt_model import GPT as RefGPT, GPTConfig as RefConfig  # baseline/_ref/models
+    ours = _loss_curve(GPT, GPTConfig, dion_b200.Muon)
+    ref = _loss_curve(RefGPT, RefConfig, ref_dion.Muon)
+    assert ours[0] == pytest.approx(ref[0], abs=1e-4)
+    for a, b in zip(ours, ref):
+        assert a == pytest.approx(b, abs=2e-2)
+    assert ours[-1] < ours[0]
+
+
+def test_state_dict_interchangeable_with_reference(ref_dion):
+    torch.manual_seed(0)
+    ps = [torch.nn.Parameter(torch.randn(16, 32)), torch.nn.Parameter(torch.randn(8))]
+    groups = lambda: [dict(params=[ps[0]]), dict(params=[ps[1]], algorithm="adamw")]  # noqa: E731
+    ours, ref = dion_b200.NorMuon(groups(), lr=0.01), ref_dion.NorMuon(groups(), lr=0.01)
+    for p in ps:
+        p.grad = torch.randn_like(p)
+    ours.step()
+    ref.load_state_dict(ours.state_dict())     # ours -> reference
+    ours.load_state_dict(ref.state_dict())     # reference -> ours
+    assert set(ours.state[ps[0]]) == {"momentum", "variance_neuron"}
+    assert set(ours.state[ps[1]]) == {"momentum", "variance", "step_dev"}
+
+
+def test_data_loaders(tmp_path):
+    toks = np.arange(5000) % 1000
+    write_datafile(str(tmp_path / "fineweb_train_000000.bin"), toks)
+    a = DistributedDataLoader(str(tmp_path / "fineweb_train_*.bin"), 2, 8, 0, 2)
+    b = DistributedDataLoader(str(tmp_path / "fineweb_train_*.bin"), 2, 8, 1, 2)
+    xa, ya = a.next_batch()
+    xb, _ = b.next_batch()
+    assert xa.shape == (2, 8) and torch.equal(ya[:, :-1], xa[:, 1:])
+    assert int(xb[0, 0]) == 16  # rank 1 starts one device batch further
+    state = a.state_dict()
+    nxt = a.next_batch()[0].clone()
+    a2 = DistributedDataLoader(str(tmp_path / "fineweb_train_*.bin"), 2, 8, 0, 2)
+    a2.load_state_dict(state)
+    assert torch.equal(a2.next_batch()[0], nxt)
+    with pytest.raises(NotImplementedError):
+        a2.load_state_dict({**state, "dataloader_world_size": 4})
+    s1 = SyntheticDataLoader(2, 8, 100, 0, 1, seed=0)
+    s2 = SyntheticDataLoader(2, 8, 100, 0, 1, seed=0)
+    assert torch.equal(s1.next_batch()[0], s2.next_batch()[0])
+    assert int(s1.next_batch()[0].max()) < 100
+
+
+def _torchrun(args, nproc=2, timeout=900):
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--standalone", "--local-addr",
+           "127.0.0.1", "--nproc-per-node", str(nproc), os.path.join(ROOT, "train.py"),
+           "--device", "cpu", "--synthetic", "--no_wandb", "--debug", "--model_dim", "64",
+           "--n_layer", "2", "--n_head", "2", "--sequence_length", "32", "--batch_size", "8",
+           "--device_batch_size", "4", "--val_loss_every", "0", "--scalar_opt", "adamw"] + args
+    env = dict(os.environ, OMP_NUM_THREADS="1")
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=env, cwd=ROOT)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
+    return res.stdout
+
+
+def test_trainer_ddp_and_fsdp_resume(tmp_path):
+    out = _torchrun(["--optimizer", "muon", "--num_iterations", "3"])
+    assert out.count("train_loss=") == 3
+    ck = str(tmp_path / "ckpt")
+    out = _torchrun(["--optimizer", "normuon", "--fs_size", "2", "--num_iterations", "2",
+                     "--checkpoint_dir", ck, "--checkpoint_freq", "1"])
+    assert os.path.isdir(os.path.join(ck, "step_00000001"))
+    out = _torchrun(["--optimizer", "normuon", "--fs_size", "2", "--num_iterations", "3",
+                     "--checkpoint_dir", ck])
+    assert "Resumed from step 1" in out and "Step 2:" in out and "Step 0:" not in out
