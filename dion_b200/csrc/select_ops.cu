@@ -179,18 +179,39 @@ topk_select_kernel(const float* norms, int num, int k, long long* idx_out, int* 
 
 // Row gather + error feedback.  grid = (k, n); U[t][j][:] = bf16(M[t][idx[j]][:]);
 // M[t][idx[j]][:] *= ef (skipped when ef_apply == 0).  M pointers from ptrs[n + t].
+// With u_ptrs the destination of matrix t is u_ptrs[t] (possibly another GPU's peer-mapped
+// memory) instead of U + t*u_stride; with ss_ptrs the sum of squares of the bf16 values of each
+// gathered row is added to *ss_ptrs[t].
 __global__ void __launch_bounds__(256)
 gather_rows_kernel(const long long* ptrs, int n, int cols, int m_dt, const long long* idx, int k,
-                   __nv_bfloat16* U, long long u_stride, float ef, int ef_apply) {
+                   __nv_bfloat16* U, long long u_stride, float ef, int ef_apply,
+                   const long long* u_ptrs, const long long* ss_ptrs) {
+  __shared__ float red[8];
   const int j = blockIdx.x, t = blockIdx.y;
   void* M = reinterpret_cast<void*>(ptrs[n + t]);
   const long long r = idx[(long long)t * k + j];
   const long long off = r * cols;
-  __nv_bfloat16* u = U + (long long)t * u_stride + (long long)j * cols;
+  __nv_bfloat16* base = u_ptrs ? reinterpret_cast<__nv_bfloat16*>(u_ptrs[t])
+                               : U + (long long)t * u_stride;
+  __nv_bfloat16* u = base + (long long)j * cols;
+  float acc = 0.f;
   for (int c = threadIdx.x; c < cols; c += 256) {
     const float m = ldv(M, m_dt, off + c);
-    u[c] = __float2bfloat16_rn(m);
+    const __nv_bfloat16 b = __float2bfloat16_rn(m);
+    u[c] = b;
+    const float f = __bfloat162float(b);
+    acc += f * f;
     if (ef_apply) stv(M, m_dt, off + c, m * ef);
+  }
+  if (ss_ptrs) {
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float s = 0.f;
+      for (int w = 0; w < 8; ++w) s += red[w];
+      atomicAdd(reinterpret_cast<float*>(ss_ptrs[t]), s);
+    }
   }
 }
 
@@ -257,14 +278,17 @@ DION_EXPORT int dion_topk_select(const float* norms, int n, int num, int k, long
 
 DION_EXPORT int dion_gather_ef(const void* ptrs, int n, int rows, int cols, int m_dt,
                                const long long* idx, int k, int select_rows, void* U,
-                               long long u_stride, float ef, int ef_apply, void* stream) {
+                               long long u_stride, float ef, int ef_apply, const void* u_ptrs,
+                               const void* ss_ptrs, void* stream) {
   if (n <= 0 || k <= 0) return 0;
   if (select_rows) {
     dim3 grid(k, n);
-    gather_rows_kernel<<<grid, 256, 0, S(stream)>>>(static_cast<const long long*>(ptrs), n, cols,
-                                                    m_dt, idx, k, static_cast<__nv_bfloat16*>(U),
-                                                    u_stride, ef, ef_apply);
+    gather_rows_kernel<<<grid, 256, 0, S(stream)>>>(
+        static_cast<const long long*>(ptrs), n, cols, m_dt, idx, k,
+        static_cast<__nv_bfloat16*>(U), u_stride, ef, ef_apply,
+        static_cast<const long long*>(u_ptrs), static_cast<const long long*>(ss_ptrs));
   } else {
+    if (u_ptrs != nullptr || ss_ptrs != nullptr) return -3;
     dim3 grid((rows + 7) / 8, n);
     gather_cols_kernel<<<grid, 256, 0, S(stream)>>>(static_cast<const long long*>(ptrs), n, rows,
                                                     cols, m_dt, idx, k,

@@ -11,7 +11,7 @@ import torch
 from torch import Tensor
 
 from . import _backend
-from .tables import build_ptr_array
+from .tables import RawPointer, build_ptr_array
 
 _DT = {torch.float32: 0, torch.bfloat16: 1}
 
@@ -47,6 +47,8 @@ def dion2_select(
     select_dim: int,
     ef_decay: float,
     apply_ef: bool = True,
+    out_addresses: Optional[List[int]] = None,
+    sumsq_addresses: Optional[List[int]] = None,
 ) -> Tuple[Tensor, Tensor, Optional[Tensor]]:
     """``M += G`` (skipped when ``G`` is None), pick the ``k`` rows (``select_dim=-2``) or columns
     (``-1``) of each matrix with the largest L1 norm, return them as a dense bf16 stack and scale
@@ -82,11 +84,26 @@ def dion2_select(
         maps = torch.empty((N, num), dtype=torch.int32, device=dev)
         _check(lib.dion_topk_select(_c(norms.data_ptr()), N, num, k, _c(idx.data_ptr()),
                                     _c(maps.data_ptr()), _stream(dev)), "dion_topk_select")
+        if out_addresses is not None:
+            # Selected rows go straight to the given addresses (peer-mapped buffers of the ranks
+            # that own the matrices); their sums of squares are added at sumsq_addresses.
+            assert select_dim == -2 and len(out_addresses) == N
+            dst = build_ptr_array([[RawPointer(a) for a in out_addresses],
+                                   [RawPointer(a) for a in (sumsq_addresses or [0] * N)]],
+                                  tag="sel_dst")
+            _check(lib.dion_gather_ef(_c(ptrs.data_ptr()), N, rows, cols, m_dt,
+                                      _c(idx.data_ptr()), k, 1, _c(0), ctypes.c_longlong(0),
+                                      ctypes.c_float(float(ef_decay)), int(bool(apply_ef)),
+                                      _c(dst[0].data_ptr()),
+                                      _c(dst[1].data_ptr() if sumsq_addresses else 0),
+                                      _stream(dev)), "dion_gather_ef")
+            return None, idx, maps
         U = torch.empty(out_shape, dtype=torch.bfloat16, device=dev)
         _check(lib.dion_gather_ef(_c(ptrs.data_ptr()), N, rows, cols, m_dt, _c(idx.data_ptr()), k,
                                   int(select_dim == -2), _c(U.data_ptr()),
                                   ctypes.c_longlong(U[0].numel()), ctypes.c_float(float(ef_decay)),
-                                  int(bool(apply_ef)), _stream(dev)), "dion_gather_ef")
+                                  int(bool(apply_ef)), _c(0), _c(0), _stream(dev)),
+               "dion_gather_ef")
         return U, idx, maps
 
     # PyTorch path

@@ -128,7 +128,9 @@ def build_ptr_array(lists: Sequence[Sequence[Optional[Tensor]]], tag: str = "") 
     hit = _cache.get(key)
     if hit is not None:
         return hit.device_tensor
-    device = next(t.device for lst in lists for t in lst if t is not None)
+    device = next((t.device for lst in lists for t in lst if isinstance(t, Tensor)), None)
+    if device is None:  # only raw addresses: they belong to the current CUDA device
+        device = torch.device("cuda", torch.cuda.current_device())
     host = torch.tensor([[_ptr(t) for t in lst] for lst in lists], dtype=torch.int64)
     dev = _upload(host, device) if device.type == "cuda" else host
     if len(_cache) > _CACHE_LIMIT:

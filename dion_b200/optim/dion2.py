@@ -23,6 +23,8 @@ from torch.distributed.tensor import DeviceMesh
 from torch.optim.optimizer import ParamsT
 
 from ..ops import foreach as F
+from ..ops import newton_schulz as NS
+from ..parallel import fused_exchange as FX
 from ..ops.select import _as_matrices, dion2_select, scatter_selected
 from ..parallel.async_runtime import AsyncTask
 from ..parallel.megabatch import MegabatchPlan
@@ -107,7 +109,8 @@ class Dion2(DistributedOrthoBase):
                     epsilon=group["epsilon"], flatten=group["flatten"],
                     adjust_lr=group["adjust_lr"], device_rank=self._device_rank,
                     world_size=self._world_size, shard_dim=shard_dim, process_group=pg,
-                    newton_schulz_func=self._newton_schulz_func, arena=self._arena, verbose=self.verbose,
+                    newton_schulz_func=self._newton_schulz_func, arena=self._arena,
+                    fused_cache=self._fused_exchanges, verbose=self.verbose,
                     selection_scope=group["selection_scope"]))
 
 
@@ -150,6 +153,7 @@ def dion2_update_megabatch_async(
     triton_post_ortho: bool = False,
     selection_scope: str = "local",
     arena=None,
+    fused_cache=None,
 ) -> Generator[None, None, None]:
     assert len(X) == len(G) == len(M)
     ndim = X[0].ndim
@@ -178,6 +182,27 @@ def dion2_update_megabatch_async(
     if k is None:
         k = max(1, int(math.ceil(fraction * num_select)))
     k_topk = min(k, num_select)
+    if fused_cache is not None and FX.eligible(Ml[0].shape, comm_dim, global_dim, world_size,
+                                               process_group, newton_schulz_func, flatten, None):
+        # Row-sharded "local" selection with the exchange inside the kernels: the gather kernel
+        # stores each rank's k selected rows straight into the owners' receive buffers, the
+        # Newton-Schulz kernels consume them as they arrive and return their rows to the shards.
+        fx = FX.get_exchange(fused_cache, (id(X[0]), N, k, Ml[0].shape[1]), process_group, N, k,
+                             Ml[0].shape[1], Ml[0].device)
+        fx.begin()
+        outs, sums = fx.push_targets()
+        _, idx, maps = dion2_select(Gl, Ml, k, select_dim, float(ef_decay),
+                                    out_addresses=[o.address for o in outs],
+                                    sumsq_addresses=sums)
+        fx.publish()
+        NS.iterate_with_exchange(fx.input_matrix(), newton_schulz_func, epsilon, fx)
+        fx.finish()
+        fx.wait_results()
+        F.dion2_post(Xl, list(fx.result_stack().unbind(0)), list(idx.unbind(0)),
+                     list(maps.unbind(0)), lr, weight_decay, ratio, select_dim)
+        fx.release()
+        yield
+        return
     U_sel, idx, maps = dion2_select(Gl, Ml, k_topk, select_dim, float(ef_decay))
     batch_shape = Ml[0].shape[:-2]
     sel_shape = tuple(batch_shape) + tuple(U_sel.shape[-2:])

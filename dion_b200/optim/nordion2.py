@@ -14,6 +14,8 @@ from torch.distributed.tensor import DeviceMesh
 from torch.optim.optimizer import ParamsT
 
 from ..ops import foreach as F
+from ..ops import newton_schulz as NS
+from ..parallel import fused_exchange as FX
 from ..ops.select import _as_matrices, dion2_select
 from ..parallel.async_runtime import AsyncTask
 from ..parallel.megabatch import MegabatchPlan
@@ -105,6 +107,7 @@ class NorDion2(DistributedOrthoBase):
                     adjust_lr=group["adjust_lr"], device_rank=self._device_rank,
                     world_size=self._world_size, shard_dim=shard_dim, process_group=pg,
                     newton_schulz_func=self._newton_schulz_func, arena=self._arena,
+                    fused_cache=self._fused_exchanges,
                     selection_scope=group["selection_scope"]))
 
 
@@ -129,6 +132,7 @@ def nordion2_update_megabatch_async(
     triton_post_ortho: bool = False,
     selection_scope: str = "local",
     arena=None,
+    fused_cache=None,
 ) -> Generator[None, None, None]:
     assert len(X) == len(G) == len(M) == len(V)
     select_dim = -2
@@ -154,6 +158,30 @@ def nordion2_update_megabatch_async(
     if k is None:
         k = max(1, int(math.ceil(fraction * num_select)))
     k_topk = min(k, num_select)
+    if fused_cache is not None and FX.eligible(Ml[0].shape, comm_dim, global_dim, world_size,
+                                               process_group, newton_schulz_func, flatten, None):
+        # Exchange carried by the kernels (see Dion2 and parallel/fused_exchange.py).
+        fx = FX.get_exchange(fused_cache, (id(X[0]), N, k, Ml[0].shape[1]), process_group, N, k,
+                             Ml[0].shape[1], Ml[0].device)
+        fx.begin()
+        outs, sums = fx.push_targets()
+        _, idx, maps = dion2_select(Gl, Ml, k, select_dim, float(momentum),
+                                    out_addresses=[o.address for o in outs],
+                                    sumsq_addresses=sums)
+        fx.publish()
+        NS.iterate_with_exchange(fx.input_matrix(), newton_schulz_func, epsilon, fx)
+        fx.finish()
+        fx.wait_results()
+        U3 = fx.result_stack()
+        idx_list = list(idx.unbind(0))
+        rinv, n_u2, n_new2 = F.normuon_rowstats(U3, _matrix_views(Vl, num_select),
+                                                float(muon_beta2), vmaps=idx_list)
+        F.dion2_post(Xl, list(U3.unbind(0)), idx_list, list(maps.unbind(0)), lr, weight_decay,
+                     ratio, select_dim, rowscale=list(rinv.unbind(0)), normU2=n_u2,
+                     normNew2=n_new2)
+        fx.release()
+        yield
+        return
     U_sel, idx, maps = dion2_select(Gl, Ml, k_topk, select_dim, float(momentum))
     sel_shape = tuple(Ml[0].shape[:-2]) + tuple(U_sel.shape[-2:])
     plan = MegabatchPlan(sel_shape, N, Ml[0].device, comm_dim, device_rank, world_size,

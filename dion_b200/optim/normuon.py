@@ -18,6 +18,8 @@ from torch.distributed.tensor import DeviceMesh
 from torch.optim.optimizer import ParamsT
 
 from ..ops import foreach as F
+from ..ops import newton_schulz as NS
+from ..parallel import fused_exchange as FX
 from ..parallel.async_runtime import AsyncTask
 from ..parallel.megabatch import MegabatchPlan
 from ..utils.tensors import group_by_shape, to_local
@@ -106,6 +108,7 @@ class NorMuon(DistributedOrthoBase):
                     device_rank=self._device_rank, world_size=self._world_size,
                     shard_dim=shard_dim, process_group=pg,
                     newton_schulz_func=self._newton_schulz_func, arena=self._arena,
+                    fused_cache=self._fused_exchanges,
                     cautious_wd=group["cautious_wd"], split_sizes=split_sizes,
                     split_scales=split_scales))
 
@@ -132,17 +135,37 @@ def normuon_update_megabatch_async(
     split_sizes: Optional[Tuple[int, ...]] = None,
     split_scales: Optional[Tuple[float, ...]] = None,
     arena=None,
+    fused_cache=None,
 ) -> Generator[None, None, None]:
     assert len(X) == len(G) == len(M) == len(V)
     Xl, Gl, Ml, Vl = to_local(X), to_local(G), to_local(M), to_local(V)
     comm_dim = (shard_dim - X[0].ndim) if shard_dim is not None else None
+    ratio = lr_ratio(adjust_lr, X[0].shape, flatten)
+    global_rows = global_comm_size(X[0], comm_dim)
+    if fused_cache is not None and FX.eligible(Ml[0].shape, comm_dim, global_rows, world_size,
+                                               process_group, newton_schulz_func, flatten,
+                                               split_sizes):
+        # Row shards travel through peer-mapped memory inside the kernels (see fused_exchange).
+        fx = FX.get_exchange(fused_cache, (id(X[0]), len(X), tuple(Ml[0].shape)), process_group,
+                             len(X), Ml[0].shape[0], Ml[0].shape[1], Ml[0].device)
+        fx.begin()
+        outs, sums = fx.push_targets()
+        F.muon_pre(Gl, Ml, float(momentum), nesterov, out=outs, sumsq_targets=sums)
+        fx.publish()
+        NS.iterate_with_exchange(fx.input_matrix(), newton_schulz_func, epsilon, fx)
+        fx.finish()
+        fx.wait_results()
+        normuon_normalize_and_apply(Xl, fx.result_stack(), Vl, float(muon_beta2), lr,
+                                    weight_decay, ratio, cautious_wd, None)
+        fx.release()
+        yield
+        return
     plan = MegabatchPlan(
         Ml[0].shape, len(X), Ml[0].device, comm_dim, device_rank, world_size, process_group,
-        global_comm_dim_size=global_comm_size(X[0], comm_dim), split_sizes=split_sizes,
+        global_comm_dim_size=global_rows, split_sizes=split_sizes,
         arena=arena)
     F.muon_pre(Gl, Ml, float(momentum), nesterov, out=plan.input_views())
     U = yield from plan.run(newton_schulz_func, flatten, epsilon, split_sizes, split_scales)
-    ratio = lr_ratio(adjust_lr, X[0].shape, flatten)
     # Row blocks keep their own Frobenius norm only where whole matrices are local.
     norm_split = split_sizes if (comm_dim is None or process_group is None) else None
     normuon_normalize_and_apply(Xl, U, Vl, float(muon_beta2), lr, weight_decay, ratio,

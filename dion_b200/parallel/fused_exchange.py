@@ -41,6 +41,15 @@ def fused_exchange_enabled() -> bool:
     return os.environ.get("DION_B200_FUSED_EXCHANGE", "1") != "0"
 
 
+def get_exchange(cache: dict, key, pg, n: int, rows_local: int, cols: int,
+                 device: torch.device) -> "FusedRowExchange":
+    """Workspace of a bucket, created (collectively, on first use) and then kept."""
+    fx = cache.get(key)
+    if fx is None:
+        fx = cache[key] = FusedRowExchange(pg, n, rows_local, cols, device)
+    return fx
+
+
 def eligible(local_shape: Sequence[int], comm_dim: Optional[int], global_rows: Optional[int],
              world: int, pg: Optional[ProcessGroup], ns_func, flatten: bool,
              split_sizes) -> bool:
@@ -53,8 +62,7 @@ def eligible(local_shape: Sequence[int], comm_dim: Optional[int], global_rows: O
         return False
     if global_rows is None or global_rows % world != 0:
         return False
-    rows, cols = global_rows // world, local_shape[1]
-    if rows % 8 or cols % 8:
+    if local_shape[1] % 8:
         return False
     return symm.symmetric_memory_available(pg)
 
@@ -159,6 +167,15 @@ class FusedRowExchange:
         """Argument for ``foreach.muon_post(wait=...)``: matrix ``i`` was produced by rank
         ``i // per_rank``."""
         return (self.flags["ret"], self.seq, self.per_rank, self.status)
+
+    def wait_results(self) -> None:
+        """Stream-level wait (bounded) until every producing rank has stored its results; for
+        consumers that do not poll the flags themselves."""
+        symm.wait_flags(self.flags["ret"], self.seq, 0, self.status)
+
+    def result_stack(self) -> Tensor:
+        """``[n, rows_local, cols]`` view of the returned updates."""
+        return self.ret[: self.n]
 
     def release(self) -> None:
         """The update has been applied: producers may overwrite the return buffer."""

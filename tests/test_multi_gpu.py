@@ -109,3 +109,17 @@ def test_wait_on_flag_nobody_sets_times_out_cleanly():
     x = torch.ones(8, device=dev)
     assert float((x * 2).sum()) == 16.0      # context still alive
     gemm.check_status()                       # status was cleared
+
+
+@pytest.mark.parametrize("name,kw", [("NorMuon", dict(use_polar_express=False)),
+                                     ("Dion2", dict(fraction=0.25)),
+                                     ("NorDion2", dict(fraction=0.5))])
+def test_fused_exchange_matches_collective_other_optimizers(tmp_path, name, kw):
+    _need(2)
+    (tmp_path / "a").mkdir()
+    (tmp_path / "b").mkdir()
+    coll, used0 = run_ranks(_sharded, 2, "nccl", (name, kw, 3, False), str(tmp_path / "a"))[0]
+    fused, used1 = run_ranks(_sharded, 2, "nccl", (name, kw, 3, True), str(tmp_path / "b"))[0]
+    assert used0 == 0 and used1 > 0
+    for c, f in zip(coll, fused):
+        assert (c - f).abs().max().item() < 2e-3, name
