@@ -113,13 +113,18 @@ def gemm_breakdown(b: int, m: int, n: int):
     Bm = torch.empty_like(A)
     C = torch.empty_like(X)
     out = {}
-    cases = {
-        "gram  A=XX^T (sym)": (lambda: gemm.ns_gemm(X, X, out=A, sym=True), 2.0 * b * m * m * n),
-        "poly  B=bA+cA^2 (sym)": (lambda: gemm.ns_gemm(A, A, out=Bm, sym=True, D=A, alpha=1.0, beta=1.0), 2.0 * b * m ** 3),
-        "upd   X'=aX+BX": (lambda: gemm.ns_gemm(Bm, X, out=C, b_is_kn=True, D=X, alpha=1.0, beta=1.0), 2.0 * b * m * m * n),
-        "gram  cuBLAS bmm": (lambda: torch.bmm(X, X.mT, out=A), 2.0 * b * m * m * n),
-        "upd   cuBLAS baddbmm": (lambda: torch.baddbmm(X, Bm, X, out=C), 2.0 * b * m * m * n),
-    }
+    cases = {}
+    for tag, pair in (("1cta", False), ("2cta", True)):
+        cases[f"gram  A=XX^T (sym) {tag}"] = (
+            lambda pair=pair: gemm.ns_gemm(X, X, out=A, sym=True, pair=pair), 2.0 * b * m * m * n)
+        cases[f"poly  B=bA+cA^2 (sym) {tag}"] = (
+            lambda pair=pair: gemm.ns_gemm(A, A, out=Bm, sym=True, D=A, alpha=1.0, beta=1.0,
+                                           pair=pair), 2.0 * b * m ** 3)
+        cases[f"upd   X'=aX+BX {tag}"] = (
+            lambda pair=pair: gemm.ns_gemm(Bm, X, out=C, b_is_kn=True, D=X, alpha=1.0, beta=1.0,
+                                           pair=pair), 2.0 * b * m * m * n)
+    cases["gram  cuBLAS bmm"] = (lambda: torch.bmm(X, X.mT, out=A), 2.0 * b * m * m * n)
+    cases["upd   cuBLAS baddbmm"] = (lambda: torch.baddbmm(X, Bm, X, out=C), 2.0 * b * m * m * n)
     for name, (fn, fl) in cases.items():
         ms = bench(fn)
         out[name] = {"ms": round(ms, 4), "nominal_tflops": round(fl / (ms * 1e-3) / 1e12, 1)}

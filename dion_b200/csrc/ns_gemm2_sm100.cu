@@ -1,0 +1,520 @@
+// Two-CTA (cta_group::2) variant of the Newton-Schulz GEMM for sm_100a:
+//
+//     C[b] = alpha * s_b^pa * A[b] * op(B[b]) + beta * s_b^pb * D[b]
+//
+// A pair of CTAs on neighbouring SMs (a cluster of two) computes one 256x256 output tile with
+// tcgen05.mma.cta_group::2 (UMMA 256x256x16).  Each CTA stages only its own 128 rows of A and its
+// own 128 of the 256 columns of B per 64-wide K slab (32 KB instead of the 48 KB a lone CTA needs
+// for a 128x256 tile), which takes the shared-memory traffic per MMA cycle below the SM's
+// bandwidth - the limit the single-CTA kernel in ns_gemm_sm100.cu runs into.  Loads are plain TMA
+// (cp.async.bulk.tensor with .cta_group::2 so that both CTAs' transfers complete on the leader's
+// barrier; no multicast).  The leader CTA's MMA thread issues the instructions for the pair and
+// releases stages / publishes accumulators in both CTAs with a cluster-multicast tcgen05.commit.
+// Each CTA drains its own half (128 TMEM lanes) of the accumulator in its epilogue warps.
+//
+// Operand layouts, symmetric half-compute with mirrored stores and the epilogue arithmetic are the
+// same as in the single-CTA kernel.  All waits are bounded.
+#include "common.cuh"
+
+namespace dion {
+
+constexpr int BM2 = 128;   // rows per CTA (256 per pair)
+constexpr int BN2 = 256;   // columns per pair (128 loaded by each CTA)
+constexpr int BK2 = 64;
+constexpr int kThreads2 = 192;
+constexpr int kStages2 = 6;
+constexpr int kABytes2 = BM2 * BK2 * 2;          // 16 KB
+constexpr int kBBytes2 = (BN2 / 2) * BK2 * 2;    // 16 KB
+constexpr int kStageBytes2 = kABytes2 + kBBytes2;
+constexpr int kDynBytes2 = kStages2 * kStageBytes2 + 1024;
+constexpr uint32_t kTmemCols2 = 2 * BN2;
+
+struct Gemm2Args {
+  int batch, M, N, K;
+  const __nv_bfloat16* D;
+  long long ldd, strideD;
+  __nv_bfloat16* C;
+  long long ldc, strideC;
+  float alpha, beta;
+  const float* scale;
+  int alpha_pow, beta_pow;
+  int sym;
+  const int2* tiles;  // (tile_m, tile_n) in units of 256 x 256
+  int tiles_per_mat;
+  int total_tiles;
+  int* status;
+};
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t cluster_id_x() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%clusterid.x;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t num_clusters_x() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%nclusterid.x;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// shared::cluster address of `local_addr` (a shared::cta address) in the CTA with rank `rank`.
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t local_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr)
+               : "memory");
+}
+// TMA load whose completion is counted on a barrier that may live in the peer CTA of the pair.
+__device__ __forceinline__ void tma_load_3d_pair(void* smem_dst, const CUtensorMap* map,
+                                                 uint32_t bar_cluster_addr, int x, int y, int z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4, %5}], [%2];" ::"r"(smem_u32(smem_dst)),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_addr), "r"(x), "r"(y), "r"(z)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_result, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                   smem_u32(smem_result)),
+               "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols)
+               : "memory");
+}
+// Arrives on the barrier at the same shared-memory offset in both CTAs of the pair once all
+// tcgen05.mma issued so far have completed.
+__device__ __forceinline__ void tc_commit_pair(uint64_t* bar) {
+  const uint16_t mask = 3;
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 "
+      "[%0], %1;" ::"r"(smem_u32(bar)),
+      "h"(mask)
+      : "memory");
+}
+__device__ __forceinline__ void tc_mma_bf16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                                 uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// Bounded wait with cluster-scope acquire (the arrivals come from both CTAs of the pair).
+__device__ __forceinline__ bool mbar_wait_bounded_cluster(uint64_t* bar, uint32_t parity) {
+  for (uint32_t i = 0; i < kMaxPolls; ++i) {
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    if (ok) return true;
+  }
+  return false;
+}
+
+__device__ __forceinline__ float ipow2(float s, int p) {
+  float r = 1.f;
+  for (int i = 0; i < p; ++i) r *= s;
+  return r;
+}
+
+template <bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(kThreads2, 1)
+ns_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                const Gemm2Args p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  __shared__ __align__(8) uint64_t full_bar[kStages2];    // used in the leader CTA
+  __shared__ __align__(8) uint64_t empty_bar[kStages2];   // one copy per CTA
+  __shared__ __align__(8) uint64_t tfull_bar[2];          // one copy per CTA
+  __shared__ __align__(8) uint64_t tempty_bar[2];         // used in the leader CTA
+  __shared__ uint32_t tmem_base_slot;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t cta = cluster_ctarank();  // 0 = leader
+  const int num_kb = (p.K + BK2 - 1) / BK2;
+  const int first_tile = (int)cluster_id_x();
+  const int tile_step = (int)num_clusters_x();
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages2; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull_bar[a], 1);
+      mbar_init(&tempty_bar[a], 8);  // four epilogue warps in each CTA of the pair
+    }
+    fence_barrier_init();
+    fence_proxy_async();
+    prefetch_tmap(&map_a);
+    prefetch_tmap(&map_b);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(&tmem_base_slot, kTmemCols2);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // barriers of both CTAs are initialised before anyone signals them
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_slot;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer (both CTAs) ------------------------------
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (int t = first_tile; t < p.total_tiles && ok; t += tile_step) {
+        const int b = t / p.tiles_per_mat;
+        const int2 tt = p.tiles[t - b * p.tiles_per_mat];
+        const int row0 = tt.x * 256 + (int)cta * BM2;          // this CTA's rows of A
+        const int col0 = tt.y * BN2 + (int)cta * (BN2 / 2);    // this CTA's columns of B
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1)) {
+            atomicExch(p.status, kStatusTimeoutEmpty);
+            ok = false;
+            break;
+          }
+          uint8_t* sa = smem + stage * kStageBytes2;
+          uint8_t* sb = sa + kABytes2;
+          const uint32_t bar = map_to_cta(smem_u32(&full_bar[stage]), 0);
+          if (cta == 0) mbar_expect_tx(&full_bar[stage], 2 * kStageBytes2);
+          if (!A_MN) {
+            tma_load_3d_pair(sa, &map_a, bar, kb * BK2, row0, b);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BM2 / 64; ++c)
+              tma_load_3d_pair(sa + c * (BK2 * 128), &map_a, bar, row0 + c * 64, kb * BK2, b);
+          }
+          if (!B_MN) {
+            tma_load_3d_pair(sb, &map_b, bar, kb * BK2, col0, b);
+          } else {
+#pragma unroll
+            for (int c = 0; c < (BN2 / 2) / 64; ++c)
+              tma_load_3d_pair(sb + c * (BK2 * 128), &map_b, bar, col0 + c * 64, kb * BK2, b);
+          }
+          if (++stage == kStages2) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer (leader CTA only) --------------------------
+    if (lane == 0 && cta == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(256, BN2, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      uint32_t stage = 0, phase = 0;
+      uint32_t aslot = 0, aphase = 0;
+      bool ok = true;
+      for (int t = first_tile; t < p.total_tiles && ok; t += tile_step) {
+        if (!mbar_wait_bounded_cluster(&tempty_bar[aslot], aphase ^ 1)) {
+          atomicExch(p.status, kStatusTimeoutTmemEmpty);
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + aslot * BN2;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait_bounded_cluster(&full_bar[stage], phase)) {
+            atomicExch(p.status, kStatusTimeoutFull);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * kStageBytes2);
+          const uint32_t sb = sa + kABytes2;
+#pragma unroll
+          for (int k = 0; k < BK2 / 16; ++k) {
+            const uint64_t da = A_MN ? make_smem_desc(sa + k * 2048, BK2 * 128, 1024)
+                                     : make_smem_desc(sa + k * 32, 16, 1024);
+            const uint64_t db = B_MN ? make_smem_desc(sb + k * 2048, BK2 * 128, 1024)
+                                     : make_smem_desc(sb + k * 32, 16, 1024);
+            tc_mma_bf16_pair(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          tc_commit_pair(&empty_bar[stage]);
+          if (++stage == kStages2) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (!ok) break;
+        tc_commit_pair(&tfull_bar[aslot]);
+        aslot ^= 1;
+        if (aslot == 0) aphase ^= 1;
+      }
+    }
+  } else {
+    // ------------------------------ epilogue (both CTAs) ----------------------------------
+    const int lane_grp = warp & 3;
+    const int row_in_tile = lane_grp * 32 + lane;
+    uint32_t aslot = 0, aphase = 0;
+    for (int t = first_tile; t < p.total_tiles; t += tile_step) {
+      const int b = t / p.tiles_per_mat;
+      const int2 tt = p.tiles[t - b * p.tiles_per_mat];
+      if (!mbar_wait_bounded(&tfull_bar[aslot], aphase)) {
+        if (lane == 0) atomicExch(p.status, kStatusTimeoutTmemFull);
+        break;
+      }
+      tc_fence_after();
+      float sc = 1.f;
+      if (p.scale != nullptr) sc = p.scale[b];
+      const float alpha = p.alpha * ipow2(sc, p.alpha_pow);
+      const float beta = p.beta * ipow2(sc, p.beta_pow);
+      const int r = tt.x * 256 + (int)cta * BM2 + row_in_tile;
+      const int warp_row0 = tt.x * 256 + (int)cta * BM2 + lane_grp * 32;
+      const bool row_ok = r < p.M;
+      const __nv_bfloat16* Drow =
+          p.D ? p.D + (long long)b * p.strideD + (long long)r * p.ldd : nullptr;
+      __nv_bfloat16* Cb = p.C + (long long)b * p.strideC;
+      __nv_bfloat16* Crow = Cb + (long long)r * p.ldc;
+      const bool vec_ok = ((p.ldc & 7) == 0) && ((p.strideC & 7) == 0) &&
+                          ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0);
+      const bool dvec_ok = p.D && ((p.ldd & 7) == 0) && ((p.strideD & 7) == 0) &&
+                           ((reinterpret_cast<uintptr_t>(p.D) & 15) == 0);
+#pragma unroll 1
+      for (int ch = 0; ch < BN2 / 32; ++ch) {
+        const int c0 = tt.y * BN2 + ch * 32;
+        if (c0 >= p.N) continue;
+        if (p.sym && c0 + 31 < warp_row0) continue;
+        float v[32];
+        tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(lane_grp * 32) << 16) + aslot * BN2 +
+                          ch * 32,
+                      v);
+        tmem_ld_wait();
+        if (!row_ok) continue;
+        if (p.D) {
+          if (dvec_ok && c0 + 32 <= p.N) {
+            const uint4* dp = reinterpret_cast<const uint4*>(Drow + c0);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              uint4 u = __ldg(dp + q);
+              const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                float2 f = unpack_bf16x2(w[e]);
+                v[q * 8 + e * 2] = alpha * v[q * 8 + e * 2] + beta * f.x;
+                v[q * 8 + e * 2 + 1] = alpha * v[q * 8 + e * 2 + 1] + beta * f.y;
+              }
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const int c = c0 + j;
+              const float d = (c < p.N) ? __bfloat162float(Drow[c]) : 0.f;
+              v[j] = alpha * v[j] + beta * d;
+            }
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] *= alpha;
+        }
+        uint32_t pk[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) pk[j] = pack_bf16x2(v[2 * j], v[2 * j + 1]);
+        const bool full_chunk = (c0 + 32 <= p.N) && (!p.sym || c0 >= r);
+        if (vec_ok && full_chunk) {
+          uint4* cp = reinterpret_cast<uint4*>(Crow + c0);
+#pragma unroll
+          for (int q = 0; q < 4; ++q)
+            cp[q] = make_uint4(pk[q * 4], pk[q * 4 + 1], pk[q * 4 + 2], pk[q * 4 + 3]);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int c = c0 + j;
+            if (c < p.N && (!p.sym || c >= r)) {
+              const uint32_t w = pk[j >> 1];
+              reinterpret_cast<uint16_t*>(Crow)[c] = (j & 1) ? (w >> 16) : (w & 0xFFFF);
+            }
+          }
+        }
+        if (p.sym) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int c = c0 + j;
+            if (c > r && c < p.N) {
+              const uint32_t w = pk[j >> 1];
+              reinterpret_cast<uint16_t*>(Cb)[(long long)c * p.ldc + r] =
+                  (j & 1) ? (w >> 16) : (w & 0xFFFF);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tempty_bar[aslot]), 0));
+      aslot ^= 1;
+      if (aslot == 0) aphase ^= 1;
+    }
+  }
+
+  // Nobody leaves while the peer may still read this CTA's shared memory or signal its barriers.
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, kTmemCols2);
+  }
+}
+
+}  // namespace dion
+
+// ---------------------------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------------------------
+namespace dion {
+
+typedef CUresult (*EncodeTiledFn2)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn2 get_encode_fn2() {
+  static EncodeTiledFn2 fn = nullptr;
+  if (fn) return fn;
+  void* sym = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) !=
+          cudaSuccess ||
+      qres != cudaDriverEntryPointSuccess)
+    return nullptr;
+  fn = reinterpret_cast<EncodeTiledFn2>(sym);
+  return fn;
+}
+
+static int make_map2(CUtensorMap* map, const void* ptr, int batch, int rows, int cols,
+                     long long ld, long long batch_stride, int box_cols, int box_rows) {
+  EncodeTiledFn2 enc = get_encode_fn2();
+  if (!enc) return -1;
+  cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)batch};
+  cuuint64_t strides[2] = {(cuuint64_t)ld * 2, (cuuint64_t)batch_stride * 2};
+  if (batch == 1) strides[1] = (cuuint64_t)ld * 2 * (cuuint64_t)rows;
+  cuuint32_t box[3] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides,
+                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -2;
+}
+
+template <bool A_MN, bool B_MN>
+static int launch2(const CUtensorMap& ma, const CUtensorMap& mb, const Gemm2Args& args,
+                   cudaStream_t stream) {
+  static bool configured = false;
+  static int max_clusters = 0;
+  auto kernel = ns_gemm2_kernel<A_MN, B_MN>;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDynBytes2) !=
+        cudaSuccess)
+      return -3;
+    cudaLaunchConfig_t probe = {};
+    probe.gridDim = dim3(2 * 74, 1, 1);
+    probe.blockDim = dim3(kThreads2, 1, 1);
+    probe.dynamicSmemBytes = kDynBytes2;
+    cudaLaunchAttribute pattr[1];
+    pattr[0].id = cudaLaunchAttributeClusterDimension;
+    pattr[0].val.clusterDim.x = 2;
+    pattr[0].val.clusterDim.y = 1;
+    pattr[0].val.clusterDim.z = 1;
+    probe.attrs = pattr;
+    probe.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kernel, &probe) != cudaSuccess || n <= 0) {
+      cudaGetLastError();
+      return -5;
+    }
+    max_clusters = n;
+    configured = true;
+  }
+  int clusters = args.total_tiles < max_clusters ? args.total_tiles : max_clusters;
+  if (clusters <= 0) return 0;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * clusters, 1, 1);
+  cfg.blockDim = dim3(kThreads2, 1, 1);
+  cfg.dynamicSmemBytes = kDynBytes2;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, kernel, ma, mb, args) != cudaSuccess) {
+    cudaGetLastError();
+    return -4;
+  }
+  return 0;
+}
+
+}  // namespace dion
+
+// Same contract as dion_ns_gemm (ns_gemm_sm100.cu) for the features it has: bf16 output, optional
+// D, per-batch scale, symmetric mode; `tiles` holds (tile_m, tile_n) pairs in units of 256 x 256.
+DION_EXPORT int dion_ns_gemm2(const void* A, long long lda, long long strideA, int a_mn,
+                              const void* B, long long ldb, long long strideB, int b_mn, void* C,
+                              long long ldc, long long strideC, const void* D, long long ldd,
+                              long long strideD, int batch, int M, int N, int K, float alpha,
+                              float beta, const float* scale, int alpha_pow, int beta_pow, int sym,
+                              const void* tiles, int tiles_per_mat, int* status, void* stream) {
+  using namespace dion;
+  if (batch <= 0 || M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((lda & 7) || (ldb & 7) || (strideA & 7) || (strideB & 7) ||
+      (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) ||
+      C == nullptr)
+    return -10;
+  CUtensorMap ma, mb;
+  if (!a_mn) {
+    if (make_map2(&ma, A, batch, M, K, lda, strideA, BK2, BM2) != 0) return -12;
+  } else {
+    if (make_map2(&ma, A, batch, K, M, lda, strideA, 64, BK2) != 0) return -12;
+  }
+  if (!b_mn) {
+    if (make_map2(&mb, B, batch, N, K, ldb, strideB, BK2, BN2 / 2) != 0) return -13;
+  } else {
+    if (make_map2(&mb, B, batch, K, N, ldb, strideB, 64, BK2) != 0) return -13;
+  }
+  Gemm2Args a;
+  a.batch = batch; a.M = M; a.N = N; a.K = K;
+  a.D = static_cast<const __nv_bfloat16*>(D); a.ldd = ldd; a.strideD = strideD;
+  a.C = static_cast<__nv_bfloat16*>(C); a.ldc = ldc; a.strideC = strideC;
+  a.alpha = alpha; a.beta = beta; a.scale = scale; a.alpha_pow = alpha_pow; a.beta_pow = beta_pow;
+  a.sym = sym;
+  a.tiles = static_cast<const int2*>(tiles); a.tiles_per_mat = tiles_per_mat;
+  a.total_tiles = tiles_per_mat * batch;
+  a.status = status;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  switch ((a_mn ? 2 : 0) | (b_mn ? 1 : 0)) {
+    case 0: return launch2<false, false>(ma, mb, a, s);
+    case 1: return launch2<false, true>(ma, mb, a, s);
+    case 2: return launch2<true, false>(ma, mb, a, s);
+    default: return launch2<true, true>(ma, mb, a, s);
+  }
+}

@@ -32,6 +32,7 @@ NVCC_FLAGS = [
 # source stem -> library stem
 SOURCES = {
     "ns_gemm_sm100": "libdion_ns_gemm.so",
+    "ns_gemm2_sm100": "libdion_ns_gemm2.so",
     "foreach_ops": "libdion_foreach.so",
     "select_ops": "libdion_select.so",
     "model_ops": "libdion_model.so",

@@ -9,6 +9,7 @@ reference's three Triton kernels and its cuBLAS ``baddbmm`` call
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Dict, Optional, Tuple
 
 import torch
@@ -64,19 +65,20 @@ def sm_count(device: torch.device) -> int:
     return n
 
 
-def tile_table(M: int, N: int, bn: int, sym: bool, device: torch.device) -> Tensor:
+def tile_table(M: int, N: int, bn: int, sym: bool, device: torch.device,
+               bm: int = _BM) -> Tensor:
     """Device array of (tile_m, tile_n) pairs.  For ``sym`` only tiles that intersect the
     upper triangle (column range reaching the tile's first row) are listed."""
-    key = (M, N, bn, sym, device.index)
+    key = (M, N, bn, sym, device.index, bm)
     t = _tile_cache.get(key)
     if t is not None:
         return t
-    tm_n = (M + _BM - 1) // _BM
+    tm_n = (M + bm - 1) // bm
     tn_n = (N + bn - 1) // bn
     pairs = []
     for tm in range(tm_n):
         for tn in range(tn_n):
-            if sym and (tn + 1) * bn - 1 < tm * _BM:
+            if sym and (tn + 1) * bn - 1 < tm * bm:
                 continue
             pairs.append((tm, tn))
     t = torch.tensor(pairs, dtype=torch.int32, device=device).contiguous()
@@ -125,6 +127,27 @@ class GemmExtra(ctypes.Structure):
     ]
 
 
+def pair_default() -> bool:
+    """Whether eligible GEMMs go to the two-CTA kernel (``DION_B200_PAIR_GEMM``, default on)."""
+    return os.environ.get("DION_B200_PAIR_GEMM", "1") != "0"
+
+
+def _pair_eligible(M: int, N: int, batch: int, extra, out_t, out_f32, out, device) -> bool:
+    """The two-CTA kernel covers the plain bf16-output forms; it pays off once the 256 x 256
+    tiles fill the pairs of SMs about as well as 128 x 256 tiles fill single SMs."""
+    if extra is not None or out_t is not None or out_f32 is not None:
+        return False
+    if M < 256 or N < 256:
+        return False
+    pairs = sm_count(device) // 2
+    tiles2 = -(-M // 256) * -(-N // 256) * batch
+    tiles1 = -(-M // 128) * -(-N // 256) * batch
+    waves2 = -(-tiles2 // pairs)
+    waves1 = -(-tiles1 // sm_count(device))
+    # One pair tile costs about as much time as one single-CTA tile of half the rows.
+    return waves2 <= waves1
+
+
 def ns_gemm(
     A: Tensor,
     B: Tensor,
@@ -144,6 +167,7 @@ def ns_gemm(
     out_t: Optional[Tensor] = None,
     out_f32: Optional[Tensor] = None,
     bn: Optional[int] = None,
+    pair: Optional[bool] = None,
 ) -> Tensor:
     A3, B3 = _as3d(A), _as3d(B)
     batch = A3.size(0)
@@ -168,12 +192,35 @@ def ns_gemm(
     ldct, sct = _ld_stride(CT3) if CT3 is not None else (0, 0)
     lda, sa = _ld_stride(A3)
     ldb, sb = _ld_stride(B3)
-    if bn is None:
-        bn = 256 if N > 128 else 128
-    tiles = tile_table(M, N, bn, sym, dev)
     if scale is not None:
         assert scale.dtype == torch.float32 and scale.numel() >= batch
     st = status_tensor(dev)
+    if pair is None:
+        pair = pair_default() and bn is None and _pair_eligible(
+            M, N, batch, extra, out_t, out_f32, out, dev)
+    if pair:
+        if extra is not None or out_t is not None or out_f32 is not None:
+            raise ValueError("the two-CTA kernel has no transposed/fp32/cross-GPU outputs")
+        tiles = tile_table(M, N, 256, sym, dev, bm=256)
+        rc = _backend.lib("ns_gemm2_sm100").dion_ns_gemm2(
+            _p(A3), ctypes.c_longlong(lda), ctypes.c_longlong(sa),
+            ctypes.c_int(1 if a_is_km else 0),
+            _p(B3), ctypes.c_longlong(ldb), ctypes.c_longlong(sb),
+            ctypes.c_int(1 if b_is_kn else 0),
+            _p(C3), ctypes.c_longlong(ldc), ctypes.c_longlong(sc),
+            _p(D3), ctypes.c_longlong(ldd), ctypes.c_longlong(sd),
+            ctypes.c_int(batch), ctypes.c_int(M), ctypes.c_int(N), ctypes.c_int(K),
+            ctypes.c_float(alpha), ctypes.c_float(beta), _p(scale),
+            ctypes.c_int(alpha_pow), ctypes.c_int(beta_pow), ctypes.c_int(1 if sym else 0),
+            _p(tiles), ctypes.c_int(tiles.size(0)), _p(st),
+            ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream),
+        )
+        if rc != 0:
+            raise RuntimeError(f"dion_ns_gemm2 launch failed with code {rc}")
+        return out
+    if bn is None:
+        bn = 256 if N > 128 else 128
+    tiles = tile_table(M, N, bn, sym, dev)
     rc = _backend.lib("ns_gemm_sm100").dion_ns_gemm_ex(
         _p(A3), ctypes.c_longlong(lda), ctypes.c_longlong(sa), ctypes.c_int(1 if a_is_km else 0),
         _p(B3), ctypes.c_longlong(ldb), ctypes.c_longlong(sb), ctypes.c_int(1 if b_is_kn else 0),

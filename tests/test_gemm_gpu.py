@@ -78,3 +78,61 @@ def test_rejects_unaligned():
     A = torch.randn(1, 64, 20, device="cuda").bfloat16()
     with pytest.raises(ValueError):
         gemm.ns_gemm(A, A)
+
+
+# ---- two-CTA (cta_group::2) kernel -----------------------------------------------------------
+
+@pytest.mark.parametrize("shape", [(1, 256, 256, 64), (3, 328, 456, 200), (4, 768, 768, 768),
+                                   (2, 512, 1024, 2048)])
+def test_pair_nt(shape):
+    from dion_b200.ops import gemm
+    b, M, N, K = shape
+    torch.manual_seed(0)
+    A = torch.randn(b, M, K, device="cuda").bfloat16()
+    B = torch.randn(b, N, K, device="cuda").bfloat16()
+    C = gemm.ns_gemm(A, B, pair=True)
+    torch.cuda.synchronize()
+    gemm.check_status()
+    assert _rel_err(C, A.float() @ B.float().mT) < 1e-2
+
+
+@pytest.mark.parametrize("shape", [(1, 256, 256, 64), (2, 768, 3072, 768), (3, 328, 456, 200)])
+def test_pair_nn_with_epilogue(shape):
+    from dion_b200.ops import gemm
+    b, M, N, K = shape
+    torch.manual_seed(1)
+    A = torch.randn(b, M, K, device="cuda").bfloat16()
+    B = torch.randn(b, K, N, device="cuda").bfloat16()
+    D = torch.randn(b, M, N, device="cuda").bfloat16()
+    sc = torch.rand(b, device="cuda") + 0.5
+    C = gemm.ns_gemm(A, B, b_is_kn=True, D=D, alpha=0.5, beta=2.0, scale=sc, alpha_pow=1,
+                     beta_pow=1, pair=True)
+    torch.cuda.synchronize()
+    gemm.check_status()
+    ref = (0.5 * (A.float() @ B.float()) + 2.0 * D.float()) * sc[:, None, None]
+    assert _rel_err(C, ref) < 1e-2
+
+
+@pytest.mark.parametrize("shape", [(2, 768, 3072), (3, 328, 136), (1, 1024, 512)])
+def test_pair_symmetric(shape):
+    from dion_b200.ops import gemm
+    b, M, K = shape
+    torch.manual_seed(2)
+    X = torch.randn(b, M, K, device="cuda").bfloat16()
+    C = torch.full((b, M, M), float("nan"), device="cuda", dtype=torch.bfloat16)
+    gemm.ns_gemm(X, X, out=C, sym=True, pair=True)
+    torch.cuda.synchronize()
+    gemm.check_status()
+    assert _rel_err(C, X.float() @ X.float().mT) < 1e-2
+    assert (C - C.mT).abs().max().item() == 0.0
+
+
+def test_pair_km_a_operand():
+    """A given as [K, M] (tall Gram matrix X^T X without a transposed copy)."""
+    from dion_b200.ops import gemm
+    torch.manual_seed(4)
+    X = torch.randn(2, 1024, 384, device="cuda").bfloat16()
+    C = gemm.ns_gemm(X, X, a_is_km=True, b_is_kn=True, sym=True, pair=True)
+    torch.cuda.synchronize()
+    gemm.check_status()
+    assert _rel_err(C, X.float().mT @ X.float()) < 1e-2
