@@ -22,11 +22,18 @@ constexpr int BM2 = 128;   // rows per CTA (256 per pair)
 constexpr int BN2 = 256;   // columns per pair (128 loaded by each CTA)
 constexpr int BK2 = 64;
 constexpr int kThreads2 = 192;
-constexpr int kStages2 = 6;
+constexpr int kStagesSym = 5;     // symmetric mode also stages transposed sub-tiles
+constexpr int kStagesPlain = 6;
 constexpr int kABytes2 = BM2 * BK2 * 2;          // 16 KB
 constexpr int kBBytes2 = (BN2 / 2) * BK2 * 2;    // 16 KB
 constexpr int kStageBytes2 = kABytes2 + kBBytes2;
-constexpr int kDynBytes2 = kStages2 * kStageBytes2 + 1024;
+constexpr int kSubCols = 64;                       // epilogue sub-tile: 128 rows x 64 columns
+constexpr int kEpiBufs = 2;
+constexpr int kEpiBufBytes = BM2 * kSubCols * 2;    // 16 KB: two 64 x 64 boxes of bf16
+// stages | kEpiBufs D/C buffers | kEpiBufs transposed buffers (symmetric mode) | alignment slack
+constexpr int dyn_bytes2(int stages, bool sym) {
+  return stages * kStageBytes2 + (sym ? 2 : 1) * kEpiBufs * kEpiBufBytes + 1024;
+}
 constexpr uint32_t kTmemCols2 = 2 * BN2;
 
 struct Gemm2Args {
@@ -136,15 +143,50 @@ __device__ __forceinline__ bool mbar_wait_bounded_cluster(uint64_t* bar, uint32_
   return false;
 }
 
+// TMA store of one box from shared memory (bulk-group completion).
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, const void* smem_src, int x,
+                                             int y, int z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(
+          reinterpret_cast<uint64_t>(map)),
+      "r"(smem_u32(smem_src)), "r"(x), "r"(y), "r"(z)
+      : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() {
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+__device__ __forceinline__ void bulk_wait_group_read_all() {
+  asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
+__device__ __forceinline__ void bulk_wait_group_all() {
+  asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+}
+// Barrier over the 128 epilogue threads (barrier 1) that also ANDs a predicate.
+__device__ __forceinline__ bool epi_barrier_and(bool mine) {
+  uint32_t out;
+  asm volatile(
+      "{\n"
+      ".reg .pred p, q;\n"
+      "setp.ne.u32 q, %1, 0;\n"
+      "barrier.cta.red.and.pred.aligned p, 1, 128, q;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(out)
+      : "r"((uint32_t)mine)
+      : "memory");
+  return out != 0;
+}
+
 __device__ __forceinline__ float ipow2(float s, int p) {
   float r = 1.f;
   for (int i = 0; i < p; ++i) r *= s;
   return r;
 }
 
-template <bool A_MN, bool B_MN>
+template <bool A_MN, bool B_MN, int kStages2>
 __global__ void __launch_bounds__(kThreads2, 1)
 ns_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                const __grid_constant__ CUtensorMap map_c, const __grid_constant__ CUtensorMap map_d,
                 const Gemm2Args p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -153,6 +195,7 @@ ns_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   __shared__ __align__(8) uint64_t empty_bar[kStages2];   // one copy per CTA
   __shared__ __align__(8) uint64_t tfull_bar[2];          // one copy per CTA
   __shared__ __align__(8) uint64_t tempty_bar[2];         // used in the leader CTA
+  __shared__ __align__(8) uint64_t dfull_bar[kEpiBufs];   // D sub-tiles, one copy per CTA
   __shared__ uint32_t tmem_base_slot;
 
   const int warp = threadIdx.x >> 5;
@@ -171,10 +214,13 @@ ns_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       mbar_init(&tfull_bar[a], 1);
       mbar_init(&tempty_bar[a], 8);  // four epilogue warps in each CTA of the pair
     }
+    for (int a = 0; a < kEpiBufs; ++a) mbar_init(&dfull_bar[a], 1);
     fence_barrier_init();
     fence_proxy_async();
     prefetch_tmap(&map_a);
     prefetch_tmap(&map_b);
+    prefetch_tmap(&map_c);
+    if (p.D) prefetch_tmap(&map_d);
   }
   if (warp == 1) {
     tmem_alloc_pair(&tmem_base_slot, kTmemCols2);
@@ -272,105 +318,164 @@ ns_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     }
   } else {
     // ------------------------------ epilogue (both CTAs) ----------------------------------
+    // The 128 x 256 half-tile of this CTA is drained in sub-tiles of 64 columns.  D arrives by
+    // TMA into a shared-memory buffer (prefetched two sub-tiles ahead), each thread combines
+    // its row in place, and the buffer leaves by TMA store; with `sym`, off-diagonal tiles also
+    // write a transposed copy that a second TMA store places at the mirrored position.
     const int lane_grp = warp & 3;
     const int row_in_tile = lane_grp * 32 + lane;
+    const bool elected = (warp == 2 && lane == 0);
+    const bool has_d = p.D != nullptr;
+    const uint32_t row_off = (uint32_t)(row_in_tile >> 6) * 8192u + (uint32_t)(row_in_tile & 63) * 128u;
+    const uint32_t row_sw = (uint32_t)(row_in_tile & 7);
+    uint8_t* dc_base = smem + kStages2 * kStageBytes2;
+    uint8_t* t_base = dc_base + kEpiBufs * kEpiBufBytes;
+
+    // Iterator over the sub-tiles this pair will process, in order (used for the D prefetch).
+    int pf_t = first_tile, pf_s = 0;
+    auto pf_valid = [&]() { return pf_t < p.total_tiles; };
+    auto pf_coords = [&](int& b, int& r0, int& c0) {
+      b = pf_t / p.tiles_per_mat;
+      const int2 tt = p.tiles[pf_t - b * p.tiles_per_mat];
+      r0 = tt.x * 256 + (int)cta * BM2;
+      c0 = tt.y * BN2 + pf_s * kSubCols;
+    };
+    auto pf_advance = [&]() {
+      const int b = pf_t / p.tiles_per_mat;
+      const int2 tt = p.tiles[pf_t - b * p.tiles_per_mat];
+      ++pf_s;
+      if (pf_s >= 4 || tt.y * BN2 + pf_s * kSubCols >= p.N) {
+        pf_s = 0;
+        pf_t += tile_step;
+      }
+    };
+    uint32_t d_issued = 0;  // D sub-tiles requested so far (elected thread)
+    auto issue_d = [&](uint32_t g) {
+      d_issued = g + 1;
+      int b, r0, c0;
+      pf_coords(b, r0, c0);
+      const uint32_t buf = g % kEpiBufs;
+      uint8_t* dst = dc_base + buf * kEpiBufBytes;
+      mbar_expect_tx(&dfull_bar[buf], kEpiBufBytes);
+      tma_load_3d(dst, &map_d, &dfull_bar[buf], c0, r0, b);
+      tma_load_3d(dst + 8192, &map_d, &dfull_bar[buf], c0, r0 + 64, b);
+    };
+    if (elected && has_d) {
+      for (uint32_t g0 = 0; g0 < 2 && pf_valid(); ++g0) {
+        issue_d(g0);
+        pf_advance();
+      }
+    }
+
     uint32_t aslot = 0, aphase = 0;
-    for (int t = first_tile; t < p.total_tiles; t += tile_step) {
+    uint32_t g = 0;  // running sub-tile count
+    bool ok = true;
+    for (int t = first_tile; t < p.total_tiles && ok; t += tile_step) {
       const int b = t / p.tiles_per_mat;
       const int2 tt = p.tiles[t - b * p.tiles_per_mat];
-      if (!mbar_wait_bounded(&tfull_bar[aslot], aphase)) {
-        if (lane == 0) atomicExch(p.status, kStatusTimeoutTmemFull);
-        break;
-      }
+      bool mine_ok = __all_sync(0xffffffffu, mbar_wait_bounded(&tfull_bar[aslot], aphase));
+      if (!mine_ok && lane == 0) atomicExch(p.status, kStatusTimeoutTmemFull);
       tc_fence_after();
       float sc = 1.f;
       if (p.scale != nullptr) sc = p.scale[b];
       const float alpha = p.alpha * ipow2(sc, p.alpha_pow);
       const float beta = p.beta * ipow2(sc, p.beta_pow);
-      const int r = tt.x * 256 + (int)cta * BM2 + row_in_tile;
-      const int warp_row0 = tt.x * 256 + (int)cta * BM2 + lane_grp * 32;
-      const bool row_ok = r < p.M;
-      const __nv_bfloat16* Drow =
-          p.D ? p.D + (long long)b * p.strideD + (long long)r * p.ldd : nullptr;
-      __nv_bfloat16* Cb = p.C + (long long)b * p.strideC;
-      __nv_bfloat16* Crow = Cb + (long long)r * p.ldc;
-      const bool vec_ok = ((p.ldc & 7) == 0) && ((p.strideC & 7) == 0) &&
-                          ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0);
-      const bool dvec_ok = p.D && ((p.ldd & 7) == 0) && ((p.strideD & 7) == 0) &&
-                           ((reinterpret_cast<uintptr_t>(p.D) & 15) == 0);
+      const int row0 = tt.x * 256 + (int)cta * BM2;
+      const bool mirror = p.sym && tt.y > tt.x;
+      int nsub = (p.N - tt.y * BN2 + kSubCols - 1) / kSubCols;
+      nsub = nsub > 4 ? 4 : nsub;
 #pragma unroll 1
-      for (int ch = 0; ch < BN2 / 32; ++ch) {
-        const int c0 = tt.y * BN2 + ch * 32;
-        if (c0 >= p.N) continue;
-        if (p.sym && c0 + 31 < warp_row0) continue;
-        float v[32];
-        tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(lane_grp * 32) << 16) + aslot * BN2 +
-                          ch * 32,
-                      v);
-        tmem_ld_wait();
-        if (!row_ok) continue;
-        if (p.D) {
-          if (dvec_ok && c0 + 32 <= p.N) {
-            const uint4* dp = reinterpret_cast<const uint4*>(Drow + c0);
+      for (int s = 0; s < nsub; ++s, ++g) {
+        const int c0 = tt.y * BN2 + s * kSubCols;
+        const uint32_t buf = g % kEpiBufs;
+        uint8_t* dc = dc_base + buf * kEpiBufBytes;
+        uint8_t* tb = t_base + buf * kEpiBufBytes;
+        if (has_d && mine_ok) {
+          mine_ok = __all_sync(0xffffffffu,
+                               mbar_wait_bounded(&dfull_bar[buf], (g / kEpiBufs) & 1));
+          if (!mine_ok && lane == 0) atomicExch(p.status, kStatusTimeoutFull);
+        }
+        if (mine_ok) {
+          float v[kSubCols];
+          const uint32_t taddr = tmem_base + (static_cast<uint32_t>(lane_grp * 32) << 16) +
+                                 aslot * BN2 + s * kSubCols;
+          tmem_ld_32x32(taddr, v);
+          tmem_ld_32x32(taddr + 32, v + 32);
+          tmem_ld_wait();
+          if (s == nsub - 1) {
+            // Last read of this accumulator: hand the TMEM slot back to the MMA thread.
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tempty_bar[aslot]), 0));
+          }
+          uint8_t* rowp = dc + row_off;
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              uint4 u = __ldg(dp + q);
+          for (int j = 0; j < kSubCols / 8; ++j) {
+            uint4* cell = reinterpret_cast<uint4*>(rowp + (((uint32_t)j ^ row_sw) << 4));
+            float* vj = v + j * 8;
+            if (has_d) {
+              const uint4 u = *cell;
               const uint32_t w[4] = {u.x, u.y, u.z, u.w};
 #pragma unroll
               for (int e = 0; e < 4; ++e) {
-                float2 f = unpack_bf16x2(w[e]);
-                v[q * 8 + e * 2] = alpha * v[q * 8 + e * 2] + beta * f.x;
-                v[q * 8 + e * 2 + 1] = alpha * v[q * 8 + e * 2 + 1] + beta * f.y;
+                const float2 f = unpack_bf16x2(w[e]);
+                vj[2 * e] = alpha * vj[2 * e] + beta * f.x;
+                vj[2 * e + 1] = alpha * vj[2 * e + 1] + beta * f.y;
+              }
+            } else {
+#pragma unroll
+              for (int e = 0; e < 8; ++e) vj[e] *= alpha;
+            }
+            uint32_t pk[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) pk[e] = pack_bf16x2(vj[2 * e], vj[2 * e + 1]);
+            *cell = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            if (mirror) {
+              // Transposed copy: element (row, c0 + c) goes to row c, column `row` of two
+              // 64 x 64 boxes (128-byte swizzled like every other buffer).
+              const uint32_t tcol = (uint32_t)(row_in_tile >> 6) * 8192u +
+                                    ((uint32_t)(row_in_tile & 7) << 1);
+              const uint32_t tchunk = (uint32_t)(row_in_tile & 63) >> 3;
+#pragma unroll
+              for (int e = 0; e < 8; ++e) {
+                const uint32_t c = (uint32_t)(j * 8 + e);
+                const uint32_t w = pk[e >> 1];
+                const uint16_t h = (e & 1) ? (uint16_t)(w >> 16) : (uint16_t)(w & 0xFFFF);
+                *reinterpret_cast<uint16_t*>(tb + tcol + c * 128u + ((tchunk ^ (c & 7)) << 4)) = h;
               }
             }
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const int c = c0 + j;
-              const float d = (c < p.N) ? __bfloat162float(Drow[c]) : 0.f;
-              v[j] = alpha * v[j] + beta * d;
-            }
           }
-        } else {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] *= alpha;
+          fence_proxy_async();
         }
-        uint32_t pk[16];
-#pragma unroll
-        for (int j = 0; j < 16; ++j) pk[j] = pack_bf16x2(v[2 * j], v[2 * j + 1]);
-        const bool full_chunk = (c0 + 32 <= p.N) && (!p.sym || c0 >= r);
-        if (vec_ok && full_chunk) {
-          uint4* cp = reinterpret_cast<uint4*>(Crow + c0);
-#pragma unroll
-          for (int q = 0; q < 4; ++q)
-            cp[q] = make_uint4(pk[q * 4], pk[q * 4 + 1], pk[q * 4 + 2], pk[q * 4 + 3]);
-        } else {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const int c = c0 + j;
-            if (c < p.N && (!p.sym || c >= r)) {
-              const uint32_t w = pk[j >> 1];
-              reinterpret_cast<uint16_t*>(Crow)[c] = (j & 1) ? (w >> 16) : (w & 0xFFFF);
-            }
+        // Every epilogue thread reaches this barrier (all waits above are bounded); it also
+        // tells whether any of them gave up.
+        ok = epi_barrier_and(mine_ok);
+        if (!ok) break;
+        if (elected) {
+          if (row0 < p.M) tma_store_3d(&map_c, dc, c0, row0, b);
+          if (row0 + 64 < p.M) tma_store_3d(&map_c, dc + 8192, c0, row0 + 64, b);
+          if (mirror) {
+            if (row0 < p.N) tma_store_3d(&map_c, tb, row0, c0, b);
+            if (row0 + 64 < p.N) tma_store_3d(&map_c, tb + 8192, row0 + 64, c0, b);
           }
-        }
-        if (p.sym) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const int c = c0 + j;
-            if (c > r && c < p.N) {
-              const uint32_t w = pk[j >> 1];
-              reinterpret_cast<uint16_t*>(Cb)[(long long)c * p.ldc + r] =
-                  (j & 1) ? (w >> 16) : (w & 0xFFFF);
-            }
+          bulk_commit_group();
+          // Once the stores have read their buffers, these are free for sub-tile g+2.
+          bulk_wait_group_read_all();
+          if (has_d && pf_valid()) {
+            issue_d(g + 2);
+            pf_advance();
           }
         }
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tempty_bar[aslot]), 0));
       aslot ^= 1;
       if (aslot == 0) aphase ^= 1;
+    }
+    if (elected) {
+      bulk_wait_group_all();
+      // After a timeout: let the D copies still in flight land before the CTA exits.
+      if (!ok)
+        for (uint32_t x = g; x < d_issued; ++x)
+          mbar_wait_bounded(&dfull_bar[x % kEpiBufs], (x / kEpiBufs) & 1);
     }
   }
 
@@ -424,12 +529,13 @@ static int make_map2(CUtensorMap* map, const void* ptr, int batch, int rows, int
   return r == CUDA_SUCCESS ? 0 : -2;
 }
 
-template <bool A_MN, bool B_MN>
-static int launch2(const CUtensorMap& ma, const CUtensorMap& mb, const Gemm2Args& args,
-                   cudaStream_t stream) {
+template <bool A_MN, bool B_MN, int STAGES>
+static int launch2(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc,
+                   const CUtensorMap& md, const Gemm2Args& args, cudaStream_t stream) {
   static bool configured = false;
   static int max_clusters = 0;
-  auto kernel = ns_gemm2_kernel<A_MN, B_MN>;
+  auto kernel = ns_gemm2_kernel<A_MN, B_MN, STAGES>;
+  constexpr int kDynBytes2 = dyn_bytes2(STAGES, STAGES == kStagesSym);
   if (!configured) {
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDynBytes2) !=
         cudaSuccess)
@@ -467,7 +573,7 @@ static int launch2(const CUtensorMap& ma, const CUtensorMap& mb, const Gemm2Args
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  if (cudaLaunchKernelEx(&cfg, kernel, ma, mb, args) != cudaSuccess) {
+  if (cudaLaunchKernelEx(&cfg, kernel, ma, mb, mc, md, args) != cudaSuccess) {
     cudaGetLastError();
     return -4;
   }
@@ -501,6 +607,14 @@ DION_EXPORT int dion_ns_gemm2(const void* A, long long lda, long long strideA, i
   } else {
     if (make_map2(&mb, B, batch, K, N, ldb, strideB, 64, BK2) != 0) return -13;
   }
+  // C leaves (and D arrives) through TMA in 64 x 64 boxes.
+  if ((ldc & 7) || (strideC & 7) || (reinterpret_cast<uintptr_t>(C) & 15)) return -11;
+  if (D && ((ldd & 7) || (strideD & 7) || (reinterpret_cast<uintptr_t>(D) & 15))) return -11;
+  CUtensorMap mc, md;
+  if (make_map2(&mc, C, batch, M, N, ldc, strideC, kSubCols, 64) != 0) return -14;
+  if (make_map2(&md, D ? D : C, batch, M, N, D ? ldd : ldc, D ? strideD : strideC, kSubCols,
+                64) != 0)
+    return -14;
   Gemm2Args a;
   a.batch = batch; a.M = M; a.N = N; a.K = K;
   a.D = static_cast<const __nv_bfloat16*>(D); a.ldd = ldd; a.strideD = strideD;
@@ -511,10 +625,19 @@ DION_EXPORT int dion_ns_gemm2(const void* A, long long lda, long long strideA, i
   a.total_tiles = tiles_per_mat * batch;
   a.status = status;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  switch ((a_mn ? 2 : 0) | (b_mn ? 1 : 0)) {
-    case 0: return launch2<false, false>(ma, mb, a, s);
-    case 1: return launch2<false, true>(ma, mb, a, s);
-    case 2: return launch2<true, false>(ma, mb, a, s);
-    default: return launch2<true, true>(ma, mb, a, s);
+  const int mode = (a_mn ? 2 : 0) | (b_mn ? 1 : 0);
+  if (sym) {
+    switch (mode) {
+      case 0: return launch2<false, false, kStagesSym>(ma, mb, mc, md, a, s);
+      case 1: return launch2<false, true, kStagesSym>(ma, mb, mc, md, a, s);
+      case 2: return launch2<true, false, kStagesSym>(ma, mb, mc, md, a, s);
+      default: return launch2<true, true, kStagesSym>(ma, mb, mc, md, a, s);
+    }
+  }
+  switch (mode) {
+    case 0: return launch2<false, false, kStagesPlain>(ma, mb, mc, md, a, s);
+    case 1: return launch2<false, true, kStagesPlain>(ma, mb, mc, md, a, s);
+    case 2: return launch2<true, false, kStagesPlain>(ma, mb, mc, md, a, s);
+    default: return launch2<true, true, kStagesPlain>(ma, mb, mc, md, a, s);
   }
 }

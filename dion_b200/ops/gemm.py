@@ -198,6 +198,10 @@ def ns_gemm(
     if pair is None:
         pair = pair_default() and bn is None and _pair_eligible(
             M, N, batch, extra, out_t, out_f32, out, dev)
+        # The two-CTA kernel moves C and D by TMA: 16-byte aligned bases, strides multiples of 8.
+        for t3, ld_, bs_ in ((C3, ldc, sc), (D3, ldd, sd)):
+            if t3 is not None and (t3.data_ptr() % 16 or ld_ % 8 or bs_ % 8):
+                pair = False
     if pair:
         if extra is not None or out_t is not None or out_f32 is not None:
             raise ValueError("the two-CTA kernel has no transposed/fp32/cross-GPU outputs")
