@@ -41,6 +41,9 @@ def parse() -> argparse.Namespace:
     p.add_argument("--optimizer", type=str, default="dion2",
                    choices=["dion2", "muon", "normuon", "nordion2", "dion"])
     p.add_argument("--no-e2e", action="store_true")
+    p.add_argument("--eager", action="store_true",
+                   help="ours: launch every kernel from Python (torch DDP for N>1) instead of "
+                        "replaying the whole step as one CUDA graph")
     return p.parse_args()
 
 
@@ -216,8 +219,15 @@ def run_ours(args) -> None:
     torch.manual_seed(0)
     model = GPT(GPTConfig(**MODEL)).to(device)
     model.init_weights()
-    call = DDP(model, device_ids=[local_rank]) if world > 1 else model
-    pg = call.process_group if world > 1 else None
+    graphed = not args.eager
+    if graphed:
+        # Same seed on every rank, so the replicas start identical; gradients are averaged by
+        # the step object's own bucketed all-reduce.
+        call = model
+        pg = dist.group.WORLD if world > 1 else None
+    else:
+        call = DDP(model, device_ids=[local_rank]) if world > 1 else model
+        pg = call.process_group if world > 1 else None
 
     groups = [dict(params=list(model.transformer.h.parameters())),
               dict(params=list(model.transformer.wte.parameters()), algorithm="adamw", lr=LR,
@@ -246,30 +256,57 @@ def run_ours(args) -> None:
     dev_batches = [h.to(device) for h in host]
     state = {"i": 0, "loss": None}
 
-    def step_device():
-        xy = dev_batches[state["i"] % len(dev_batches)]
-        state["i"] += 1
-        with autocast:
-            loss = call(xy[0], xy[1])
-        loss.backward()
-        opt.step()
-        call.zero_grad(set_to_none=True)
-        state["loss"] = loss.detach()
+    if graphed:
+        from dion_b200.parallel.graph_step import GraphedTrainStep
 
-    def step_e2e():
-        xy = host[state["i"] % len(host)].to(device, non_blocking=True)
-        state["i"] += 1
-        with autocast:
-            loss = call(xy[0], xy[1])
-        loss.backward()
-        opt.step()
-        call.zero_grad(set_to_none=True)
-        state["loss_host"] = loss.item()
+        gstep = GraphedTrainStep(lambda x, y: model(x, y), list(model.parameters()), opt,
+                                 [dev_batches[0][0], dev_batches[0][1]], device=device,
+                                 process_group=pg, warmup=2)
+        # Prime: two eager steps, then the capture; count the kernels one replay launches.
+        for i in range(2):
+            gstep(dev_batches[i][0], dev_batches[i][1])
+        _backend.reset_launch_count()
+        gstep(dev_batches[2][0], dev_batches[2][1])
+        launches_per_step = _backend.launch_count()
+        torch.cuda.synchronize()
+
+        def step_device():
+            xy = dev_batches[state["i"] % len(dev_batches)]
+            state["i"] += 1
+            state["loss"] = gstep(xy[0], xy[1])
+
+        def step_e2e():
+            xy = host[state["i"] % len(host)]
+            state["i"] += 1
+            state["loss_host"] = gstep(xy[0], xy[1]).item()
+    else:
+        launches_per_step = None
+
+        def step_device():
+            xy = dev_batches[state["i"] % len(dev_batches)]
+            state["i"] += 1
+            with autocast:
+                loss = call(xy[0], xy[1])
+            loss.backward()
+            opt.step()
+            call.zero_grad(set_to_none=True)
+            state["loss"] = loss.detach()
+
+        def step_e2e():
+            xy = host[state["i"] % len(host)].to(device, non_blocking=True)
+            state["i"] += 1
+            with autocast:
+                loss = call(xy[0], xy[1])
+            loss.backward()
+            opt.step()
+            call.zero_grad(set_to_none=True)
+            state["loss_host"] = loss.item()
 
     sampler = ClockSampler(local_rank) if rank == 0 else None
     ms, clocks = time_loop(step_device, args.steps, args.warmup, world, device, sampler,
                            on_start=_backend.reset_launch_count)
-    launches = _backend.launch_count()
+    launches = (_backend.launch_count() if launches_per_step is None
+                else launches_per_step * args.steps)
     from dion_b200.ops.gemm import check_status
 
     check_status()
@@ -278,7 +315,12 @@ def run_ours(args) -> None:
         e2e_ms, _ = time_loop(step_e2e, args.steps, 2, world, device, None)
     if rank == 0:
         emit(args, "ours", ms, e2e_ms, clocks, launches, world,
-             {"final_loss": float(state["loss"].item())})
+             {"final_loss": float(state["loss"].item()),
+              "launch_mode": "one CUDA graph per step (forward, backward, gradient all-reduce, "
+                             "optimizer); gpu_launches counts the kernels of this package "
+                             "recorded in the graph x steps" if graphed else "eager"})
+    if graphed:
+        gstep.release()
     if world > 1:
         dist.destroy_process_group()
 
@@ -357,25 +399,51 @@ def run_reference(args) -> None:
     dev_batches = [h.to(device) for h in host]
     state = {"i": 0, "loss": None}
 
-    def step_device():
-        xy = dev_batches[state["i"] % len(dev_batches)]
-        state["i"] += 1
-        with autocast:
-            loss = call(xy[0], xy[1])
-        loss.backward()
-        opt.step()
-        call.zero_grad(set_to_none=True)
-        state["loss"] = loss.detach()
+    if graphed:
+        from dion_b200.parallel.graph_step import GraphedTrainStep
 
-    def step_e2e():
-        xy = host[state["i"] % len(host)].to(device, non_blocking=True)
-        state["i"] += 1
-        with autocast:
-            loss = call(xy[0], xy[1])
-        loss.backward()
-        opt.step()
-        call.zero_grad(set_to_none=True)
-        state["loss_host"] = loss.item()
+        gstep = GraphedTrainStep(lambda x, y: model(x, y), list(model.parameters()), opt,
+                                 [dev_batches[0][0], dev_batches[0][1]], device=device,
+                                 process_group=pg, warmup=2)
+        # Prime: two eager steps, then the capture; count the kernels one replay launches.
+        for i in range(2):
+            gstep(dev_batches[i][0], dev_batches[i][1])
+        _backend.reset_launch_count()
+        gstep(dev_batches[2][0], dev_batches[2][1])
+        launches_per_step = _backend.launch_count()
+        torch.cuda.synchronize()
+
+        def step_device():
+            xy = dev_batches[state["i"] % len(dev_batches)]
+            state["i"] += 1
+            state["loss"] = gstep(xy[0], xy[1])
+
+        def step_e2e():
+            xy = host[state["i"] % len(host)]
+            state["i"] += 1
+            state["loss_host"] = gstep(xy[0], xy[1]).item()
+    else:
+        launches_per_step = None
+
+        def step_device():
+            xy = dev_batches[state["i"] % len(dev_batches)]
+            state["i"] += 1
+            with autocast:
+                loss = call(xy[0], xy[1])
+            loss.backward()
+            opt.step()
+            call.zero_grad(set_to_none=True)
+            state["loss"] = loss.detach()
+
+        def step_e2e():
+            xy = host[state["i"] % len(host)].to(device, non_blocking=True)
+            state["i"] += 1
+            with autocast:
+                loss = call(xy[0], xy[1])
+            loss.backward()
+            opt.step()
+            call.zero_grad(set_to_none=True)
+            state["loss_host"] = loss.item()
 
     try:
         step_device()  # first call compiles / autotunes; failures here fall back to eager

@@ -217,6 +217,79 @@ def rope_qknorm(q: Tensor, k: Tensor, cos: Tensor, sin: Tensor) -> Tuple[Tensor,
     return tF.rms_norm(q, (D,)), tF.rms_norm(k, (D,))
 
 
+class _QKVRope(torch.autograd.Function):
+    """``q, k, v = h W_q^T, h W_k^T, h W_v^T`` as ONE GEMM against the stacked weight, followed by
+    rotary embedding and RMS-norm of q and k.  The three weights stay separate parameters (the
+    optimizers orthogonalize them as separate matrices, as the reference model's c_q / c_k / c_v
+    are, models/gpt_model.py:60-63); only the arithmetic is fused: one forward GEMM, one
+    input-gradient GEMM over K = 3C with no summation of three partial gradients, and one
+    weight-gradient GEMM written directly in the parameters' dtype."""
+
+    @staticmethod
+    def forward(ctx, h: Tensor, wq: Tensor, wk: Tensor, wv: Tensor, cos: Tensor, sin: Tensor,
+                n_head: int, eps: float):
+        B, T, C = h.shape
+        D = C // n_head
+        h2 = h.reshape(B * T, C)
+        W = torch.empty((3 * C, C), dtype=h.dtype, device=h.device)
+        W[:C].copy_(wq)
+        W[C:2 * C].copy_(wk)
+        W[2 * C:].copy_(wv)
+        qkv = torch.mm(h2, W.t())                       # [B*T, 3C]
+        q = qkv[:, :C]
+        k = qkv[:, C:2 * C]
+        qo = torch.empty((B, T, n_head, D), dtype=h.dtype, device=h.device)
+        ko = torch.empty_like(qo)
+        rstd = torch.empty((2, B * T * n_head), dtype=torch.float32, device=h.device)
+        _check(_lib().dion_rope_qknorm_fwd(_c(q), _c(k), ctypes.c_longlong(3 * C), _c(cos),
+                                           _c(sin), _c(qo), _c(ko), _c(rstd), B, T, n_head, D,
+                                           ctypes.c_float(eps), _stream(h.device)),
+               "dion_rope_qknorm_fwd")
+        ctx.save_for_backward(h2, W, qkv, cos, sin, rstd)
+        ctx.dims = (B, T, C, n_head, D)
+        ctx.wdtype = wq.dtype
+        v = qkv.view(B, T, 3, n_head, D)[:, :, 2]
+        return qo, ko, v
+
+    @staticmethod
+    def backward(ctx, dqo: Tensor, dko: Tensor, dv: Tensor):
+        h2, W, qkv, cos, sin, rstd = ctx.saved_tensors
+        B, T, C, H, D = ctx.dims
+        dqkv = torch.empty_like(qkv)
+        dqo, dko = dqo.contiguous(), dko.contiguous()
+        _check(_lib().dion_rope_qknorm_bwd(_c(qkv[:, :C]), _c(qkv[:, C:2 * C]),
+                                           ctypes.c_longlong(3 * C), _c(cos), _c(sin), _c(dqo),
+                                           _c(dko), _c(rstd), _c(dqkv[:, :C]),
+                                           _c(dqkv[:, C:2 * C]), ctypes.c_longlong(3 * C),
+                                           B, T, H, D, _stream(h2.device)),
+               "dion_rope_qknorm_bwd")
+        dqkv.view(B, T, 3, H, D)[:, :, 2].copy_(dv)
+        dh = torch.mm(dqkv, W).view(B, T, C)
+        if ctx.wdtype == torch.float32 and dqkv.dtype == torch.bfloat16:
+            dW = torch.mm(dqkv.t(), h2, out_dtype=torch.float32)
+        else:
+            dW = torch.mm(dqkv.t(), h2).to(ctx.wdtype)
+        return dh, dW[:C], dW[C:2 * C], dW[2 * C:], None, None, None, None
+
+
+def qkv_rope(h: Tensor, wq: Tensor, wk: Tensor, wv: Tensor, cos: Tensor, sin: Tensor,
+             n_head: int) -> Tuple[Tensor, Tensor, Tensor]:
+    """``(q, k, v)`` of shape ``[B, T, H, D]`` from the normalized hidden state ``h [B, T, C]``:
+    the three projections, rotary embedding and QK RMS-norm (q and k are contiguous, v is a
+    strided view of the projection output)."""
+    B, T, C = h.shape
+    D = C // n_head
+    if (h.is_cuda and h.dtype == torch.bfloat16 and D in (32, 64, 128, 256) and C % 8 == 0
+            and cos.dtype == torch.bfloat16 and cos.is_contiguous() and sin.is_contiguous()
+            and wq.shape == wk.shape == wv.shape == (C, C)):
+        return _QKVRope.apply(h, wq, wk, wv, cos, sin, n_head, _eps_for(torch.bfloat16))
+    q = tF.linear(h, wq).view(B, T, n_head, D)
+    k = tF.linear(h, wk).view(B, T, n_head, D)
+    v = tF.linear(h, wv).view(B, T, n_head, D)
+    q, k = rope_qknorm(q, k, cos, sin)
+    return q, k, v
+
+
 # ------------------------------------------------------------------------------------------------
 # ReLU^2
 # ------------------------------------------------------------------------------------------------

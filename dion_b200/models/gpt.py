@@ -83,11 +83,10 @@ class CausalSelfAttention(nn.Module):
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         B, T, _ = x.size()
-        q = self.c_q(x).view(B, T, self.n_head, self.head_dim)
-        k = self.c_k(x).view(B, T, self.n_head, self.head_dim)
-        v = self.c_v(x).view(B, T, self.n_head, self.head_dim)
-        cos, sin = self.rotary(q)
-        q, k = Fn.rope_qknorm(q, k, cos, sin)  # rotary embedding, then RMS-norm over head_dim
+        cos, sin = self.rotary(x)
+        # q/k/v projections (one GEMM), rotary embedding, then RMS-norm over head_dim
+        q, k, v = Fn.qkv_rope(x, self.c_q.weight, self.c_k.weight, self.c_v.weight, cos, sin,
+                              self.n_head)
         y = tF.scaled_dot_product_attention(
             q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), is_causal=True)
         y = y.transpose(1, 2).contiguous().view(B, T, -1)

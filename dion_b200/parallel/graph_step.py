@@ -1,0 +1,220 @@
+"""Whole training step as one CUDA graph, with a capturable data-parallel gradient all-reduce.
+
+A small model's step is hundreds of short kernels; launched one by one from Python the GPU idles
+between them.  :class:`GraphedTrainStep` records forward, backward, the gradient all-reduce and
+the optimizer step once and replays the recording, so a step costs one launch on the host.  The
+optimizers of this package are built for that: they read the learning rate from device tensors,
+keep their counters on the device and never synchronize with the host (the per-optimizer variant
+is ``dion_b200.optim.cuda_graph.CudaGraphOptimizer``, the counterpart of dion/cuda_graph.py in
+the reference, which captures ``optimizer.step()`` only).
+
+:class:`BucketedGradSync` is the data-parallel piece: post-accumulate hooks launch one coalesced
+NCCL all-reduce per bucket on a side stream as soon as the bucket's last gradient exists, so the
+reduction overlaps the rest of backward.  It works eagerly and under stream capture (the side
+stream is forked from and joined to the capturing stream with events), which the hook machinery
+of ``torch.nn.parallel.DistributedDataParallel`` does not.
+"""
+from __future__ import annotations
+
+import contextlib
+from typing import Callable, Dict, List, Optional, Sequence
+
+import torch
+import torch.distributed as dist
+from torch import Tensor
+
+
+class BucketedGradSync:
+    """Average gradients over ``process_group`` in buckets, overlapped with backward.
+
+    Parameters are bucketed in reverse registration order (the order in which backward produces
+    their gradients).  ``finish()`` must be called after ``backward()``: it joins the side stream
+    and re-arms the buckets."""
+
+    def __init__(self, params: Sequence[Tensor], process_group=None, bucket_mb: float = 64.0):
+        self.pg = process_group
+        self.world = dist.get_world_size(process_group) if dist.is_initialized() else 1
+        self.params = [p for p in params if p.requires_grad]
+        self.buckets: List[List[Tensor]] = []
+        limit = int(bucket_mb * (1 << 20))
+        cur: List[Tensor] = []
+        size = 0
+        for p in reversed(self.params):
+            cur.append(p)
+            size += p.numel() * p.element_size()
+            if size >= limit:
+                self.buckets.append(cur)
+                cur, size = [], 0
+        if cur:
+            self.buckets.append(cur)
+        self._bucket_of: Dict[Tensor, int] = {}
+        for bi, bucket in enumerate(self.buckets):
+            for p in bucket:
+                self._bucket_of[p] = bi
+        self._pending = [len(b) for b in self.buckets]
+        self._launched = [False] * len(self.buckets)
+        self._stream: Optional[torch.cuda.Stream] = None
+        self._handles = []
+        self.enabled = self.world > 1
+        if self.enabled:
+            for p in self.params:
+                self._handles.append(p.register_post_accumulate_grad_hook(self._on_grad))
+
+    def remove(self) -> None:
+        for h in self._handles:
+            h.remove()
+        self._handles = []
+
+    # ----------------------------------------------------------------------------------------
+    def _on_grad(self, p: Tensor) -> None:
+        bi = self._bucket_of[p]
+        self._pending[bi] -= 1
+        if self._pending[bi] == 0:
+            self._reduce_bucket(bi)
+
+    def _reduce_bucket(self, bi: int) -> None:
+        grads = [p.grad for p in self.buckets[bi] if p.grad is not None]
+        self._launched[bi] = True
+        if not grads:
+            return
+        if grads[0].is_cuda:
+            if self._stream is None:
+                self._stream = torch.cuda.Stream(device=grads[0].device)
+            # Fork: the side stream starts after everything recorded so far on this stream.
+            self._stream.wait_stream(torch.cuda.current_stream(grads[0].device))
+            with torch.cuda.stream(self._stream):
+                self._all_reduce(grads)
+        else:
+            self._all_reduce(grads)
+
+    def _all_reduce(self, grads: List[Tensor]) -> None:
+        nccl = grads[0].is_cuda
+        op = dist.ReduceOp.AVG if nccl else dist.ReduceOp.SUM
+        manager = getattr(dist, "_coalescing_manager", None)
+        if nccl and manager is not None:
+            with manager(group=self.pg, async_ops=False):
+                for g in grads:
+                    dist.all_reduce(g, op=op, group=self.pg)
+        else:
+            for g in grads:
+                dist.all_reduce(g, op=op, group=self.pg)
+        if not nccl:
+            torch._foreach_div_(grads, float(self.world))
+
+    def finish(self) -> None:
+        """Join the reductions into the current stream; reduce buckets whose parameters did not
+        all receive a gradient this step; re-arm."""
+        if not self.enabled:
+            return
+        for bi in range(len(self.buckets)):
+            if not self._launched[bi]:
+                self._reduce_bucket(bi)
+        if self._stream is not None:
+            torch.cuda.current_stream(self._stream.device).wait_stream(self._stream)
+        self._pending = [len(b) for b in self.buckets]
+        self._launched = [False] * len(self.buckets)
+
+
+class GraphedTrainStep:
+    """``loss = step(*inputs)`` runs ``loss_fn(*inputs)`` under autocast, ``backward()``, the
+    gradient all-reduce (when ``process_group`` spans more than one rank) and
+    ``optimizer.step()``.  The first ``warmup`` calls run eagerly on a side stream, the next one
+    is captured, later ones replay the graph.  Inputs are copied into static buffers (so they may
+    be pinned host tensors: the copy is the host-to-device transfer); the returned loss is a
+    static device tensor that the next call overwrites.
+
+    ``use_graph=False`` keeps the same step eager (for debugging and as the fallback on CPU).
+    """
+
+    def __init__(self, loss_fn: Callable[..., Tensor], params: Sequence[Tensor],
+                 optimizer: torch.optim.Optimizer, example_inputs: Sequence[Tensor], *,
+                 device: torch.device, process_group=None,
+                 autocast_dtype: Optional[torch.dtype] = torch.bfloat16,
+                 warmup: int = 3, use_graph: bool = True, bucket_mb: float = 64.0):
+        self.loss_fn = loss_fn
+        self.params = [p for p in params]
+        self.optimizer = optimizer
+        self.device = device
+        self.autocast_dtype = autocast_dtype
+        self.warmup = max(1, warmup)
+        self.use_graph = use_graph and device.type == "cuda"
+        self.sync = BucketedGradSync(self.params, process_group, bucket_mb)
+        self.static_inputs = [torch.empty(t.shape, dtype=t.dtype, device=device)
+                              for t in example_inputs]
+        self.static_loss: Optional[Tensor] = None
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self._calls = 0
+        self._side: Optional[torch.cuda.Stream] = None
+
+    # ----------------------------------------------------------------------------------------
+    def _autocast(self):
+        if self.autocast_dtype is None:
+            return contextlib.nullcontext()
+        return torch.autocast(device_type=self.device.type, dtype=self.autocast_dtype)
+
+    def _one_step(self) -> Tensor:
+        with self._autocast():
+            loss = self.loss_fn(*self.static_inputs)
+        loss.backward()
+        self.sync.finish()
+        self.optimizer.step()
+        # Gradients are dropped, not zeroed: under capture the next backward re-creates them in
+        # the graph's private pool at the same addresses.
+        for p in self.params:
+            p.grad = None
+        return loss.detach()
+
+    def _load_inputs(self, inputs: Sequence[Tensor]) -> None:
+        assert len(inputs) == len(self.static_inputs)
+        for dst, src in zip(self.static_inputs, inputs):
+            dst.copy_(src, non_blocking=True)
+
+    def _pre_replay(self) -> None:
+        sync = getattr(self.optimizer, "_sync_hyperparam_tensors", None)
+        if sync is not None:
+            sync()
+
+    def _post_replay(self) -> None:
+        advance = getattr(self.optimizer, "_advance_host_step_counters", None)
+        if advance is not None:
+            advance()
+
+    def __call__(self, *inputs: Tensor) -> Tensor:
+        self._load_inputs(inputs)
+        self._calls += 1
+        if not self.use_graph:
+            self.static_loss = self._one_step()
+            return self.static_loss
+        if self.graph is not None:
+            self._pre_replay()
+            self.graph.replay()
+            self._post_replay()
+            return self.static_loss
+        cur = torch.cuda.current_stream(self.device)
+        if self._calls <= self.warmup:
+            # Eager warm-up on a side stream (allocates optimizer state, workspaces, caches).
+            if self._side is None:
+                self._side = torch.cuda.Stream(device=self.device)
+            self._side.wait_stream(cur)
+            with torch.cuda.stream(self._side):
+                loss = self._one_step()
+            cur.wait_stream(self._side)
+            self.static_loss = loss
+            return loss
+        self._pre_replay()
+        torch.cuda.synchronize(self.device)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            loss = self._one_step()
+        self.graph, self.static_loss = graph, loss
+        graph.replay()
+        self._post_replay()
+        return self.static_loss
+
+    def release(self) -> None:
+        """Drop the graph (before ``destroy_process_group()`` when it holds collectives)."""
+        graph, self.graph = self.graph, None
+        if graph is not None:
+            torch.cuda.synchronize(self.device)
+            graph.reset()
+        self.sync.remove()

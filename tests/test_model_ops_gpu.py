@@ -60,6 +60,42 @@ def test_rope_qknorm(D):
     assert (k.grad.float() - kr.grad).abs().max().item() < 5e-2
 
 
+def test_qkv_rope_matches_unfused():
+    """Fused projection + RoPE + QK-norm against the three separate linears in fp32."""
+    torch.manual_seed(0)
+    B, T, H, D = 2, 48, 4, 64
+    C = H * D
+    h = (torch.randn(B, T, C, device="cuda") * 0.5).bfloat16().requires_grad_()
+    ws = [(torch.randn(C, C, device="cuda") * C ** -0.5).requires_grad_() for _ in range(3)]
+    inv = 1.0 / (10000 ** (torch.arange(0, D, 2, device="cuda").float() / D))
+    fr = torch.outer(torch.arange(T, device="cuda").float(), inv)
+    cos, sin = fr.cos().bfloat16(), fr.sin().bfloat16()
+    q, k, v = Fn.qkv_rope(h, ws[0], ws[1], ws[2], cos, sin, H)
+    assert q.shape == k.shape == v.shape == (B, T, H, D)
+    gq, gk, gv = (torch.randn(B, T, H, D, device="cuda") for _ in range(3))
+    (q.float() * gq + k.float() * gk + v.float() * gv).sum().backward()
+
+    hr = h.detach().float().requires_grad_()
+    wr = [w.detach().bfloat16().float().requires_grad_() for w in ws]
+
+    def rope_norm(x):
+        d = D // 2
+        c, s = cos.float()[None, :, None, :], sin.float()[None, :, None, :]
+        y = torch.cat([x[..., :d] * c + x[..., d:] * s, x[..., d:] * c - x[..., :d] * s], 3)
+        return tF.rms_norm(y, (D,), eps=torch.finfo(torch.bfloat16).eps)
+
+    qr = rope_norm((hr @ wr[0].T).view(B, T, H, D))
+    kr = rope_norm((hr @ wr[1].T).view(B, T, H, D))
+    vr = (hr @ wr[2].T).view(B, T, H, D)
+    (qr * gq + kr * gk + vr * gv).sum().backward()
+    for got, ref in ((q, qr), (k, kr), (v, vr)):
+        assert (got.float() - ref).abs().max().item() < 5e-2
+    assert (h.grad.float() - hr.grad).abs().max().item() < 0.05 * hr.grad.abs().max().item() + 5e-2
+    for w, r in zip(ws, wr):
+        assert w.grad.dtype == torch.float32
+        assert (w.grad - r.grad).abs().max().item() < 0.03 * r.grad.abs().max().item() + 5e-2
+
+
 def test_relu2():
     x = torch.randn(16, 3072, device="cuda").bfloat16().requires_grad_()
     xr = x.detach().float().requires_grad_()
