@@ -195,12 +195,15 @@ rope_qknorm_bwd_kernel(const __nv_bfloat16* Q, const __nv_bfloat16* K, long long
                        const __nv_bfloat16* COS, const __nv_bfloat16* SIN,
                        const __nv_bfloat16* DQO, const __nv_bfloat16* DKO, const float* rstd,
                        __nv_bfloat16* DQ, __nv_bfloat16* DK, long long out_row_stride,
+                       const __nv_bfloat16* DVI, __nv_bfloat16* DVO,
                        long long n_vec, int T, int H) {
   constexpr int HALF = D / 2, TPV = D / 16;
   const long long gid = (long long)blockIdx.x * 256 + threadIdx.x;
   const long long w_raw = gid / TPV;
   const int sub = (int)(gid % TPV);
   const bool valid = w_raw < 2 * n_vec;  // no early exit: the shuffles below need whole warps
+  // Optional third section: copy the gradient of v (dense) beside dq and dk (strided rows).
+  const bool is_v = DVI != nullptr && w_raw >= 2 * n_vec && w_raw < 3 * n_vec;
   const long long w = valid ? w_raw : 0;
   const bool is_k = w >= n_vec;
   const long long vec = is_k ? w - n_vec : w;
@@ -227,6 +230,16 @@ rope_qknorm_bwd_kernel(const __nv_bfloat16* Q, const __nv_bfloat16* K, long long
   }
 #pragma unroll
   for (int o = TPV / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+  if (is_v) {
+    const long long vv = w_raw - 2 * n_vec;
+    const long long vbt = vv / H;
+    const int vh = (int)(vv - vbt * H);
+    const uint4* src = reinterpret_cast<const uint4*>(DVI + vv * D);
+    uint4* dst = reinterpret_cast<uint4*>(DVO + vbt * out_row_stride + (long long)vh * D);
+    dst[sub] = src[sub];
+    dst[HALF / 8 + sub] = src[HALF / 8 + sub];
+    return;
+  }
   if (!valid) return;
   dot = dot * r / (float)D;
   float o1[8], o2[8];
@@ -239,6 +252,32 @@ rope_qknorm_bwd_kernel(const __nv_bfloat16* Q, const __nv_bfloat16* K, long long
   }
   store8(dx, DT_BF16, sub * 8, o1);
   store8(dx, DT_BF16, HALF + sub * 8, o2);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Embedding backward.  `sorted` holds the token ids in ascending order and `perm` the position
+// each came from; the block at the first position of a run of equal ids sums the run's rows of
+// DY in fp32 (in position order, so the result is deterministic) and writes the row of GW.
+// Rows of GW whose id does not occur are not touched (the caller zero-fills).
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(128)
+embedding_bwd_kernel(const long long* __restrict__ sorted, const long long* __restrict__ perm,
+                     const void* __restrict__ DY, int dy_dt, float* __restrict__ GW, long long n,
+                     int C, long long V) {
+  const long long i = blockIdx.x;
+  const long long tok = sorted[i];
+  if (tok < 0 || tok >= V) return;
+  if (i > 0 && sorted[i - 1] == tok) return;
+  for (int c8 = threadIdx.x; c8 < C / 8; c8 += 128) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (long long j = i; j < n && sorted[j] == tok; ++j) {
+      float v[8];
+      load8(DY, dy_dt, perm[j] * C + c8 * 8, v);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] += v[e];
+    }
+    store8(GW, DT_F32, tok * C + c8 * 8, acc);
+  }
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -436,18 +475,30 @@ DION_EXPORT int dion_rope_qknorm_fwd(const void* Q, const void* K, long long in_
 DION_EXPORT int dion_rope_qknorm_bwd(const void* Q, const void* K, long long in_row_stride,
                                      const void* COS, const void* SIN, const void* DQO,
                                      const void* DKO, const float* rstd, void* DQ, void* DK,
-                                     long long out_row_stride, int B, int T, int H, int D,
-                                     void* stream) {
+                                     long long out_row_stride, const void* DVI, void* DVO,
+                                     int B, int T, int H, int D, void* stream) {
   const long long n_vec = (long long)B * T * H;
   if (n_vec <= 0) return 0;
   if (in_row_stride % 8 || out_row_stride % 8) return -2;
-  const long long threads = 2 * n_vec * (D / 16);
+  if (DVI != nullptr && ((reinterpret_cast<uintptr_t>(DVI) | reinterpret_cast<uintptr_t>(DVO)) & 15))
+    return -2;
+  const long long threads = (DVI != nullptr ? 3 : 2) * n_vec * (D / 16);
   const unsigned grid = (unsigned)((threads + 255) / 256);
   typedef const __nv_bfloat16* CP;
   typedef __nv_bfloat16* P;
   DION_ROPE_DISPATCH(D, (rope_qknorm_bwd_kernel<DD><<<grid, 256, 0, S(stream)>>>(
                             (CP)Q, (CP)K, in_row_stride, (CP)COS, (CP)SIN, (CP)DQO, (CP)DKO, rstd,
-                            (P)DQ, (P)DK, out_row_stride, n_vec, T, H)))
+                            (P)DQ, (P)DK, out_row_stride, (CP)DVI, (P)DVO, n_vec, T, H)))
+  return rc();
+}
+
+DION_EXPORT int dion_embedding_bwd(const void* sorted, const void* perm, const void* DY, int dy_dt,
+                                   float* GW, long long n, int C, long long V, void* stream) {
+  if (n <= 0) return 0;
+  if (C % 8) return -2;
+  embedding_bwd_kernel<<<(unsigned)n, 128, 0, S(stream)>>>(
+      static_cast<const long long*>(sorted), static_cast<const long long*>(perm), DY, dy_dt, GW,
+      n, C, V);
   return rc();
 }
 

@@ -200,8 +200,8 @@ class _RopeQKNorm(torch.autograd.Function):
         dk = torch.empty_like(dq)
         _check(_lib().dion_rope_qknorm_bwd(_c(q), _c(k), ctypes.c_longlong(ctx.rs), _c(cos),
                                            _c(sin), _c(dqo), _c(dko), _c(rstd), _c(dq), _c(dk),
-                                           ctypes.c_longlong(H * D), B, T, H, D,
-                                           _stream(q.device)), "dion_rope_qknorm_bwd")
+                                           ctypes.c_longlong(H * D), _c(None), _c(None),
+                                           B, T, H, D, _stream(q.device)), "dion_rope_qknorm_bwd")
         return dq, dk, None, None, None
 
 
@@ -256,14 +256,15 @@ class _QKVRope(torch.autograd.Function):
         h2, W, qkv, cos, sin, rstd = ctx.saved_tensors
         B, T, C, H, D = ctx.dims
         dqkv = torch.empty_like(qkv)
-        dqo, dko = dqo.contiguous(), dko.contiguous()
+        dqo, dko, dv = dqo.contiguous(), dko.contiguous(), dv.contiguous()
+        # One kernel: RoPE/QK-norm backward into the q and k columns, dv copied into the v columns.
         _check(_lib().dion_rope_qknorm_bwd(_c(qkv[:, :C]), _c(qkv[:, C:2 * C]),
                                            ctypes.c_longlong(3 * C), _c(cos), _c(sin), _c(dqo),
                                            _c(dko), _c(rstd), _c(dqkv[:, :C]),
                                            _c(dqkv[:, C:2 * C]), ctypes.c_longlong(3 * C),
+                                           _c(dv), _c(dqkv[:, 2 * C:]),
                                            B, T, H, D, _stream(h2.device)),
                "dion_rope_qknorm_bwd")
-        dqkv.view(B, T, 3, H, D)[:, :, 2].copy_(dv)
         dh = torch.mm(dqkv, W).view(B, T, C)
         if ctx.wdtype == torch.float32 and dqkv.dtype == torch.bfloat16:
             dW = torch.mm(dqkv.t(), h2, out_dtype=torch.float32)
@@ -288,6 +289,74 @@ def qkv_rope(h: Tensor, wq: Tensor, wk: Tensor, wv: Tensor, cos: Tensor, sin: Te
     v = tF.linear(h, wv).view(B, T, n_head, D)
     q, k = rope_qknorm(q, k, cos, sin)
     return q, k, v
+
+
+# ------------------------------------------------------------------------------------------------
+# Embedding and linear layers with mixed-precision-aware backward passes
+# ------------------------------------------------------------------------------------------------
+class _Embedding(torch.autograd.Function):
+    """``weight[idx]`` whose backward sorts the token ids once and sums the rows of each id in a
+    single kernel (deterministic; replaces the several passes of the stock dense backward)."""
+
+    @staticmethod
+    def forward(ctx, idx: Tensor, weight: Tensor):
+        ctx.save_for_backward(idx)
+        ctx.wshape = weight.shape
+        return tF.embedding(idx, weight)
+
+    @staticmethod
+    def backward(ctx, dy: Tensor):
+        (idx,) = ctx.saved_tensors
+        V, C = ctx.wshape
+        flat = idx.reshape(-1)
+        sorted_idx, perm = torch.sort(flat, stable=True)
+        dy2 = dy.reshape(-1, C)
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        gw = torch.zeros((V, C), dtype=torch.float32, device=dy.device)
+        _check(_lib().dion_embedding_bwd(_c(sorted_idx), _c(perm), _c(dy2), _DT[dy2.dtype], _c(gw),
+                                         ctypes.c_longlong(flat.numel()), C, ctypes.c_longlong(V),
+                                         _stream(dy.device)), "dion_embedding_bwd")
+        return None, gw
+
+
+def embedding(idx: Tensor, weight: Tensor) -> Tensor:
+    if (weight.is_cuda and weight.dtype == torch.float32 and weight.size(1) % 8 == 0
+            and idx.dtype == torch.int64 and weight.requires_grad and torch.is_grad_enabled()):
+        return _Embedding.apply(idx, weight)
+    return tF.embedding(idx, weight)
+
+
+class _LinearBF16(torch.autograd.Function):
+    """``x @ W^T`` in bf16 for an fp32 master weight: the weight gradient is accumulated in fp32
+    by the GEMM itself (no bf16 round trip and no cast kernel)."""
+
+    @staticmethod
+    def forward(ctx, x: Tensor, weight: Tensor):
+        wb = weight.to(torch.bfloat16)
+        x2 = x.reshape(-1, x.size(-1))
+        ctx.save_for_backward(x2, wb)
+        ctx.xshape = x.shape
+        ctx.wdtype = weight.dtype
+        return torch.mm(x2, wb.t()).view(*x.shape[:-1], weight.size(0))
+
+    @staticmethod
+    def backward(ctx, dy: Tensor):
+        x2, wb = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.size(-1))
+        dx = torch.mm(dy2, wb).view(ctx.xshape) if ctx.needs_input_grad[0] else None
+        dw = torch.mm(dy2.t(), x2, out_dtype=torch.float32)
+        return dx, dw if ctx.wdtype == torch.float32 else dw.to(ctx.wdtype)
+
+
+def linear(x: Tensor, weight: Tensor) -> Tensor:
+    """Bias-free linear layer.  Under bf16 autocast on a GPU (bf16 activations, fp32 weight) the
+    mixed-precision form above is used; otherwise ``torch.nn.functional.linear``."""
+    if (x.is_cuda and x.dtype == torch.bfloat16 and weight.dtype == torch.float32
+            and type(weight) in (Tensor, torch.nn.Parameter) and x.size(-1) % 8 == 0
+            and weight.size(0) % 8 == 0):
+        return _LinearBF16.apply(x, weight)
+    return tF.linear(x, weight)
 
 
 # ------------------------------------------------------------------------------------------------

@@ -69,6 +69,21 @@ def apply_rotary_emb(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> t
     return torch.cat([x1 * c + x2 * s, x2 * c - x1 * s], 3).type_as(x)
 
 
+def _is_plain(module: nn.Module) -> bool:
+    """True when ``module`` can be bypassed by a functional call on its weight: the weight is an
+    ordinary tensor (not a DTensor shard) and nothing hooks the module's forward (tensor
+    parallelism redistributes activations in such hooks)."""
+    w = module.weight
+    return (type(w) in (torch.Tensor, nn.Parameter) and not module._forward_hooks
+            and not module._forward_pre_hooks)
+
+
+def _linear(module: nn.Linear, x: torch.Tensor) -> torch.Tensor:
+    if module.bias is None and _is_plain(module):
+        return Fn.linear(x, module.weight)
+    return module(x)
+
+
 class CausalSelfAttention(nn.Module):
     def __init__(self, config: GPTConfig):
         super().__init__()
@@ -84,13 +99,19 @@ class CausalSelfAttention(nn.Module):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         B, T, _ = x.size()
         cos, sin = self.rotary(x)
-        # q/k/v projections (one GEMM), rotary embedding, then RMS-norm over head_dim
-        q, k, v = Fn.qkv_rope(x, self.c_q.weight, self.c_k.weight, self.c_v.weight, cos, sin,
-                              self.n_head)
+        if _is_plain(self.c_q) and _is_plain(self.c_k) and _is_plain(self.c_v):
+            # q/k/v projections (one GEMM), rotary embedding, then RMS-norm over head_dim
+            q, k, v = Fn.qkv_rope(x, self.c_q.weight, self.c_k.weight, self.c_v.weight, cos, sin,
+                                  self.n_head)
+        else:
+            q = self.c_q(x).view(B, T, -1, self.head_dim)
+            k = self.c_k(x).view(B, T, -1, self.head_dim)
+            v = self.c_v(x).view(B, T, -1, self.head_dim)
+            q, k = Fn.rope_qknorm(q, k, cos, sin)
         y = tF.scaled_dot_product_attention(
             q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), is_causal=True)
         y = y.transpose(1, 2).contiguous().view(B, T, -1)
-        return self.c_proj(y)
+        return _linear(self.c_proj, y)
 
 
 class MLP(nn.Module):
@@ -100,7 +121,7 @@ class MLP(nn.Module):
         self.c_proj = nn.Linear(4 * config.n_embd, config.n_embd, bias=False)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return self.c_proj(Fn.relu2(self.c_fc(x)))
+        return _linear(self.c_proj, Fn.relu2(_linear(self.c_fc, x)))
 
 
 class Block(nn.Module):
@@ -147,13 +168,14 @@ class GPT(nn.Module):
 
     def forward(self, idx: torch.Tensor, targets: Optional[torch.Tensor] = None,
                 return_logits: bool = False):
-        x = self.transformer.wte(idx)
+        wte = self.transformer.wte
+        x = Fn.embedding(idx, wte.weight) if _is_plain(wte) else wte(idx)
         h = None
         for block in self.transformer.h:
             x, h = block(x, h)
         x = h if h is not None else Fn.rms_norm(x)  # final norm rides on the last residual add
         if targets is not None:
-            logits = self.lm_head(x)
+            logits = _linear(self.lm_head, x)
             if return_logits:
                 return logits.float()
             return Fn.cross_entropy(logits.view(-1, logits.size(-1)), targets.view(-1),

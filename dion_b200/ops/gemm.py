@@ -137,7 +137,7 @@ def _pair_eligible(M: int, N: int, batch: int, extra, out_t, out_f32, out, devic
     tiles fill the pairs of SMs about as well as 128 x 256 tiles fill single SMs."""
     if extra is not None or out_t is not None or out_f32 is not None:
         return False
-    if M < 256 or N < 256:
+    if M <= 128 or N <= 128:
         return False
     pairs = sm_count(device) // 2
     tiles2 = -(-M // 256) * -(-N // 256) * batch

@@ -83,7 +83,7 @@ def test_rejects_unaligned():
 # ---- two-CTA (cta_group::2) kernel -----------------------------------------------------------
 
 @pytest.mark.parametrize("shape", [(1, 256, 256, 64), (3, 328, 456, 200), (4, 768, 768, 768),
-                                   (2, 512, 1024, 2048)])
+                                   (2, 512, 1024, 2048), (5, 192, 192, 768), (2, 136, 200, 72)])
 def test_pair_nt(shape):
     from dion_b200.ops import gemm
     b, M, N, K = shape
@@ -96,7 +96,8 @@ def test_pair_nt(shape):
     assert _rel_err(C, A.float() @ B.float().mT) < 1e-2
 
 
-@pytest.mark.parametrize("shape", [(1, 256, 256, 64), (2, 768, 3072, 768), (3, 328, 456, 200)])
+@pytest.mark.parametrize("shape", [(1, 256, 256, 64), (2, 768, 3072, 768), (3, 328, 456, 200),
+                                   (3, 192, 768, 192)])
 def test_pair_nn_with_epilogue(shape):
     from dion_b200.ops import gemm
     b, M, N, K = shape
@@ -113,7 +114,7 @@ def test_pair_nn_with_epilogue(shape):
     assert _rel_err(C, ref) < 1e-2
 
 
-@pytest.mark.parametrize("shape", [(2, 768, 3072), (3, 328, 136), (1, 1024, 512)])
+@pytest.mark.parametrize("shape", [(2, 768, 3072), (3, 328, 136), (1, 1024, 512), (4, 192, 768)])
 def test_pair_symmetric(shape):
     from dion_b200.ops import gemm
     b, M, K = shape

@@ -96,6 +96,38 @@ def test_qkv_rope_matches_unfused():
         assert (w.grad - r.grad).abs().max().item() < 0.03 * r.grad.abs().max().item() + 5e-2
 
 
+def test_embedding_backward_matches_torch():
+    torch.manual_seed(0)
+    V, C = 1000, 64
+    w = torch.randn(V, C, device="cuda", requires_grad=True)
+    wr = w.detach().clone().requires_grad_()
+    idx = torch.randint(0, 50, (4, 200), device="cuda")  # many repeated ids
+    idx[0, 0] = V - 1
+    g = torch.randn(4, 200, C, device="cuda")
+    Fn.embedding(idx, w).backward(g)
+    tF.embedding(idx, wr).backward(g)
+    assert torch.allclose(w.grad, wr.grad, atol=1e-4, rtol=1e-5)
+    assert w.grad[60:V - 1].abs().max().item() == 0.0
+
+
+def test_linear_bf16_fp32_weight_grad():
+    torch.manual_seed(0)
+    x = torch.randn(3, 40, 256, device="cuda").bfloat16().requires_grad_()
+    w = (torch.randn(128, 256, device="cuda") * 0.05).requires_grad_()
+    y = Fn.linear(x, w)
+    assert y.dtype == torch.bfloat16 and y.shape == (3, 40, 128)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr = x.detach().float().requires_grad_()
+    wr = w.detach().bfloat16().float().requires_grad_()
+    yr = xr @ wr.T
+    yr.backward(g.float())
+    assert w.grad.dtype == torch.float32
+    assert (y.float() - yr).abs().max().item() < 5e-2
+    assert (w.grad - wr.grad).abs().max().item() < 1e-2 * wr.grad.abs().max().item() + 1e-3
+    assert (x.grad.float() - xr.grad).abs().max().item() < 5e-2
+
+
 def test_relu2():
     x = torch.randn(16, 3072, device="cuda").bfloat16().requires_grad_()
     xr = x.detach().float().requires_grad_()
