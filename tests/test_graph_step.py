@@ -105,3 +105,42 @@ def test_graphed_step_matches_eager(name):
     assert losses[True][0] == pytest.approx(losses[False][0], rel=1e-5)
     for a, b in zip(losses[True], losses[False]):
         assert a == pytest.approx(b, rel=2e-2, abs=2e-2)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name", ["muon", "dion2"])
+def test_cuda_graph_optimizer_matches_eager(name):
+    """Captured ``optimizer.step()`` (warm-up, capture, replay) against the eager optimizer."""
+    import dion_b200
+    from dion_b200.optim.cuda_graph import CudaGraphOptimizer
+    from dion_b200.ops.gemm import check_status
+
+    def run(graphed):
+        torch.manual_seed(0)
+        mats = [torch.nn.Parameter(torch.randn(256, 128, device="cuda") * 0.1) for _ in range(4)]
+        vecs = [torch.nn.Parameter(torch.randn(128, device="cuda"))]
+        groups = [dict(params=mats), dict(params=vecs, algorithm="adamw", lr=0.01)]
+        if name == "muon":
+            opt = dion_b200.Muon(groups, lr=0.02, mu=0.9, weight_decay=0.01)
+        else:
+            opt = dion_b200.Dion2(groups, lr=0.02, fraction=0.5, ef_decay=0.9, weight_decay=0.01)
+        stepper = CudaGraphOptimizer(opt, warmup_steps=2) if graphed else opt
+        sched = torch.optim.lr_scheduler.LambdaLR(opt, lambda s: 1.0 / (1 + s))
+        g = torch.Generator(device="cuda").manual_seed(1)
+        for p in mats + vecs:
+            p.grad = torch.zeros_like(p)
+        for _ in range(6):
+            for p in mats + vecs:
+                p.grad.copy_(torch.randn(p.shape, device="cuda", generator=g))
+            stepper.step()
+            sched.step()
+        torch.cuda.synchronize()
+        check_status()
+        if graphed:
+            assert stepper._graph is not None
+            stepper.release()
+        return [p.detach().clone() for p in mats + vecs]
+
+    eager, graphed = run(False), run(True)
+    for a, b in zip(eager, graphed):
+        assert torch.allclose(a, b, atol=1e-5, rtol=1e-4)
