@@ -10,10 +10,16 @@
 // (cp.async.bulk.tensor with .cta_group::2 so that both CTAs' transfers complete on the leader's
 // barrier; no multicast).  The leader CTA's MMA thread issues the instructions for the pair and
 // releases stages / publishes accumulators in both CTAs with a cluster-multicast tcgen05.commit.
-// Each CTA drains its own half (128 TMEM lanes) of the accumulator in its epilogue warps.
+// Each CTA drains its own half (128 TMEM lanes) of the accumulator in its epilogue warps, 64 columns
+// at a time through shared memory: D arrives by TMA (prefetched two sub-tiles ahead), each thread
+// combines its row in place in the 128-byte-swizzled buffer, and the buffer leaves by TMA store.
+// In symmetric mode only tiles on or above the diagonal are computed; an off-diagonal tile also
+// writes a transposed copy of each sub-tile that a second TMA store places at the mirrored
+// position, so both halves of the output are written with full-width bursts.
 //
-// Operand layouts, symmetric half-compute with mirrored stores and the epilogue arithmetic are the
-// same as in the single-CTA kernel.  All waits are bounded.
+// Operand layouts and the epilogue arithmetic are the same as in the single-CTA kernel.  All waits
+// are bounded; the epilogue threads meet at a barrier that also ANDs their wait results, so a
+// timeout makes all of them leave together.
 #include "common.cuh"
 
 namespace dion {
