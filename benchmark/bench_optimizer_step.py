@@ -43,7 +43,7 @@ def ns_flops(shapes, fraction=1.0, iters=5) -> float:
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--model", default="1b", choices=list(MODELS))
-    ap.add_argument("--optimizer", default="muon", choices=["muon", "normuon", "dion2", "nordion2"])
+    ap.add_argument("--optimizer", default="muon", choices=["muon", "normuon", "dion2", "nordion2", "dion"])
     ap.add_argument("--mode", default="fsdp", choices=["fsdp", "ddp", "single"])
     ap.add_argument("--impl", default="ours", choices=["ours", "ours_nccl", "reference"])
     ap.add_argument("--steps", type=int, default=10)
@@ -115,6 +115,11 @@ def main() -> None:
         if ref:
             kw["triton_post_ortho"] = True
         opt = pkg.Dion2([dict(params=params)], distributed_mesh=dmesh, lr=0.02, fraction=0.25, **kw)
+    elif name == "dion":
+        # Legacy low-rank Dion (rank fraction 0.25); replicated over the ranks in ddp mode.
+        fraction = 0.0
+        dkw = dict(replicate_mesh=pg, replicate_mesh_grad_sync=False) if world > 1 else {}
+        opt = pkg.Dion([dict(params=params)], lr=0.02, rank_fraction=0.25, **dkw)
     else:
         fraction = 0.25
         if ref:

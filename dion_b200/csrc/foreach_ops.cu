@@ -440,24 +440,60 @@ dion2_post_kernel(const long long* raw, const Dion2PostArgs a) {
   float cb = lr * a.ratio;
   if (a.normU2) cb *= sqrtf(a.normU2[tt]) / fmaxf(sqrtf(a.normNew2[tt]), 1e-8f);
   const bool vx = aligned4(X, a.x_dt);
+  const bool vu = aligned4(U, DT_BF16);
+  // With a row length that is a multiple of 4 every 4-element group lies in one row: one
+  // division and one map lookup per group, and U is read 4 wide.
+  const bool row_groups = (a.cols & 3) == 0;
+  const bool vmap = (reinterpret_cast<uintptr_t>(map) & 15) == 0;
   DION_CHUNK_LOOP(tb, {
     float x[4];
     if (full) ld4(X, a.x_dt, i, vx, x);
     else for (int k = 0; k < 4; ++k) x[k] = (i + k < end) ? ld(X, a.x_dt, i + k) : 0.f;
-#pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      const long long e = i + k;
-      if (e >= end) break;
-      const int r = (int)(e / a.cols), c = (int)(e - (long long)r * a.cols);
-      float u = 0.f;
+    if (row_groups && full) {
+      const int r = (int)(i / a.cols), c = (int)(i - (long long)r * a.cols);
+      float u[4] = {0.f, 0.f, 0.f, 0.f};
       if (a.select_rows) {
         const int j = map[r];
-        if (j >= 0) { u = __bfloat162float(U[(long long)j * a.cols + c]); if (rs) u *= rs[j]; }
+        if (j >= 0) {
+          ld4(U, DT_BF16, (long long)j * a.cols + c, vu, u);
+          if (rs) {
+            const float s = rs[j];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) u[k] *= s;
+          }
+        }
       } else {
-        const int j = map[c];
-        if (j >= 0) u = __bfloat162float(U[(long long)r * a.k + j]);
+        int js[4];
+        if (vmap) {
+          const int4 jj = *reinterpret_cast<const int4*>(map + c);
+          js[0] = jj.x; js[1] = jj.y; js[2] = jj.z; js[3] = jj.w;
+        } else {
+#pragma unroll
+          for (int k = 0; k < 4; ++k) js[k] = map[c + k];
+        }
+        const __nv_bfloat16* urow = U + (long long)r * a.k;
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          if (js[k] >= 0) u[k] = __bfloat162float(urow[js[k]]);
       }
-      x[k] = ca * x[k] - cb * u;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) x[k] = ca * x[k] - cb * u[k];
+    } else {
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const long long e = i + k;
+        if (e >= end) break;
+        const int r = (int)(e / a.cols), c = (int)(e - (long long)r * a.cols);
+        float u = 0.f;
+        if (a.select_rows) {
+          const int j = map[r];
+          if (j >= 0) { u = __bfloat162float(U[(long long)j * a.cols + c]); if (rs) u *= rs[j]; }
+        } else {
+          const int j = map[c];
+          if (j >= 0) u = __bfloat162float(U[(long long)r * a.k + j]);
+        }
+        x[k] = ca * x[k] - cb * u;
+      }
     }
     if (full) st4(X, a.x_dt, i, vx, x);
     else for (int k = 0; k < 4 && i + k < end; ++k) st(X, a.x_dt, i + k, x[k]);

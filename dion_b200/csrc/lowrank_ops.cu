@@ -1,0 +1,275 @@
+// Batched dense factorizations for Dion's randomized Cholesky-QR (fp32, sm_100a):
+//
+//   dion_qr_r_factor   : R (upper triangular, r x r) of a batch of k x r matrices, k >= r,
+//                        by Householder reflections;
+//   dion_cholesky_upper: upper Cholesky factor of a batch of r x r symmetric matrices.
+//
+// They stand in for the per-matrix cuSOLVER calls behind torch.linalg.qr / cholesky_ex in the
+// reference's orthogonalize() (dion/dion.py:1265-1308), which run one matrix after the other.
+// Here one CTA owns one matrix and all matrices of a batch run at once.  A warp owns one column
+// and keeps it in registers (rows lane, lane+32, ...).  Columns are processed in panels of 16:
+// a panel's columns first receive every earlier panel's transformations (no synchronization,
+// the earlier reflectors / factor columns are read back from global memory through L1), then the
+// panel is factored column by column, each finished column being handed to the later warps of the
+// panel through shared memory.
+#include "common.cuh"
+
+namespace dion {
+
+constexpr int kLrThreads = 512;
+constexpr int kPanel = kLrThreads / 32;   // 16 columns per panel
+constexpr int kTilePitch = kPanel + 1;
+
+__device__ __forceinline__ float warp_sum_f(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// Shared memory: tile[k][17] staging of a 16-column block | vs[2][k] published column.
+template <int KPL>
+__global__ void __launch_bounds__(kLrThreads)
+qr_r_kernel(const float* __restrict__ A, float* V, float* tau_g, float* __restrict__ R, int k,
+            int r) {
+  extern __shared__ float lr_smem[];
+  float* tile = lr_smem;
+  float* vs = lr_smem + (size_t)k * kTilePitch;
+  __shared__ float tau_s[2];
+  const int n = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const float* An = A + (size_t)n * k * r;
+  float* Vn = V + (size_t)n * r * k;
+  float* tn = tau_g + (size_t)n * r;
+  float* Rn = R + (size_t)n * r * r;
+
+  for (int c0 = 0; c0 < r; c0 += kPanel) {
+    const int c = c0 + warp;
+    const bool active = c < r;
+    // Stage the block of columns [c0, c0+16) with row-contiguous reads.
+    for (int e = threadIdx.x; e < k * kPanel; e += kLrThreads) {
+      const int i = e / kPanel, cc = e - i * kPanel;
+      tile[i * kTilePitch + cc] = (c0 + cc < r) ? An[(size_t)i * r + c0 + cc] : 0.f;
+    }
+    __syncthreads();
+    float x[KPL];
+#pragma unroll
+    for (int t = 0; t < KPL; ++t) {
+      const int i = lane + 32 * t;
+      x[t] = (i < k) ? tile[i * kTilePitch + warp] : 0.f;
+    }
+    // Reflectors of earlier panels.
+    if (active) {
+      for (int j = 0; j < c0; ++j) {
+        const float* vj = Vn + (size_t)j * k;
+        float v[KPL];
+        float dot = 0.f;
+#pragma unroll
+        for (int t = 0; t < KPL; ++t) {
+          const int i = lane + 32 * t;
+          v[t] = (i < k) ? vj[i] : 0.f;
+          dot += v[t] * x[t];
+        }
+        dot = warp_sum_f(dot) * tn[j];
+#pragma unroll
+        for (int t = 0; t < KPL; ++t) x[t] -= dot * v[t];
+      }
+    }
+    // Factor the panel.
+    for (int jj = 0; jj < kPanel; ++jj) {
+      const int cj = c0 + jj;
+      if (cj >= r) break;  // uniform over the block
+      float* vbuf = vs + (size_t)(jj & 1) * k;
+      if (warp == jj) {
+        float nrm2 = 0.f, xd = 0.f;
+#pragma unroll
+        for (int t = 0; t < KPL; ++t) {
+          const int i = lane + 32 * t;
+          if (i >= cj && i < k) nrm2 += x[t] * x[t];
+          if (i == cj) xd = x[t];
+        }
+        nrm2 = warp_sum_f(nrm2);
+        xd = warp_sum_f(xd);  // only one lane contributed
+        const float nrm = sqrtf(nrm2);
+        const float alpha = (xd >= 0.f) ? -nrm : nrm;
+        const float vd = xd - alpha;
+        const float vtv = nrm2 - xd * xd + vd * vd;
+        const float tau = (vtv > 0.f) ? 2.f / vtv : 0.f;
+#pragma unroll
+        for (int t = 0; t < KPL; ++t) {
+          const int i = lane + 32 * t;
+          if (i < k) {
+            const float vi = (i < cj) ? 0.f : (i == cj ? vd : x[t]);
+            vbuf[i] = vi;
+            Vn[(size_t)cj * k + i] = vi;
+            if (i == cj) x[t] = alpha;
+            else if (i > cj) x[t] = 0.f;
+          }
+        }
+        if (lane == 0) {
+          tau_s[jj & 1] = tau;
+          tn[cj] = tau;
+        }
+      }
+      __syncthreads();
+      if (warp > jj && active) {
+        const float tau = tau_s[jj & 1];
+        float v[KPL];
+        float dot = 0.f;
+#pragma unroll
+        for (int t = 0; t < KPL; ++t) {
+          const int i = lane + 32 * t;
+          v[t] = (i < k) ? vbuf[i] : 0.f;
+          dot += v[t] * x[t];
+        }
+        dot = warp_sum_f(dot) * tau;
+#pragma unroll
+        for (int t = 0; t < KPL; ++t) x[t] -= dot * v[t];
+      }
+      // vbuf alternates, and the warp that writes it next has passed the barrier above after
+      // every reader of the previous use: one barrier per column is enough.
+    }
+    // The later panels read this panel's reflectors from global memory.
+    __threadfence_block();
+    __syncthreads();
+    // Write the finished columns of R (rows <= column index) through the staging tile.
+#pragma unroll
+    for (int t = 0; t < KPL; ++t) {
+      const int i = lane + 32 * t;
+      if (i < k) tile[i * kTilePitch + warp] = x[t];
+    }
+    __syncthreads();
+    const int rows_out = min(r, c0 + kPanel);
+    for (int e = threadIdx.x; e < rows_out * kPanel; e += kLrThreads) {
+      const int i = e / kPanel, cc = e - i * kPanel;
+      if (c0 + cc < r) Rn[(size_t)i * r + c0 + cc] = (i <= c0 + cc) ? tile[i * kTilePitch + cc] : 0.f;
+    }
+    // Rows below the panel's last column are zero in R.
+    for (int e = threadIdx.x; e < (r - rows_out) * kPanel; e += kLrThreads) {
+      const int i = rows_out + e / kPanel, cc = e % kPanel;
+      if (c0 + cc < r) Rn[(size_t)i * r + c0 + cc] = 0.f;
+    }
+    __syncthreads();
+  }
+}
+
+// Upper Cholesky factor U (G = U^T U).  Row j of U is column j of the lower factor, so the rows
+// already written to U serve as the earlier columns.  A non-positive pivot yields NaNs in the
+// rest of that matrix (as LAPACK's info > 0 would signal); the caller screens for NaNs.
+template <int KPL>
+__global__ void __launch_bounds__(kLrThreads)
+cholesky_upper_kernel(const float* __restrict__ G, float* U, int r) {
+  extern __shared__ float lr_smem[];
+  float* vs = lr_smem;  // [2][r]
+  const int n = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const float* Gn = G + (size_t)n * r * r;
+  float* Un = U + (size_t)n * r * r;
+  for (int c0 = 0; c0 < r; c0 += kPanel) {
+    const int c = c0 + warp;
+    const bool active = c < r;
+    float x[KPL];
+    // Column c of the symmetric input equals its row c: contiguous reads.
+#pragma unroll
+    for (int t = 0; t < KPL; ++t) {
+      const int i = lane + 32 * t;
+      x[t] = (active && i < r && i >= c) ? Gn[(size_t)c * r + i] : 0.f;
+    }
+    if (active) {
+      for (int j = 0; j < c0; ++j) {
+        const float* lj = Un + (size_t)j * r;
+        const float ljc = lj[c];
+#pragma unroll
+        for (int t = 0; t < KPL; ++t) {
+          const int i = lane + 32 * t;
+          if (i < r && i >= c) x[t] -= lj[i] * ljc;
+        }
+      }
+    }
+    for (int jj = 0; jj < kPanel; ++jj) {
+      const int cj = c0 + jj;
+      if (cj >= r) break;
+      float* vbuf = vs + (size_t)(jj & 1) * r;
+      if (warp == jj) {
+        float d = 0.f;
+#pragma unroll
+        for (int t = 0; t < KPL; ++t)
+          if (lane + 32 * t == cj) d = x[t];
+        d = warp_sum_f(d);
+        const float piv = sqrtf(d);  // NaN for a negative pivot
+        const float inv = 1.f / piv;
+#pragma unroll
+        for (int t = 0; t < KPL; ++t) {
+          const int i = lane + 32 * t;
+          if (i < r) {
+            const float li = (i < cj) ? 0.f : (i == cj ? piv : x[t] * inv);
+            vbuf[i] = li;
+            Un[(size_t)cj * r + i] = li;
+          }
+        }
+      }
+      __syncthreads();
+      if (warp > jj && active) {
+        const float ljc = vbuf[c];
+#pragma unroll
+        for (int t = 0; t < KPL; ++t) {
+          const int i = lane + 32 * t;
+          if (i < r && i >= c) x[t] -= vbuf[i] * ljc;
+        }
+      }
+    }
+    __threadfence_block();
+    __syncthreads();
+  }
+}
+
+}  // namespace dion
+
+using namespace dion;
+static inline cudaStream_t S(void* s) { return static_cast<cudaStream_t>(s); }
+
+template <int KPL>
+static int launch_qr(const float* A, float* V, float* tau, float* R, int n, int k, int r,
+                     cudaStream_t s) {
+  const size_t smem = ((size_t)k * kTilePitch + 2 * (size_t)k) * sizeof(float);
+  if (cudaFuncSetAttribute(qr_r_kernel<KPL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           (int)smem) != cudaSuccess)
+    return -3;
+  qr_r_kernel<KPL><<<n, kLrThreads, smem, s>>>(A, V, tau, R, k, r);
+  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+// A: [n][k][r] fp32 (dense).  V: scratch [n][r][k], tau: scratch [n][r], R: out [n][r][r].
+// Limits: r <= k <= 1024.
+DION_EXPORT int dion_qr_r_factor(const void* A, void* V, void* tau, void* R, int n, int k, int r,
+                                 void* stream) {
+  if (n <= 0 || r <= 0) return 0;
+  if (k < r || k > 1024) return -2;
+  const float* a = static_cast<const float*>(A);
+  float* v = static_cast<float*>(V);
+  float* t = static_cast<float*>(tau);
+  float* rr = static_cast<float*>(R);
+  if (k <= 256) return launch_qr<8>(a, v, t, rr, n, k, r, S(stream));
+  if (k <= 512) return launch_qr<16>(a, v, t, rr, n, k, r, S(stream));
+  if (k <= 768) return launch_qr<24>(a, v, t, rr, n, k, r, S(stream));
+  return launch_qr<32>(a, v, t, rr, n, k, r, S(stream));
+}
+
+template <int KPL>
+static int launch_chol(const float* G, float* U, int n, int r, cudaStream_t s) {
+  const size_t smem = 2 * (size_t)r * sizeof(float);
+  cholesky_upper_kernel<KPL><<<n, kLrThreads, smem, s>>>(G, U, r);
+  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+// G: [n][r][r] fp32 symmetric (only the upper triangle of each row is read), U: out [n][r][r].
+// Limit: r <= 1024.
+DION_EXPORT int dion_cholesky_upper(const void* G, void* U, int n, int r, void* stream) {
+  if (n <= 0 || r <= 0) return 0;
+  if (r > 1024) return -2;
+  const float* g = static_cast<const float*>(G);
+  float* u = static_cast<float*>(U);
+  if (r <= 256) return launch_chol<8>(g, u, n, r, S(stream));
+  if (r <= 512) return launch_chol<16>(g, u, n, r, S(stream));
+  if (r <= 768) return launch_chol<24>(g, u, n, r, S(stream));
+  return launch_chol<32>(g, u, n, r, S(stream));
+}

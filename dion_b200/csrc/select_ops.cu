@@ -27,8 +27,37 @@ __device__ __forceinline__ float rnd(float v, int dt) {
   return dt == DT_F32 ? v : __bfloat162float(__float2bfloat16_rn(v));
 }
 
+// 8 consecutive elements as floats / back (16-byte accesses for bf16, 2 x 16 for fp32).
+__device__ __forceinline__ void ld8v(const void* p, int dt, long long i, float (&v)[8]) {
+  if (dt == DT_F32) {
+    const float4* q = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p) + i);
+    const float4 a = q[0], b = q[1];
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+  } else {
+    const uint4 u = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p) + i);
+    const float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z),
+                 d = unpack_bf16x2(u.w);
+    v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y; v[4] = c.x; v[5] = c.y; v[6] = d.x; v[7] = d.y;
+  }
+}
+__device__ __forceinline__ void st8v(void* p, int dt, long long i, const float (&v)[8]) {
+  if (dt == DT_F32) {
+    float4* q = reinterpret_cast<float4*>(reinterpret_cast<float*>(p) + i);
+    q[0] = make_float4(v[0], v[1], v[2], v[3]);
+    q[1] = make_float4(v[4], v[5], v[6], v[7]);
+  } else {
+    *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p) + i) =
+        make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]),
+                   pack_bf16x2(v[6], v[7]));
+  }
+}
+__device__ __forceinline__ bool aligned16(const void* p) {
+  return (reinterpret_cast<uintptr_t>(p) & 15) == 0;
+}
+
 // ptrs: device array [2][n] of int64 = G pointers (may be 0) then M pointers.
-// Row selection: one warp per row.
+// Row selection: one warp per row; 8 elements per lane per step when the row length is a
+// multiple of 8 and the buffers are 16-byte aligned.
 __global__ void __launch_bounds__(256)
 row_norms_kernel(const long long* ptrs, int n, int rows, int cols, int g_dt, int m_dt,
                  float* norms) {
@@ -40,13 +69,29 @@ row_norms_kernel(const long long* ptrs, int n, int rows, int cols, int g_dt, int
   void* M = reinterpret_cast<void*>(ptrs[n + t]);
   const long long off = (long long)r * cols;
   float s = 0.f;
-  for (int c = lane; c < cols; c += 32) {
-    float m = ldv(M, m_dt, off + c);
-    if (G) {
-      m = rnd(m + rnd(ldv(G, g_dt, off + c), m_dt), m_dt);
-      stv(M, m_dt, off + c, m);
+  if ((cols & 7) == 0 && aligned16(M) && (G == nullptr || aligned16(G))) {
+    for (int c = lane * 8; c < cols; c += 256) {
+      float m[8];
+      ld8v(M, m_dt, off + c, m);
+      if (G) {
+        float g[8];
+        ld8v(G, g_dt, off + c, g);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) m[e] = rnd(m[e] + rnd(g[e], m_dt), m_dt);
+        st8v(M, m_dt, off + c, m);
+      }
+#pragma unroll
+      for (int e = 0; e < 8; ++e) s += fabsf(m[e]);
     }
-    s += fabsf(m);
+  } else {
+    for (int c = lane; c < cols; c += 32) {
+      float m = ldv(M, m_dt, off + c);
+      if (G) {
+        m = rnd(m + rnd(ldv(G, g_dt, off + c), m_dt), m_dt);
+        stv(M, m_dt, off + c, m);
+      }
+      s += fabsf(m);
+    }
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
@@ -78,6 +123,61 @@ col_norms_kernel(const long long* ptrs, int n, int rows, int cols, int g_dt, int
     s += fabsf(m);
   }
   atomicAdd(&norms[(long long)t * cols + c], s);
+}
+
+// Same for row lengths that are multiples of 8 and 16-byte aligned buffers: a thread owns 8
+// adjacent columns; 256 threads = 32 column groups (256 columns) x 8 row lanes; the row lanes
+// are combined in shared memory before one atomic per column.
+__global__ void __launch_bounds__(256)
+col_norms_vec_kernel(const long long* ptrs, int n, int rows, int cols, int g_dt, int m_dt,
+                     float* norms) {
+  __shared__ float part[8][256 + 8];
+  const int t = blockIdx.z;
+  const int cg = threadIdx.x & 31, rlane = threadIdx.x >> 5;
+  const int c = blockIdx.x * 256 + cg * 8;
+  const int r0 = blockIdx.y * kColStrip;
+  const int r1 = min(rows, r0 + kColStrip);
+  const void* G = reinterpret_cast<const void*>(ptrs[t]);
+  void* M = reinterpret_cast<void*>(ptrs[n + t]);
+  float s[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  const bool vec = aligned16(M) && (G == nullptr || aligned16(G));
+  if (c < cols) {
+    for (int r = r0 + rlane; r < r1; r += 8) {
+      const long long e = (long long)r * cols + c;
+      float m[8];
+      if (vec) {
+        ld8v(M, m_dt, e, m);
+        if (G) {
+          float g[8];
+          ld8v(G, g_dt, e, g);
+#pragma unroll
+          for (int q = 0; q < 8; ++q) m[q] = rnd(m[q] + rnd(g[q], m_dt), m_dt);
+          st8v(M, m_dt, e, m);
+        }
+      } else {  // a matrix that starts off a 16-byte boundary
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          m[q] = ldv(M, m_dt, e + q);
+          if (G) {
+            m[q] = rnd(m[q] + rnd(ldv(G, g_dt, e + q), m_dt), m_dt);
+            stv(M, m_dt, e + q, m[q]);
+          }
+        }
+      }
+#pragma unroll
+      for (int q = 0; q < 8; ++q) s[q] += fabsf(m[q]);
+    }
+  }
+#pragma unroll
+  for (int q = 0; q < 8; ++q) part[rlane][cg * 8 + q] = s[q];
+  __syncthreads();
+  const int col = blockIdx.x * 256 + threadIdx.x;
+  if (col < cols) {
+    float tot = 0.f;
+#pragma unroll
+    for (int l = 0; l < 8; ++l) tot += part[l][threadIdx.x];
+    atomicAdd(&norms[(long long)t * cols + col], tot);
+  }
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -261,9 +361,15 @@ DION_EXPORT int dion_slice_norms(const void* ptrs, int n, int rows, int cols, in
     row_norms_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, S(stream)>>>(
         static_cast<const long long*>(ptrs), n, rows, cols, g_dt, m_dt, norms);
   } else {
-    dim3 grid((cols + 63) / 64, (rows + kColStrip - 1) / kColStrip, n);
-    col_norms_kernel<<<grid, 256, 0, S(stream)>>>(static_cast<const long long*>(ptrs), n, rows,
-                                                  cols, g_dt, m_dt, norms);
+    if ((cols & 7) == 0) {
+      dim3 grid((cols + 255) / 256, (rows + kColStrip - 1) / kColStrip, n);
+      col_norms_vec_kernel<<<grid, 256, 0, S(stream)>>>(static_cast<const long long*>(ptrs), n,
+                                                        rows, cols, g_dt, m_dt, norms);
+    } else {
+      dim3 grid((cols + 63) / 64, (rows + kColStrip - 1) / kColStrip, n);
+      col_norms_kernel<<<grid, 256, 0, S(stream)>>>(static_cast<const long long*>(ptrs), n, rows,
+                                                    cols, g_dt, m_dt, norms);
+    }
   }
   return rc();
 }

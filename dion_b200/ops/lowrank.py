@@ -7,11 +7,24 @@ Batched operands are ``[B, rows, cols]``.
 """
 from __future__ import annotations
 
+import ctypes
 import math
 from typing import Callable, List, Optional, Tuple
 
 import torch
 from torch import Tensor
+
+from . import _backend
+
+_MAX_FACTOR_DIM = 1024  # row limit of the batched factorization kernels (csrc/lowrank_ops.cu)
+
+
+def _ptr(t: Tensor) -> ctypes.c_void_p:
+    return ctypes.c_void_p(t.data_ptr())
+
+
+def _stream(dev) -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
 
 
 def sketch_rows(r: int, oversample: float) -> int:
@@ -34,13 +47,36 @@ def householder_q(P: Tensor) -> Tensor:
 
 
 def qr_r_factor(A: Tensor) -> Tensor:
-    """Upper-triangular factor of ``A`` (fp32)."""
-    return torch.linalg.qr(A.to(torch.float32), mode="r")[1]
+    """Upper-triangular factor of every ``A[b]`` (``[B, k, r]``, ``k >= r``) in fp32.  On a GPU
+    all matrices of the batch are factored at once by one kernel (Householder reflections, one
+    CTA per matrix); the sign of a row of ``R`` may differ from LAPACK's."""
+    A32 = A.to(torch.float32)
+    if A32.is_cuda and A32.ndim == 3 and A32.size(-1) <= A32.size(-2) <= _MAX_FACTOR_DIM:
+        A32 = A32.contiguous()
+        B, k, r = A32.shape
+        V = torch.empty((B, r, k), dtype=torch.float32, device=A32.device)
+        tau = torch.empty((B, r), dtype=torch.float32, device=A32.device)
+        R = torch.empty((B, r, r), dtype=torch.float32, device=A32.device)
+        rc = _backend.lib("lowrank_ops").dion_qr_r_factor(
+            _ptr(A32), _ptr(V), _ptr(tau), _ptr(R), B, k, r, _stream(A32.device))
+        if rc != 0:
+            raise RuntimeError(f"dion_qr_r_factor launch failed (code {rc})")
+        return R
+    return torch.linalg.qr(A32, mode="r")[1]
 
 
 def cholesky_upper(G: Tensor) -> Tensor:
     """Upper Cholesky factor without raising on failure (NaNs propagate and are handled by
-    :func:`fix_all_zero_or_nan`)."""
+    :func:`fix_all_zero_or_nan`).  GPU batches of fp32 matrices go to one kernel."""
+    if (G.is_cuda and G.dtype == torch.float32 and G.ndim == 3
+            and G.size(-1) == G.size(-2) <= _MAX_FACTOR_DIM):
+        Gc = G.contiguous()
+        U = torch.empty_like(Gc)
+        rc = _backend.lib("lowrank_ops").dion_cholesky_upper(
+            _ptr(Gc), _ptr(U), Gc.size(0), Gc.size(-1), _stream(Gc.device))
+        if rc != 0:
+            raise RuntimeError(f"dion_cholesky_upper launch failed (code {rc})")
+        return U
     return torch.linalg.cholesky_ex(G, upper=True)[0]
 
 

@@ -44,7 +44,7 @@ from ..ops import foreach as F
 from ..ops import lowrank as LR
 from ..parallel import collectives as C
 from ..parallel.async_runtime import AsyncRuntime, AsyncTask
-from ..utils.tensors import create_param_batches, to_local
+from ..utils.tensors import create_param_batches, group_by_shape, to_local
 
 
 @dataclass
@@ -236,12 +236,19 @@ class Dion(Optimizer):
                 if not plist:
                     continue
                 if kind == "inner_sharded":
-                    batch = self._inner_shard_mesh.size()
+                    batches = create_param_batches(plist, self._inner_shard_mesh.size())
                 elif kind == "outer_sharded":
-                    batch = self._outer_shard_mesh.size()
+                    batches = create_param_batches(plist, self._outer_shard_mesh.size())
                 else:
-                    batch = self._replicate_world_size
-                for params in create_param_batches(plist, batch):
+                    batches = self._replicated_batches(plist)
+                for params in batches:
+                    if kind == "inner_sharded":
+                        batch = self._inner_shard_mesh.size()
+                    elif kind == "outer_sharded":
+                        batch = self._outer_shard_mesh.size()
+                    else:
+                        W = self._replicate_world_size
+                        batch = W * ((len(params) + W - 1) // W)
                     states = [self._get_or_initialize_state(p, group) for p in params]
                     cfg = self._get_dion_param_config(params[0])
                     task_id += 1
@@ -249,6 +256,22 @@ class Dion(Optimizer):
                         kind, batch, params, [p.grad for p in params],
                         [s["momentum"] for s in states], [s["Q"] for s in states], cfg, group,
                         task_id))
+
+    # Stacked copies of the momentum of one batch are kept below this many bytes.
+    _BATCH_BYTES = 2 << 30
+
+    def _replicated_batches(self, plist: List[Tensor]) -> Iterable[List[Tensor]]:
+        """Unsharded parameters: every rank orthogonalizes ``L`` matrices of a batch of
+        ``world * L`` instead of one of ``world`` (the reference's layout, dion/dion.py:419-424),
+        so that the batched kernels see all same-shape matrices at once; ``L`` is bounded by the
+        size of the stacked momentum."""
+        W = self._replicate_world_size
+        for bucket in group_by_shape(plist).values():
+            nbytes = max(1, bucket[0].numel() * 4)
+            per_rank = max(1, min((len(bucket) + W - 1) // W, self._BATCH_BYTES // (nbytes * W)))
+            size = W * per_rank
+            for start in range(0, len(bucket), size):
+                yield bucket[start:start + size]
 
     def _scalar_lists(self, group, keys):
         params = [p for p in group["params"] if p.grad is not None]
@@ -452,7 +475,8 @@ class Dion(Optimizer):
                 yield
                 work.wait()
             else:
-                P1 = P[rank:rank + 1]
+                per_rank = batch // self._replicate_world_size
+                P1 = P[rank * per_rank:(rank + 1) * per_rank]
             gen = self._generator(dev, step, task_id, rank)
             P1 = LR.orthogonalize(P1, oversample, generator=gen)
             if rep is not None:
