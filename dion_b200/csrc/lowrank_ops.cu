@@ -26,7 +26,8 @@ __device__ __forceinline__ float warp_sum_f(float v) {
   return v;
 }
 
-// Shared memory: tile[k][17] staging of a 16-column block | vs[2][k] published column.
+// Shared memory: tile[k][17] staging of a 16-column block | vs[2][k] published column |
+// prev[16][k] reflectors of an earlier panel.
 template <int KPL>
 __global__ void __launch_bounds__(kLrThreads)
 qr_r_kernel(const float* __restrict__ A, float* V, float* tau_g, float* __restrict__ R, int k,
@@ -34,7 +35,9 @@ qr_r_kernel(const float* __restrict__ A, float* V, float* tau_g, float* __restri
   extern __shared__ float lr_smem[];
   float* tile = lr_smem;
   float* vs = lr_smem + (size_t)k * kTilePitch;
+  float* prev = vs + 2 * (size_t)k;          // [16][k] reflectors of an earlier panel
   __shared__ float tau_s[2];
+  __shared__ float prev_tau[kPanel];
   const int n = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const float* An = A + (size_t)n * k * r;
@@ -57,22 +60,30 @@ qr_r_kernel(const float* __restrict__ A, float* V, float* tau_g, float* __restri
       const int i = lane + 32 * t;
       x[t] = (i < k) ? tile[i * kTilePitch + warp] : 0.f;
     }
-    // Reflectors of earlier panels.
-    if (active) {
-      for (int j = 0; j < c0; ++j) {
-        const float* vj = Vn + (size_t)j * k;
-        float v[KPL];
-        float dot = 0.f;
+    // Reflectors of earlier panels, 16 at a time through shared memory (all threads fetch them
+    // with row-contiguous reads; every warp then applies them to its column).
+    for (int jb = 0; jb < c0; jb += kPanel) {
+      for (int e = threadIdx.x; e < kPanel * k; e += kLrThreads) prev[e] = Vn[(size_t)jb * k + e];
+      if (threadIdx.x < kPanel) prev_tau[threadIdx.x] = tn[jb + threadIdx.x];
+      __syncthreads();
+      if (active) {
+#pragma unroll 1
+        for (int j = 0; j < kPanel; ++j) {
+          const float* vj = prev + (size_t)j * k;
+          float v[KPL];
+          float dot = 0.f;
 #pragma unroll
-        for (int t = 0; t < KPL; ++t) {
-          const int i = lane + 32 * t;
-          v[t] = (i < k) ? vj[i] : 0.f;
-          dot += v[t] * x[t];
+          for (int t = 0; t < KPL; ++t) {
+            const int i = lane + 32 * t;
+            v[t] = (i < k) ? vj[i] : 0.f;
+            dot += v[t] * x[t];
+          }
+          dot = warp_sum_f(dot) * prev_tau[j];
+#pragma unroll
+          for (int t = 0; t < KPL; ++t) x[t] -= dot * v[t];
         }
-        dot = warp_sum_f(dot) * tn[j];
-#pragma unroll
-        for (int t = 0; t < KPL; ++t) x[t] -= dot * v[t];
       }
+      __syncthreads();
     }
     // Factor the panel.
     for (int jj = 0; jj < kPanel; ++jj) {
@@ -159,7 +170,8 @@ template <int KPL>
 __global__ void __launch_bounds__(kLrThreads)
 cholesky_upper_kernel(const float* __restrict__ G, float* U, int r) {
   extern __shared__ float lr_smem[];
-  float* vs = lr_smem;  // [2][r]
+  float* vs = lr_smem;            // [2][r]
+  float* prev = lr_smem + 2 * (size_t)r;  // [16][r] earlier columns
   const int n = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const float* Gn = G + (size_t)n * r * r;
@@ -174,16 +186,23 @@ cholesky_upper_kernel(const float* __restrict__ G, float* U, int r) {
       const int i = lane + 32 * t;
       x[t] = (active && i < r && i >= c) ? Gn[(size_t)c * r + i] : 0.f;
     }
-    if (active) {
-      for (int j = 0; j < c0; ++j) {
-        const float* lj = Un + (size_t)j * r;
-        const float ljc = lj[c];
+    // Earlier columns of the factor, 16 at a time through shared memory.
+    for (int jb = 0; jb < c0; jb += kPanel) {
+      for (int e = threadIdx.x; e < kPanel * r; e += kLrThreads) prev[e] = Un[(size_t)jb * r + e];
+      __syncthreads();
+      if (active) {
+#pragma unroll 2
+        for (int j = 0; j < kPanel; ++j) {
+          const float* lj = prev + (size_t)j * r;
+          const float ljc = lj[c];
 #pragma unroll
-        for (int t = 0; t < KPL; ++t) {
-          const int i = lane + 32 * t;
-          if (i < r && i >= c) x[t] -= lj[i] * ljc;
+          for (int t = 0; t < KPL; ++t) {
+            const int i = lane + 32 * t;
+            if (i < r && i >= c) x[t] -= lj[i] * ljc;
+          }
         }
       }
+      __syncthreads();
     }
     for (int jj = 0; jj < kPanel; ++jj) {
       const int cj = c0 + jj;
@@ -230,7 +249,7 @@ static inline cudaStream_t S(void* s) { return static_cast<cudaStream_t>(s); }
 template <int KPL>
 static int launch_qr(const float* A, float* V, float* tau, float* R, int n, int k, int r,
                      cudaStream_t s) {
-  const size_t smem = ((size_t)k * kTilePitch + 2 * (size_t)k) * sizeof(float);
+  const size_t smem = ((size_t)k * kTilePitch + 2 * (size_t)k + (size_t)kPanel * k) * sizeof(float);
   if (cudaFuncSetAttribute(qr_r_kernel<KPL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            (int)smem) != cudaSuccess)
     return -3;
@@ -256,7 +275,10 @@ DION_EXPORT int dion_qr_r_factor(const void* A, void* V, void* tau, void* R, int
 
 template <int KPL>
 static int launch_chol(const float* G, float* U, int n, int r, cudaStream_t s) {
-  const size_t smem = 2 * (size_t)r * sizeof(float);
+  const size_t smem = (2 + kPanel) * (size_t)r * sizeof(float);
+  if (cudaFuncSetAttribute(cholesky_upper_kernel<KPL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           (int)smem) != cudaSuccess)
+    return -3;
   cholesky_upper_kernel<KPL><<<n, kLrThreads, smem, s>>>(G, U, r);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
