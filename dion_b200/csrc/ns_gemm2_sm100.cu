@@ -42,6 +42,9 @@ constexpr int dyn_bytes2(int stages, bool sym) {
 }
 constexpr uint32_t kTmemCols2 = 2 * BN2;
 
+// Epilogue forms: C = alpha*acc + beta*D | relu(alpha*acc)^2 | alpha*acc * 2*sqrt(D).
+enum : int { kEpiAxpby = 0, kEpiRelu2 = 1, kEpiMul2Sqrt = 2 };
+
 struct Gemm2Args {
   int batch, M, N, K;
   const __nv_bfloat16* D;
@@ -56,6 +59,7 @@ struct Gemm2Args {
   int tiles_per_mat;
   int total_tiles;
   int* status;
+  int epi;      // kEpi*
 };
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -332,6 +336,7 @@ ns_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     const int row_in_tile = lane_grp * 32 + lane;
     const bool elected = (warp == 2 && lane == 0);
     const bool has_d = p.D != nullptr;
+    const int epi = p.epi;
     const uint32_t row_off = (uint32_t)(row_in_tile >> 6) * 8192u + (uint32_t)(row_in_tile & 63) * 128u;
     const uint32_t row_sw = (uint32_t)(row_in_tile & 7);
     uint8_t* dc_base = smem + kStages2 * kStageBytes2;
@@ -422,11 +427,26 @@ ns_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             if (has_d) {
               const uint4 u = *cell;
               const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+              if (epi == kEpiMul2Sqrt) {
 #pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                const float2 f = unpack_bf16x2(w[e]);
-                vj[2 * e] = alpha * vj[2 * e] + beta * f.x;
-                vj[2 * e + 1] = alpha * vj[2 * e + 1] + beta * f.y;
+                for (int e = 0; e < 4; ++e) {
+                  const float2 f = unpack_bf16x2(w[e]);
+                  vj[2 * e] = alpha * vj[2 * e] * (2.f * sqrtf(f.x));
+                  vj[2 * e + 1] = alpha * vj[2 * e + 1] * (2.f * sqrtf(f.y));
+                }
+              } else {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  const float2 f = unpack_bf16x2(w[e]);
+                  vj[2 * e] = alpha * vj[2 * e] + beta * f.x;
+                  vj[2 * e + 1] = alpha * vj[2 * e + 1] + beta * f.y;
+                }
+              }
+            } else if (epi == kEpiRelu2) {
+#pragma unroll
+              for (int e = 0; e < 8; ++e) {
+                const float t = fmaxf(alpha * vj[e], 0.f);
+                vj[e] = t * t;
               }
             } else {
 #pragma unroll
@@ -595,7 +615,8 @@ DION_EXPORT int dion_ns_gemm2(const void* A, long long lda, long long strideA, i
                               long long ldc, long long strideC, const void* D, long long ldd,
                               long long strideD, int batch, int M, int N, int K, float alpha,
                               float beta, const float* scale, int alpha_pow, int beta_pow, int sym,
-                              const void* tiles, int tiles_per_mat, int* status, void* stream) {
+                              const void* tiles, int tiles_per_mat, int epi, int* status,
+                              void* stream) {
   using namespace dion;
   if (batch <= 0 || M <= 0 || N <= 0 || K <= 0) return 0;
   if ((lda & 7) || (ldb & 7) || (strideA & 7) || (strideB & 7) ||
@@ -631,6 +652,9 @@ DION_EXPORT int dion_ns_gemm2(const void* A, long long lda, long long strideA, i
   a.total_tiles = tiles_per_mat * batch;
   a.status = status;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  a.epi = epi;
+  if (epi == kEpiMul2Sqrt && D == nullptr) return -16;
+  if (epi == kEpiRelu2 && D != nullptr) return -16;
   const int mode = (a_mn ? 2 : 0) | (b_mn ? 1 : 0);
   if (sym) {
     switch (mode) {

@@ -121,6 +121,9 @@ class MLP(nn.Module):
         self.c_proj = nn.Linear(4 * config.n_embd, config.n_embd, bias=False)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if (self.c_fc.bias is None and self.c_proj.bias is None and _is_plain(self.c_fc)
+                and _is_plain(self.c_proj)):
+            return Fn.mlp_relu2(x, self.c_fc.weight, self.c_proj.weight)
         return _linear(self.c_proj, Fn.relu2(_linear(self.c_fc, x)))
 
 

@@ -127,6 +127,9 @@ class GemmExtra(ctypes.Structure):
     ]
 
 
+_EPILOGUES = {"axpby": 0, "relu2": 1, "mul_2sqrt": 2}
+
+
 def pair_default() -> bool:
     """Whether eligible GEMMs go to the two-CTA kernel (``DION_B200_PAIR_GEMM``, default on)."""
     return os.environ.get("DION_B200_PAIR_GEMM", "1") != "0"
@@ -168,7 +171,11 @@ def ns_gemm(
     out_f32: Optional[Tensor] = None,
     bn: Optional[int] = None,
     pair: Optional[bool] = None,
+    epilogue: str = "axpby",
 ) -> Tensor:
+    """``epilogue``: ``"axpby"`` (``alpha*acc + beta*D``), ``"relu2"`` (``relu(alpha*acc)**2``) or
+    ``"mul_2sqrt"`` (``alpha*acc * 2*sqrt(D)``, the backward of ReLU^2 expressed through its
+    output); the last two exist in the two-CTA kernel only."""
     A3, B3 = _as3d(A), _as3d(B)
     batch = A3.size(0)
     M, K = (A3.size(-1), A3.size(-2)) if a_is_km else (A3.size(-2), A3.size(-1))
@@ -195,6 +202,9 @@ def ns_gemm(
     if scale is not None:
         assert scale.dtype == torch.float32 and scale.numel() >= batch
     st = status_tensor(dev)
+    epi = _EPILOGUES[epilogue]
+    if epi != 0:
+        pair = True
     if pair is None:
         pair = pair_default() and bn is None and _pair_eligible(
             M, N, batch, extra, out_t, out_f32, out, dev)
@@ -216,7 +226,7 @@ def ns_gemm(
             ctypes.c_int(batch), ctypes.c_int(M), ctypes.c_int(N), ctypes.c_int(K),
             ctypes.c_float(alpha), ctypes.c_float(beta), _p(scale),
             ctypes.c_int(alpha_pow), ctypes.c_int(beta_pow), ctypes.c_int(1 if sym else 0),
-            _p(tiles), ctypes.c_int(tiles.size(0)), _p(st),
+            _p(tiles), ctypes.c_int(tiles.size(0)), ctypes.c_int(epi), _p(st),
             ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream),
         )
         if rc != 0:

@@ -137,3 +137,22 @@ def test_pair_km_a_operand():
     torch.cuda.synchronize()
     gemm.check_status()
     assert _rel_err(C, X.float().mT @ X.float()) < 1e-2
+
+
+def test_pair_relu2_epilogues():
+    """relu(A B^T)^2 and its backward form (dY W) * 2 sqrt(act) fused into the GEMM epilogue."""
+    from dion_b200.ops import gemm
+    torch.manual_seed(5)
+    T, C, F = 1000, 256, 1024
+    h = (torch.randn(T, C, device="cuda") * 0.3).bfloat16()
+    Wfc = (torch.randn(F, C, device="cuda") * 0.1).bfloat16()
+    act = gemm.ns_gemm(h, Wfc, epilogue="relu2")
+    ref = torch.relu(h.float() @ Wfc.float().T).square()
+    assert _rel_err(act, ref) < 1e-2
+    dy = torch.randn(T, C, device="cuda").bfloat16()
+    Wpr = (torch.randn(C, F, device="cuda") * 0.1).bfloat16()
+    dz = gemm.ns_gemm(dy, Wpr, b_is_kn=True, D=act, epilogue="mul_2sqrt")
+    torch.cuda.synchronize()
+    gemm.check_status()
+    ref_dz = (dy.float() @ Wpr.float()) * 2.0 * act.float().sqrt()
+    assert _rel_err(dz, ref_dz) < 1e-2

@@ -142,5 +142,7 @@ def test_cuda_graph_optimizer_matches_eager(name):
         return [p.detach().clone() for p in mats + vecs]
 
     eager, graphed = run(False), run(True)
+    # The Frobenius norms are accumulated with floating-point atomics, so two runs can differ by
+    # a bf16 rounding of the orthogonalized update (about lr * 2^-8 per step).
     for a, b in zip(eager, graphed):
-        assert torch.allclose(a, b, atol=1e-5, rtol=1e-4)
+        assert torch.allclose(a, b, atol=1e-3, rtol=1e-3)

@@ -128,6 +128,31 @@ def test_linear_bf16_fp32_weight_grad():
     assert (x.grad.float() - xr.grad).abs().max().item() < 5e-2
 
 
+def test_mlp_relu2_fused_matches_composition(monkeypatch):
+    monkeypatch.setenv("DION_B200_FUSED_MLP", "1")
+    torch.manual_seed(0)
+    B, T, C = 2, 300, 256
+    h = (torch.randn(B, T, C, device="cuda") * 0.5).bfloat16().requires_grad_()
+    wfc = (torch.randn(4 * C, C, device="cuda") * C ** -0.5).requires_grad_()
+    wpr = (torch.randn(C, 4 * C, device="cuda") * (4 * C) ** -0.5).requires_grad_()
+    y = Fn.mlp_relu2(h, wfc, wpr)
+    g = torch.randn_like(y)
+    y.backward(g)
+    hr = h.detach().float().requires_grad_()
+    wf = wfc.detach().bfloat16().float().requires_grad_()
+    wp = wpr.detach().bfloat16().float().requires_grad_()
+    yr = torch.relu(hr @ wf.T).square() @ wp.T
+    yr.backward(g.float())
+
+    def close(a, b, tol=3e-2):
+        return (a.float() - b).abs().max().item() < tol * b.abs().max().item() + 1e-3
+
+    assert close(y, yr)
+    assert close(h.grad, hr.grad)
+    assert wfc.grad.dtype == torch.float32 and close(wfc.grad, wf.grad)
+    assert close(wpr.grad, wp.grad)
+
+
 def test_relu2():
     x = torch.randn(16, 3072, device="cuda").bfloat16().requires_grad_()
     xr = x.detach().float().requires_grad_()
