@@ -1,0 +1,114 @@
+"""Behaviour every optimizer class must show on any device (run here on CPU): parameters move,
+identical runs agree bit for bit, mixed parameter groups and missing gradients are handled,
+bad arguments are rejected."""
+import pytest
+import torch
+
+import dion_b200
+
+
+def _make(seed=0):
+    torch.manual_seed(seed)
+    mats = [torch.nn.Parameter(torch.randn(32, 48) * 0.1), torch.nn.Parameter(torch.randn(48, 32) * 0.1),
+            torch.nn.Parameter(torch.randn(32, 32) * 0.1)]
+    vecs = [torch.nn.Parameter(torch.randn(48)), torch.nn.Parameter(torch.randn(32))]
+    return mats, vecs
+
+
+FACTORIES = {
+    "muon": lambda g: dion_b200.Muon(g, lr=0.02, mu=0.9, weight_decay=0.01),
+    "muon_nesterov_pe": lambda g: dion_b200.Muon(g, lr=0.02, nesterov=True, use_polar_express=True),
+    "normuon": lambda g: dion_b200.NorMuon(g, lr=0.02),
+    "dion2": lambda g: dion_b200.Dion2(g, lr=0.02, fraction=0.25),
+    "dion2_global": lambda g: dion_b200.Dion2(g, lr=0.02, fraction=0.5, selection_scope="global"),
+    "nordion2": lambda g: dion_b200.NorDion2(g, lr=0.02, fraction=0.5),
+    "dion": lambda g: dion_b200.Dion(g, lr=0.02, rank_fraction=0.5),
+    "dion_reference": lambda g: dion_b200.DionReference(g, lr=0.02, rank_fraction=0.5),
+    "dion_simple": lambda g: dion_b200.DionSimple(g, lr=0.02, rank=8),
+    "muon_reference": lambda g: dion_b200.MuonReference(g, lr=0.02),
+}
+
+
+def _run(name, steps=3, seed=0, scalar_algo="adamw"):
+    mats, vecs = _make(seed)
+    groups = [dict(params=mats), dict(params=vecs, algorithm=scalar_algo, lr=0.01)]
+    opt = FACTORIES[name](groups)
+    g = torch.Generator().manual_seed(3)
+    for _ in range(steps):
+        for p in mats + vecs:
+            p.grad = torch.randn(p.shape, generator=g)
+        opt.step()
+    return [p.detach().clone() for p in mats + vecs], opt
+
+
+@pytest.mark.parametrize("name", list(FACTORIES))
+def test_parameters_move_and_stay_finite(name):
+    before = [p.detach().clone() for p in sum(_make(), [])]
+    after, _ = _run(name)
+    for b, a in zip(before, after):
+        assert torch.isfinite(a).all()
+        assert not torch.equal(a, b)
+
+
+@pytest.mark.parametrize("name", list(FACTORIES))
+def test_two_identical_runs_agree_exactly(name):
+    a, _ = _run(name)
+    b, _ = _run(name)
+    for x, y in zip(a, b):
+        assert torch.equal(x, y)
+
+
+@pytest.mark.parametrize("name", ["muon", "dion2", "normuon", "dion"])
+def test_lion_group_works_beside_the_matrix_algorithm(name):
+    after, opt = _run(name, scalar_algo="lion")
+    assert all(torch.isfinite(a).all() for a in after)
+    algos = {g["algorithm"] for g in opt.param_groups}
+    assert "lion" in algos and len(algos) == 2
+
+
+@pytest.mark.parametrize("name", ["muon", "normuon", "dion2", "nordion2", "dion"])
+def test_parameters_without_gradient_are_left_alone(name):
+    mats, vecs = _make()
+    opt = FACTORIES[name]([dict(params=mats), dict(params=vecs, algorithm="adamw", lr=0.01)])
+    frozen = mats[1].detach().clone()
+    for p in mats + vecs:
+        p.grad = torch.randn_like(p)
+    mats[1].grad = None
+    opt.step()
+    assert torch.equal(mats[1], frozen)
+    assert not torch.equal(mats[0], _make()[0][0])
+
+
+def test_vector_in_matrix_group_is_rejected():
+    _, vecs = _make()
+    opt = dion_b200.Muon([dict(params=vecs)], lr=0.02)
+    for p in vecs:
+        p.grad = torch.randn_like(p)
+    with pytest.raises((AssertionError, ValueError, RuntimeError)):
+        opt.step()
+
+
+@pytest.mark.parametrize("kw", [dict(lr=-1.0), dict(mu=-0.1), dict(adjust_lr="bogus")])
+def test_bad_hyperparameters_are_rejected(kw):
+    mats, _ = _make()
+    with pytest.raises(ValueError):
+        dion_b200.Muon([dict(params=mats)], **kw)
+
+
+def test_dion2_scope_default_is_local_and_full_fraction_makes_scopes_equal():
+    mats, _ = _make()
+    opt = dion_b200.Dion2([dict(params=mats)], lr=0.02, fraction=0.25)
+    assert opt.param_groups[0].get("selection_scope", "local") == "local"
+
+    def run(scope):
+        ms, _ = _make()
+        o = dion_b200.Dion2([dict(params=ms)], lr=0.02, fraction=1.0, selection_scope=scope)
+        g = torch.Generator().manual_seed(9)
+        for _ in range(2):
+            for p in ms:
+                p.grad = torch.randn(p.shape, generator=g)
+            o.step()
+        return [p.detach().clone() for p in ms]
+
+    for a, b in zip(run("local"), run("global")):
+        assert torch.allclose(a, b, atol=1e-6)
