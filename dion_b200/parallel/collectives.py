@@ -65,6 +65,19 @@ class _Chain:
             self.epilogue = None
 
 
+def _symmetric_route(ts: Sequence[Tensor], pg: ProcessGroup) -> bool:
+    """``DION_B200_SYMM_ALLREDUCE=1`` sends CUDA fp32/bf16 all-reduces of a single NCCL group
+    through the NVLS / peer-memory kernel of :mod:`dion_b200.parallel.symm` instead of NCCL."""
+    import os
+
+    if os.environ.get("DION_B200_SYMM_ALLREDUCE", "0") != "1" or _is_gloo(pg):
+        return False
+    if dist.get_world_size(pg) > 8:
+        return False
+    return all(t.is_cuda and t.is_contiguous() and t.dtype in (torch.float32, torch.bfloat16)
+               for t in ts)
+
+
 def all_reduce_(tensors: Union[Tensor, Sequence[Tensor]], group: Group, op: str = "sum",
                 async_op: bool = False):
     """In-place all-reduce (``sum`` or ``avg``) of one tensor or a list over every group of
@@ -77,6 +90,12 @@ def all_reduce_(tensors: Union[Tensor, Sequence[Tensor]], group: Group, op: str 
     works = []
     scale = 1.0
     live = [pg for pg in pgs if dist.get_world_size(pg) > 1]
+    if len(live) == 1 and _symmetric_route(ts, live[0]):
+        from . import symm
+
+        for t in ts:
+            symm.symmetric_all_reduce_(t, live[0], op)
+        return _Done() if async_op else None
     for i, pg in enumerate(live):
         n = dist.get_world_size(pg)
         use_avg = op == "avg" and not _is_gloo(pg)

@@ -132,3 +132,113 @@ def scale_from_partials(partials: Tensor, n_mats: int, n_src: int, mult: float, 
 def address_table(addresses: List[int], device: torch.device) -> Tensor:
     """int64 device tensor holding raw addresses."""
     return torch.tensor(addresses, dtype=torch.int64).to(device)
+
+
+# ------------------------------------------------------------------------------------------------
+# All-reduce inside symmetric memory (NVLS multimem through the NVSwitch, or plain peer access)
+# ------------------------------------------------------------------------------------------------
+def nvls_enabled() -> bool:
+    import os
+    return os.environ.get("DION_B200_NVLS", "1") != "0"
+
+
+class SymmetricAllReduce:
+    """In-place all-reduce of up to ``capacity`` bytes that live in a symmetric buffer.
+
+    Two-shot: after a flag barrier every rank reduces its 1/W slice over all ranks and writes the
+    result into every rank's copy; a second flag barrier publishes the result.  With NVLS the
+    slice is read with ``multimem.ld_reduce`` (the switch adds the ranks' copies) and written
+    with ``multimem.st`` (the switch replicates it); with ``DION_B200_NVLS=0`` or without
+    multicast support the kernel loads from and stores to the peers' copies one by one.  This is
+    the communication step of Dion's compressed data-parallel sync (all-reduce of the small
+    ``P``/``R`` factors; dion/dion.py:1162-1194 of the reference uses NCCL) and of
+    ``synchronize_for_checkpoint``.  All waits are bounded; a missing peer surfaces through
+    ``dion_b200.ops.gemm.check_status``.
+
+    ``view(shape, dtype)`` exposes the start of the buffer, so a producer (e.g. ``torch.bmm(...,
+    out=view)``) can write its result in place and no copy is needed; ``all_reduce_tensor_``
+    copies an ordinary tensor in and out."""
+
+    def __init__(self, pg: ProcessGroup, capacity: int, device: torch.device):
+        from ..ops import gemm
+
+        self.pg, self.device = pg, device
+        self.rank, self.world = dist.get_rank(pg), dist.get_world_size(pg)
+        lay = Layout()
+        self.capacity = (capacity + 4095) // 4096 * 4096
+        self.off_data = lay.add("data", self.capacity)
+        self.off_in = lay.add("in", self.world * 4)
+        self.off_out = lay.add("out", self.world * 4)
+        self.buf = SymmetricBuffer(lay.size, pg)
+        self.flags_in = self.buf.view(self.off_in, (self.world,), torch.int32)
+        self.flags_out = self.buf.view(self.off_out, (self.world,), torch.int32)
+        self.in_table = address_table(
+            [self.buf.peer_address(p, self.off_in) for p in range(self.world)], device)
+        self.out_table = address_table(
+            [self.buf.peer_address(p, self.off_out) for p in range(self.world)], device)
+        self.data_table = address_table(
+            [self.buf.peer_address(p, self.off_data) for p in range(self.world)], device)
+        self.seq = torch.zeros((), dtype=torch.int32, device=device)
+        self.status = gemm.status_tensor(device)
+        mc = 0
+        if nvls_enabled():
+            try:
+                mc = int(getattr(self.buf.handle, "multicast_ptr", 0) or 0)
+            except Exception:
+                mc = 0
+        self.multicast_base = mc + self.off_data if mc else 0
+        self.num_blocks = 4 * torch.cuda.get_device_properties(device).multi_processor_count
+
+    @property
+    def uses_multimem(self) -> bool:
+        return self.multicast_base != 0
+
+    def view(self, shape, dtype: torch.dtype) -> Tensor:
+        return self.buf.view(self.off_data, shape, dtype)
+
+    def all_reduce_(self, numel: int, dtype: torch.dtype, op: str = "sum") -> None:
+        """Reduce the first ``numel`` elements of ``dtype`` in place on every rank."""
+        esize = 4 if dtype == torch.float32 else 2
+        if dtype not in (torch.float32, torch.bfloat16):
+            raise TypeError("SymmetricAllReduce handles fp32 and bf16")
+        nbytes = numel * esize
+        if nbytes > self.capacity:
+            raise ValueError("tensor exceeds the symmetric all-reduce buffer")
+        nvec = (nbytes + 15) // 16
+        per = (nvec + self.world - 1) // self.world
+        begin, end = self.rank * per, min(nvec, (self.rank + 1) * per)
+        scale = 1.0 / self.world if op == "avg" else 1.0
+        bump_seq(self.seq)
+        signal_peers(self.in_table, self.rank, self.seq)
+        wait_flags(self.flags_in, self.seq, 0, self.status)
+        rc = _backend.lib("comm_ops").dion_allreduce_slice(
+            _c(self.multicast_base), _c(self.data_table.data_ptr()), self.world,
+            ctypes.c_longlong(begin), ctypes.c_longlong(end),
+            0 if dtype == torch.float32 else 1, ctypes.c_float(scale), self.num_blocks,
+            _stream(self.device))
+        if rc != 0:
+            raise RuntimeError(f"dion_allreduce_slice failed (code {rc})")
+        signal_peers(self.out_table, self.rank, self.seq)
+        wait_flags(self.flags_out, self.seq, 0, self.status)
+
+    def all_reduce_tensor_(self, t: Tensor, op: str = "sum") -> Tensor:
+        flat = self.view((t.numel(),), t.dtype)
+        flat.copy_(t.reshape(-1))
+        self.all_reduce_(t.numel(), t.dtype, op)
+        t.copy_(flat.view(t.shape))
+        return t
+
+
+_all_reducers: Dict[Tuple[int, int], SymmetricAllReduce] = {}
+
+
+def symmetric_all_reduce_(t: Tensor, pg: ProcessGroup, op: str = "sum") -> Tensor:
+    """All-reduce ``t`` in place through a cached :class:`SymmetricAllReduce` of ``pg`` (created
+    collectively on first use, regrown when a larger tensor comes; every rank must call this with
+    the same sizes in the same order)."""
+    key = (id(pg), t.device.index or 0)
+    red = _all_reducers.get(key)
+    need = t.numel() * t.element_size()
+    if red is None or need > red.capacity:
+        red = _all_reducers[key] = SymmetricAllReduce(pg, max(need, 1 << 22), t.device)
+    return red.all_reduce_tensor_(t, op)

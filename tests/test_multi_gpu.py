@@ -123,3 +123,88 @@ def test_fused_exchange_matches_collective_other_optimizers(tmp_path, name, kw):
     assert used0 == 0 and used1 > 0
     for c, f in zip(coll, fused):
         assert (c - f).abs().max().item() < 2e-3, name
+
+
+def _symm_allreduce_worker(rank, world, use_nvls):
+    import os
+    os.environ["DION_B200_NVLS"] = "1" if use_nvls else "0"
+    from dion_b200.ops.gemm import check_status
+    from dion_b200.parallel import symm
+    dev = torch.device("cuda", rank)
+    pg = dist.group.WORLD
+    red = symm.SymmetricAllReduce(pg, 8 << 20, dev)
+    out = {"multimem": red.uses_multimem}
+    for dtype, n in ((torch.float32, 1000003), (torch.bfloat16, 65536 + 8), (torch.float32, 5)):
+        g = torch.Generator(device=dev).manual_seed(100 + rank)
+        t = torch.randn(n, device=dev, generator=g).to(dtype)
+        ref = t.clone().float()
+        dist.all_reduce(ref)
+        for op in ("sum", "avg"):
+            x = t.clone()
+            red.all_reduce_tensor_(x, op)
+            torch.cuda.synchronize()
+            check_status()
+            want = ref / world if op == "avg" else ref
+            tol = 1e-5 if dtype == torch.float32 else 2e-2
+            assert (x.float() - want).abs().max().item() <= tol * max(1.0, want.abs().max().item())
+    # Zero-copy form and the cached helper.
+    v = red.view((4096,), torch.float32)
+    v.fill_(float(rank + 1))
+    red.all_reduce_(4096, torch.float32, "sum")
+    torch.cuda.synchronize()
+    assert torch.all(v == world * (world + 1) / 2)
+    y = torch.full((3, 7), float(rank), device=dev)
+    symm.symmetric_all_reduce_(y, pg, "avg")
+    torch.cuda.synchronize()
+    assert torch.allclose(y, torch.full_like(y, (world - 1) / 2))
+    return out
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("use_nvls", [True, False])
+def test_symmetric_all_reduce_matches_nccl(tmp_path, use_nvls):
+    _need(2)
+    world = 4 if torch.cuda.device_count() >= 4 else 2
+    res = run_ranks(_symm_allreduce_worker, world, backend="nccl", args=(use_nvls,),
+                    result_dir=str(tmp_path))
+    assert len(res) == world
+    if not use_nvls:
+        assert not any(r["multimem"] for r in res)
+
+
+def _dion_ddp_worker(rank, world, symmetric):
+    import os
+    os.environ["DION_B200_SYMM_ALLREDUCE"] = "1" if symmetric else "0"
+    from dion_b200.ops.gemm import check_status
+    dev = torch.device("cuda", rank)
+    torch.manual_seed(3)
+    params = [torch.nn.Parameter(torch.randn(256, 128, device=dev) * 0.1) for _ in range(3)]
+    params += [torch.nn.Parameter(torch.randn(128, 256, device=dev) * 0.1) for _ in range(2)]
+    opt = dion_b200.Dion([dict(params=params)], replicate_mesh=dist.group.WORLD,
+                         replicate_mesh_grad_sync=True, rank_fraction=0.25, lr=0.02)
+    g = torch.Generator(device=dev).manual_seed(50 + rank)   # different gradients per rank
+    for _ in range(3):
+        for p in params:
+            p.grad = torch.randn(p.shape, device=dev, generator=g)
+        opt.step()
+    opt.synchronize_for_checkpoint()
+    torch.cuda.synchronize()
+    check_status()
+    return [p.detach().cpu() for p in params]
+
+
+def test_dion_compressed_sync_through_symmetric_all_reduce(tmp_path):
+    """Legacy Dion under DDP with compressed P/R synchronization: the NVLS / peer-memory
+    all-reduce gives the result of the NCCL path, and replicas stay identical."""
+    _need(2)
+    out = {}
+    for symmetric in (False, True):
+        d = tmp_path / str(symmetric)
+        d.mkdir()
+        out[symmetric] = run_ranks(_dion_ddp_worker, 2, backend="nccl", args=(symmetric,),
+                                   result_dir=str(d))
+    for res in out.values():
+        for a, b in zip(res[0], res[1]):
+            assert torch.allclose(a, b, atol=1e-5)
+    for a, b in zip(out[False][0], out[True][0]):
+        assert torch.allclose(a, b, atol=2e-3, rtol=1e-2)
