@@ -169,6 +169,115 @@ allreduce_peer_kernel(const long long* peer_bases, int world, long long vec_begi
   }
 }
 
+// Single-launch form: the flag barriers are part of the kernel.  Block 0 tells every peer that
+// this rank's input is in place (the kernel runs after its producers in stream order); every
+// block waits (bounded) for all peers' inputs, reduces its share of this rank's slice and
+// writes it everywhere; the block that finishes last publishes "slice written" to the peers,
+// waits (bounded) for theirs and advances the sequence number.  Blocks never wait for each
+// other, only for other GPUs.
+struct AllReduceArgs {
+  char* mc_base;                 // multicast address of the data (0 = use peer_bases)
+  const long long* peer_bases;   // [world] data base addresses
+  const long long* peer_in;      // [world] base of each peer's "input ready" flags
+  const long long* peer_out;     // [world] base of each peer's "slice written" flags
+  const int* flags_in;           // local flags, one per source rank
+  const int* flags_out;
+  int* seq;
+  unsigned* counter;
+  int* status;
+  long long vec_begin, vec_end;
+  int world, rank, dt;
+  float scale;
+};
+
+__global__ void __launch_bounds__(256)
+allreduce_fused_kernel(const AllReduceArgs a) {
+  __shared__ int s_ok;
+  __shared__ int s_last;
+  const int seq = *a.seq + 1;
+  if (threadIdx.x == 0) s_ok = 1;
+  __syncthreads();
+  if (blockIdx.x == 0 && threadIdx.x < a.world) {
+    __threadfence_system();
+    st_release_sys_i32(reinterpret_cast<int*>(a.peer_in[threadIdx.x]) + a.rank, seq);
+  }
+  if (threadIdx.x < a.world) {
+    bool got = false;
+    for (unsigned k = 0; k < kMaxFlagPolls; ++k) {
+      if (ld_acquire_sys_i32(a.flags_in + threadIdx.x) >= seq) { got = true; break; }
+      __nanosleep(32);
+    }
+    if (!got) { atomicExch(a.status, kStatusTimeoutPeer); s_ok = 0; }
+  }
+  __syncthreads();
+  if (s_ok) {
+    for (long long i = a.vec_begin + (long long)blockIdx.x * 256 + threadIdx.x; i < a.vec_end;
+         i += (long long)gridDim.x * 256) {
+      if (a.mc_base != nullptr) {
+        char* p = a.mc_base + i * 16;
+        uint4 v;
+        if (a.dt == 0) {
+          const float4 f = mm_ld_reduce_f32(p);
+          v = make_uint4(__float_as_uint(f.x), __float_as_uint(f.y), __float_as_uint(f.z),
+                         __float_as_uint(f.w));
+        } else {
+          v = mm_ld_reduce_bf16(p);
+        }
+        mm_st_b32x4(p, scale_vec(v, a.dt, a.scale));
+      } else {
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int r = 0; r < a.world; ++r) {
+          const uint4 u = *reinterpret_cast<const uint4*>(
+              reinterpret_cast<const char*>(a.peer_bases[r]) + i * 16);
+          if (a.dt == 0) {
+            acc[0] += __uint_as_float(u.x); acc[1] += __uint_as_float(u.y);
+            acc[2] += __uint_as_float(u.z); acc[3] += __uint_as_float(u.w);
+          } else {
+            const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float2 f = unpack_bf16x2(w[e]);
+              acc[2 * e] += f.x; acc[2 * e + 1] += f.y;
+            }
+          }
+        }
+        uint4 out;
+        if (a.dt == 0) {
+          out = make_uint4(__float_as_uint(acc[0] * a.scale), __float_as_uint(acc[1] * a.scale),
+                           __float_as_uint(acc[2] * a.scale), __float_as_uint(acc[3] * a.scale));
+        } else {
+          out = make_uint4(pack_bf16x2(acc[0] * a.scale, acc[1] * a.scale),
+                           pack_bf16x2(acc[2] * a.scale, acc[3] * a.scale),
+                           pack_bf16x2(acc[4] * a.scale, acc[5] * a.scale),
+                           pack_bf16x2(acc[6] * a.scale, acc[7] * a.scale));
+        }
+        for (int r = 0; r < a.world; ++r)
+          *reinterpret_cast<uint4*>(reinterpret_cast<char*>(a.peer_bases[r]) + i * 16) = out;
+      }
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) s_last = (atomicAdd(a.counter, 1u) == gridDim.x - 1) ? 1 : 0;
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence_system();
+  if (threadIdx.x < a.world) {
+    st_release_sys_i32(reinterpret_cast<int*>(a.peer_out[threadIdx.x]) + a.rank, seq);
+    bool got = false;
+    for (unsigned k = 0; k < kMaxFlagPolls; ++k) {
+      if (ld_acquire_sys_i32(a.flags_out + threadIdx.x) >= seq) { got = true; break; }
+      __nanosleep(32);
+    }
+    if (!got) atomicExch(a.status, kStatusTimeoutPeer);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    *a.counter = 0u;
+    *a.seq = seq;
+  }
+}
+
 }  // namespace dion
 
 using namespace dion;
@@ -221,5 +330,31 @@ DION_EXPORT int dion_allreduce_slice(void* mc_base, const void* peer_bases, int 
     allreduce_peer_kernel<<<blocks, 256, 0, S(stream)>>>(
         static_cast<const long long*>(peer_bases), world, vec_begin, vec_end, dt, scale);
   }
+  return rc();
+}
+
+// In-place all-reduce of 16-byte vectors of a symmetric buffer in one launch (see
+// allreduce_fused_kernel).  `seq` and `counter` are device words owned by the workspace.
+DION_EXPORT int dion_allreduce_fused(void* mc_base, const void* peer_bases, const void* peer_in,
+                                     const void* peer_out, const int* flags_in,
+                                     const int* flags_out, int* seq, unsigned* counter,
+                                     int* status, int world, int rank, long long vec_begin,
+                                     long long vec_end, int dt, float scale, int num_blocks,
+                                     void* stream) {
+  if (world <= 0 || world > 256 || (dt != 0 && dt != 1)) return -2;
+  long long n = vec_end > vec_begin ? vec_end - vec_begin : 0;
+  long long need = (n + 255) / 256;
+  int blocks = (int)(need < (long long)num_blocks ? need : (long long)num_blocks);
+  if (blocks < 1) blocks = 1;  // an empty slice still takes part in the barriers
+  AllReduceArgs a;
+  a.mc_base = static_cast<char*>(mc_base);
+  a.peer_bases = static_cast<const long long*>(peer_bases);
+  a.peer_in = static_cast<const long long*>(peer_in);
+  a.peer_out = static_cast<const long long*>(peer_out);
+  a.flags_in = flags_in; a.flags_out = flags_out;
+  a.seq = seq; a.counter = counter; a.status = status;
+  a.vec_begin = vec_begin; a.vec_end = vec_end > vec_begin ? vec_end : vec_begin;
+  a.world = world; a.rank = rank; a.dt = dt; a.scale = scale;
+  allreduce_fused_kernel<<<blocks, 256, 0, S(stream)>>>(a);
   return rc();
 }

@@ -137,16 +137,23 @@ def address_table(addresses: List[int], device: torch.device) -> Tensor:
 # ------------------------------------------------------------------------------------------------
 # All-reduce inside symmetric memory (NVLS multimem through the NVSwitch, or plain peer access)
 # ------------------------------------------------------------------------------------------------
-def nvls_enabled() -> bool:
+def nvls_enabled(world: int = 8) -> bool:
+    """``DION_B200_NVLS``: "1" multimem, "0" plain peer access; unset: multimem for more than two
+    ranks (between two GPUs the switch has nothing to combine and plain peer access measured
+    faster: 638 against 390 GB/s bus bandwidth at 256 MiB)."""
     import os
-    return os.environ.get("DION_B200_NVLS", "1") != "0"
+    v = os.environ.get("DION_B200_NVLS")
+    if v is None:
+        return world > 2
+    return v != "0"
 
 
 class SymmetricAllReduce:
     """In-place all-reduce of up to ``capacity`` bytes that live in a symmetric buffer.
 
-    Two-shot: after a flag barrier every rank reduces its 1/W slice over all ranks and writes the
-    result into every rank's copy; a second flag barrier publishes the result.  With NVLS the
+    Two-shot, one kernel launch per call: after a flag barrier every rank reduces its 1/W slice
+    over all ranks and writes the result into every rank's copy; a second flag barrier (by the
+    block that finishes last) publishes the result.  With NVLS the
     slice is read with ``multimem.ld_reduce`` (the switch adds the ranks' copies) and written
     with ``multimem.st`` (the switch replicates it); with ``DION_B200_NVLS=0`` or without
     multicast support the kernel loads from and stores to the peers' copies one by one.  This is
@@ -179,9 +186,10 @@ class SymmetricAllReduce:
         self.data_table = address_table(
             [self.buf.peer_address(p, self.off_data) for p in range(self.world)], device)
         self.seq = torch.zeros((), dtype=torch.int32, device=device)
+        self.counter = torch.zeros((), dtype=torch.int32, device=device)
         self.status = gemm.status_tensor(device)
         mc = 0
-        if nvls_enabled():
+        if nvls_enabled(self.world):
             try:
                 mc = int(getattr(self.buf.handle, "multicast_ptr", 0) or 0)
             except Exception:
@@ -208,18 +216,16 @@ class SymmetricAllReduce:
         per = (nvec + self.world - 1) // self.world
         begin, end = self.rank * per, min(nvec, (self.rank + 1) * per)
         scale = 1.0 / self.world if op == "avg" else 1.0
-        bump_seq(self.seq)
-        signal_peers(self.in_table, self.rank, self.seq)
-        wait_flags(self.flags_in, self.seq, 0, self.status)
-        rc = _backend.lib("comm_ops").dion_allreduce_slice(
-            _c(self.multicast_base), _c(self.data_table.data_ptr()), self.world,
-            ctypes.c_longlong(begin), ctypes.c_longlong(end),
+        rc = _backend.lib("comm_ops").dion_allreduce_fused(
+            _c(self.multicast_base), _c(self.data_table.data_ptr()),
+            _c(self.in_table.data_ptr()), _c(self.out_table.data_ptr()),
+            _c(self.flags_in.data_ptr()), _c(self.flags_out.data_ptr()),
+            _c(self.seq.data_ptr()), _c(self.counter.data_ptr()), _c(self.status.data_ptr()),
+            self.world, self.rank, ctypes.c_longlong(begin), ctypes.c_longlong(end),
             0 if dtype == torch.float32 else 1, ctypes.c_float(scale), self.num_blocks,
             _stream(self.device))
         if rc != 0:
-            raise RuntimeError(f"dion_allreduce_slice failed (code {rc})")
-        signal_peers(self.out_table, self.rank, self.seq)
-        wait_flags(self.flags_out, self.seq, 0, self.status)
+            raise RuntimeError(f"dion_allreduce_fused failed (code {rc})")
 
     def all_reduce_tensor_(self, t: Tensor, op: str = "sum") -> Tensor:
         flat = self.view((t.numel(),), t.dtype)
