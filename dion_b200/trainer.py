@@ -115,6 +115,9 @@ def parse_cli_args(argv: Optional[List[str]] = None) -> argparse.Namespace:
     p.add_argument("--no_triton", action="store_true", help="accepted; kernels are always CUDA")
     p.add_argument("--use_polar_express", action="store_true")
     p.add_argument("--use_gram_newton_schulz", action="store_true")
+    p.add_argument("--graph_step", action="store_true",
+                   help="Replay forward + backward + gradient all-reduce + optimizer as ONE CUDA "
+                        "graph per step (single GPU or DDP, no gradient accumulation)")
     p.add_argument("--cuda_graph", action="store_true",
                    help="capture the optimizer step in a CUDA graph after warm-up")
     p.add_argument("--synthetic", action="store_true", help="uniform-random tokens, seed 0")
@@ -335,7 +338,7 @@ def lr_multiplier(step: int, num_iterations: int, warmup_ratio: float, warmdown_
 
 
 def build_model(hp: Hyperparameters, device_mesh: Optional[DeviceMesh], device: torch.device,
-                fast_fsdp: bool = False):
+                fast_fsdp: bool = False, wrap_ddp: bool = True):
     """-> (model to call, raw GPT, DDP wrapper or None)"""
     config = GPTConfig(sequence_len=hp.sequence_length, vocab_size=VOCAB_SIZE, n_layer=hp.n_layer,
                        n_head=hp.n_head, n_embd=hp.model_dim)
@@ -350,7 +353,7 @@ def build_model(hp: Hyperparameters, device_mesh: Optional[DeviceMesh], device: 
     model.init_weights()
     ddp = None
     call = model
-    if device_mesh is None and dist.is_initialized() and dist.get_world_size() > 1:
+    if wrap_ddp and device_mesh is None and dist.is_initialized() and dist.get_world_size() > 1:
         if device.type == "cuda":
             ddp = DDP(model, device_ids=[device.index], output_device=device.index)
         else:
@@ -427,7 +430,16 @@ def main(argv: Optional[List[str]] = None) -> None:
                                            hp.device_batch_size, hp.sequence_length, dp_rank,
                                            dp_world, device=device)
 
-    model, raw_model, ddp = build_model(hp, mesh, device, fast_fsdp=args.fast_fsdp)
+    graph_step = bool(args.graph_step) and device.type == "cuda"
+    if graph_step and (mesh is not None or grad_accum != 1):
+        raise ValueError("--graph_step needs plain data parallelism (no --dp_size/--fs_size/"
+                         "--tp_size) and a batch that fits without gradient accumulation")
+    model, raw_model, ddp = build_model(hp, mesh, device, fast_fsdp=args.fast_fsdp,
+                                        wrap_ddp=not graph_step)
+    if graph_step and world > 1:
+        # Without the DDP wrapper nothing has made the replicas identical yet.
+        for t in list(raw_model.parameters()) + list(raw_model.buffers()):
+            dist.broadcast(t.data, src=0)
     print0(f"Total parameters: {sum(p.numel() for p in raw_model.parameters())}")
     optimizer = init_optimizer(raw_model, mesh, ddp, hp, args)
     scheduler = torch.optim.lr_scheduler.LambdaLR(
@@ -468,6 +480,14 @@ def main(argv: Optional[List[str]] = None) -> None:
     tot_fb = tot_opt = tot_all = 0.0
     timed = 0
     x, y = train_loader.next_batch()
+    gstep = None
+    if graph_step:
+        from .parallel.graph_step import GraphedTrainStep
+
+        sync_pg = dist.group.WORLD if (world > 1 and not hp.replicate_mesh_grad_sync) else None
+        gstep = GraphedTrainStep(lambda a, b: raw_model(a, b), list(raw_model.parameters()),
+                                 optimizer, [x, y], device=device, process_group=sync_pg,
+                                 warmup=3)
     for step in range(start_step, hp.num_iterations + 1):
         last = step == hp.num_iterations
         if hp.val_loss_every > 0 and (last or step % hp.val_loss_every == 0):
@@ -498,6 +518,23 @@ def main(argv: Optional[List[str]] = None) -> None:
         if step == start_step + 10:  # discard warm-up steps from the averages
             tot_fb = tot_opt = tot_all = 0.0
             timed = 0
+        if gstep is not None:
+            timer_all.start()
+            train_loss = gstep(x, y).clone()
+            scheduler.step()
+            x, y = train_loader.next_batch()
+            if args.time_optimizer:
+                tot_all += max_over_ranks(timer_all.stop(), device)
+                timed += 1
+            if wandb:
+                wandb.log({"train/loss": train_loss.item(), "step": step})
+            if args.debug:
+                print0(f"Step {step}: train_loss={train_loss.item():.4f}")
+            if ckpt and hp.checkpoint_freq > 0 and step % hp.checkpoint_freq == 0 and step > 0:
+                if hasattr(optimizer, "synchronize_for_checkpoint"):
+                    optimizer.synchronize_for_checkpoint()
+                ckpt.save(step)
+            continue
         timer_all.start()
         timer_fb.start()
         for micro in range(1, grad_accum + 1):
@@ -550,6 +587,8 @@ def main(argv: Optional[List[str]] = None) -> None:
         print0(f"Peak memory consumption: {torch.cuda.max_memory_allocated() // 1024 // 1024} MiB")
     if hasattr(stepper, "release"):
         stepper.release()
+    if gstep is not None:
+        gstep.release()
     dist.destroy_process_group()
 
 

@@ -146,3 +146,24 @@ def test_cuda_graph_optimizer_matches_eager(name):
     # a bf16 rounding of the orthogonalized update (about lr * 2^-8 per step).
     for a, b in zip(eager, graphed):
         assert torch.allclose(a, b, atol=1e-3, rtol=1e-3)
+
+
+@pytest.mark.gpu
+def test_trainer_with_graph_step_runs_and_loss_falls():
+    """`train.py --graph_step` on one GPU: the captured step trains (repeated synthetic data)."""
+    import os
+    import re
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--standalone", "--local-addr",
+           "127.0.0.1", "--nproc-per-node", "1", os.path.join(root, "train.py"),
+           "--synthetic", "--no_wandb", "--debug", "--model_dim", "128", "--n_layer", "2",
+           "--n_head", "2", "--sequence_length", "64", "--batch_size", "8",
+           "--device_batch_size", "8", "--val_loss_every", "0", "--scalar_opt", "adamw",
+           "--optimizer", "muon", "--num_iterations", "12", "--graph_step"]
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=600, cwd=root)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
+    losses = [float(m) for m in re.findall(r"train_loss=([0-9.]+)", res.stdout)]
+    assert len(losses) == 12
+    assert all(l == l and l < 20 for l in losses)
