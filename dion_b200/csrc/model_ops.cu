@@ -322,12 +322,24 @@ __global__ void ce_count_kernel(const long long* tgt, long long n, int ignore_in
 }
 
 constexpr int kCeThreads = 512;
+constexpr float kLog2e = 1.4426950408889634f;
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 
+// One block per row.  Pass 1: online (max, sum of exp) over 8-element vectors; pass 2 (optional):
+// d(loss)/d(logits) = (softmax - onehot) / count written over the logits.  The exponentials are
+// taken in base 2 on pre-scaled arguments (one FFMA + one EX2 each); the dtype is a template
+// parameter and the target column is patched per vector, not compared per element, because the
+// kernel is bound by instruction issue and the special-function unit, not by memory.
+template <int DT>
 __global__ void __launch_bounds__(kCeThreads)
-ce_fwd_bwd_kernel(void* L, int dt, const long long* tgt, long long n, int V, long long ld,
+ce_fwd_bwd_kernel(void* L, const long long* tgt, long long n, int V, long long ld,
                   int ignore_index, float* losses, const float* count, int write_grad) {
   __shared__ float s_m[kCeThreads / 32], s_s[kCeThreads / 32];
-  __shared__ float s_lse;
+  __shared__ float s_lse2;
   const long long row = blockIdx.x;
   const long long base = row * ld;
   const long long target = tgt[row];
@@ -337,57 +349,59 @@ ce_fwd_bwd_kernel(void* L, int dt, const long long* tgt, long long n, int V, lon
     if (threadIdx.x == 0) losses[row] = 0.f;
     if (write_grad) {
       float z[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-      for (int j = threadIdx.x; j < nvec; j += kCeThreads) store8(L, dt, base + j * 8, z);
+      for (int j = threadIdx.x; j < nvec; j += kCeThreads) store8(L, DT, base + j * 8, z);
     }
     return;
   }
+  // m, s in the base-2 domain: m = max(x) * log2(e), s = sum 2^(x*log2e - m).
   float m = -INFINITY, s = 0.f;
   for (int j = threadIdx.x; j < nvec; j += kCeThreads) {
     float v[8];
-    load8(L, dt, base + j * 8, v);
+    load8(L, DT, base + j * 8, v);
     float vm = v[0];
 #pragma unroll
     for (int e = 1; e < 8; ++e) vm = fmaxf(vm, v[e]);
-    const float nm = fmaxf(m, vm);
+    const float nm = fmaxf(m, vm * kLog2e);
     float acc = 0.f;
 #pragma unroll
-    for (int e = 0; e < 8; ++e) acc += __expf(v[e] - nm);
-    s = s * __expf(m - nm) + acc;
+    for (int e = 0; e < 8; ++e) acc += fast_exp2(fmaf(v[e], kLog2e, -nm));
+    s = s * fast_exp2(m - nm) + acc;
     m = nm;
   }
-  // combine (m, s) pairs across the block
   const float wm = warp_max(m);
-  s = warp_sum(m == -INFINITY ? 0.f : s * __expf(m - wm));
+  s = warp_sum(m == -INFINITY ? 0.f : s * fast_exp2(m - wm));
   if (lane == 0) { s_m[warp] = wm; s_s[warp] = s; }
   __syncthreads();
   if (warp == 0) {
     float mm = lane < kCeThreads / 32 ? s_m[lane] : -INFINITY;
     float ssum = lane < kCeThreads / 32 ? s_s[lane] : 0.f;
     const float bm = warp_max(mm);
-    ssum = warp_sum(mm == -INFINITY ? 0.f : ssum * __expf(mm - bm));
-    if (lane == 0) s_lse = bm + logf(ssum);
+    ssum = warp_sum(mm == -INFINITY ? 0.f : ssum * fast_exp2(mm - bm));
+    if (lane == 0) s_lse2 = bm + log2f(ssum);   // log2 of the sum of exp(x)
   }
   __syncthreads();
-  const float lse = s_lse;
+  const float lse2 = s_lse2;
   if (threadIdx.x == 0) {
-    const float xt = dt == DT_F32
+    const float xt = DT == DT_F32
                          ? reinterpret_cast<const float*>(L)[base + target]
                          : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(L)[base + target]);
-    losses[row] = lse - xt;
+    losses[row] = lse2 * 0.6931471805599453f - xt;
   }
   if (!write_grad) return;
   __syncthreads();  // the target logit has been read before it is overwritten
   const float inv = 1.f / fmaxf(*count, 1.f);
+  const int tj = (int)(target >> 3), te = (int)(target & 7);
   for (int j = threadIdx.x; j < nvec; j += kCeThreads) {
     float v[8];
-    load8(L, dt, base + j * 8, v);
+    load8(L, DT, base + j * 8, v);
 #pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      float g = __expf(v[e] - lse);
-      if ((long long)j * 8 + e == target) g -= 1.f;
-      v[e] = g * inv;
+    for (int e = 0; e < 8; ++e) v[e] = fast_exp2(fmaf(v[e], kLog2e, -lse2)) * inv;
+    if (j == tj) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e)
+        if (e == te) v[e] -= inv;
     }
-    store8(L, dt, base + j * 8, v);
+    store8(L, DT, base + j * 8, v);
   }
 }
 
@@ -527,8 +541,12 @@ DION_EXPORT int dion_ce_fwd_bwd(void* L, int dt, const void* tgt, long long n, i
                                 int write_grad, void* stream) {
   if (n <= 0) return 0;
   if (V % 8 || ld % 8) return -2;
-  ce_fwd_bwd_kernel<<<(unsigned)n, kCeThreads, 0, S(stream)>>>(
-      L, dt, static_cast<const long long*>(tgt), n, V, ld, ignore_index, losses, count, write_grad);
+  if (dt == DT_F32)
+    ce_fwd_bwd_kernel<DT_F32><<<(unsigned)n, kCeThreads, 0, S(stream)>>>(
+        L, static_cast<const long long*>(tgt), n, V, ld, ignore_index, losses, count, write_grad);
+  else
+    ce_fwd_bwd_kernel<DT_BF16><<<(unsigned)n, kCeThreads, 0, S(stream)>>>(
+        L, static_cast<const long long*>(tgt), n, V, ld, ignore_index, losses, count, write_grad);
   return rc();
 }
 DION_EXPORT int dion_scale_unless_one(void* X, int dt, long long n, const float* scale,
