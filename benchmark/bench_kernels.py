@@ -38,7 +38,10 @@ def hbm_peak() -> float:
 _flush = None
 
 
-def timed(fn, iters=10, warmup=3):
+def timed(fn, iters=10, warmup=3, inner=4):
+    """Mean time of one call; ``inner`` calls are queued back to back per measurement so that
+    short kernels are not timed by the host's launch latency (their working sets are several
+    times the L2, so the calls do not feed each other from cache)."""
     global _flush
     if _flush is None:
         _flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
@@ -50,10 +53,11 @@ def timed(fn, iters=10, warmup=3):
         _flush.zero_()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        fn()
+        for _ in range(inner):
+            fn()
         e1.record()
         torch.cuda.synchronize()
-        total += e0.elapsed_time(e1)
+        total += e0.elapsed_time(e1) / inner
     return total / iters
 
 

@@ -110,14 +110,23 @@ rmsnorm_bwd_kernel(const void* X, int x_dt, const void* DY, int dy_dt, const flo
   const long long base = row * D;
   const int nvec = D / 8;
   const float r = rstd[row];
-  float x[VPL][8], g[VPL][8];
+  float x[VPL][8], g[VPL][8], gx[VPL][8];
   float dot = 0.f;
+  // All loads of the row (x, dy and the residual-path gradient) are issued before the first use,
+  // so one memory latency covers them.
 #pragma unroll
   for (int i = 0; i < VPL; ++i) {
     const int j = lane + 32 * i;
     if (j < nvec) {
       load8(X, x_dt, base + j * 8, x[i]);
       load8(DY, dy_dt, base + j * 8, g[i]);
+      if (GX) load8(GX, x_dt, base + j * 8, gx[i]);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) {
+    const int j = lane + 32 * i;
+    if (j < nvec) {
 #pragma unroll
       for (int e = 0; e < 8; ++e) dot += g[i][e] * x[i][e];
     }
@@ -131,10 +140,8 @@ rmsnorm_bwd_kernel(const void* X, int x_dt, const void* DY, int dy_dt, const flo
 #pragma unroll
       for (int e = 0; e < 8; ++e) o[e] = r * (g[i][e] - x[i][e] * r * dot);
       if (GX) {
-        float gx[8];
-        load8(GX, x_dt, base + j * 8, gx);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) o[e] += gx[e];
+        for (int e = 0; e < 8; ++e) o[e] += gx[i][e];
       }
       store8(DX, x_dt, base + j * 8, o);
       if (DX2) store8(DX2, DT_BF16, base + j * 8, o);
@@ -433,6 +440,7 @@ static inline unsigned grid_for(long long n8) {
 #define DION_VPL_DISPATCH(D_, CALL)                              \
   if ((D_) <= 256) { constexpr int VPL = 1; CALL; }              \
   else if ((D_) <= 512) { constexpr int VPL = 2; CALL; }         \
+  else if ((D_) <= 768) { constexpr int VPL = 3; CALL; }         \
   else if ((D_) <= 1024) { constexpr int VPL = 4; CALL; }        \
   else if ((D_) <= 2048) { constexpr int VPL = 8; CALL; }        \
   else if ((D_) <= 4096) { constexpr int VPL = 16; CALL; }       \
