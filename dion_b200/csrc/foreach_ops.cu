@@ -84,6 +84,22 @@ __device__ __forceinline__ bool aligned4(const void* p, int dt) {
   return (reinterpret_cast<uintptr_t>(p) & (dt == DT_F32 ? 15 : 7)) == 0;
 }
 
+// 8 bf16 elements (16 bytes) at once.
+__device__ __forceinline__ void ld8b(const void* p, long long i, float (&v)[8]) {
+  const uint4 u = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p) + i);
+  const float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z),
+               d = unpack_bf16x2(u.w);
+  v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y; v[4] = c.x; v[5] = c.y; v[6] = d.x; v[7] = d.y;
+}
+__device__ __forceinline__ void st8b(void* p, long long i, const float (&v)[8]) {
+  *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p) + i) =
+      make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]),
+                 pack_bf16x2(v[6], v[7]));
+}
+__device__ __forceinline__ bool aligned16(const void* p) {
+  return (reinterpret_cast<uintptr_t>(p) & 15) == 0;
+}
+
 __device__ __forceinline__ float block_sum(float v) {
   __shared__ float red[kThreads / 32];
 #pragma unroll
@@ -129,6 +145,50 @@ muon_pre_kernel(const long long* raw, int g_dt, int m_dt, float mu, int nesterov
     G = tb.ptr(0, t0); M = tb.ptr(1, t0); U = tb.ptr(2, t0);
   }
   const bool vg = aligned4(G, g_dt), vm = aligned4(M, m_dt), vu = aligned4(U, DT_BF16);
+  // All-bf16, 16-byte aligned tensors whose size is a multiple of 8: 16-byte accesses, and the
+  // loads of both halves of the chunk are issued before either is used.
+  if (g_dt == DT_BF16 && m_dt == DT_BF16 && aligned16(G) && aligned16(M) &&
+      (U == nullptr || aligned16(U))) {
+    const int t = find_tensor(tb, blockIdx.x);
+    const long long numel = tb.numel(t);
+    if ((numel & 7) == 0) {
+      const long long base = ((long long)blockIdx.x - tb.prefix()[t]) * kChunk;
+      const long long end = (base + kChunk < numel) ? base + kChunk : numel;
+      const long long i0 = base + (long long)threadIdx.x * 8;
+      const long long i1 = i0 + kThreads * 8;
+      float g0[8], m0[8], g1[8], m1[8];
+      const bool h0 = i0 < end, h1 = i1 < end;
+      if (h0) { ld8b(G, i0, g0); ld8b(M, i0, m0); }
+      if (h1) { ld8b(G, i1, g1); ld8b(M, i1, m1); }
+      auto body = [&](float (&g)[8], float (&m)[8], long long i) {
+        float u[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const float gk = g[k];
+          float mk = add_only ? (m[k] + gk) : (mu * m[k] + gk);
+          mk = round_to(mk, DT_BF16);
+          m[k] = mk;
+          float uk = (nesterov && !add_only) ? (mu * mk + gk) : mk;
+          uk = round_to(uk, DT_BF16);
+          u[k] = uk;
+          acc += uk * uk;
+        }
+        st8b(M, i, m);
+        if (U) st8b(U, i, u);
+      };
+      if (h0) body(g0, m0, i0);
+      if (h1) body(g1, m1, i1);
+      if (sumsq) {
+        const float s = block_sum(acc);
+        if (threadIdx.x == 0) atomicAdd(&sumsq[t], s);
+      } else if (sumsq_in_table) {
+        float* target = reinterpret_cast<float*>(tb.ptr(3, t));
+        const float s = block_sum(acc);
+        if (threadIdx.x == 0 && target != nullptr) atomicAdd(target, s);
+      }
+      return;
+    }
+  }
   DION_CHUNK_LOOP(tb, {
     float g[4], m[4], u[4];
     if (full) {
@@ -238,6 +298,38 @@ muon_post_kernel(const long long* raw, const ApplyArgs a) {
     step *= nu / nn;
   }
   const bool vx = aligned4(X, a.x_dt), vu = aligned4(U, DT_BF16);
+  if (a.x_dt == DT_BF16 && aligned16(X) && aligned16(U) && (rs == nullptr || (a.cols & 7) == 0)) {
+    const long long numel = tb.numel(tt);
+    if ((numel & 7) == 0) {
+      const long long base = ((long long)blockIdx.x - tb.prefix()[tt]) * kChunk;
+      const long long end = (base + kChunk < numel) ? base + kChunk : numel;
+      const long long i0 = base + (long long)threadIdx.x * 8;
+      const long long i1 = i0 + kThreads * 8;
+      float x0[8], u0[8], x1[8], u1[8];
+      const bool h0 = i0 < end, h1 = i1 < end;
+      if (h0) { ld8b(X, i0, x0); ld8b(U, i0, u0); }
+      if (h1) { ld8b(X, i1, x1); ld8b(U, i1, u1); }
+      auto body = [&](float (&x)[8], float (&u)[8], long long i) {
+        const float rsv = rs ? rs[i / a.cols] : 1.f;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const float uk = u[k] * rsv;
+          float xk = x[k];
+          if (a.cautious) {
+            const float prod = xk * uk;
+            xk = (prod >= 0.f) ? (xk - xk * coeff) : xk;
+          } else {
+            xk = xk * decay;
+          }
+          x[k] = xk - step * uk;
+        }
+        st8b(X, i, x);
+      };
+      if (h0) body(x0, u0, i0);
+      if (h1) body(x1, u1, i1);
+      return;
+    }
+  }
   DION_CHUNK_LOOP(tb, {
     float x[4], u[4];
     if (full) {
