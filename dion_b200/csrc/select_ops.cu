@@ -295,13 +295,31 @@ gather_rows_kernel(const long long* ptrs, int n, int cols, int m_dt, const long 
                                : U + (long long)t * u_stride;
   __nv_bfloat16* u = base + (long long)j * cols;
   float acc = 0.f;
-  for (int c = threadIdx.x; c < cols; c += 256) {
-    const float m = ldv(M, m_dt, off + c);
-    const __nv_bfloat16 b = __float2bfloat16_rn(m);
-    u[c] = b;
-    const float f = __bfloat162float(b);
-    acc += f * f;
-    if (ef_apply) stv(M, m_dt, off + c, m * ef);
+  if ((cols & 7) == 0 && aligned16(M) && aligned16(u)) {
+    for (int c = threadIdx.x * 8; c < cols; c += 256 * 8) {
+      float m[8], o[8];
+      ld8v(M, m_dt, off + c, m);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        o[e] = __bfloat162float(__float2bfloat16_rn(m[e]));
+        acc += o[e] * o[e];
+      }
+      st8v(u, DT_BF16, c, o);
+      if (ef_apply) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) m[e] *= ef;
+        st8v(M, m_dt, off + c, m);
+      }
+    }
+  } else {
+    for (int c = threadIdx.x; c < cols; c += 256) {
+      const float m = ldv(M, m_dt, off + c);
+      const __nv_bfloat16 b = __float2bfloat16_rn(m);
+      u[c] = b;
+      const float f = __bfloat162float(b);
+      acc += f * f;
+      if (ef_apply) stv(M, m_dt, off + c, m * ef);
+    }
   }
   if (ss_ptrs) {
     for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);

@@ -23,12 +23,19 @@ import torch.nn.functional as tF
 from torch import Tensor
 
 from ..ops import _backend
+from ..utils.tensors import is_plain_tensor, materialize, unwrap
 
 _DT = {torch.float32: 0, torch.bfloat16: 1}
 
 
 def _c(t: Optional[Tensor]):
-    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+    if t is None:
+        return ctypes.c_void_p(0)
+    ptr = t.data_ptr()
+    if ptr == 0 and t.numel():
+        # e.g. a wrapper tensor subclass without storage of its own: never give a kernel address 0
+        raise RuntimeError(f"{type(t).__name__} has no device storage to hand to a kernel")
+    return ctypes.c_void_p(ptr)
 
 
 def _stream(dev):
@@ -77,6 +84,7 @@ class _RMSNorm(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dy: Tensor):
+        dy = unwrap(dy)
         x2, rstd = ctx.saved_tensors
         rows, D = x2.shape
         dy2 = _rows(dy)
@@ -111,6 +119,7 @@ class _AddRMSNorm(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, g_x: Tensor, g_h: Tensor):
+        g_x, g_h = unwrap(g_x), unwrap(g_h)
         x_new, rstd = ctx.saved_tensors
         rows, D = x_new.shape
         gx2 = _rows(g_x) if g_x is not None else None
@@ -128,12 +137,14 @@ class _AddRMSNorm(torch.autograd.Function):
 
 
 def _norm_kernel_ok(x: Tensor) -> bool:
-    return x.is_cuda and x.dtype in _DT and x.size(-1) % 8 == 0 and x.size(-1) <= 4096
+    return (is_plain_tensor(x) and x.is_cuda and x.dtype in _DT and x.size(-1) % 8 == 0
+            and x.size(-1) <= 4096)
 
 
 def rms_norm(x: Tensor, eps: Optional[float] = None) -> Tensor:
     """``x * rsqrt(mean(x**2, -1) + eps)``; ``eps`` defaults to the machine epsilon of ``x``'s
     dtype, as in ``torch.nn.functional.rms_norm``."""
+    x = materialize(x)
     if _norm_kernel_ok(x):
         out_dtype = torch.bfloat16 if _autocast_bf16(x) else x.dtype
         return _RMSNorm.apply(x, _eps_for(x.dtype) if eps is None else eps, out_dtype)
@@ -143,7 +154,9 @@ def rms_norm(x: Tensor, eps: Optional[float] = None) -> Tensor:
 def add_rms_norm(x: Tensor, delta: Tensor, eps: Optional[float] = None) -> Tuple[Tensor, Tensor]:
     """``(x + delta, rms_norm(x + delta))``: the residual update of a transformer block together
     with the normalisation that feeds the next sub-layer."""
-    if _norm_kernel_ok(x) and delta.is_cuda and delta.dtype in _DT and delta.shape == x.shape:
+    x, delta = materialize(x), materialize(delta)
+    if (_norm_kernel_ok(x) and is_plain_tensor(delta) and delta.is_cuda and delta.dtype in _DT
+            and delta.shape == x.shape):
         out_dtype = torch.bfloat16 if _autocast_bf16(x) else x.dtype
         return _AddRMSNorm.apply(x, delta, _eps_for(x.dtype) if eps is None else eps, out_dtype)
     x = x + delta
@@ -193,6 +206,7 @@ class _RopeQKNorm(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dqo: Tensor, dko: Tensor):
+        dqo, dko = unwrap(dqo), unwrap(dko)
         q, k, cos, sin, rstd = ctx.saved_tensors
         B, T, H, D = q.shape
         dqo, dko = dqo.contiguous(), dko.contiguous()
@@ -208,8 +222,10 @@ class _RopeQKNorm(torch.autograd.Function):
 def rope_qknorm(q: Tensor, k: Tensor, cos: Tensor, sin: Tensor) -> Tuple[Tensor, Tensor]:
     """Rotary embedding (``cos/sin``: ``[T, D/2]``) then RMS-norm over the last dim, for ``q``
     and ``k`` of shape ``[B, T, H, D]``."""
+    q, k = materialize(q), materialize(k)
     D = q.size(-1)
-    if (q.is_cuda and q.dtype == torch.bfloat16 and k.dtype == torch.bfloat16
+    if (is_plain_tensor(q) and is_plain_tensor(k) and q.is_cuda and q.dtype == torch.bfloat16
+            and k.dtype == torch.bfloat16
             and D in (32, 64, 128, 256) and cos.dtype == torch.bfloat16 and q.shape == k.shape
             and cos.is_contiguous() and sin.is_contiguous()):
         return _RopeQKNorm.apply(q, k, cos, sin, _eps_for(torch.bfloat16))
@@ -253,6 +269,7 @@ class _QKVRope(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dqo: Tensor, dko: Tensor, dv: Tensor):
+        dqo, dko, dv = unwrap(dqo), unwrap(dko), unwrap(dv)
         h2, W, qkv, cos, sin, rstd = ctx.saved_tensors
         B, T, C, H, D = ctx.dims
         dqkv = torch.empty_like(qkv)
@@ -278,9 +295,11 @@ def qkv_rope(h: Tensor, wq: Tensor, wk: Tensor, wv: Tensor, cos: Tensor, sin: Te
     """``(q, k, v)`` of shape ``[B, T, H, D]`` from the normalized hidden state ``h [B, T, C]``:
     the three projections, rotary embedding and QK RMS-norm (q and k are contiguous, v is a
     strided view of the projection output)."""
+    h = materialize(h)
     B, T, C = h.shape
     D = C // n_head
-    if (h.is_cuda and h.dtype == torch.bfloat16 and D in (32, 64, 128, 256) and C % 8 == 0
+    if (is_plain_tensor(h) and is_plain_tensor(wq) and is_plain_tensor(wk) and is_plain_tensor(wv)
+            and h.is_cuda and h.dtype == torch.bfloat16 and D in (32, 64, 128, 256) and C % 8 == 0
             and cos.dtype == torch.bfloat16 and cos.is_contiguous() and sin.is_contiguous()
             and wq.shape == wk.shape == wv.shape == (C, C)):
         return _QKVRope.apply(h, wq, wk, wv, cos, sin, n_head, _eps_for(torch.bfloat16))
@@ -306,6 +325,7 @@ class _Embedding(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dy: Tensor):
+        dy = unwrap(dy)
         (idx,) = ctx.saved_tensors
         V, C = ctx.wshape
         flat = idx.reshape(-1)
@@ -321,7 +341,9 @@ class _Embedding(torch.autograd.Function):
 
 
 def embedding(idx: Tensor, weight: Tensor) -> Tensor:
-    if (weight.is_cuda and weight.dtype == torch.float32 and weight.size(1) % 8 == 0
+    idx = materialize(idx)
+    if (is_plain_tensor(idx) and is_plain_tensor(weight) and weight.is_cuda
+            and weight.dtype == torch.float32 and weight.size(1) % 8 == 0
             and idx.dtype == torch.int64 and weight.requires_grad and torch.is_grad_enabled()):
         return _Embedding.apply(idx, weight)
     return tF.embedding(idx, weight)
@@ -342,6 +364,7 @@ class _LinearBF16(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dy: Tensor):
+        dy = unwrap(dy)
         x2, wb = ctx.saved_tensors
         dy2 = dy.reshape(-1, dy.size(-1))
         dx = torch.mm(dy2, wb).view(ctx.xshape) if ctx.needs_input_grad[0] else None
@@ -352,8 +375,9 @@ class _LinearBF16(torch.autograd.Function):
 def linear(x: Tensor, weight: Tensor) -> Tensor:
     """Bias-free linear layer.  Under bf16 autocast on a GPU (bf16 activations, fp32 weight) the
     mixed-precision form above is used; otherwise ``torch.nn.functional.linear``."""
-    if (x.is_cuda and x.dtype == torch.bfloat16 and weight.dtype == torch.float32
-            and type(weight) in (Tensor, torch.nn.Parameter) and x.size(-1) % 8 == 0
+    x = materialize(x)
+    if (is_plain_tensor(x) and x.is_cuda and x.dtype == torch.bfloat16
+            and weight.dtype == torch.float32 and is_plain_tensor(weight) and x.size(-1) % 8 == 0
             and weight.size(0) % 8 == 0):
         return _LinearBF16.apply(x, weight)
     return tF.linear(x, weight)
@@ -381,6 +405,7 @@ class _MLPRelu2(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dy: Tensor):
+        dy = unwrap(dy)
         from ..ops import gemm
         x2, act, wfb, wpb = ctx.saved_tensors
         dy2 = dy.reshape(-1, dy.size(-1))
@@ -400,8 +425,9 @@ def mlp_relu2(h: Tensor, wfc: Tensor, wproj: Tensor) -> Tensor:
     GPT-160M training step the fused form is slower (39.2 against 35.8 ms per step) although
     it saves two element-wise passes, because at K = 768 the two-CTA kernel is bound by operand
     traffic from L2 (no multicast loads) and trails the library GEMM by about 10 %."""
-    if (h.is_cuda and h.dtype == torch.bfloat16 and type(wfc) in (Tensor, torch.nn.Parameter)
-            and type(wproj) in (Tensor, torch.nn.Parameter)
+    h = materialize(h)
+    if (is_plain_tensor(h) and h.is_cuda and h.dtype == torch.bfloat16 and is_plain_tensor(wfc)
+            and is_plain_tensor(wproj)
             and wfc.dtype in (torch.float32, torch.bfloat16) and wfc.dtype == wproj.dtype
             and h.size(-1) % 8 == 0 and wfc.size(0) % 8 == 0 and wfc.size(0) > 128
             and h.numel() // h.size(-1) > 128 and fused_mlp_enabled()):
@@ -429,6 +455,7 @@ class _Relu2(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dy: Tensor):
+        dy = unwrap(dy)
         (x,) = ctx.saved_tensors
         dy = dy.contiguous()
         dx = torch.empty_like(x)
@@ -439,7 +466,8 @@ class _Relu2(torch.autograd.Function):
 
 
 def relu2(x: Tensor) -> Tensor:
-    if x.is_cuda and x.dtype in _DT and x.numel() % 8 == 0:
+    x = materialize(x)
+    if is_plain_tensor(x) and x.is_cuda and x.dtype in _DT and x.numel() % 8 == 0:
         return _Relu2.apply(x)
     return tF.relu(x).square()
 
@@ -471,6 +499,7 @@ class _CrossEntropy(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dloss: Tensor):
+        dloss = unwrap(dloss)
         (grad,) = ctx.saved_tensors
         # The upstream gradient is 1 for a plain ``loss.backward()``: the kernel reads it on the
         # device and returns at once in that case, otherwise it rescales the stored gradient.
@@ -484,7 +513,9 @@ class _CrossEntropy(torch.autograd.Function):
 def cross_entropy(logits: Tensor, targets: Tensor, ignore_index: int = -1) -> Tensor:
     """Mean cross entropy over the rows whose target is not ``ignore_index``; softmax
     arithmetic in fp32 regardless of the logits' dtype."""
-    if (logits.is_cuda and logits.dtype in _DT and logits.ndim == 2 and logits.stride(1) == 1
+    logits, targets = materialize(logits), materialize(targets)
+    if (is_plain_tensor(logits) and is_plain_tensor(targets) and logits.is_cuda
+            and logits.dtype in _DT and logits.ndim == 2 and logits.stride(1) == 1
             and logits.size(1) % 8 == 0):
         return _CrossEntropy.apply(logits, targets, ignore_index)
     return tF.cross_entropy(logits.float(), targets, ignore_index=ignore_index)

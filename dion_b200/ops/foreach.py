@@ -20,6 +20,7 @@ import torch
 from torch import Tensor
 
 from . import _backend
+from ..utils.tensors import is_plain_tensor
 from .tables import RawPointer, build_table
 
 Scalar = Union[float, Tensor]
@@ -43,7 +44,7 @@ def _kernel_ok(*lists: Sequence[Tensor]) -> bool:
         for t in lst:
             if t is None or isinstance(t, RawPointer):
                 continue
-            if t.dtype not in _DT or not t.is_contiguous():
+            if not is_plain_tensor(t) or t.dtype not in _DT or not t.is_contiguous():
                 return False
     return True
 

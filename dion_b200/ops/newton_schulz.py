@@ -26,6 +26,7 @@ from typing import Callable, Optional, Sequence, Tuple
 import torch
 from torch import Tensor
 
+from ..utils.tensors import unwrap
 from . import foreach as F
 from . import gemm
 
@@ -132,6 +133,7 @@ def _gram_torch(G: Tensor, coeffs: Coeffs, norm_mult: float, epsilon: float,
 def _prepare_cuda(G: Tensor, allow_tall: bool = False):
     """-> (X [B, m, n] bf16 contiguous with m, n multiples of 8, restore).  Tall inputs are
     transposed to wide unless ``allow_tall`` (the caller then iterates in right-multiply form)."""
+    G = unwrap(G)  # a pending functional collective must complete before its address is used
     shape = G.shape
     X = G.to(torch.bfloat16)
     if X.ndim == 2:

@@ -86,7 +86,12 @@ class RawPointer:
 
 
 def _ptr(t) -> int:
-    return 0 if t is None else t.data_ptr()
+    if t is None:
+        return 0
+    ptr = t.data_ptr()
+    if ptr == 0 and not isinstance(t, RawPointer) and t.numel():
+        raise RuntimeError(f"{type(t).__name__} has no device storage to hand to a kernel")
+    return ptr
 
 
 def build_table(

@@ -24,11 +24,58 @@ def as_scalar_tensor(value) -> Tensor:
     return value if isinstance(value, Tensor) else torch.tensor(value)
 
 
+def unwrap(t):
+    """Complete a pending functional collective and return the ordinary tensor behind an
+    ``AsyncCollectiveTensor`` (what tensor-parallel layers and ``DTensor.to_local()`` hand out
+    after an all-reduce / all-gather); anything else passes through.  The kernels of this package
+    take raw device pointers, which bypasses the operator dispatch that would otherwise wait.
+    Not differentiable: for use in optimizer code and inside autograd ``Function`` bodies."""
+    if type(t) is Tensor or t is None:
+        return t
+    try:
+        from torch.distributed._functional_collectives import AsyncCollectiveTensor
+    except Exception:  # pragma: no cover - torch without functional collectives
+        return t
+    if isinstance(t, AsyncCollectiveTensor):
+        return t.trigger_wait()
+    return t
+
+
+class _Wait(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, t):
+        return unwrap(t)
+
+    @staticmethod
+    def backward(ctx, grad):
+        return grad
+
+
+def materialize(t):
+    """Differentiable form of :func:`unwrap` for activations."""
+    if type(t) is Tensor or t is None:
+        return t
+    try:
+        from torch.distributed._functional_collectives import AsyncCollectiveTensor
+    except Exception:  # pragma: no cover
+        return t
+    if isinstance(t, AsyncCollectiveTensor):
+        return _Wait.apply(t)
+    return t
+
+
+def is_plain_tensor(t) -> bool:
+    """True for ordinary tensors / parameters (no DTensor, no wrapper subclass): only those may
+    be handed to a kernel by address."""
+    return type(t) is Tensor or type(t) is torch.nn.Parameter
+
+
 def to_local(x: TensorOrList) -> TensorOrList:
-    """Local shard(s) of DTensor(s); plain tensors pass through."""
+    """Local shard(s) of DTensor(s), with pending collectives completed; plain tensors pass
+    through."""
     if isinstance(x, Tensor):
-        return x.to_local() if isinstance(x, DTensor) else x
-    return [t.to_local() if isinstance(t, DTensor) else t for t in x]
+        return unwrap(x.to_local() if isinstance(x, DTensor) else x)
+    return [unwrap(t.to_local() if isinstance(t, DTensor) else t) for t in x]
 
 
 def dtensor_from_local(x: TensorOrList, ref: Tensor) -> TensorOrList:

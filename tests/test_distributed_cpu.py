@@ -168,3 +168,31 @@ def test_dion_distributed_modes_run_and_descend(tmp_path, modes, world):
             assert a.shape == b.shape and torch.isfinite(b).all(), mode
             assert (a - b).abs().max().item() > 0, mode
         assert qs[0][1] == 8, mode  # r = ceil(0.25 * 32)
+
+
+def _wrapper_tensor_worker(rank, world):
+    """Results of functional collectives are lazy wrapper tensors; code that hands addresses to
+    kernels has to complete and unwrap them first, without cutting the autograd graph."""
+    import torch.distributed._functional_collectives as fc
+    from dion_b200.models import functional as Fn
+    from dion_b200.utils.tensors import is_plain_tensor, materialize, to_local, unwrap
+
+    x = torch.full((4, 8), float(rank + 1), requires_grad=True)
+    y = fc.all_reduce(x * 2.0, "sum", dist.group.WORLD)
+    assert isinstance(y, fc.AsyncCollectiveTensor) and not is_plain_tensor(y)
+    z = materialize(y)
+    assert is_plain_tensor(z)
+    assert torch.equal(z.detach(), torch.full((4, 8), 2.0 * sum(range(1, world + 1))))
+    z.sum().backward()
+    assert x.grad is not None and torch.isfinite(x.grad).all() and x.grad.abs().sum() > 0
+    w = fc.all_reduce(torch.ones(3), "sum", dist.group.WORLD)
+    assert is_plain_tensor(unwrap(w)) and is_plain_tensor(to_local([w])[0])
+    # The model functions accept the wrapper (fallback arithmetic on CPU) and differentiate.
+    h = fc.all_reduce(torch.randn(2, 4, 16), "sum", dist.group.WORLD)
+    out = Fn.rms_norm(h)
+    assert is_plain_tensor(out) and out.shape == (2, 4, 16)
+    return True
+
+
+def test_functional_collective_results_are_unwrapped(tmp_path):
+    run_ranks(_wrapper_tensor_worker, 2)
