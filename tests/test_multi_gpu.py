@@ -208,3 +208,24 @@ def test_dion_compressed_sync_through_symmetric_all_reduce(tmp_path):
             assert torch.allclose(a, b, atol=1e-5)
     for a, b in zip(out[False][0], out[True][0]):
         assert torch.allclose(a, b, atol=2e-3, rtol=1e-2)
+
+
+def test_trainer_dion_with_fsdp_and_tensor_parallel_on_gpus():
+    """`train.py` with fs=2 x tp=2 on four GPUs: tensor-parallel layers hand the model kernels
+    lazy collective results, which have to be completed before a kernel reads them."""
+    _need(4)
+    import re
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "4",
+           "--master-addr", "127.0.0.1", "--master-port", "29733", os.path.join(root, "train.py"),
+           "--synthetic", "--no_wandb", "--debug", "--model_dim", "256", "--n_layer", "2",
+           "--n_head", "4", "--sequence_length", "128", "--batch_size", "16",
+           "--device_batch_size", "4", "--val_loss_every", "0", "--scalar_opt", "adamw",
+           "--num_iterations", "3", "--optimizer", "dion", "--dp_size", "1", "--fs_size", "2",
+           "--tp_size", "2"]
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=600, cwd=root)
+    assert res.returncode == 0, res.stdout[-1500:] + res.stderr[-1500:]
+    losses = [float(m) for m in re.findall(r"train_loss=([0-9.]+)", res.stdout)]
+    assert len(losses) == 3 and all(l == l and l < 20 for l in losses)
