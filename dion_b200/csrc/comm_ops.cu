@@ -71,8 +71,7 @@ __global__ void scale_from_partials_kernel(float* partials, int n_mats, int n_sr
 //   multimem: one `multimem.ld_reduce` per vector (the NVSwitch adds the ranks' copies) and one
 //             `multimem.st` (the switch replicates the store), on the multicast address;
 //   peer    : plain loads from every peer's copy and plain stores to every peer's copy.
-// The caller brackets the kernel with flag barriers (every rank's input is in place before,
-// every slice has been written after).  dt: 0 = fp32, 1 = bf16 (accumulated in fp32).
+// dt: 0 = fp32, 1 = bf16 (accumulated in fp32).
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ float4 mm_ld_reduce_f32(const void* mc) {
   float4 v;
@@ -115,61 +114,7 @@ __device__ __forceinline__ uint4 scale_vec(uint4 v, int dt, float scale) {
   return v;
 }
 
-__global__ void __launch_bounds__(256)
-allreduce_multimem_kernel(char* mc_base, long long vec_begin, long long vec_end, int dt,
-                          float scale) {
-  for (long long i = vec_begin + (long long)blockIdx.x * 256 + threadIdx.x; i < vec_end;
-       i += (long long)gridDim.x * 256) {
-    char* p = mc_base + i * 16;
-    uint4 v;
-    if (dt == 0) {
-      const float4 f = mm_ld_reduce_f32(p);
-      v = make_uint4(__float_as_uint(f.x), __float_as_uint(f.y), __float_as_uint(f.z),
-                     __float_as_uint(f.w));
-    } else {
-      v = mm_ld_reduce_bf16(p);
-    }
-    mm_st_b32x4(p, scale_vec(v, dt, scale));
-  }
-}
-
-__global__ void __launch_bounds__(256)
-allreduce_peer_kernel(const long long* peer_bases, int world, long long vec_begin,
-                      long long vec_end, int dt, float scale) {
-  for (long long i = vec_begin + (long long)blockIdx.x * 256 + threadIdx.x; i < vec_end;
-       i += (long long)gridDim.x * 256) {
-    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    for (int r = 0; r < world; ++r) {
-      const uint4 u = *reinterpret_cast<const uint4*>(
-          reinterpret_cast<const char*>(peer_bases[r]) + i * 16);
-      if (dt == 0) {
-        acc[0] += __uint_as_float(u.x); acc[1] += __uint_as_float(u.y);
-        acc[2] += __uint_as_float(u.z); acc[3] += __uint_as_float(u.w);
-      } else {
-        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float2 f = unpack_bf16x2(w[e]);
-          acc[2 * e] += f.x; acc[2 * e + 1] += f.y;
-        }
-      }
-    }
-    uint4 out;
-    if (dt == 0) {
-      out = make_uint4(__float_as_uint(acc[0] * scale), __float_as_uint(acc[1] * scale),
-                       __float_as_uint(acc[2] * scale), __float_as_uint(acc[3] * scale));
-    } else {
-      out = make_uint4(pack_bf16x2(acc[0] * scale, acc[1] * scale),
-                       pack_bf16x2(acc[2] * scale, acc[3] * scale),
-                       pack_bf16x2(acc[4] * scale, acc[5] * scale),
-                       pack_bf16x2(acc[6] * scale, acc[7] * scale));
-    }
-    for (int r = 0; r < world; ++r)
-      *reinterpret_cast<uint4*>(reinterpret_cast<char*>(peer_bases[r]) + i * 16) = out;
-  }
-}
-
-// Single-launch form: the flag barriers are part of the kernel.  Block 0 tells every peer that
+// The flag barriers are part of the kernel (one launch per all-reduce).  Block 0 tells every peer that
 // this rank's input is in place (the kernel runs after its producers in stream order); every
 // block waits (bounded) for all peers' inputs, reduces its share of this rank's slice and
 // writes it everywhere; the block that finishes last publishes "slice written" to the peers,
@@ -308,28 +253,6 @@ DION_EXPORT int dion_scale_from_partials(float* partials, int n_mats, int n_src,
   if (n_mats <= 0) return 0;
   scale_from_partials_kernel<<<(n_mats + 127) / 128, 128, 0, S(stream)>>>(partials, n_mats, n_src,
                                                                           mult, eps, scale, clear);
-  return rc();
-}
-
-// Reduce 16-byte vectors [vec_begin, vec_end) of the symmetric buffer over all ranks and write
-// them back everywhere.  mc_base != 0 selects the multimem form; otherwise peer_bases (device
-// array of `world` base addresses) is used.
-DION_EXPORT int dion_allreduce_slice(void* mc_base, const void* peer_bases, int world,
-                                     long long vec_begin, long long vec_end, int dt, float scale,
-                                     int num_blocks, void* stream) {
-  if (vec_end <= vec_begin) return 0;
-  if (dt != 0 && dt != 1) return -2;
-  long long need = (vec_end - vec_begin + 255) / 256;
-  int blocks = (int)(need < (long long)num_blocks ? need : (long long)num_blocks);
-  if (blocks < 1) blocks = 1;
-  if (mc_base != nullptr) {
-    allreduce_multimem_kernel<<<blocks, 256, 0, S(stream)>>>(static_cast<char*>(mc_base),
-                                                             vec_begin, vec_end, dt, scale);
-  } else {
-    if (peer_bases == nullptr || world <= 0) return -2;
-    allreduce_peer_kernel<<<blocks, 256, 0, S(stream)>>>(
-        static_cast<const long long*>(peer_bases), world, vec_begin, vec_end, dt, scale);
-  }
   return rc();
 }
 
