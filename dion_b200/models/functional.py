@@ -248,9 +248,7 @@ class _QKVRope(torch.autograd.Function):
         D = C // n_head
         h2 = h.reshape(B * T, C)
         W = torch.empty((3 * C, C), dtype=h.dtype, device=h.device)
-        W[:C].copy_(wq)
-        W[C:2 * C].copy_(wk)
-        W[2 * C:].copy_(wv)
+        torch._foreach_copy_([W[:C], W[C:2 * C], W[2 * C:]], [wq, wk, wv])  # one launch, casts
         qkv = torch.mm(h2, W.t())                       # [B*T, 3C]
         q = qkv[:, :C]
         k = qkv[:, C:2 * C]

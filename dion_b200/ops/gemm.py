@@ -135,20 +135,45 @@ def pair_default() -> bool:
     return os.environ.get("DION_B200_PAIR_GEMM", "1") != "0"
 
 
-def _pair_eligible(M: int, N: int, batch: int, extra, out_t, out_f32, out, device) -> bool:
-    """The two-CTA kernel covers the plain bf16-output forms; it pays off once the 256 x 256
-    tiles fill the pairs of SMs about as well as 128 x 256 tiles fill single SMs."""
-    if extra is not None or out_t is not None or out_f32 is not None:
-        return False
-    if M <= 128 or N <= 128:
-        return False
-    pairs = sm_count(device) // 2
-    tiles2 = -(-M // 256) * -(-N // 256) * batch
-    tiles1 = -(-M // 128) * -(-N // 256) * batch
-    waves2 = -(-tiles2 // pairs)
-    waves1 = -(-tiles1 // sm_count(device))
-    # One pair tile costs about as much time as one single-CTA tile of half the rows.
-    return waves2 <= waves1
+def _num_tiles(M: int, N: int, bm: int, bn: int, sym: bool) -> int:
+    tm_n, tn_n = -(-M // bm), -(-N // bn)
+    if not sym:
+        return tm_n * tn_n
+    return sum(1 for tm in range(tm_n) for tn in range(tn_n) if (tn + 1) * bn - 1 >= tm * bm)
+
+
+_config_cache: Dict[Tuple, Tuple[bool, int]] = {}
+
+
+def _choose_config(M: int, N: int, K: int, batch: int, sym: bool, pair_ok: bool,
+                   device: torch.device) -> Tuple[bool, int]:
+    """-> (use the two-CTA kernel, BN of the single-CTA kernel).  Picks the tiling with the
+    smallest estimated time ``waves x tile size x (K / efficiency + fixed cost)``: large batches
+    go to 256 x 256 pair tiles, while a lone matrix whose tiles would leave most SMs idle goes to
+    smaller tiles (e.g. the 2048 x 2048 Gram matrix of one 2048 x 8192 input: 36 pair tiles for
+    74 pairs, but 136 single-CTA 128 x 128 tiles for 148 SMs).  Efficiencies and the fixed cost
+    per tile (pipeline fill + epilogue, expressed in K elements) are fitted to the timings of
+    ``benchmark/bench_newton_schulz.py --gemms``."""
+    key = (M, N, K, batch, sym, pair_ok, device.index)
+    hit = _config_cache.get(key)
+    if hit is not None:
+        return hit
+    sms = sm_count(device)
+    cands = []
+    # (pair?, bn, execution units, tile size per unit, efficiency, fixed cost in K elements)
+    if pair_ok and M > 128 and N > 128:
+        cands.append((True, 256, sms // 2, 1.0, 1.0, 768.0))
+    if N > 128:
+        cands.append((False, 256, sms, 1.0, 0.7 if sym else 0.9, 2048.0 if sym else 1024.0))
+    cands.append((False, 128, sms, 0.5, 0.6 if sym else 0.8, 2048.0 if sym else 1024.0))
+    best, best_t = None, None
+    for is_pair, bn, units, size, eff, fixed in cands:
+        tiles = _num_tiles(M, N, 256 if is_pair else _BM, bn, sym) * batch
+        t = -(-tiles // units) * size * (K / eff + fixed)
+        if best_t is None or t < best_t - 1e-9:
+            best, best_t = (is_pair, bn), t
+    _config_cache[key] = best
+    return best
 
 
 def ns_gemm(
@@ -206,12 +231,18 @@ def ns_gemm(
     if epi != 0:
         pair = True
     if pair is None:
-        pair = pair_default() and bn is None and _pair_eligible(
-            M, N, batch, extra, out_t, out_f32, out, dev)
+        pair_ok = pair_default() and bn is None and extra is None and out_t is None \
+            and out_f32 is None
         # The two-CTA kernel moves C and D by TMA: 16-byte aligned bases, strides multiples of 8.
         for t3, ld_, bs_ in ((C3, ldc, sc), (D3, ldd, sd)):
             if t3 is not None and (t3.data_ptr() % 16 or ld_ % 8 or bs_ % 8):
-                pair = False
+                pair_ok = False
+        if bn is None:
+            pair, bn_pick = _choose_config(M, N, K, batch, sym, pair_ok, dev)
+            if not pair:
+                bn = bn_pick
+        else:
+            pair = False
     if pair:
         if extra is not None or out_t is not None or out_f32 is not None:
             raise ValueError("the two-CTA kernel has no transposed/fp32/cross-GPU outputs")
