@@ -71,6 +71,22 @@ def bench(fn, iters: int = 10, warmup: int = 3) -> float:
     return total / iters
 
 
+def graphed(fn, G):
+    """``fn(G)`` captured once in a CUDA graph; returns a callable that replays it (device time
+    without the per-launch host cost, which is what a captured optimizer or training step pays)."""
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(2):
+            fn(G)
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        fn(G)
+    return graph.replay
+
+
 def reference_drivers():
     ref_root = os.path.join(ROOT, "baseline", "_ref")
     if not os.path.isdir(os.path.join(ref_root, "dion")):
@@ -87,7 +103,8 @@ def reference_drivers():
         return {}
 
 
-def run_case(b: int, m: int, n: int, drivers, peak: float, max_bytes: float = 6e9):
+def run_case(b: int, m: int, n: int, drivers, peak: float, max_bytes: float = 6e9,
+             graph_too: bool = False):
     if b * m * n * 2 * 4 > max_bytes:
         return None
     G = torch.randn(b, m, n, device="cuda", dtype=torch.bfloat16)
@@ -103,6 +120,14 @@ def run_case(b: int, m: int, n: int, drivers, peak: float, max_bytes: float = 6e
         tf = fl / (ms * 1e-3) / 1e12
         row[name] = {"ms": round(ms, 4), "tflops": round(tf, 1),
                      "frac_of_measured_cublas_peak": round(tf / peak, 3)}
+        if graph_too and name.startswith("ours_quintic"):
+            try:
+                replay = graphed(fn, G)
+                gms = bench(replay)
+                row[name + "_graphed"] = {"ms": round(gms, 4),
+                                          "tflops": round(fl / (gms * 1e-3) / 1e12, 1)}
+            except Exception as exc:  # noqa: BLE001
+                row[name + "_graphed"] = {"error": str(exc)[:120]}
     gemm.check_status()
     return row
 
@@ -139,6 +164,8 @@ def main() -> None:
     ap.add_argument("--gemms", nargs=2, type=int, metavar=("M", "N"))
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--no-reference", action="store_true")
+    ap.add_argument("--graph", action="store_true",
+                    help="also time our quintic driver replayed from a CUDA graph")
     ap.add_argument("--out", type=str, default=None)
     args = ap.parse_args()
     peak = peak_tflops()
@@ -159,7 +186,7 @@ def main() -> None:
     cases = ([(b, m, n) for (m, n) in GRID_SHAPES for b in GRID_BATCH] if args.grid
              else [(args.batch, *(args.single or (4096, 4096)))])
     for b, m, n in cases:
-        row = run_case(b, m, n, drivers, peak)
+        row = run_case(b, m, n, drivers, peak, graph_too=args.graph)
         if row is None:
             continue
         results.append(row)

@@ -671,3 +671,45 @@ DION_EXPORT int dion_ns_gemm2(const void* A, long long lda, long long strideA, i
     default: return launch2<true, true, kStagesPlain>(ma, mb, mc, md, a, s);
   }
 }
+
+// Whole Newton-Schulz iteration from one host call: for every coefficient triple (a, b, c)
+//   A  = s^2 * X X^T            (wide / square; X^T X for tall matrices), symmetric
+//   B  = b * A + c * A A        symmetric
+//   X' = s * (a * X + B X)      (X B for tall matrices)
+// with the input scale s applied in the first iteration only, ping-ponging between the buffers
+// X and Xalt.  All operands are dense [batch, rows, cols] bf16.  The result of the last
+// iteration lies in Xalt when `iters` is odd, else in X.  This only saves the host the 3 * iters
+// trips through the Python front end; the launches are the same as issued one by one.
+DION_EXPORT int dion_ns_iterate2(void* X, void* Xalt, void* A, void* Bm, int batch, int m, int n,
+                                 const float* coeffs, int iters, const float* scale,
+                                 const void* tiles_gg, int n_tiles_gg, const void* tiles_mn,
+                                 int n_tiles_mn, int* status, void* stream) {
+  const int tall = m > n;
+  const int g = tall ? n : m;
+  const long long sx = (long long)m * n, sg = (long long)g * g;
+  void* cur = X;
+  void* nxt = Xalt;
+  for (int it = 0; it < iters; ++it) {
+    const float a = coeffs[3 * it], b = coeffs[3 * it + 1], c = coeffs[3 * it + 2];
+    const float* sc = (it == 0) ? scale : nullptr;
+    const int p2 = sc ? 2 : 0, p1 = sc ? 1 : 0;
+    // Gram matrix: wide X [g, K=n] against itself; tall X read as [K=m, g] on both sides.
+    int rc = dion_ns_gemm2(cur, n, sx, tall, cur, n, sx, tall, A, g, sg, nullptr, 0, 0, batch, g, g,
+                           tall ? m : n, 1.f, 0.f, sc, p2, 0, 1, tiles_gg, n_tiles_gg, 0, status,
+                           stream);
+    if (rc != 0) return rc;
+    rc = dion_ns_gemm2(A, g, sg, 0, A, g, sg, 0, Bm, g, sg, A, g, sg, batch, g, g, g, c, b, nullptr,
+                       0, 0, 1, tiles_gg, n_tiles_gg, 0, status, stream);
+    if (rc != 0) return rc;
+    if (tall) {  // X' = a X + X B, B symmetric: given as [N, K]
+      rc = dion_ns_gemm2(cur, n, sx, 0, Bm, g, sg, 0, nxt, n, sx, cur, n, sx, batch, m, n, g, 1.f, a,
+                         sc, p1, p1, 0, tiles_mn, n_tiles_mn, 0, status, stream);
+    } else {     // X' = a X + B X, X given as [K, N]
+      rc = dion_ns_gemm2(Bm, g, sg, 0, cur, n, sx, 1, nxt, n, sx, cur, n, sx, batch, m, n, g, 1.f, a,
+                         sc, p1, p1, 0, tiles_mn, n_tiles_mn, 0, status, stream);
+    }
+    if (rc != 0) return rc;
+    void* t = cur; cur = nxt; nxt = t;
+  }
+  return 0;
+}

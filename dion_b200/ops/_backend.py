@@ -86,7 +86,7 @@ def build(force: bool = False, verbose: bool = False) -> List[str]:
 
 
 # Kernels launched per exported entry point (default 1); used for the launch counter.
-_KERNELS_PER_CALL = {"dion_adamw": 2}
+_KERNELS_PER_CALL = {"dion_adamw": 2, "dion_ns_iterate2": 0}  # the latter counts itself
 _launches = 0
 
 
@@ -110,6 +110,12 @@ class _CountingLib:
 
             self._cache[name] = fn
         return fn
+
+
+def add_launches(n: int) -> None:
+    """For entry points that launch a data-dependent number of kernels."""
+    global _launches
+    _launches += n
 
 
 def launch_count() -> int:

@@ -284,3 +284,43 @@ def ns_gemm(
     if rc != 0:
         raise RuntimeError(f"dion_ns_gemm launch failed with code {rc}")
     return out if out is not None else out_f32
+
+
+def iterate_in_one_call(X: Tensor, batch: int, m: int, n: int) -> bool:
+    """True when all three GEMMs of a Newton-Schulz iteration on ``[batch, m, n]`` would go to the
+    two-CTA kernel, so that the whole iteration can be issued by one host call."""
+    if not pair_default() or not X.is_contiguous() or X.data_ptr() % 16 or m % 8 or n % 8:
+        return False
+    dev = X.device
+    tall = m > n
+    g = n if tall else m
+    k_gram = m if tall else n
+    return (_choose_config(g, g, k_gram, batch, True, True, dev)[0]
+            and _choose_config(g, g, g, batch, True, True, dev)[0]
+            and _choose_config(m, n, g, batch, False, True, dev)[0])
+
+
+def ns_iterate(X: Tensor, Xalt: Tensor, A: Tensor, Bm: Tensor, coeffs, scale: Optional[Tensor]
+               ) -> Tensor:
+    """All iterations ``(a, b, c) in coeffs`` of ``X <- aX + (bA + cA^2)X`` with ``A = X X^T``
+    (right-multiplied forms for tall ``X``) issued by one call into the library; ``scale`` (one
+    fp32 per matrix) normalizes the input inside the first iteration.  ``X`` is overwritten;
+    returns whichever of ``X`` / ``Xalt`` holds the result."""
+    batch, m, n = X.shape
+    dev = X.device
+    g = min(m, n)
+    tiles_gg = tile_table(g, g, 256, True, dev, bm=256)
+    tiles_mn = tile_table(m, n, 256, False, dev, bm=256)
+    flat = (ctypes.c_float * (3 * len(coeffs)))(*[float(v) for abc in coeffs for v in abc])
+    if scale is not None:
+        assert scale.dtype == torch.float32 and scale.numel() >= batch
+    st = status_tensor(dev)
+    rc = _backend.lib("ns_gemm2_sm100").dion_ns_iterate2(
+        _p(X), _p(Xalt), _p(A), _p(Bm), ctypes.c_int(batch), ctypes.c_int(m), ctypes.c_int(n),
+        flat, ctypes.c_int(len(coeffs)), _p(scale), _p(tiles_gg), ctypes.c_int(tiles_gg.size(0)),
+        _p(tiles_mn), ctypes.c_int(tiles_mn.size(0)), _p(st),
+        ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream))
+    if rc != 0:
+        raise RuntimeError(f"dion_ns_iterate2 failed with code {rc}")
+    _backend.add_launches(3 * len(coeffs))
+    return Xalt if len(coeffs) % 2 else X

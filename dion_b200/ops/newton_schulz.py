@@ -182,6 +182,8 @@ def _iterate_cuda(X: Tensor, coeffs: Coeffs, scale: Optional[Tensor], hooks=None
     A = torch.empty((B_, g, g), dtype=torch.bfloat16, device=X.device)
     Bm = torch.empty_like(A)
     C = torch.empty_like(X)
+    if hooks is None and gemm.iterate_in_one_call(X, B_, m, n):
+        return gemm.ns_iterate(X, C, A, Bm, coeffs, scale)
     last = len(coeffs) - 1
     for it, (a, b, c) in enumerate(coeffs):
         sc = scale if it == 0 else None
