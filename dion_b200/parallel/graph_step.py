@@ -207,8 +207,9 @@ class GraphedTrainStep:
         with torch.cuda.graph(graph):
             loss = self._one_step()
         self.graph, self.static_loss = graph, loss
+        # Capturing ran the host side of the step once (counters included) without executing
+        # anything on the device; this replay is that step's device work.
         graph.replay()
-        self._post_replay()
         return self.static_loss
 
     def release(self) -> None:
