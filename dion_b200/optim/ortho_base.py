@@ -179,11 +179,19 @@ class DistributedOrthoBase(Optimizer):
             else:
                 raise ValueError(f"Unknown algorithm: {algo}")
 
-        tasks = chain(
-            self._create_ortho_tasks(buckets["ortho"]),
-            self._create_lion_tasks(buckets["lion"]),
-            self._create_adamw_tasks(buckets["adamw"]),
-        )
+        def scalar_tasks():
+            # Runs when the runtime first asks for a scalar task, i.e. after every matrix task
+            # has been started.  A data-parallel driver may hang a callback here that makes the
+            # stream wait for gradient reductions it let run past the start of the step (the
+            # embedding gradient is produced last in backward; its all-reduce then overlaps the
+            # orthogonalization work, which does not read it).
+            hook = getattr(self, "before_scalar_tasks", None)
+            if hook is not None:
+                hook()
+            yield from self._create_lion_tasks(buckets["lion"])
+            yield from self._create_adamw_tasks(buckets["adamw"])
+
+        tasks = chain(self._create_ortho_tasks(buckets["ortho"]), scalar_tasks())
         AsyncRuntime(tasks, max_concurrent_tasks=MAX_CONCURRENT_TASKS).run()
         return loss
 

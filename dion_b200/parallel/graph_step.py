@@ -55,6 +55,7 @@ class BucketedGradSync:
         self._launched = [False] * len(self.buckets)
         self._stream: Optional[torch.cuda.Stream] = None
         self._handles = []
+        self._events: List = []  # (bucket index, event) in launch order on the side stream
         self.enabled = self.world > 1
         if self.enabled:
             for p in self.params:
@@ -84,6 +85,9 @@ class BucketedGradSync:
             self._stream.wait_stream(torch.cuda.current_stream(grads[0].device))
             with torch.cuda.stream(self._stream):
                 self._all_reduce(grads)
+                ev = torch.cuda.Event()
+                ev.record(self._stream)
+                self._events.append((bi, ev))
         else:
             self._all_reduce(grads)
 
@@ -101,18 +105,41 @@ class BucketedGradSync:
         if not nccl:
             torch._foreach_div_(grads, float(self.world))
 
-    def finish(self) -> None:
-        """Join the reductions into the current stream; reduce buckets whose parameters did not
-        all receive a gradient this step; re-arm."""
+    def finish(self, deferrable: Optional[Sequence[Tensor]] = None) -> bool:
+        """Reduce buckets whose parameters did not all receive a gradient this step, make the
+        current stream wait for the reductions and re-arm.  With ``deferrable`` (parameters whose
+        gradients are not needed until :meth:`join` is called) the wait stops at the last bucket
+        that holds any other parameter; returns True when something was left for ``join``."""
         if not self.enabled:
-            return
+            return False
         for bi in range(len(self.buckets)):
             if not self._launched[bi]:
                 self._reduce_bucket(bi)
-        if self._stream is not None:
-            torch.cuda.current_stream(self._stream.device).wait_stream(self._stream)
         self._pending = [len(b) for b in self.buckets]
         self._launched = [False] * len(self.buckets)
+        if self._stream is None:
+            self._events.clear()
+            return False
+        cur = torch.cuda.current_stream(self._stream.device)
+        if deferrable is not None and self._events:
+            later = set(id(p) for p in deferrable)
+            needed = None  # position (in launch order) of the last bucket needed right away
+            for pos, (bi, _) in enumerate(self._events):
+                if any(id(p) not in later for p in self.buckets[bi]):
+                    needed = pos
+            if needed is None or needed != len(self._events) - 1:
+                if needed is not None:
+                    cur.wait_event(self._events[needed][1])
+                self._events.clear()
+                return True
+        cur.wait_stream(self._stream)
+        self._events.clear()
+        return False
+
+    def join(self) -> None:
+        """Make the current stream wait for everything :meth:`finish` deferred."""
+        if self.enabled and self._stream is not None:
+            torch.cuda.current_stream(self._stream.device).wait_stream(self._stream)
 
 
 class GraphedTrainStep:
@@ -139,12 +166,26 @@ class GraphedTrainStep:
         self.warmup = max(1, warmup)
         self.use_graph = use_graph and device.type == "cuda"
         self.sync = BucketedGradSync(self.params, process_group, bucket_mb)
+        self._deferrable = self._scalar_group_params(optimizer)
         self.static_inputs = [torch.empty(t.shape, dtype=t.dtype, device=device)
                               for t in example_inputs]
         self.static_loss: Optional[Tensor] = None
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self._calls = 0
         self._side: Optional[torch.cuda.Stream] = None
+
+    @staticmethod
+    def _scalar_group_params(optimizer) -> Optional[List[Tensor]]:
+        """Parameters updated by the element-wise algorithms of an optimizer of this package that
+        runs them after its matrix tasks (``DistributedOrthoBase.step``); their gradient
+        reductions may run past the start of the step."""
+        from ..optim.ortho_base import DistributedOrthoBase
+
+        if not isinstance(optimizer, DistributedOrthoBase):
+            return None
+        out = [p for g in optimizer.param_groups if g.get("algorithm") in ("adamw", "lion")
+               for p in g["params"]]
+        return out or None
 
     # ----------------------------------------------------------------------------------------
     def _autocast(self):
@@ -156,8 +197,15 @@ class GraphedTrainStep:
         with self._autocast():
             loss = self.loss_fn(*self.static_inputs)
         loss.backward()
-        self.sync.finish()
-        self.optimizer.step()
+        deferred = self.sync.finish(self._deferrable)
+        if deferred:
+            self.optimizer.before_scalar_tasks = self.sync.join
+        try:
+            self.optimizer.step()
+        finally:
+            if deferred:
+                self.optimizer.before_scalar_tasks = None
+                self.sync.join()  # a no-op when the hook already ran; keeps capture joined
         # Gradients are dropped, not zeroed: under capture the next backward re-creates them in
         # the graph's private pool at the same addresses.
         for p in self.params:

@@ -100,6 +100,7 @@ def test_graphed_step_matches_eager(name):
         check_status()
         if use_graph:
             assert step.graph is not None
+        assert all(g["step"] == len(batches) for g in opt.param_groups)
         losses[use_graph] = out
         step.release()
     assert losses[True][0] == pytest.approx(losses[False][0], rel=1e-5)

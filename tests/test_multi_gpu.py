@@ -229,3 +229,45 @@ def test_trainer_dion_with_fsdp_and_tensor_parallel_on_gpus():
     assert res.returncode == 0, res.stdout[-1500:] + res.stderr[-1500:]
     losses = [float(m) for m in re.findall(r"train_loss=([0-9.]+)", res.stdout)]
     assert len(losses) == 3 and all(l == l and l < 20 for l in losses)
+
+
+def _graphed_ddp_worker(rank, world, use_graph):
+    from dion_b200.models.gpt import GPT, GPTConfig
+    from dion_b200.ops.gemm import check_status
+    from dion_b200.parallel.graph_step import GraphedTrainStep
+    dev = torch.device("cuda", rank)
+    torch.manual_seed(0)
+    model = GPT(GPTConfig(n_layer=2, n_embd=128, n_head=2, vocab_size=512, sequence_len=64)).to(dev)
+    model.init_weights()
+    groups = [dict(params=list(model.transformer.h.parameters())),
+              dict(params=list(model.transformer.wte.parameters()) + list(model.lm_head.parameters()),
+                   algorithm="adamw", lr=0.01, weight_decay=0)]
+    opt = dion_b200.Dion2(groups, distributed_mesh=dist.group.WORLD, lr=0.02, fraction=0.25,
+                          use_polar_express=False)
+    g = torch.Generator().manual_seed(10 + rank)          # different data on every rank
+    batches = [torch.randint(0, 512, (2, 4, 64), generator=g).to(dev) for _ in range(6)]
+    step = GraphedTrainStep(lambda x, y: model(x, y), list(model.parameters()), opt,
+                            [batches[0][0], batches[0][1]], device=dev,
+                            process_group=dist.group.WORLD, warmup=2, use_graph=use_graph,
+                            bucket_mb=0.05)               # several buckets
+    losses = [float(step(b[0], b[1]).item()) for b in batches]
+    torch.cuda.synchronize()
+    check_status()
+    flat = torch.cat([p.detach().reshape(-1).float() for p in model.parameters()])
+    step.release()
+    return {"losses": losses, "params": flat.cpu()}
+
+
+def test_graphed_data_parallel_step_keeps_replicas_identical_and_matches_eager(tmp_path):
+    _need(2)
+    out = {}
+    for use_graph in (False, True):
+        d = tmp_path / str(use_graph)
+        d.mkdir()
+        out[use_graph] = run_ranks(_graphed_ddp_worker, 2, backend="nccl", args=(use_graph,),
+                                   result_dir=str(d))
+    for res in out.values():
+        assert torch.equal(res[0]["params"], res[1]["params"])
+        assert all(l == l for l in res[0]["losses"])
+    a, b = out[False][0]["params"], out[True][0]["params"]
+    assert (a - b).abs().max().item() < 5e-3
