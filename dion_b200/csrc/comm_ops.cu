@@ -133,6 +133,7 @@ struct AllReduceArgs {
   long long vec_begin, vec_end;
   int world, rank, dt;
   float scale;
+  int gather;                    // 1: all-gather (push this rank's slice to everyone), 0: reduce
 };
 
 __global__ void __launch_bounds__(256)
@@ -155,7 +156,21 @@ allreduce_fused_kernel(const AllReduceArgs a) {
     if (!got) { atomicExch(a.status, kStatusTimeoutPeer); s_ok = 0; }
   }
   __syncthreads();
-  if (s_ok) {
+  if (s_ok && a.gather) {
+    // All-gather: this rank's slice already lies in its own copy; replicate it.
+    const char* own = reinterpret_cast<const char*>(a.peer_bases[a.rank]);
+    for (long long i = a.vec_begin + (long long)blockIdx.x * 256 + threadIdx.x; i < a.vec_end;
+         i += (long long)gridDim.x * 256) {
+      const uint4 v = *reinterpret_cast<const uint4*>(own + i * 16);
+      if (a.mc_base != nullptr) {
+        mm_st_b32x4(a.mc_base + i * 16, v);   // the switch delivers it to every rank
+      } else {
+        for (int r = 0; r < a.world; ++r)
+          if (r != a.rank)
+            *reinterpret_cast<uint4*>(reinterpret_cast<char*>(a.peer_bases[r]) + i * 16) = v;
+      }
+    }
+  } else if (s_ok) {
     for (long long i = a.vec_begin + (long long)blockIdx.x * 256 + threadIdx.x; i < a.vec_end;
          i += (long long)gridDim.x * 256) {
       if (a.mc_base != nullptr) {
@@ -256,14 +271,14 @@ DION_EXPORT int dion_scale_from_partials(float* partials, int n_mats, int n_src,
   return rc();
 }
 
-// In-place all-reduce of 16-byte vectors of a symmetric buffer in one launch (see
-// allreduce_fused_kernel).  `seq` and `counter` are device words owned by the workspace.
+// In-place all-reduce (gather = 0) or all-gather (gather = 1: [vec_begin, vec_end) is this rank's
+// slice) of 16-byte vectors of a symmetric buffer in one launch (see allreduce_fused_kernel).  `seq` and `counter` are device words owned by the workspace.
 DION_EXPORT int dion_allreduce_fused(void* mc_base, const void* peer_bases, const void* peer_in,
                                      const void* peer_out, const int* flags_in,
                                      const int* flags_out, int* seq, unsigned* counter,
                                      int* status, int world, int rank, long long vec_begin,
-                                     long long vec_end, int dt, float scale, int num_blocks,
-                                     void* stream) {
+                                     long long vec_end, int dt, float scale, int gather,
+                                     int num_blocks, void* stream) {
   if (world <= 0 || world > 256 || (dt != 0 && dt != 1)) return -2;
   long long n = vec_end > vec_begin ? vec_end - vec_begin : 0;
   long long need = (n + 255) / 256;
@@ -277,7 +292,7 @@ DION_EXPORT int dion_allreduce_fused(void* mc_base, const void* peer_bases, cons
   a.flags_in = flags_in; a.flags_out = flags_out;
   a.seq = seq; a.counter = counter; a.status = status;
   a.vec_begin = vec_begin; a.vec_end = vec_end > vec_begin ? vec_end : vec_begin;
-  a.world = world; a.rank = rank; a.dt = dt; a.scale = scale;
+  a.world = world; a.rank = rank; a.dt = dt; a.scale = scale; a.gather = gather;
   allreduce_fused_kernel<<<blocks, 256, 0, S(stream)>>>(a);
   return rc();
 }

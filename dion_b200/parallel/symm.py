@@ -216,13 +216,25 @@ class SymmetricAllReduce:
         per = (nvec + self.world - 1) // self.world
         begin, end = self.rank * per, min(nvec, (self.rank + 1) * per)
         scale = 1.0 / self.world if op == "avg" else 1.0
+        self._launch(begin, end, 0 if dtype == torch.float32 else 1, scale, gather=False)
+
+    def all_gather_(self, slot_bytes: int) -> None:
+        """All-gather in place: every rank's ``slot_bytes`` (a multiple of 16) already lie at
+        byte offset ``rank * slot_bytes`` of its own copy; afterwards every copy holds all
+        slots."""
+        if slot_bytes % 16 or slot_bytes * self.world > self.capacity:
+            raise ValueError("slot size must be a multiple of 16 bytes and fit the buffer")
+        per = slot_bytes // 16
+        self._launch(self.rank * per, (self.rank + 1) * per, 0, 1.0, gather=True)
+
+    def _launch(self, begin: int, end: int, dt: int, scale: float, gather: bool) -> None:
         rc = _backend.lib("comm_ops").dion_allreduce_fused(
             _c(self.multicast_base), _c(self.data_table.data_ptr()),
             _c(self.in_table.data_ptr()), _c(self.out_table.data_ptr()),
             _c(self.flags_in.data_ptr()), _c(self.flags_out.data_ptr()),
             _c(self.seq.data_ptr()), _c(self.counter.data_ptr()), _c(self.status.data_ptr()),
             self.world, self.rank, ctypes.c_longlong(begin), ctypes.c_longlong(end),
-            0 if dtype == torch.float32 else 1, ctypes.c_float(scale), self.num_blocks,
+            dt, ctypes.c_float(scale), 1 if gather else 0, self.num_blocks,
             _stream(self.device))
         if rc != 0:
             raise RuntimeError(f"dion_allreduce_fused failed (code {rc})")

@@ -115,6 +115,9 @@ def parse_cli_args(argv: Optional[List[str]] = None) -> argparse.Namespace:
     p.add_argument("--no_triton", action="store_true", help="accepted; kernels are always CUDA")
     p.add_argument("--use_polar_express", action="store_true")
     p.add_argument("--use_gram_newton_schulz", action="store_true")
+    p.add_argument("--symm_all_gather", action="store_true",
+                   help="FSDP2 parameter all-gather by this package's kernel over symmetric "
+                        "memory (NVLS multimem / peer stores) instead of NCCL")
     p.add_argument("--graph_step", action="store_true",
                    help="Replay forward + backward + gradient all-reduce + optimizer as ONE CUDA "
                         "graph per step (single GPU or DDP, no gradient accumulation)")
@@ -441,6 +444,12 @@ def main(argv: Optional[List[str]] = None) -> None:
         for t in list(raw_model.parameters()) + list(raw_model.buffers()):
             dist.broadcast(t.data, src=0)
     print0(f"Total parameters: {sum(p.numel() for p in raw_model.parameters())}")
+    if args.symm_all_gather and mesh is not None and device.type == "cuda":
+        from .parallel.fsdp_comm import use_symmetric_all_gather
+
+        comm = use_symmetric_all_gather(raw_model, mesh["fs"].get_group(), device)
+        print0("FSDP all-gather: " + ("symmetric-memory kernel" if comm is not None
+                                      else "NCCL (symmetric memory unavailable)"))
     optimizer = init_optimizer(raw_model, mesh, ddp, hp, args)
     scheduler = torch.optim.lr_scheduler.LambdaLR(
         optimizer, lambda s: lr_multiplier(s, hp.num_iterations, hp.warmup_ratio, hp.warmdown_ratio))

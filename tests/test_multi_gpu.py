@@ -271,3 +271,54 @@ def test_graphed_data_parallel_step_keeps_replicas_identical_and_matches_eager(t
         assert all(l == l for l in res[0]["losses"])
     a, b = out[False][0]["params"], out[True][0]["params"]
     assert (a - b).abs().max().item() < 5e-3
+
+
+def _fsdp_symm_ag_worker(rank, world, symmetric):
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.fsdp import fully_shard
+    from dion_b200.models.gpt import GPT, GPTConfig
+    from dion_b200.ops.gemm import check_status
+    from dion_b200.parallel.fsdp_comm import use_symmetric_all_gather
+    dev = torch.device("cuda", rank)
+    torch.manual_seed(0)
+    model = GPT(GPTConfig(n_layer=3, n_embd=128, n_head=2, vocab_size=512, sequence_len=64)).to(dev)
+    model.init_weights()
+    mesh = init_device_mesh("cuda", (world,))
+    for block in model.transformer.h:
+        fully_shard(block, mesh=mesh)
+    fully_shard(model, mesh=mesh)
+    comm = use_symmetric_all_gather(model, mesh.get_group(), dev) if symmetric else None
+    opt = dion_b200.Muon(
+        [dict(params=list(model.transformer.h.parameters())),
+         dict(params=list(model.transformer.wte.parameters()) + list(model.lm_head.parameters()),
+              algorithm="adamw", lr=0.01, weight_decay=0)],
+        distributed_mesh=mesh, lr=0.02, use_polar_express=False)
+    g = torch.Generator().manual_seed(20 + rank)
+    losses = []
+    for _ in range(4):
+        xy = torch.randint(0, 512, (2, 4, 64), generator=g).to(dev)
+        loss = model(xy[0], xy[1])
+        loss.backward()
+        opt.step()
+        model.zero_grad(set_to_none=True)
+        losses.append(float(loss.item()))
+    torch.cuda.synchronize()
+    check_status()
+    flat = torch.cat([p.detach().to_local().reshape(-1).float() for p in model.parameters()])
+    return {"losses": losses, "params": flat.cpu(),
+            "kernel_calls": comm.calls if comm is not None else 0,
+            "fallbacks": comm.fallbacks if comm is not None else 0}
+
+
+def test_fsdp_all_gather_through_symmetric_memory_matches_nccl(tmp_path):
+    _need(2)
+    out = {}
+    for symmetric in (False, True):
+        d = tmp_path / str(symmetric)
+        d.mkdir()
+        out[symmetric] = run_ranks(_fsdp_symm_ag_worker, 2, backend="nccl", args=(symmetric,),
+                                   result_dir=str(d))
+    assert out[True][0]["kernel_calls"] > 0
+    for r in range(2):
+        assert out[True][r]["losses"] == out[False][r]["losses"]
+        assert torch.equal(out[True][r]["params"], out[False][r]["params"])
