@@ -42,15 +42,21 @@ def newton_schulz_dispatch(
     split_sizes: Optional[Tuple[int, ...]] = None,
     split_scales: Optional[Tuple[float, ...]] = None,
 ) -> Tensor:
-    """Shape handling around the Newton-Schulz callable: ``flatten`` folds trailing dims into
-    one, >=4-D inputs fold their leading dims into the batch, and ``split_sizes`` orthogonalizes
-    row blocks independently (reference: megabatch_base.py:884-949)."""
+    """Shape handling around the Newton-Schulz callable.  ``X`` is a stack ``[N, *param_shape]``.
+    With ``flatten`` every parameter is folded to ``[shape[0], prod(shape[1:])]`` (convolution
+    kernels); otherwise parameters with more than two dims are batches of matrices and their
+    leading dims join the batch.  ``split_sizes`` orthogonalizes row blocks independently
+    (reference: megabatch_base.py:884-949; there the fold is applied to whatever tensor reaches
+    the function, which for a stack of several parameters also folds the parameter's own first
+    dim - here the documented per-parameter meaning is applied for any number of parameters, and
+    the two agree for a single parameter)."""
     if split_sizes is not None:
         assert not flatten, "split_sizes is incompatible with flatten=True"
         return _row_block_newton_schulz(X, split_sizes, split_scales, newton_schulz_func, epsilon)
     shape = X.shape
-    if flatten and X.ndim >= 3:
-        X = X.flatten(start_dim=1)
+    if flatten:
+        if X.ndim >= 4:
+            X = X.flatten(start_dim=2)
     elif X.ndim >= 4:
         X = X.flatten(end_dim=-3)
     return newton_schulz_func(X, epsilon=epsilon).reshape(shape)

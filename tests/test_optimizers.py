@@ -34,6 +34,10 @@ MEGABATCH = [
     ("Dion2", dict(fraction=0.5, ef_decay=0.9)),
     ("NorDion2", dict()),
     ("NorDion2", dict(fraction=0.5)),
+    ("Muon", dict(mu=0.8, betas=(0.8, 0.9), epsilon=1e-6)),
+    ("NorMuon", dict(muon_beta2=0.9, use_polar_express=False)),
+    ("Dion2", dict(selection_scope="global", fraction=0.25)),
+    ("NorDion2", dict(fraction=0.25, use_polar_express=False)),
 ]
 
 
@@ -49,6 +53,17 @@ def test_megabatch_parity_with_reference(ref_dion, name, kw):
         assert set(sa["state"][k]) == set(sb["state"][k])
         for kk, val in sa["state"][k].items():
             assert val.shape == sb["state"][k][kk].shape and val.dtype == sb["state"][k][kk].dtype
+
+
+def test_flatten_parity_with_reference_single_parameters(ref_dion):
+    """``flatten=True`` folds a >2-D parameter to [shape[0], rest]; 2-D parameters are unchanged.
+    Compared one parameter per shape, where the reference applies exactly this meaning."""
+    kw = dict(flatten=True, adjust_lr="spectral_norm", weight_decay=0.0, use_polar_express=False)
+    shapes = ((64, 128), (128, 64), (4, 32, 48), (8, 6, 3, 3))
+    a, _ = _run(ref_dion.Muon, kw, shapes=shapes)
+    b, _ = _run(dion_b200.Muon, kw, shapes=shapes)
+    for x, y in zip(a, b):
+        assert (x - y).abs().max().item() < 2e-4
 
 
 def _same_q_init(opt, ps):
