@@ -9,7 +9,7 @@ from __future__ import annotations
 
 import ctypes
 import math
-from typing import Callable, List, Optional, Tuple
+from typing import List, Optional, Tuple
 
 import torch
 from torch import Tensor

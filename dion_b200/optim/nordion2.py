@@ -21,7 +21,7 @@ from ..parallel.async_runtime import AsyncTask
 from ..parallel.megabatch import MegabatchPlan
 from ..utils.tensors import group_by_shape, to_local
 from .dion2 import _validate_dion2, make_select_and_orthogonalize, selection_count
-from .muon import _validate_common, contiguous_list, global_comm_size
+from .muon import _validate_common, global_comm_size
 from .normuon import _matrix_views, normuon_normalization_stacked
 from .ortho_base import DistributedOrthoBase, lr_ratio
 

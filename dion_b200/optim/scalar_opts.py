@@ -5,7 +5,6 @@ from __future__ import annotations
 
 from typing import Generator, List, Optional
 
-import torch
 from torch import Tensor
 
 from ..ops import foreach as F

@@ -17,7 +17,6 @@ from torch import Tensor
 from torch.distributed import ProcessGroup
 
 from ..ops import _backend
-from ..ops.tables import build_ptr_array
 
 
 def symmetric_memory_available(pg: Optional[ProcessGroup]) -> bool:

@@ -9,7 +9,6 @@ ranks, and wandb / tqdm are optional.
 from __future__ import annotations
 
 import argparse
-import math
 import os
 import shutil
 import time

@@ -119,7 +119,7 @@ def test_uneven_and_empty_shards_do_not_hang(tmp_path):
 
 def _dion_worker(rank, world, mode, steps):
     from torch.distributed.device_mesh import init_device_mesh
-    from torch.distributed.tensor import Replicate, Shard, distribute_tensor
+    from torch.distributed.tensor import Shard, distribute_tensor
     shapes = ((32, 64), (32, 64), (64, 32), (64, 32))
     torch.manual_seed(0)
     if mode == "ddp":
