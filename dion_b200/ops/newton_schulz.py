@@ -26,6 +26,7 @@ from typing import Callable, Optional, Sequence, Tuple
 import torch
 from torch import Tensor
 
+from ..utils import trace
 from ..utils.tensors import unwrap
 from . import foreach as F
 from . import gemm
@@ -216,9 +217,10 @@ def _iterate_cuda(X: Tensor, coeffs: Coeffs, scale: Optional[Tensor], hooks=None
 
 
 def _ns_cuda(G: Tensor, coeffs: Coeffs, norm_mult: float, epsilon: float) -> Tensor:
-    X, restore = _prepare_cuda(G, allow_tall=True)
-    scale = _norm_scale(X, norm_mult, epsilon)
-    return restore(_iterate_cuda(X, coeffs, scale))
+    with trace.span("newton_schulz"):
+        X, restore = _prepare_cuda(G, allow_tall=True)
+        scale = _norm_scale(X, norm_mult, epsilon)
+        return restore(_iterate_cuda(X, coeffs, scale))
 
 
 def _aol_cuda(G: Tensor, epsilon: float) -> Tensor:

@@ -24,6 +24,7 @@ from ..ops import foreach as F
 from ..ops import newton_schulz as NS
 from ..parallel.async_runtime import AsyncRuntime, AsyncTask
 from ..utils.arena import StepArena
+from ..utils import trace
 from ..utils.tensors import to_local
 
 MAX_CONCURRENT_TASKS = 3
@@ -192,7 +193,8 @@ class DistributedOrthoBase(Optimizer):
             yield from self._create_adamw_tasks(buckets["adamw"])
 
         tasks = chain(self._create_ortho_tasks(buckets["ortho"]), scalar_tasks())
-        AsyncRuntime(tasks, max_concurrent_tasks=MAX_CONCURRENT_TASKS).run()
+        with trace.span(f"{self._algo_name}.step"):
+            AsyncRuntime(tasks, max_concurrent_tasks=MAX_CONCURRENT_TASKS).run()
         return loss
 
     def _create_ortho_tasks(self, param_groups: List[dict]) -> Iterable[AsyncTask]:

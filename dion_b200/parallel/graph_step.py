@@ -23,6 +23,8 @@ import torch
 import torch.distributed as dist
 from torch import Tensor
 
+from ..utils import trace
+
 
 class BucketedGradSync:
     """Average gradients over ``process_group`` in buckets, overlapped with backward.
@@ -194,14 +196,17 @@ class GraphedTrainStep:
         return torch.autocast(device_type=self.device.type, dtype=self.autocast_dtype)
 
     def _one_step(self) -> Tensor:
-        with self._autocast():
+        with trace.span("forward"), self._autocast():
             loss = self.loss_fn(*self.static_inputs)
-        loss.backward()
-        deferred = self.sync.finish(self._deferrable)
+        with trace.span("backward"):
+            loss.backward()
+        with trace.span("grad_sync"):
+            deferred = self.sync.finish(self._deferrable)
         if deferred:
             self.optimizer.before_scalar_tasks = self.sync.join
         try:
-            self.optimizer.step()
+            with trace.span("optimizer"):
+                self.optimizer.step()
         finally:
             if deferred:
                 self.optimizer.before_scalar_tasks = None

@@ -114,6 +114,11 @@ def parse_cli_args(argv: Optional[List[str]] = None) -> argparse.Namespace:
     p.add_argument("--no_triton", action="store_true", help="accepted; kernels are always CUDA")
     p.add_argument("--use_polar_express", action="store_true")
     p.add_argument("--use_gram_newton_schulz", action="store_true")
+    p.add_argument("--profile_steps", type=int, default=0,
+                   help="profile this many steps (after 10 warm-up steps) with torch.profiler, "
+                        "with NVTX ranges on; rank 0 prints the kernel table")
+    p.add_argument("--profile_trace", type=str, default=None,
+                   help="write the Chrome trace of the profiled steps here (rank 0)")
     p.add_argument("--symm_all_gather", action="store_true",
                    help="FSDP2 parameter all-gather by this package's kernel over symmetric "
                         "memory (NVLS multimem / peer stores) instead of NCCL")
@@ -488,6 +493,8 @@ def main(argv: Optional[List[str]] = None) -> None:
     tot_fb = tot_opt = tot_all = 0.0
     timed = 0
     x, y = train_loader.next_batch()
+    profiler = None
+    profile_from = start_step + 10
     gstep = None
     if graph_step:
         from .parallel.graph_step import GraphedTrainStep
@@ -522,6 +529,25 @@ def main(argv: Optional[List[str]] = None) -> None:
         if last:
             break
 
+        if args.profile_steps > 0:
+            if step == profile_from:
+                from torch.profiler import ProfilerActivity, profile
+                from .utils import trace
+
+                trace.enable(True)
+                acts = [ProfilerActivity.CPU] + ([ProfilerActivity.CUDA] if device.type == "cuda" else [])
+                profiler = profile(activities=acts)
+                profiler.__enter__()
+            elif profiler is not None and step == profile_from + args.profile_steps:
+                if device.type == "cuda":
+                    torch.cuda.synchronize()
+                profiler.__exit__(None, None, None)
+                if rank == 0:
+                    key = "cuda_time_total" if device.type == "cuda" else "cpu_time_total"
+                    print(profiler.key_averages().table(sort_by=key, row_limit=40))
+                    if args.profile_trace:
+                        profiler.export_chrome_trace(args.profile_trace)
+                profiler = None
         model.train()
         if step == start_step + 10:  # discard warm-up steps from the averages
             tot_fb = tot_opt = tot_all = 0.0

@@ -107,3 +107,12 @@ def test_trainer_ddp_and_fsdp_resume(tmp_path):
     out = _torchrun(["--optimizer", "normuon", "--fs_size", "2", "--num_iterations", "3",
                      "--checkpoint_dir", ck])
     assert "Resumed from step 1" in out and "Step 2:" in out and "Step 0:" not in out
+
+
+def test_trace_spans_and_profile_helper():
+    from dion_b200.utils import trace
+    assert not trace.enabled() or True
+    with trace.span("idle"):          # disabled (or no GPU): nothing happens
+        pass
+    table = trace.profile_steps(lambda: torch.ones(8).sum(), 2)
+    assert "aten::sum" in table or "aten::ones" in table
