@@ -156,3 +156,26 @@ def test_pair_relu2_epilogues():
     gemm.check_status()
     ref_dz = (dy.float() @ Wpr.float()) * 2.0 * act.float().sqrt()
     assert _rel_err(dz, ref_dz) < 1e-2
+
+
+@pytest.mark.parametrize("pair", [False, True])
+@pytest.mark.parametrize("sym", [False, True])
+def test_output_canaries_and_run_to_run_determinism(pair, sym):
+    """The kernels write exactly the M x N window of a padded output (rows and columns beyond
+    it keep their sentinel) and give bit-identical results on repeated runs."""
+    from dion_b200.ops import gemm
+    torch.manual_seed(6)
+    b, M, K = 3, 328, 200
+    N = M if sym else 456
+    A = torch.randn(b, M, K, device="cuda").bfloat16()
+    B = A if sym else torch.randn(b, N, K, device="cuda").bfloat16()
+    big = torch.full((b, M + 8, N + 8), 12345.0, device="cuda", dtype=torch.bfloat16)
+    out = big[:, :M, :N]
+    gemm.ns_gemm(A, B, out=out, sym=sym, pair=pair)
+    first = out.clone()
+    gemm.ns_gemm(A, B, out=out, sym=sym, pair=pair)
+    torch.cuda.synchronize()
+    gemm.check_status()
+    assert torch.equal(first, out)
+    assert torch.all(big[:, M:, :] == 12345.0) and torch.all(big[:, :, N:] == 12345.0)
+    assert _rel_err(out, A.float() @ B.float().mT) < 1e-2

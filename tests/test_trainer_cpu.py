@@ -111,7 +111,6 @@ def test_trainer_ddp_and_fsdp_resume(tmp_path):
 
 def test_trace_spans_and_profile_helper():
     from dion_b200.utils import trace
-    assert not trace.enabled() or True
     with trace.span("idle"):          # disabled (or no GPU): nothing happens
         pass
     table = trace.profile_steps(lambda: torch.ones(8).sum(), 2)
