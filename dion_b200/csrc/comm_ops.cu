@@ -27,6 +27,16 @@ __device__ __forceinline__ void st_release_sys_i32(int* p, int v) {
 
 constexpr unsigned kMaxFlagPolls = 1u << 22;
 
+// status[0] = error code, [1] = index of the flag (source rank) that did not arrive,
+// [2] = sequence number waited for, [3] = value found.  The first reporter wins.
+__device__ __forceinline__ void report_peer_timeout(int* status, int who, int want, int found) {
+  if (atomicCAS(status, 0, kStatusTimeoutPeer) == 0) {
+    status[1] = who;
+    status[2] = want;
+    status[3] = found;
+  }
+}
+
 __global__ void bump_seq_kernel(int* seq) {
   if (threadIdx.x == 0 && blockIdx.x == 0) *seq += 1;
 }
@@ -48,7 +58,7 @@ __global__ void wait_flags_kernel(const int* flags, int n, const int* seq, int d
     if (ld_acquire_sys_i32(flags + i) >= want) return;
     __nanosleep(64);
   }
-  atomicExch(status, kStatusTimeoutPeer);
+  report_peer_timeout(status, i, want, ld_acquire_sys_i32(flags + i));
 }
 
 // scale[b] = 1 / (sqrt(sum_s partials[b*n_src + s]) * mult + eps); optionally clears partials.
@@ -153,7 +163,10 @@ allreduce_fused_kernel(const AllReduceArgs a) {
       if (ld_acquire_sys_i32(a.flags_in + threadIdx.x) >= seq) { got = true; break; }
       __nanosleep(32);
     }
-    if (!got) { atomicExch(a.status, kStatusTimeoutPeer); s_ok = 0; }
+    if (!got) {
+      report_peer_timeout(a.status, threadIdx.x, seq, ld_acquire_sys_i32(a.flags_in + threadIdx.x));
+      s_ok = 0;
+    }
   }
   __syncthreads();
   if (s_ok && a.gather) {
@@ -229,7 +242,9 @@ allreduce_fused_kernel(const AllReduceArgs a) {
       if (ld_acquire_sys_i32(a.flags_out + threadIdx.x) >= seq) { got = true; break; }
       __nanosleep(32);
     }
-    if (!got) atomicExch(a.status, kStatusTimeoutPeer);
+    if (!got)
+      report_peer_timeout(a.status, threadIdx.x, seq,
+                          ld_acquire_sys_i32(a.flags_out + threadIdx.x));
   }
   __syncthreads();
   if (threadIdx.x == 0) {

@@ -50,9 +50,14 @@ def check_status(device: Optional[torch.device] = None) -> None:
             continue
         code = int(t[0].item())
         if code != 0:
+            who, want, found = (int(v) for v in t[1:4].tolist())
             t.zero_()
+            detail = ""
+            if code == 5 and (who or want or found):
+                detail = (f" (flag of source rank {who}: waited for sequence {want}, "
+                          f"found {found})")
             raise RuntimeError(
-                f"dion_b200 kernel error on cuda:{idx}: {STATUS_MESSAGES.get(code, code)}"
+                f"dion_b200 kernel error on cuda:{idx}: {STATUS_MESSAGES.get(code, code)}{detail}"
             )
 
 

@@ -104,8 +104,9 @@ def test_wait_on_flag_nobody_sets_times_out_cleanly():
     status.zero_()
     symm.wait_flags(flags, seq, 0, status)   # nothing ever raises these flags
     torch.cuda.synchronize()
-    with pytest.raises(RuntimeError, match="peer"):
+    with pytest.raises(RuntimeError, match="peer") as err:
         gemm.check_status()
+    assert "waited for sequence 1, found 0" in str(err.value)   # who / what is reported
     x = torch.ones(8, device=dev)
     assert float((x * 2).sum()) == 16.0      # context still alive
     gemm.check_status()                       # status was cleared
