@@ -399,51 +399,27 @@ def run_reference(args) -> None:
     dev_batches = [h.to(device) for h in host]
     state = {"i": 0, "loss": None}
 
-    if graphed:
-        from dion_b200.parallel.graph_step import GraphedTrainStep
+    # The reference runs through its own public API only: its model (compiled as its trainer
+    # does), its optimizer, torch DDP; nothing of dion_b200 is on this path.
+    def step_device():
+        xy = dev_batches[state["i"] % len(dev_batches)]
+        state["i"] += 1
+        with autocast:
+            loss = call(xy[0], xy[1])
+        loss.backward()
+        opt.step()
+        call.zero_grad(set_to_none=True)
+        state["loss"] = loss.detach()
 
-        gstep = GraphedTrainStep(lambda x, y: model(x, y), list(model.parameters()), opt,
-                                 [dev_batches[0][0], dev_batches[0][1]], device=device,
-                                 process_group=pg, warmup=2)
-        # Prime: two eager steps, then the capture; count the kernels one replay launches.
-        for i in range(2):
-            gstep(dev_batches[i][0], dev_batches[i][1])
-        _backend.reset_launch_count()
-        gstep(dev_batches[2][0], dev_batches[2][1])
-        launches_per_step = _backend.launch_count()
-        torch.cuda.synchronize()
-
-        def step_device():
-            xy = dev_batches[state["i"] % len(dev_batches)]
-            state["i"] += 1
-            state["loss"] = gstep(xy[0], xy[1])
-
-        def step_e2e():
-            xy = host[state["i"] % len(host)]
-            state["i"] += 1
-            state["loss_host"] = gstep(xy[0], xy[1]).item()
-    else:
-        launches_per_step = None
-
-        def step_device():
-            xy = dev_batches[state["i"] % len(dev_batches)]
-            state["i"] += 1
-            with autocast:
-                loss = call(xy[0], xy[1])
-            loss.backward()
-            opt.step()
-            call.zero_grad(set_to_none=True)
-            state["loss"] = loss.detach()
-
-        def step_e2e():
-            xy = host[state["i"] % len(host)].to(device, non_blocking=True)
-            state["i"] += 1
-            with autocast:
-                loss = call(xy[0], xy[1])
-            loss.backward()
-            opt.step()
-            call.zero_grad(set_to_none=True)
-            state["loss_host"] = loss.item()
+    def step_e2e():
+        xy = host[state["i"] % len(host)].to(device, non_blocking=True)
+        state["i"] += 1
+        with autocast:
+            loss = call(xy[0], xy[1])
+        loss.backward()
+        opt.step()
+        call.zero_grad(set_to_none=True)
+        state["loss_host"] = loss.item()
 
     try:
         step_device()  # first call compiles / autotunes; failures here fall back to eager
