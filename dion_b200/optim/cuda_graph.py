@@ -1,73 +1,75 @@
-"""Capture ``optimizer.step()`` in a CUDA graph and replay it.
+"""Replay ``optimizer.step()`` from a CUDA graph.
 
-The megabatch optimizers issue a fixed sequence of kernels per step with no host
-synchronization, read their learning rate (and optionally weight decay) from persistent device
-tensors and advance AdamW's bias-correction counter on the device, so one captured graph stays
-valid for the whole run while a stock ``torch.optim`` scheduler keeps filling the LR tensor
-outside the graph.  Behaviour follows dion/cuda_graph.py:88-313 of the reference:
+The megabatch optimizers of this package issue the same kernels every step, never synchronize
+with the host, read learning rate (and, when opted in, weight decay) from persistent device
+tensors and keep AdamW's bias-correction counter on the device.  One recording therefore stays
+valid for a whole run while an ordinary ``torch.optim`` scheduler keeps refreshing the LR tensor
+between replays.  What this wrapper guarantees (the behaviours of dion/cuda_graph.py:88-313 in
+the reference):
 
-* the first ``warmup_steps`` steps run eagerly (they allocate state, workspaces and exchange
-  buffers); the next step is captured and replayed once; later steps only replay;
-* capture refuses to start while a ``requires_grad`` parameter has ``.grad is None`` - such a
-  parameter would be left out of the graph for good;
-* gradients must live in stable ``.grad`` buffers: ``zero_grad`` always zeroes in place;
-* ``release()`` drops the graph (``add_param_group`` / ``load_state_dict`` call it too); call
-  it before ``destroy_process_group()`` when the graph holds collectives;
-* a group that starts carrying a hyper-parameter as a device tensor after capture raises
-  instead of silently replaying the value baked at capture.
+* ``warmup_steps`` eager steps come first: they allocate optimizer state, workspaces and
+  exchange buffers.  The following step is recorded and executed by one replay; every later step
+  is a replay.
+* Recording is refused while a trainable parameter has no ``.grad``: it would be left out of the
+  recording for good.  A refused or failed recording leaves nothing behind that could be replayed.
+* Gradients have to keep their buffers, so ``zero_grad`` always zeroes in place.
+* ``release()`` discards the recording (``add_param_group`` and ``load_state_dict`` do it
+  implicitly).  Call it before ``destroy_process_group()`` when the recording holds collectives.
+* A hyper-parameter that turns into a live device tensor only after the recording was made is an
+  error, not a silent replay of the stale value.
 """
 from __future__ import annotations
 
 import warnings
 from collections import OrderedDict
-from typing import Callable, Optional
+from typing import Callable, List, Optional
 
 import torch
 
+_HOOK_TABLES = (
+    "_optimizer_step_pre_hooks", "_optimizer_step_post_hooks",
+    "_optimizer_state_dict_pre_hooks", "_optimizer_state_dict_post_hooks",
+    "_optimizer_load_state_dict_pre_hooks", "_optimizer_load_state_dict_post_hooks",
+)
+
+
+def _call_if_present(obj, name: str):
+    fn = getattr(obj, name, None)
+    return fn() if fn is not None else None
+
 
 class CudaGraphOptimizer(torch.optim.Optimizer):
-    """``torch.optim.Optimizer`` facade around ``optimizer`` with captured steps.  All state
-    lives in the inner optimizer; ``param_groups`` is shared, so an LR scheduler may be built on
-    either object."""
+    """A ``torch.optim.Optimizer`` face on ``optimizer`` whose steps are recorded once and then
+    replayed.  It owns no parameters or state of its own: ``param_groups`` and ``state`` are the
+    inner optimizer's, so a scheduler can be attached to either object."""
 
     def __init__(self, optimizer: torch.optim.Optimizer, warmup_steps: int = 10,
                  capture_error_mode: str = "thread_local"):
         if warmup_steps < 1:
             raise ValueError(
-                f"warmup_steps must be >= 1, got {warmup_steps}. Capture needs at least one "
-                "eager step to have allocated the optimizer state and communication buffers.")
-        # Optimizer.__init__ is skipped on purpose: this object owns no parameters.  The hook
-        # tables it would create are still expected by torch's profiling wrappers.
+                f"warmup_steps must be >= 1, got {warmup_steps}: at least one eager step has to "
+                "run before a recording so that state and communication buffers exist.")
+        # torch.optim.Optimizer.__init__ is deliberately not called (there are no parameters to
+        # register); torch's profiling wrappers only need the hook tables to exist.
+        for table in _HOOK_TABLES:
+            setattr(self, table, OrderedDict())
         self.optimizer = optimizer
         self.warmup_steps = warmup_steps
         self.capture_error_mode = capture_error_mode
-        self._step_count = 0
         self._graph: Optional[torch.cuda.CUDAGraph] = None
-        self._captured_hyperparam_count = 0
-        self._warned_set_to_none = False
-        for name in ("_optimizer_step_pre_hooks", "_optimizer_step_post_hooks",
-                     "_optimizer_state_dict_pre_hooks", "_optimizer_state_dict_post_hooks",
-                     "_optimizer_load_state_dict_pre_hooks",
-                     "_optimizer_load_state_dict_post_hooks"):
-            setattr(self, name, OrderedDict())
+        self._steps_taken = 0
+        self._live_tensors_at_capture = 0
+        self._told_about_set_to_none = False
 
-    # -- delegation ---------------------------------------------------------------------------
+    # -- everything else is the inner optimizer's ----------------------------------------------
     def __getattr__(self, name):
-        if name == "optimizer":
+        if name == "optimizer":           # not constructed yet (e.g. during unpickling)
             raise AttributeError(name)
         return getattr(self.optimizer, name)
 
-    @property
-    def param_groups(self):
-        return self.optimizer.param_groups
-
-    @param_groups.setter
-    def param_groups(self, value):
-        self.optimizer.param_groups = value
-
-    @property
-    def state(self):
-        return self.optimizer.state
+    param_groups = property(lambda self: self.optimizer.param_groups,
+                            lambda self, groups: setattr(self.optimizer, "param_groups", groups))
+    state = property(lambda self: self.optimizer.state)
 
     def state_dict(self):
         return self.optimizer.state_dict()
@@ -81,82 +83,74 @@ class CudaGraphOptimizer(torch.optim.Optimizer):
         return self.optimizer.add_param_group(param_group)
 
     def zero_grad(self, set_to_none: bool = False):
-        if set_to_none and not self._warned_set_to_none:
-            self._warned_set_to_none = True
-            warnings.warn(
-                "CudaGraphOptimizer needs stable .grad buffers for graph replay; ignoring "
-                "set_to_none=True and zeroing in place.", RuntimeWarning)
+        if set_to_none and not self._told_about_set_to_none:
+            self._told_about_set_to_none = True
+            warnings.warn("a recorded step reads the gradients at fixed addresses: "
+                          "set_to_none=True is ignored and gradients are zeroed in place.",
+                          RuntimeWarning)
         self.optimizer.zero_grad(set_to_none=False)
 
-    # -- graph lifetime -----------------------------------------------------------------------
+    # -- recording -----------------------------------------------------------------------------
     def release(self) -> None:
-        """Drop the captured graph; the next steps warm up and capture again."""
-        graph, self._graph = self._graph, None
-        self._captured_hyperparam_count = 0
-        self._step_count = 0
-        if graph is not None:
+        """Forget the recording; the next steps warm up and record again."""
+        old, self._graph = self._graph, None
+        self._steps_taken = 0
+        self._live_tensors_at_capture = 0
+        if old is not None:
             torch.cuda.synchronize()
-            graph.reset()
+            old.reset()
 
-    def _live_hyperparam_count(self) -> int:
-        tensors = getattr(self.optimizer, "_hyperparam_tensors", None)
-        return len(tensors) if tensors is not None else 0
+    def _count_live_tensors(self) -> int:
+        return len(getattr(self.optimizer, "_hyperparam_tensors", None) or ())
 
-    def _check_live_hyperparams_unchanged(self) -> None:
-        if self._live_hyperparam_count() != self._captured_hyperparam_count:
+    def _params_without_grad(self) -> List[str]:
+        return [f"group {g}[{i}] shape {tuple(p.shape)}"
+                for g, group in enumerate(self.param_groups)
+                for i, p in enumerate(group["params"])
+                if p.requires_grad and p.grad is None]
+
+    def _record(self) -> None:
+        orphans = self._params_without_grad()
+        if orphans:
+            listed = ", ".join(orphans[:5])
+            if len(orphans) > 5:
+                listed += f", ... (+{len(orphans) - 5} more)"
             raise RuntimeError(
-                "a param group started carrying a hyperparameter as a live device tensor after "
-                "the CUDA graph was captured (weight_decay=Tensor is the way in). The captured "
-                "graph baked the previous host value and cannot read the new tensor. Opt in "
-                "before the first capture, or call release() to re-capture.")
-
-    def _check_params_have_grads(self) -> None:
-        missing = [
-            f"group {gi}[{pi}] shape {tuple(p.shape)}"
-            for gi, group in enumerate(self.param_groups)
-            for pi, p in enumerate(group["params"])
-            if p.requires_grad and p.grad is None
-        ]
-        if missing:
-            shown = ", ".join(missing[:5]) + (f", ... (+{len(missing) - 5} more)" if len(missing) > 5 else "")
-            raise RuntimeError(
-                f"{len(missing)} parameter(s) require a gradient but have .grad=None at CUDA graph "
-                f"capture, so replay would never update them: {shown}. Capture after every "
-                "parameter has taken part in a backward pass (raise warmup_steps), or set "
-                "requires_grad=False on the ones that are meant to be frozen.")
-
-    def _sync_host_hyperparams(self) -> None:
-        sync = getattr(self.optimizer, "_sync_hyperparam_tensors", None)
-        if sync is not None:
-            sync()
-
-    def _capture(self) -> None:
-        self._check_params_have_grads()
+                f"cannot record the optimizer step: {len(orphans)} trainable parameter(s) have "
+                f"no .grad yet and would never be updated by replays: {listed}.  Record after "
+                "every parameter has received a gradient (more warmup_steps), or freeze the "
+                "ones that are meant to stay fixed (requires_grad=False).")
         torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
-        # A failed capture leaves self._graph unset, so nothing half-built is ever replayed.
         with torch.cuda.graph(graph, capture_error_mode=self.capture_error_mode):
             self.optimizer.step()
+        # Only a completed recording is kept.
         self._graph = graph
-        self._captured_hyperparam_count = self._live_hyperparam_count()
-        graph.replay()
+        self._live_tensors_at_capture = self._count_live_tensors()
+        graph.replay()   # recording executed nothing on the device; this is that step's work
+
+    def _replay(self) -> None:
+        if self._count_live_tensors() != self._live_tensors_at_capture:
+            raise RuntimeError(
+                "a hyper-parameter became a live device tensor after the step was recorded "
+                "(assigning a Tensor weight_decay is the way in); the recording holds the old "
+                "host value and cannot see the tensor.  Opt in before the first recording or "
+                "call release() to record again.")
+        self._graph.replay()
+        _call_if_present(self.optimizer, "_advance_host_step_counters")
 
     def step(self, closure: Optional[Callable] = None):
         loss = None
         if closure is not None:
             with torch.enable_grad():
                 loss = closure()
-        if self._step_count < self.warmup_steps:
+        if self._steps_taken < self.warmup_steps:
             self.optimizer.step()
         else:
-            self._sync_host_hyperparams()
+            _call_if_present(self.optimizer, "_sync_hyperparam_tensors")
             if self._graph is None:
-                self._capture()
+                self._record()
             else:
-                self._check_live_hyperparams_unchanged()
-                self._graph.replay()
-                advance = getattr(self.optimizer, "_advance_host_step_counters", None)
-                if advance is not None:
-                    advance()
-        self._step_count += 1
+                self._replay()
+        self._steps_taken += 1
         return loss

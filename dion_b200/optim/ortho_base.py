@@ -71,6 +71,22 @@ def compute_split_lr_scales(split_sizes, param_shape, adjust_lr: Optional[str]):
     return tuple(lr_ratio(adjust_lr, (rows, cols), False) / whole for rows in split_sizes)
 
 
+def _mesh_coordinates(mesh) -> Tuple[int, int, Optional[ProcessGroup]]:
+    """(this rank, number of ranks, process group) of the 1-D mesh or process group over which
+    matrices are sharded / work is divided; ``None`` means a single device."""
+    if mesh is None:
+        return 0, 1, None
+    if isinstance(mesh, ProcessGroup):
+        return dist.get_rank(mesh), dist.get_world_size(mesh), mesh
+    if isinstance(mesh, DeviceMesh):
+        if mesh.ndim == 1:
+            return mesh.get_local_rank(), mesh.size(), mesh.get_group()
+        raise ValueError(f"Only 1D DeviceMesh supported, but got {mesh.ndim}D. "
+                         f"For HSDP, provide the 1D sharded sub-mesh.")
+    raise TypeError(f"Invalid distributed_mesh type: {type(mesh)}. "
+                    f"Expected DeviceMesh or ProcessGroup.")
+
+
 class DistributedOrthoBase(Optimizer):
     """Base class; subclasses implement ``_create_ortho_tasks(groups)``."""
 
@@ -88,24 +104,8 @@ class DistributedOrthoBase(Optimizer):
         super().__init__(params, defaults)
         self._algo_name = algo_name
 
-        if isinstance(distributed_mesh, DeviceMesh):
-            if distributed_mesh.ndim != 1:
-                raise ValueError(
-                    f"Only 1D DeviceMesh supported, but got {distributed_mesh.ndim}D. "
-                    f"For HSDP, provide the 1D sharded sub-mesh.")
-            self._device_rank = distributed_mesh.get_local_rank()
-            self._world_size = distributed_mesh.size()
-            self._process_group = distributed_mesh.get_group()
-        elif isinstance(distributed_mesh, ProcessGroup):
-            self._device_rank = dist.get_rank(distributed_mesh)
-            self._world_size = dist.get_world_size(distributed_mesh)
-            self._process_group = distributed_mesh
-        elif distributed_mesh is None:
-            self._device_rank, self._world_size, self._process_group = 0, 1, None
-        else:
-            raise TypeError(
-                f"Invalid distributed_mesh type: {type(distributed_mesh)}. "
-                f"Expected DeviceMesh or ProcessGroup.")
+        self._device_rank, self._world_size, self._process_group = _mesh_coordinates(
+            distributed_mesh)
         self._distributed_mesh = distributed_mesh
 
         # Newton-Schulz driver.  ``use_triton`` is accepted for signature compatibility: on CUDA
@@ -141,22 +141,25 @@ class DistributedOrthoBase(Optimizer):
 
     def add_param_group(self, param_group: dict) -> None:
         super().add_param_group(param_group)
-        if getattr(self, "_state_prepopulated", False):
-            index = len(self.param_groups) - 1
-            for name in self._live_hyperparams(index):
-                self._ensure_hyperparam_tensor(index, name)
-            self._prepopulate_group_state(self.param_groups[-1])
+        if not getattr(self, "_state_prepopulated", False):
+            return  # still inside __init__: the constructor finishes the job for every group
+        newest = len(self.param_groups) - 1
+        for hyper in self._live_hyperparams(newest):
+            self._ensure_hyperparam_tensor(newest, hyper)
+        self._prepopulate_group_state(self.param_groups[newest])
 
     def _get_or_initialize_state(self, param: Tensor, algo: str) -> dict:
         state = self.state[param]
-        if not state:
+        is_adamw = algo == "adamw"
+        if len(state) == 0:
             state["momentum"] = torch.zeros_like(param)
-            if algo == "adamw":
+            if is_adamw:
                 state["variance"] = torch.zeros_like(param)
-        if algo == "adamw" and "step_dev" not in state:
-            # fp32 device counter: bias correction has to advance under graph replay, and a
-            # bf16 counter would stop counting at 256.
-            state["step_dev"] = torch.zeros((), dtype=torch.float32, device=to_local(param).device)
+        if is_adamw and state.get("step_dev") is None:
+            # The bias-correction counter lives on the device so that it advances under graph
+            # replay; fp32 because a bf16 counter stops counting at 256.
+            state["step_dev"] = torch.zeros((), dtype=torch.float32,
+                                            device=to_local(param).device)
         return state
 
     # ------------------------------------------------------------------ step ----------------
@@ -354,86 +357,83 @@ class DistributedOrthoBase(Optimizer):
         """Hyper-parameters of group ``index`` that live in persistent device tensors.  ``lr``
         always; ``weight_decay`` once the caller has supplied a Tensor for it (the opt-in
         latches: later float assignments refill the tensor instead of replacing it)."""
-        live = self._live_hyperparams_by_group.get(index)
-        if live is None or "weight_decay" not in live:
-            if isinstance(self.param_groups[index].get("weight_decay"), Tensor):
-                live = ("lr", "weight_decay")
-            elif live is None:
-                live = ("lr",)
-            self._live_hyperparams_by_group[index] = live
-        return live
+        known = self._live_hyperparams_by_group.get(index, ())
+        if "weight_decay" not in known and isinstance(
+                self.param_groups[index].get("weight_decay"), Tensor):
+            known = ("lr", "weight_decay")
+        elif not known:
+            known = ("lr",)
+        self._live_hyperparams_by_group[index] = known
+        return known
 
     def _ensure_hyperparam_tensor(self, index: int, name: str) -> Optional[Tensor]:
         """Make ``param_groups[index][name]`` the group's persistent 0-d fp32 device tensor.
         The tensor is allocated once and afterwards only filled, because a captured graph keeps
         reading the tensor it recorded."""
         group = self.param_groups[index]
-        if not group["params"]:
+        if len(group["params"]) == 0:
             return None
-        value = group[name]
-        tensor = self._hyperparam_tensors.get((index, name))
-        if value is tensor:
-            return tensor
+        slot = (index, name)
+        held = self._hyperparam_tensors.get(slot)
+        current = group[name]
+        if current is held:          # already the persistent tensor (possibly refilled in place)
+            return held
         if torch.cuda.is_available() and torch.cuda.is_current_stream_capturing():
             raise RuntimeError(
-                f"param group {index} has a {name} that is not its persistent device tensor "
-                f"({type(value).__name__}), and CUDA graph capture is already underway so it "
-                f"cannot be refreshed. Sync {name} before capturing (CudaGraphOptimizer does "
-                f"this for you).")
+                f"param group {index}: {name} is a {type(current).__name__}, not the group's "
+                f"persistent device tensor, and it cannot be refreshed while a CUDA graph is "
+                f"being captured.  Sync {name} before capturing (CudaGraphOptimizer does).")
         device = to_local(group["params"][0]).device
-        if tensor is None or tensor.device != device:
-            tensor = torch.empty((), dtype=torch.float32, device=device)
-            self._hyperparam_tensors[(index, name)] = tensor
-        if isinstance(value, Tensor):
-            tensor.copy_(value)
-        else:
-            tensor.fill_(value)
-        group[name] = tensor
-        return tensor
+        if held is None or held.device != device:
+            held = self._hyperparam_tensors[slot] = torch.empty((), dtype=torch.float32,
+                                                               device=device)
+        held.copy_(current) if isinstance(current, Tensor) else held.fill_(current)
+        group[name] = held
+        return held
 
     def _sync_hyperparam_tensors(self) -> None:
-        for index in range(len(self.param_groups)):
+        for index, _ in enumerate(self.param_groups):
             for name in self._live_hyperparams(index):
                 self._ensure_hyperparam_tensor(index, name)
 
     def _advance_host_step_counters(self) -> None:
         """Host ``group["step"]`` bookkeeping for a step that ran as a graph replay."""
         for group in self.param_groups:
-            group["step"] += 1
+            group["step"] = group["step"] + 1
 
     # ------------------------------------------------------------------ checkpointing -------
     def state_dict(self):
+        """As ``Optimizer.state_dict`` with every 0-d tensor hyper-parameter (lr, a scheduler's
+        initial_lr, tensor weight decay) written as a python number: checkpoints carry no device
+        tensors in their param groups."""
         sd = super().state_dict()
-        # 0-d tensor hyper-parameters (lr, a scheduler's initial_lr, tensor weight decay) are
-        # written as python numbers so that checkpoints carry no device tensors.
-        for group in sd["param_groups"]:
-            for key, value in list(group.items()):
-                if key != "params" and isinstance(value, Tensor) and value.ndim == 0:
-                    group[key] = value.item()
+        sd["param_groups"] = [
+            {k: (v.item() if k != "params" and isinstance(v, Tensor) and v.ndim == 0 else v)
+             for k, v in group.items()}
+            for group in sd["param_groups"]]
         return sd
 
     def load_state_dict(self, state_dict):
         super().load_state_dict(state_dict)
         self._sync_hyperparam_tensors()
-        for group in self.param_groups:
-            if group["algorithm"] != "adamw":
-                continue
-            for param in group["params"]:
-                state = self.state.get(param)
-                if state is not None:
-                    self._restore_step_tensor(state, param, group)
+        adamw_params = [(p, g) for g in self.param_groups if g["algorithm"] == "adamw"
+                        for p in g["params"]]
+        for param, group in adamw_params:
+            state = self.state.get(param)
+            if state is not None:
+                self._restore_step_tensor(state, param, group)
 
     def _restore_step_tensor(self, state: dict, param: Tensor, group: dict) -> None:
         """``Optimizer.load_state_dict`` casts state to the parameter dtype and device; put the
         AdamW counter back to fp32 on the parameter's device, or rebuild it from the host step
         for checkpoints that predate it."""
         device = to_local(param).device
-        step = state.get("step_dev")
-        if step is None:
-            step = torch.full((), float(group["step"]), dtype=torch.float32, device=device)
-        elif step.dtype != torch.float32 or step.device != device:
-            step = step.to(dtype=torch.float32, device=device)
-        state["step_dev"] = step
+        counter = state.get("step_dev")
+        if counter is None:
+            counter = torch.full((), float(group["step"]), dtype=torch.float32, device=device)
+        elif counter.dtype != torch.float32 or counter.device != device:
+            counter = counter.to(dtype=torch.float32, device=device)
+        state["step_dev"] = counter
 
 
 def _as_task(fn: Callable, *args, **kwargs) -> Generator[None, None, None]:
