@@ -41,30 +41,37 @@ class Dion(Optimizer):
                  betas: Tuple[float, float] = (0.9, 0.95), weight_decay: float = 0.01,
                  rank: int = 768, epsilon: float = 1e-8,
                  mixed_precision_config: Optional[DionMixedPrecisionConfig] = None):
-        if lr < 0.0:
-            raise ValueError(f"Invalid learning rate: {lr}")
-        if mu < 0.0:
-            raise ValueError(f"Invalid momentum factor (mu): {mu}")
-        if len(betas) != 2 or betas[0] < 0.0 or betas[1] < 0.0:
-            raise ValueError(f"Invalid betas: {betas}")
-        if weight_decay < 0.0:
-            raise ValueError(f"Invalid weight_decay value: {weight_decay}")
-        if rank < 1:
-            raise ValueError(f"Invalid rank value: {rank}")
-        super().__init__(params, dict(lr=lr, mu=mu, beta1=betas[0], beta2=betas[1],
-                                      weight_decay=weight_decay, algorithm="dion", step=0))
+        checks = (("learning rate", lr, lr >= 0.0), ("momentum factor (mu)", mu, mu >= 0.0),
+                  ("betas", betas, len(betas) == 2 and min(betas) >= 0.0),
+                  ("weight_decay value", weight_decay, weight_decay >= 0.0),
+                  ("rank value", rank, rank >= 1))
+        for what, value, ok in checks:
+            if not ok:
+                raise ValueError(f"Invalid {what}: {value}")
+        defaults = dict(lr=lr, mu=mu, beta1=betas[0], beta2=betas[1], weight_decay=weight_decay,
+                        algorithm="dion", step=0)
+        super().__init__(params, defaults)
         self.rank = rank
         self.epsilon = torch.tensor(epsilon)
         self._mixed_precision_config = mixed_precision_config or DionMixedPrecisionConfig()
-        for group in self.param_groups:
-            if group["algorithm"] != "dion":
-                continue
-            for p in group["params"]:
-                if p.dim() != 2:
-                    raise ValueError(f"Expected Dion parameters to be 2D tensor, but got {p.dim()}D.")
-                if isinstance(p, DTensor):
-                    raise NotImplementedError(
-                        "This version of Dion optimizer does not support distributed tensors.")
+        matrices = [p for g in self.param_groups if g["algorithm"] == "dion" for p in g["params"]]
+        for p in matrices:
+            if p.dim() != 2:
+                raise ValueError(f"Expected Dion parameters to be 2D tensor, but got {p.dim()}D.")
+            if isinstance(p, DTensor):
+                raise NotImplementedError(
+                    "This version of Dion optimizer does not support distributed tensors.")
+
+    def _new_state(self, p: Tensor, algo: str) -> dict:
+        mp = self._mixed_precision_config
+        if algo == "dion":
+            r = min(self.rank, min(p.shape))
+            return {"momentum": torch.zeros_like(p, dtype=mp.momentum_dtype or p.dtype),
+                    "Q": torch.randn((p.size(1), r), device=p.device, dtype=mp.Q_dtype or p.dtype)}
+        state = {"momentum": torch.zeros_like(p)}
+        if algo == "adamw":
+            state["variance"] = torch.zeros_like(p)
+        return state
 
     @torch.no_grad()
     def step(self, closure=None):
@@ -72,33 +79,23 @@ class Dion(Optimizer):
         if closure is not None:
             with torch.enable_grad():
                 loss = closure()
-        mp = self._mixed_precision_config
         for group in self.param_groups:
             algo = group["algorithm"]
-            group["step"] += 1
             if algo not in ("dion", "adamw", "lion"):
                 raise ValueError(f"Unknown algorithm: {algo}")
-            for p in group["params"]:
-                if p.grad is None:
-                    continue
+            group["step"] += 1
+            for p in (q for q in group["params"] if q.grad is not None):
                 st = self.state[p]
+                if len(st) == 0:
+                    st.update(self._new_state(p, algo))
                 if algo == "dion":
-                    if not st:
-                        st["momentum"] = torch.zeros_like(p, dtype=mp.momentum_dtype or p.dtype)
-                        st["Q"] = torch.randn((p.size(1), min(self.rank, min(p.shape))),
-                                              device=p.device, dtype=mp.Q_dtype or p.dtype)
                     dion_update(p, p.grad, st["momentum"], st["Q"], group["lr"], group["mu"],
                                 group["weight_decay"], self.epsilon)
                 elif algo == "adamw":
-                    if not st:
-                        st["momentum"] = torch.zeros_like(p)
-                        st["variance"] = torch.zeros_like(p)
                     F.adamw([p], [p.grad], [st["momentum"]], [st["variance"]], group["lr"],
                             group["beta1"], group["beta2"], group["weight_decay"],
                             float(self.epsilon), step=group["step"])
                 else:
-                    if not st:
-                        st["momentum"] = torch.zeros_like(p)
                     F.lion([p], [p.grad], [st["momentum"]], group["lr"], group["beta1"],
                            group["beta2"], group["weight_decay"])
         return loss
