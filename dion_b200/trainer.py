@@ -136,7 +136,7 @@ def parse_cli_args(argv: Optional[List[str]] = None) -> argparse.Namespace:
         import yaml
 
         with open(args.config) as f:
-            cfg = yaml.safe_load(f) or {}
+            cfg = flatten_config(yaml.safe_load(f) or {})
         store_true = {a.dest for a in p._actions if isinstance(a, argparse._StoreTrueAction)}
         for key, value in cfg.items():
             if not hasattr(args, key):
@@ -147,6 +147,20 @@ def parse_cli_args(argv: Optional[List[str]] = None) -> argparse.Namespace:
             elif getattr(args, key) is None:
                 setattr(args, key, value)
     return args
+
+
+def flatten_config(cfg: dict) -> dict:
+    """Configuration files may group their keys in sections (``model: {...}``,
+    ``optimizer: {...}``, ...); the section names carry no meaning, every leaf key is a flag of
+    this script.  Flat files (one ``flag: value`` per line, the reference's layout) load the
+    same way."""
+    flat: dict = {}
+    for key, value in cfg.items():
+        if isinstance(value, dict):
+            flat.update(flatten_config(value))
+        else:
+            flat[key] = value
+    return flat
 
 
 def override_args_from_cli(hp: Hyperparameters, args: argparse.Namespace) -> Hyperparameters:

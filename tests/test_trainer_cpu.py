@@ -115,3 +115,21 @@ def test_trace_spans_and_profile_helper():
         pass
     table = trace.profile_steps(lambda: torch.ones(8).sum(), 2)
     assert "aten::sum" in table or "aten::ones" in table
+
+
+def test_sectioned_and_flat_config_files_load_alike(tmp_path):
+    from dion_b200.trainer import flatten_config, parse_cli_args
+    assert flatten_config({"a": 1, "s": {"b": 2, "t": {"c": 3}}}) == {"a": 1, "b": 2, "c": 3}
+    sectioned = tmp_path / "s.yaml"
+    sectioned.write_text("model: {model_dim: 96, n_layer: 3}\noptimizer: {optimizer: muon, lr: 0.5}\n"
+                         "logging: {no_wandb: true}\n")
+    flat = tmp_path / "f.yaml"
+    flat.write_text("model_dim: 96\nn_layer: 3\noptimizer: muon\nlr: 0.5\nno_wandb: true\n")
+    a, b = parse_cli_args(["--config", str(sectioned)]), parse_cli_args(["--config", str(flat)])
+    assert vars(a) | {"config": None} == vars(b) | {"config": None}
+    assert a.model_dim == 96 and a.optimizer == "muon" and a.no_wandb is True
+    # a flag on the command line wins over the file
+    assert parse_cli_args(["--config", str(sectioned), "--lr", "0.1"]).lr == 0.1
+    for name in os.listdir(os.path.join(ROOT, "configs")):
+        args = parse_cli_args(["--config", os.path.join(ROOT, "configs", name)])
+        assert args.optimizer and args.model_dim
