@@ -58,6 +58,7 @@ class BucketedGradSync:
         self._stream: Optional[torch.cuda.Stream] = None
         self._handles = []
         self._events: List = []  # (bucket index, event) in launch order on the side stream
+        self.active = True       # False: let gradients accumulate locally (like DDP.no_sync)
         self.enabled = self.world > 1
         if self.enabled:
             for p in self.params:
@@ -70,6 +71,8 @@ class BucketedGradSync:
 
     # ----------------------------------------------------------------------------------------
     def _on_grad(self, p: Tensor) -> None:
+        if not self.active:
+            return
         bi = self._bucket_of[p]
         self._pending[bi] -= 1
         if self._pending[bi] == 0:
@@ -153,13 +156,17 @@ class GraphedTrainStep:
     static device tensor that the next call overwrites.
 
     ``use_graph=False`` keeps the same step eager (for debugging and as the fallback on CPU).
+    With ``accumulation_steps = k > 1`` every input carries a leading dimension ``k``: the step
+    runs ``k`` forward/backward passes whose gradients accumulate (the loss is their mean) and
+    reduces / applies them once.
     """
 
     def __init__(self, loss_fn: Callable[..., Tensor], params: Sequence[Tensor],
                  optimizer: torch.optim.Optimizer, example_inputs: Sequence[Tensor], *,
                  device: torch.device, process_group=None,
                  autocast_dtype: Optional[torch.dtype] = torch.bfloat16,
-                 warmup: int = 3, use_graph: bool = True, bucket_mb: float = 64.0):
+                 warmup: int = 3, use_graph: bool = True, bucket_mb: float = 64.0,
+                 accumulation_steps: int = 1):
         self.loss_fn = loss_fn
         self.params = [p for p in params]
         self.optimizer = optimizer
@@ -169,7 +176,11 @@ class GraphedTrainStep:
         self.use_graph = use_graph and device.type == "cuda"
         self.sync = BucketedGradSync(self.params, process_group, bucket_mb)
         self._deferrable = self._scalar_group_params(optimizer)
-        self.static_inputs = [torch.empty(t.shape, dtype=t.dtype, device=device)
+        if accumulation_steps < 1:
+            raise ValueError("accumulation_steps must be >= 1")
+        self.accumulation_steps = accumulation_steps
+        lead = (accumulation_steps,) if accumulation_steps > 1 else ()
+        self.static_inputs = [torch.empty(lead + tuple(t.shape), dtype=t.dtype, device=device)
                               for t in example_inputs]
         self.static_loss: Optional[Tensor] = None
         self.graph: Optional[torch.cuda.CUDAGraph] = None
@@ -196,10 +207,25 @@ class GraphedTrainStep:
         return torch.autocast(device_type=self.device.type, dtype=self.autocast_dtype)
 
     def _one_step(self) -> Tensor:
-        with trace.span("forward"), self._autocast():
-            loss = self.loss_fn(*self.static_inputs)
-        with trace.span("backward"):
-            loss.backward()
+        k = self.accumulation_steps
+        if k == 1:
+            with trace.span("forward"), self._autocast():
+                loss = self.loss_fn(*self.static_inputs)
+            with trace.span("backward"):
+                loss.backward()
+        else:
+            # Micro-batches accumulate into the same gradients; only the last backward hands
+            # them to the bucketed all-reduce.
+            total = None
+            for i in range(k):
+                self.sync.active = i == k - 1
+                with trace.span("forward"), self._autocast():
+                    part = self.loss_fn(*[t[i] for t in self.static_inputs]) / k
+                with trace.span("backward"):
+                    part.backward()
+                total = part.detach() if total is None else total + part.detach()
+            self.sync.active = True
+            loss = total
         with trace.span("grad_sync"):
             deferred = self.sync.finish(self._deferrable)
         if deferred:

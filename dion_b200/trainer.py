@@ -452,9 +452,9 @@ def main(argv: Optional[List[str]] = None) -> None:
                                            dp_world, device=device)
 
     graph_step = bool(args.graph_step) and device.type == "cuda"
-    if graph_step and (mesh is not None or grad_accum != 1):
+    if graph_step and mesh is not None:
         raise ValueError("--graph_step needs plain data parallelism (no --dp_size/--fs_size/"
-                         "--tp_size) and a batch that fits without gradient accumulation")
+                         "--tp_size)")
     model, raw_model, ddp = build_model(hp, mesh, device, fast_fsdp=args.fast_fsdp,
                                         wrap_ddp=not graph_step)
     if graph_step and world > 1:
@@ -516,7 +516,7 @@ def main(argv: Optional[List[str]] = None) -> None:
         sync_pg = dist.group.WORLD if (world > 1 and not hp.replicate_mesh_grad_sync) else None
         gstep = GraphedTrainStep(lambda a, b: raw_model(a, b), list(raw_model.parameters()),
                                  optimizer, [x, y], device=device, process_group=sync_pg,
-                                 warmup=3)
+                                 warmup=3, accumulation_steps=grad_accum)
     for step in range(start_step, hp.num_iterations + 1):
         last = step == hp.num_iterations
         if hp.val_loss_every > 0 and (last or step % hp.val_loss_every == 0):
@@ -568,7 +568,15 @@ def main(argv: Optional[List[str]] = None) -> None:
             timed = 0
         if gstep is not None:
             timer_all.start()
-            train_loss = gstep(x, y).clone()
+            if grad_accum == 1:
+                train_loss = gstep(x, y).clone()
+            else:  # the graph holds all micro-batches of the step
+                xs, ys = [x], [y]
+                for _ in range(grad_accum - 1):
+                    x, y = train_loader.next_batch()
+                    xs.append(x)
+                    ys.append(y)
+                train_loss = gstep(torch.stack(xs), torch.stack(ys)).clone()
             scheduler.step()
             x, y = train_loader.next_batch()
             if args.time_optimizer:

@@ -160,7 +160,7 @@ def test_trainer_with_graph_step_runs_and_loss_falls():
     cmd = [sys.executable, "-m", "torch.distributed.run", "--standalone", "--local-addr",
            "127.0.0.1", "--nproc-per-node", "1", os.path.join(root, "train.py"),
            "--synthetic", "--no_wandb", "--debug", "--model_dim", "128", "--n_layer", "2",
-           "--n_head", "2", "--sequence_length", "64", "--batch_size", "8",
+           "--n_head", "2", "--sequence_length", "64", "--batch_size", "16",   # 2 micro-batches
            "--device_batch_size", "8", "--val_loss_every", "0", "--scalar_opt", "adamw",
            "--optimizer", "muon", "--num_iterations", "12", "--graph_step"]
     res = subprocess.run(cmd, capture_output=True, text=True, timeout=600, cwd=root)
@@ -168,3 +168,35 @@ def test_trainer_with_graph_step_runs_and_loss_falls():
     losses = [float(m) for m in re.findall(r"train_loss=([0-9.]+)", res.stdout)]
     assert len(losses) == 12
     assert all(l == l and l < 20 for l in losses)
+
+
+def _accum_worker(rank, world):
+    """k micro-batches through the step object == one batch of k times the size."""
+    from dion_b200.parallel.graph_step import GraphedTrainStep
+
+    def run(k):
+        model = _mlp()
+        opt = torch.optim.SGD(model.parameters(), lr=0.1)
+        ex = torch.zeros(4 // k, 16)
+        step = GraphedTrainStep(lambda a: model(a).pow(2).mean(), list(model.parameters()), opt,
+                                [ex], device=torch.device("cpu"), autocast_dtype=None,
+                                use_graph=False, accumulation_steps=k)
+        losses = []
+        for i in range(3):
+            torch.manual_seed(11 * rank + i)
+            data = torch.randn(4, 16)
+            losses.append(float(step(data if k == 1 else data.view(k, 4 // k, 16))))
+        return losses, torch.cat([p.detach().reshape(-1) for p in model.parameters()])
+
+    l1, p1 = run(1)
+    l2, p2 = run(2)
+    assert torch.allclose(p1, p2, atol=1e-6)
+    assert all(abs(a - b) < 1e-6 for a, b in zip(l1, l2))
+    gathered = [torch.empty_like(p2) for _ in range(world)]
+    dist.all_gather(gathered, p2)
+    assert all(torch.equal(g, p2) for g in gathered)
+    return True
+
+
+def test_gradient_accumulation_in_step_object_gloo():
+    run_ranks(_accum_worker, 2)
