@@ -81,3 +81,23 @@ def test_training_reduces_loss_on_a_repeated_batch():
         first = float(loss.detach()) if first is None else first
         last = float(loss.detach())
     assert last < first - 0.5
+
+
+def test_weights_interchange_with_the_reference_model(ref_dion):
+    """Same parameter names and the same function: a reference checkpoint loads into this model
+    and gives the same loss and logits (and the other way round)."""
+    from models.gpt_model import GPT as RefGPT, GPTConfig as RefConfig  # baseline/_ref/models
+    ours = _model(3)
+    torch.manual_seed(4)
+    ref = RefGPT(RefConfig(**CFG))
+    ref.init_weights()
+    missing, unexpected = ref.load_state_dict(ours.state_dict(), strict=False)
+    assert not [k for k in missing if "inv_freq" not in k] and not unexpected
+    x = torch.randint(0, 128, (2, 16), generator=torch.Generator().manual_seed(5))
+    y = torch.randint(0, 128, (2, 16), generator=torch.Generator().manual_seed(6))
+    with torch.no_grad():
+        assert abs(float(ours(x, y)) - float(ref(x, y))) < 1e-5
+    assert torch.allclose(ours(x, y, return_logits=True), ref(x, y, return_logits=True), atol=1e-4)
+    ours2 = _model(7)
+    ours2.load_state_dict({k: v for k, v in ref.state_dict().items() if "inv_freq" not in k})
+    assert torch.allclose(ours2(x, y, return_logits=True), ours(x, y, return_logits=True), atol=1e-6)
