@@ -108,8 +108,10 @@ def orthogonalize(P: Tensor, oversample: float = 1.25,
 def fix_all_zero_or_nan(P: Tensor, R: Tensor, Q_init: Tensor, B: Tensor) -> Tuple[Tensor, Tensor]:
     """Branch-free guard: where the (local) momentum ``B[b]`` is entirely zero, return ``P = 0``
     and ``R = Q_init``; elsewhere replace NaNs by zero.  Shards are judged independently so no
-    communication is needed."""
-    zero = (B == 0).all(dim=(-2, -1), keepdim=True)
+    communication is needed.  "Entirely zero" is read off the max-norm (one pass over ``B`` with
+    no full-size temporary; a NaN in ``B`` makes the norm NaN, which is not zero, exactly as an
+    element-wise comparison would decide)."""
+    zero = (torch.linalg.vector_norm(B, ord=float("inf"), dim=(-2, -1), keepdim=True) == 0)
     keep = ~zero
     return P.nan_to_num() * keep, R.nan_to_num() * keep + Q_init * zero
 
@@ -131,13 +133,23 @@ def column_normalize(X: Tensor, full_column_sum_sq: Optional[Tensor] = None,
 
 def foreach_baddbmm_(X: List[Tensor], A: Tensor, B: Tensor, alpha=1.0, beta=1.0,
                      transpose: bool = False) -> None:
-    """``X[i] = beta*X[i] + alpha*(A[i] @ B[i]^T)`` (or ``B[i] @ A[i]^T`` when ``transpose``)."""
+    """``X[i] = beta*X[i] + alpha*(A[i] @ B[i]^T)`` (or ``B[i] @ A[i]^T`` when ``transpose``).
+    One fused GEMM-with-epilogue per matrix: the rank-r product is never materialized at full
+    size and every ``X[i]`` is read and written once."""
     assert A.size(0) == B.size(0) == len(X)
-    upd = (B @ A.mT) if transpose else (A @ B.mT)
-    upd = torch._foreach_mul(list(upd.unbind(0)), alpha)
-    if not (isinstance(beta, float) and beta == 1.0):
+    if isinstance(alpha, Tensor) or isinstance(beta, Tensor):
+        # Device-resident scalars (no host read): scale with multi-tensor ops instead.
+        upd = (B @ A.mT) if transpose else (A @ B.mT)
+        upd = torch._foreach_mul(list(upd.unbind(0)), alpha)
         torch._foreach_mul_(X, beta)
-    torch._foreach_add_(X, [u.to(x.dtype) for u, x in zip(upd, X)])
+        torch._foreach_add_(X, [u.to(x.dtype) for u, x in zip(upd, X)])
+        return
+    alpha, beta = float(alpha), float(beta)
+    for i, x in enumerate(X):
+        a, b = (B[i], A[i]) if transpose else (A[i], B[i])
+        if a.dtype != x.dtype:
+            a, b = a.to(x.dtype), b.to(x.dtype)
+        torch.addmm(x, a, b.mT, beta=beta, alpha=alpha, out=x)
 
 
 def stack_for_power_iteration(M: List[Tensor], Q: List[Tensor], transposed: bool):
