@@ -1,0 +1,60 @@
+"""The JSON line bench.py prints (checked here without a GPU) and its reference-arm fall-back."""
+import argparse
+import importlib.util
+import json
+import os
+import subprocess
+import sys
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _bench():
+    spec = importlib.util.spec_from_file_location("bench_mod", os.path.join(ROOT, "bench.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def test_json_line_has_the_contract_fields(capsys):
+    bench = _bench()
+    args = argparse.Namespace(steps=20, warmup=5, optimizer="dion2")
+    clocks = {"sm_mhz": 1700.0, "sm_max_mhz": 1965.0, "reasons": ["sw_power_cap"]}
+    bench.emit(args, "ours", 700.0, 720.0, clocks, 3380, 2, {"final_loss": 1.0})
+    line = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    for key in ("metric", "value", "unit", "n_gpus", "steps", "warmup", "ms_per_step",
+                "higher_is_better", "scaling", "vs_baseline", "dtype", "data", "config", "clocks",
+                "gpu_launches", "e2e"):
+        assert key in line, key
+    assert line["n_gpus"] == 2 and line["steps"] == 20 and line["warmup"] == 5
+    assert line["higher_is_better"] is True and line["scaling"] == "weak" and line["dtype"] == "bf16"
+    assert line["ms_per_step"] == 35.0
+    tokens = 2 * bench.DEVICE_BATCH * bench.SEQ * 20
+    assert abs(line["value"] - tokens / 0.7) < 1e-6          # whole-job tokens/s
+    assert line["config"]["global_batch"] == 2 * bench.DEVICE_BATCH
+    assert line["config"]["seq_len"] == bench.SEQ and line["config"]["parallelism"] == "ddp2"
+    assert set(line["e2e"]) >= {"value", "unit", "h2d_bytes_per_step", "d2h_bytes_per_step"}
+    assert line["e2e"]["h2d_bytes_per_step"] == 2 * bench.DEVICE_BATCH * bench.SEQ * 8
+    assert line["gpu_launches"] == 3380
+
+
+def test_defaults_are_one_gpu_and_a_short_run():
+    bench = _bench()
+    old = sys.argv
+    sys.argv = ["bench.py"]
+    try:
+        args = bench.parse()
+    finally:
+        sys.argv = old
+    assert args.gpus == 1 and args.impl == "ours" and args.warmup >= 3 and args.steps <= 50
+
+
+def test_reference_arm_reports_unavailable_when_not_installed(tmp_path):
+    """Without baseline/_ref the reference arm prints its `unavailable` line and exits 0."""
+    copy = tmp_path / "bench.py"
+    copy.write_text(open(os.path.join(ROOT, "bench.py")).read())
+    res = subprocess.run([sys.executable, str(copy), "--impl", "reference"], capture_output=True,
+                         text=True, timeout=300, cwd=str(tmp_path))
+    assert res.returncode == 0, res.stderr[-500:]
+    line = json.loads(res.stdout.strip().splitlines()[-1])
+    assert line["impl"] == "reference" and "unavailable" in line
