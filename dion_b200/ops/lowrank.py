@@ -152,6 +152,35 @@ def foreach_baddbmm_(X: List[Tensor], A: Tensor, B: Tensor, alpha=1.0, beta=1.0,
         torch.addmm(x, a, b.mT, beta=beta, alpha=alpha, out=x)
 
 
+def _tcgen05_ok(A: Tensor, B: Tensor) -> bool:
+    from . import gemm
+    from ..utils.tensors import is_plain_tensor
+
+    return (A.is_cuda and A.dtype == torch.bfloat16 and B.dtype == torch.bfloat16
+            and A.ndim == 3 and B.ndim == 3 and is_plain_tensor(A) and is_plain_tensor(B)
+            and A.is_contiguous() and B.is_contiguous() and gemm.supported(A, B)
+            and B.size(-1) % 8 == 0 and min(A.shape[-2:]) >= 64 and B.size(-1) >= 64)
+
+
+def power_iteration_p(Mb: Tensor, Qb: Tensor) -> Tensor:
+    """``P = M Q`` for batches ``Mb [B, m, n]``, ``Qb [B, n, r]`` (reference: dion/dion.py:798).
+    bf16 batches on a GPU run on this package's tcgen05 GEMM (``Q`` read as a [K, N] operand),
+    anything else through ``torch.bmm``."""
+    if _tcgen05_ok(Mb, Qb):
+        from . import gemm
+        return gemm.ns_gemm(Mb, Qb, b_is_kn=True)
+    return Mb @ Qb
+
+
+def power_iteration_r(Mb: Tensor, P: Tensor) -> Tensor:
+    """``R = M^T P`` for ``Mb [B, m, n]``, ``P [B, m, r]`` (reference: dion/dion.py:836) without
+    a transposed copy of ``M``: both operands are read K-outermost."""
+    if _tcgen05_ok(Mb, P):
+        from . import gemm
+        return gemm.ns_gemm(Mb, P, a_is_km=True, b_is_kn=True)
+    return Mb.mT @ P
+
+
 def stack_for_power_iteration(M: List[Tensor], Q: List[Tensor], transposed: bool):
     """``(M_batch, Q_batch)`` with ``M_batch[i] = M[i]^T`` when ``transposed``; ``Q`` is cast to
     the momentum dtype."""

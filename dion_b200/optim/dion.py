@@ -466,7 +466,7 @@ class Dion(Optimizer):
         else:
             Q_full = Q
         Mb, Qb = LR.stack_for_power_iteration(M, Q_full, cfg.is_transposed)
-        P = Mb @ Qb  # [B, rows_loc, r], partial over the outer mesh when that is sharded
+        P = LR.power_iteration_p(Mb, Qb)  # [B, rows_loc, r]; partial over a sharded outer mesh
 
         if kind == "non_sharded":
             rank = C.group_rank(rep) if rep is not None else 0
@@ -512,7 +512,7 @@ class Dion(Optimizer):
             gen = self._generator(dev, step, task_id, i_rank)
             P = distributed_orthogonalize(P, oversample, inner_pg, generator=gen)
 
-        R = Mb.mT @ P  # [B, cols_loc, r]
+        R = LR.power_iteration_r(Mb, P)  # [B, cols_loc, r]
         if kind == "inner_sharded":
             work = C.all_reduce_(R, inner_pg, op="sum", async_op=True)
             yield

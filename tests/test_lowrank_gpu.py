@@ -72,3 +72,26 @@ def test_orthogonalize_batched_matches_fp64():
     assert (Q.mT @ Q - eye).abs().max().item() < 1e-3
     # Same column space: projecting P onto Q loses nothing.
     assert ((Q @ (Q.mT @ P)) - P).abs().max().item() < 1e-3 * P.abs().max().item()
+
+
+@pytest.mark.parametrize("shape", [(6, 768, 768, 192), (3, 3072, 768, 192), (2, 2048, 8192, 512)])
+def test_power_iteration_gemms_on_tcgen05(shape):
+    """P = M Q and R = M^T P for bf16 batches run on the package's GEMM kernels."""
+    from dion_b200.ops import _backend, lowrank as LR
+    from dion_b200.ops.gemm import check_status
+    B, m, n, r = shape
+    torch.manual_seed(3)
+    M = torch.randn(B, m, n, device="cuda").bfloat16()
+    Q = (torch.randn(B, n, r, device="cuda") / n ** 0.5).bfloat16()
+    before = _backend.launch_count()
+    P = LR.power_iteration_p(M, Q)
+    R = LR.power_iteration_r(M, P)
+    torch.cuda.synchronize()
+    check_status()
+    assert _backend.launch_count() == before + 2          # own kernels, not torch.bmm
+    Pref = M.float() @ Q.float()
+    assert (P.float() - Pref).abs().max().item() < 1e-2 * Pref.abs().max().item()
+    Rref = M.float().mT @ P.float()
+    assert (R.float() - Rref).abs().max().item() < 1e-2 * Rref.abs().max().item()
+    # fp32 batches keep the library path
+    assert torch.allclose(LR.power_iteration_p(M.float(), Q.float()), Pref, rtol=1e-3, atol=1e-3)
