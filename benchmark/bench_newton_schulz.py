@@ -6,6 +6,8 @@ Triton kernels.
     python benchmark/bench_newton_schulz.py --grid            # shapes x batch sizes
     python benchmark/bench_newton_schulz.py --single 4096 4096 --batch 8
     python benchmark/bench_newton_schulz.py --gemms 2048 2048 --batch 24   # per-GEMM breakdown
+    python benchmark/bench_newton_schulz.py --sweep --expansion 4          # d x 4d, speed-ups
+    python benchmark/bench_newton_schulz.py --curve --batch 4 --out-dir plots  # TFLOP/s vs size
 
 FLOP model (the reference's, benchmark/benchmark_newton_shultz.py:40-48): ``4 m^2 n + 2 m^3``
 per iteration with ``m <= n``, i.e. without crediting the symmetric half-work, so the numbers
@@ -157,6 +159,56 @@ def gemm_breakdown(b: int, m: int, n: int):
     return out
 
 
+def speedup_sweep(dims, expansion: int, batch: int, drivers, peak: float):
+    """Square / rectangular sweep ``d x (d * expansion)`` with the speed-up of the symmetric
+    kernels over the plain-PyTorch iteration and its upper bound ``(4e + 2) / (3e + 1)`` from
+    skipping the mirrored half of the two symmetric products (the reference prints the same
+    summary, benchmark/benchmark_newton_shultz.py:90-108)."""
+    rows, ups = [], []
+    for d in dims:
+        row = run_case(batch, d, d * expansion, drivers, peak, max_bytes=24e9)
+        if row is None:
+            continue
+        rows.append(row)
+        print(json.dumps(row), flush=True)
+        if "ms" in row.get("ours_quintic", {}) and "ms" in row.get("torch_quintic", {}):
+            ups.append(row["torch_quintic"]["ms"] / row["ours_quintic"]["ms"])
+    print("speed-up over torch:", ", ".join(f"{u:4.2f}x" for u in ups))
+    print(f"bound from symmetry alone: {(4 * expansion + 2) / (3 * expansion + 1):4.2f}x")
+    return rows
+
+
+def write_curve(rows, names, out_dir: str, title: str) -> str:
+    """TFLOP/s against matrix size as a CSV file and a text chart (and a PNG when matplotlib is
+    importable; the reference draws this with Triton's perf_report,
+    benchmark/benchmark_newton_shultz.py:111-137).  Returns the CSV path."""
+    os.makedirs(out_dir, exist_ok=True)
+    path = os.path.join(out_dir, title + ".csv")
+    with open(path, "w") as f:
+        f.write("dim," + ",".join(names) + "\n")
+        for row in rows:
+            f.write(str(row["m"]) + "," + ",".join(
+                str(row.get(n, {}).get("tflops", "")) for n in names) + "\n")
+    top = max([row.get(n, {}).get("tflops", 0.0) for row in rows for n in names] + [1e-9])
+    for row in rows:
+        for n in names:
+            tf = row.get(n, {}).get("tflops")
+            if tf is not None:
+                print(f"{row['m']:6d} {n:22s} {tf:8.1f} " + "#" * int(round(50 * tf / top)))
+    try:
+        import matplotlib
+        matplotlib.use("Agg")
+        import matplotlib.pyplot as plt
+        for n in names:
+            plt.plot([r["m"] for r in rows], [r.get(n, {}).get("tflops", float("nan")) for r in rows],
+                     marker="o", label=n)
+        plt.xlabel("dim"); plt.ylabel("TFLOPS"); plt.legend(); plt.title(title)
+        plt.savefig(os.path.join(out_dir, title + ".png"), dpi=120)
+    except ImportError:
+        pass
+    return path
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--grid", action="store_true")
@@ -167,6 +219,12 @@ def main() -> None:
     ap.add_argument("--graph", action="store_true",
                     help="also time our quintic driver replayed from a CUDA graph")
     ap.add_argument("--out", type=str, default=None)
+    ap.add_argument("--sweep", action="store_true",
+                    help="d x (d*expansion) for d in 512..8192 with speed-ups over torch")
+    ap.add_argument("--expansion", type=int, default=1)
+    ap.add_argument("--curve", action="store_true",
+                    help="TFLOP/s for dim = 128..896 (CSV, text chart, PNG with matplotlib)")
+    ap.add_argument("--out-dir", type=str, default="plots")
     args = ap.parse_args()
     peak = peak_tflops()
     drivers = {
@@ -182,6 +240,19 @@ def main() -> None:
     if args.gemms:
         r = gemm_breakdown(args.batch, *args.gemms)
         print(json.dumps({"gemm_breakdown": r, "batch": args.batch, "shape": args.gemms}, indent=1))
+        return
+    if args.sweep:
+        results = speedup_sweep([512, 1024, 2048, 4096, 8192], args.expansion, args.batch,
+                                drivers, peak)
+        if args.out:
+            json.dump({"measured_cublas_bf16_peak_tflops": peak, "rows": results},
+                      open(args.out, "w"), indent=1)
+        return
+    if args.curve:
+        rows = [r for r in (run_case(args.batch, 128 * i, 128 * i, drivers, peak)
+                            for i in range(1, 8)) if r is not None]
+        print("wrote", write_curve(rows, list(drivers), args.out_dir,
+                                   f"newton_schulz_batch{args.batch}"))
         return
     cases = ([(b, m, n) for (m, n) in GRID_SHAPES for b in GRID_BATCH] if args.grid
              else [(args.batch, *(args.single or (4096, 4096)))])

@@ -58,3 +58,21 @@ def test_reference_arm_reports_unavailable_when_not_installed(tmp_path):
     assert res.returncode == 0, res.stderr[-500:]
     line = json.loads(res.stdout.strip().splitlines()[-1])
     assert line["impl"] == "reference" and "unavailable" in line
+
+
+def test_newton_schulz_benchmark_curve_writer(tmp_path, capsys):
+    """The size sweep of the Newton-Schulz benchmark writes a CSV and a text chart without a
+    plotting library."""
+    import importlib.util
+    import os
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    spec = importlib.util.spec_from_file_location(
+        "bench_newton_schulz", os.path.join(root, "benchmark", "bench_newton_schulz.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    rows = [{"batch": 1, "m": 128, "n": 128, "a": {"tflops": 10.0}, "b": {"tflops": 5.0}},
+            {"batch": 1, "m": 256, "n": 256, "a": {"tflops": 30.0}, "b": {"error": "x"}}]
+    path = mod.write_curve(rows, ["a", "b"], str(tmp_path), "curve")
+    assert open(path).read().splitlines() == ["dim,a,b", "128,10.0,5.0", "256,30.0,"]
+    assert "#" * 50 in capsys.readouterr().out
+    assert mod.ns_flops(2, 8, 4) == 2 * 5 * (4.0 * 16 * 8 + 2.0 * 64)
