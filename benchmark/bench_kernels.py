@@ -61,77 +61,154 @@ def timed(fn, iters=10, warmup=3, inner=4):
     return total / iters
 
 
-def cases():
-    dev = "cuda"
-    T, C, V = 32768, 768, 50304
-    bf, f32 = torch.bfloat16, torch.float32
-    out = {}
+T, C, V = 32768, 768, 50304
+DEV = "cuda"
+BF, F32 = torch.bfloat16, torch.float32
+CASES = {}
 
-    x = torch.randn(T, C, device=dev)
-    delta = torch.randn(T, C, device=dev).to(bf)
 
-    def rms_fwd():
-        with torch.autocast("cuda", dtype=bf):
+def case(name):
+    """Register ``builder() -> (callable, algorithmic bytes)`` under ``name``; inputs are built
+    only for the cases that run, so a capture of one kernel holds little else on the device."""
+    def deco(builder):
+        CASES[name] = builder
+        return builder
+    return deco
+
+
+@case("add_rms_norm_fwd")
+def _():
+    x = torch.randn(T, C, device=DEV)
+    delta = torch.randn(T, C, device=DEV).to(BF)
+
+    def run():
+        with torch.autocast("cuda", dtype=BF):
             Fn.add_rms_norm(x, delta)
-    out["add_rms_norm_fwd"] = (rms_fwd, T * C * (4 + 2 + 4 + 2))
+    return run, T * C * (4 + 2 + 4 + 2)
 
-    xr = x.clone().requires_grad_()
-    dr = delta.clone().requires_grad_()
-    with torch.autocast("cuda", dtype=bf):
+
+@case("add_rms_norm_bwd")
+def _():
+    xr = torch.randn(T, C, device=DEV).requires_grad_()
+    dr = torch.randn(T, C, device=DEV).to(BF).requires_grad_()
+    with torch.autocast("cuda", dtype=BF):
         xn, h = Fn.add_rms_norm(xr, dr)
     gx, gh = torch.randn_like(xn), torch.randn_like(h)
+    return (lambda: torch.autograd.grad((xn, h), (xr, dr), (gx, gh), retain_graph=True),
+            T * C * (4 + 2 + 4 + 4 + 2))
 
-    def rms_bwd():
-        torch.autograd.grad((xn, h), (xr, dr), (gx, gh), retain_graph=True)
-    out["add_rms_norm_bwd"] = (rms_bwd, T * C * (4 + 2 + 4 + 4 + 2))
 
-    act = torch.randn(T, 4 * C, device=dev).to(bf).requires_grad_()
-    out["relu2_fwd"] = (lambda: Fn.relu2(act.detach()), T * 4 * C * 4)
+def _act():
+    return torch.randn(T, 4 * C, device=DEV).to(BF).requires_grad_()
+
+
+@case("relu2_fwd")
+def _():
+    act = _act()
+    return (lambda: Fn.relu2(act.detach())), T * 4 * C * 4
+
+
+@case("relu2_bwd")
+def _():
+    act = _act()
     y = Fn.relu2(act)
     gy = torch.randn_like(y)
-    out["relu2_bwd"] = (lambda: torch.autograd.grad(y, act, gy, retain_graph=True), T * 4 * C * 6)
+    return (lambda: torch.autograd.grad(y, act, gy, retain_graph=True)), T * 4 * C * 6
 
-    logits = torch.randn(T // 4, V, device=dev).to(bf)
-    tgt = torch.randint(0, V, (T // 4,), device=dev)
 
-    def ce():
+@case("ce")
+def _():
+    logits = torch.randn(T // 4, V, device=DEV).to(BF)
+    tgt = torch.randint(0, V, (T // 4,), device=DEV)
+
+    def run():
         lg = logits.detach().requires_grad_()
         Fn.cross_entropy(lg, tgt)
-    out["ce"] = (ce, (T // 4) * V * 4)
+    return run, (T // 4) * V * 4
 
-    W = torch.randn(V, C, device=dev, requires_grad=True)
-    idx = torch.randint(0, V, (32, 1024), device=dev)
+
+@case("embedding_bwd")
+def _():
+    W = torch.randn(V, C, device=DEV, requires_grad=True)
+    idx = torch.randint(0, V, (32, 1024), device=DEV)
     emb = Fn.embedding(idx, W)
     ge = torch.randn_like(emb)
-    out["embedding_bwd"] = (lambda: torch.autograd.grad(emb, W, ge, retain_graph=True),
-                            T * C * 4 + V * C * 4)
+    return (lambda: torch.autograd.grad(emb, W, ge, retain_graph=True)), T * C * 4 + V * C * 4
 
-    # Optimizer kernels on a GPT-1B-sized bucket: 24 matrices of 2048 x 2048 (bf16 weights).
-    n, d = 24, 2048
-    G = [torch.randn(d, d, device=dev).to(bf) for _ in range(n)]
-    M = [torch.zeros(d, d, device=dev, dtype=bf) for _ in range(n)]
-    X = [torch.randn(d, d, device=dev).to(bf) for _ in range(n)]
-    U = [torch.empty(d, d, device=dev, dtype=bf) for _ in range(n)]
-    lr = F.device_scalar(0.02, torch.device(dev))
-    out["muon_pre"] = (lambda: F.muon_pre(G, M, 0.95, True, out=U), n * d * d * (2 + 2 + 2 + 2))
-    out["muon_post"] = (lambda: F.muon_post(X, U, lr, 0.01, 1.0), n * d * d * (2 + 2 + 2))
-    Xf = [torch.randn(d, d, device=dev) for _ in range(8)]
-    Gf = [torch.randn(d, d, device=dev) for _ in range(8)]
-    Mf = [torch.zeros(d, d, device=dev) for _ in range(8)]
-    Vf = [torch.zeros(d, d, device=dev) for _ in range(8)]
-    steps = [torch.zeros((), device=dev) for _ in range(8)]
-    out["adamw_fp32"] = (lambda: F.adamw(Xf, Gf, Mf, Vf, lr, 0.9, 0.95, 0.01, 1e-8,
-                                         state_steps=steps), 8 * d * d * 4 * 7)
-    out["dion2_select_rows"] = (lambda: SEL.dion2_select(G, M, d // 4, -2, 0.95, True),
-                                n * d * d * (2 + 2 + 2) + n * (d // 4) * d * (2 + 2 + 2))
 
-    A = torch.randn(48, 256, 192, device=dev)
-    out["qr_r_factor_48x256x192"] = (lambda: LR.qr_r_factor(A), A.numel() * 4)
-    A2 = torch.randn(96, 640, 512, device=dev)
-    out["qr_r_factor_96x640x512"] = (lambda: LR.qr_r_factor(A2), A2.numel() * 4)
-    Gm = A2.mT @ A2
-    out["cholesky_96x512"] = (lambda: LR.cholesky_upper(Gm), Gm.numel() * 8)
-    return out
+# Optimizer kernels on a GPT-1B-sized bucket: 24 matrices of 2048 x 2048 (bf16 weights).
+N_MAT, D_MAT = 24, 2048
+
+
+def _bucket(kind, n=N_MAT, dtype=BF):
+    make = {"randn": lambda: torch.randn(D_MAT, D_MAT, device=DEV).to(dtype),
+            "zeros": lambda: torch.zeros(D_MAT, D_MAT, device=DEV, dtype=dtype),
+            "empty": lambda: torch.empty(D_MAT, D_MAT, device=DEV, dtype=dtype)}[kind]
+    return [make() for _ in range(n)]
+
+
+@case("muon_pre")
+def _():
+    G, M, U = _bucket("randn"), _bucket("zeros"), _bucket("empty")
+    return (lambda: F.muon_pre(G, M, 0.95, True, out=U)), N_MAT * D_MAT * D_MAT * (2 + 2 + 2 + 2)
+
+
+@case("muon_post")
+def _():
+    X, U = _bucket("randn"), _bucket("randn")
+    lr = F.device_scalar(0.02, torch.device(DEV))
+    return (lambda: F.muon_post(X, U, lr, 0.01, 1.0)), N_MAT * D_MAT * D_MAT * (2 + 2 + 2)
+
+
+@case("adamw_fp32")
+def _():
+    Xf, Gf = _bucket("randn", 8, F32), _bucket("randn", 8, F32)
+    Mf, Vf = _bucket("zeros", 8, F32), _bucket("zeros", 8, F32)
+    steps = [torch.zeros((), device=DEV) for _ in range(8)]
+    lr = F.device_scalar(0.02, torch.device(DEV))
+    return (lambda: F.adamw(Xf, Gf, Mf, Vf, lr, 0.9, 0.95, 0.01, 1e-8, state_steps=steps),
+            8 * D_MAT * D_MAT * 4 * 7)
+
+
+@case("lion_fp32")
+def _():
+    Xf, Gf, Mf = _bucket("randn", 8, F32), _bucket("randn", 8, F32), _bucket("zeros", 8, F32)
+    lr = F.device_scalar(0.02, torch.device(DEV))
+    return (lambda: F.lion(Xf, Gf, Mf, lr, 0.9, 0.99, 0.01)), 8 * D_MAT * D_MAT * 4 * 5
+
+
+@case("normuon_rowstats")
+def _():
+    U = torch.randn(N_MAT, D_MAT, D_MAT, device=DEV).to(BF)
+    Vs = [torch.zeros(D_MAT, 1, device=DEV) for _ in range(N_MAT)]
+    return (lambda: F.normuon_rowstats(U, Vs, 0.95)), N_MAT * D_MAT * D_MAT * 2
+
+
+@case("dion2_select_rows")
+def _():
+    G, M = _bucket("randn"), _bucket("zeros")
+    d = D_MAT
+    return (lambda: SEL.dion2_select(G, M, d // 4, -2, 0.95, True),
+            N_MAT * d * d * (2 + 2 + 2) + N_MAT * (d // 4) * d * (2 + 2 + 2))
+
+
+@case("qr_r_factor_48x256x192")
+def _():
+    A = torch.randn(48, 256, 192, device=DEV)
+    return (lambda: LR.qr_r_factor(A)), A.numel() * 4
+
+
+@case("qr_r_factor_96x640x512")
+def _():
+    A = torch.randn(96, 640, 512, device=DEV)
+    return (lambda: LR.qr_r_factor(A)), A.numel() * 4
+
+
+@case("cholesky_96x512")
+def _():
+    A = torch.randn(96, 640, 512, device=DEV)
+    Gm = A.mT @ A
+    return (lambda: LR.cholesky_upper(Gm)), Gm.numel() * 8
 
 
 def main() -> None:
@@ -140,9 +217,12 @@ def main() -> None:
     ap.add_argument("--iters", type=int, default=10)
     args = ap.parse_args()
     peak = hbm_peak()
-    for name, (fn, nbytes) in cases().items():
+    if args.only and args.only not in CASES:
+        raise SystemExit(f"unknown kernel {args.only!r}; one of: {', '.join(CASES)}")
+    for name, builder in CASES.items():
         if args.only and args.only != name:
             continue
+        fn, nbytes = builder()
         ms = timed(fn, iters=args.iters)
         gbs = nbytes / ms / 1e6
         print(json.dumps({"kernel": name, "ms": round(ms, 4), "algorithmic_MB": round(nbytes / 1e6, 1),

@@ -179,3 +179,25 @@ def test_output_canaries_and_run_to_run_determinism(pair, sym):
     assert torch.equal(first, out)
     assert torch.all(big[:, M:, :] == 12345.0) and torch.all(big[:, :, N:] == 12345.0)
     assert _rel_err(out, A.float() @ B.float().mT) < 1e-2
+
+
+@pytest.mark.parametrize("pair", [False, True])
+def test_batch_offsets_beyond_32_bits(pair):
+    """Operands and output of more than 2^31 elements: the last matrix of the batch starts past
+    the range of 32-bit element offsets (the reference guards the same case with int64 batch
+    offsets, dion/newton_schulz_triton.py:48-50)."""
+    from dion_b200.ops import gemm
+    b, m, n = 260, 1024, 8192
+    assert (b - 1) * m * n > 2 ** 31
+    torch.manual_seed(11)
+    X = torch.randn(b, m, n, device="cuda", dtype=torch.bfloat16)
+    Bm = (torch.randn(b, m, m, device="cuda", dtype=torch.bfloat16) / m ** 0.5)
+    out = torch.empty_like(X)
+    gemm.ns_gemm(Bm, X, out=out, b_is_kn=True, D=X, alpha=1.0, beta=0.5, pair=pair)
+    A = gemm.ns_gemm(X, X, sym=True, pair=pair)
+    torch.cuda.synchronize()
+    gemm.check_status()
+    for i in (0, b - 1):
+        ref = Bm[i].float() @ X[i].float() + 0.5 * X[i].float()
+        assert _rel_err(out[i], ref) < 1e-2
+        assert _rel_err(A[i], X[i].float() @ X[i].float().T) < 1e-2
