@@ -1,0 +1,7 @@
+"""Forwarder: token-shard data loaders (reference module models/gpt_utils.py)."""
+import dion_b200.models.data as _m
+from dion_b200.models.data import *  # noqa: F401,F403
+
+
+def __getattr__(name):
+    return getattr(_m, name)

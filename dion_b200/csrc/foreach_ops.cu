@@ -15,6 +15,7 @@ namespace dion {
 
 constexpr int kChunk = 4096;    // elements per block
 constexpr int kThreads = 256;
+static_assert(kChunk == kThreads * 16, "the vector paths read 16 elements per thread and chunk");
 
 enum : int { DT_F32 = 0, DT_BF16 = 1 };
 
@@ -600,43 +601,76 @@ dion2_post_kernel(const long long* raw, const Dion2PostArgs a) {
 // pointer 1, int64 per U-row) redirects U-row j to V-row vmap[j] (NorDion2 selected rows).
 // One warp per row.
 // ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ float sumsq8(const uint4 q) {
+  const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+  float s = 0.f;
+#pragma unroll
+  for (int e = 0; e < 4; ++e) { const float2 f = unpack_bf16x2(w[e]); s += f.x * f.x + f.y * f.y; }
+  return s;
+}
+
 __global__ void __launch_bounds__(kThreads)
 normuon_rowstats_kernel(const long long* raw, const __nv_bfloat16* U, int rows, int cols, int v_dt,
                         float beta2, float* rinv, float* normU2, float* normNew2, int n_mats) {
+  constexpr int kWarps = kThreads / 32;
+  __shared__ int s_t[kWarps];
+  __shared__ float s_u2[kWarps], s_n2[kWarps];
   Table tb{raw};
-  const int warps_per_block = kThreads / 32;
-  const long long row_global = (long long)blockIdx.x * warps_per_block + (threadIdx.x >> 5);
-  const int lane = threadIdx.x & 31;
-  if (row_global >= (long long)n_mats * rows) return;
-  const int t = (int)(row_global / rows);
-  const int r = (int)(row_global - (long long)t * rows);
-  const __nv_bfloat16* u = U + row_global * cols;
-  float s = 0.f;
-  if ((cols & 7) == 0 && (reinterpret_cast<uintptr_t>(u) & 15) == 0) {
-    for (int c = lane * 8; c < cols; c += 256) {
-      uint4 q = *reinterpret_cast<const uint4*>(u + c);
-      const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long row_global = (long long)blockIdx.x * kWarps + warp;
+  int t = -1;
+  float su = 0.f, sn = 0.f;
+  if (row_global < (long long)n_mats * rows) {
+    t = (int)(row_global / rows);
+    const int r = (int)(row_global - (long long)t * rows);
+    const __nv_bfloat16* u = U + row_global * cols;
+    float s = 0.f;
+    if ((cols & 7) == 0 && (reinterpret_cast<uintptr_t>(u) & 15) == 0) {
+      // Four independent 16-byte loads per lane are issued before any is consumed: a warp keeps
+      // 2 KB in flight, which is what hides the DRAM latency at one warp per row.
+      for (int c0 = lane * 8; c0 < cols; c0 += 4 * 256) {
+        uint4 q[4];
 #pragma unroll
-      for (int e = 0; e < 4; ++e) { float2 f = unpack_bf16x2(w[e]); s += f.x * f.x + f.y * f.y; }
+        for (int j = 0; j < 4; ++j) {
+          const int c = c0 + j * 256;
+          q[j] = c < cols ? __ldg(reinterpret_cast<const uint4*>(u + c)) : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) s += sumsq8(q[j]);
+      }
+    } else {
+      for (int c = lane; c < cols; c += 32) { float f = __bfloat162float(u[c]); s += f * f; }
     }
-  } else {
-    for (int c = lane; c < cols; c += 32) { float f = __bfloat162float(u[c]); s += f * f; }
-  }
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-  if (lane == 0) {
-    void* V = tb.ptr(0, t);
-    const long long* vmap = reinterpret_cast<const long long*>(tb.ptr(1, t));
-    const long long vr = vmap ? vmap[r] : r;
-    const float ms = s / (float)cols;
-    float v = ld(V, v_dt, vr);
-    v = v + (1.f - beta2) * (ms - v);
-    const float vst = round_to(v, v_dt);
-    st(V, v_dt, vr, vst);
-    const float inv = 1.f / (sqrtf(v) + 1e-8f);
-    rinv[row_global] = inv;
-    atomicAdd(&normU2[t], s);
-    atomicAdd(&normNew2[t], s * inv * inv);
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (lane == 0) {
+      void* V = tb.ptr(0, t);
+      const long long* vmap = reinterpret_cast<const long long*>(tb.ptr(1, t));
+      const long long vr = vmap ? vmap[r] : r;
+      const float ms = s / (float)cols;
+      float v = ld(V, v_dt, vr);
+      v = v + (1.f - beta2) * (ms - v);
+      const float vst = round_to(v, v_dt);
+      st(V, v_dt, vr, vst);
+      const float inv = 1.f / (sqrtf(v) + 1e-8f);
+      rinv[row_global] = inv;
+      su = s;
+      sn = s * inv * inv;
+    }
+  }
+  if (lane == 0) { s_t[warp] = t; s_u2[warp] = su; s_n2[warp] = sn; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    // One pair of atomics per run of rows of the same matrix (usually one per block) instead of
+    // one per row: thousands of rows add into the same two words per matrix.
+    int ct = s_t[0];
+    float au = s_u2[0], an = s_n2[0];
+    for (int w = 1; w < kWarps; ++w) {
+      if (s_t[w] == ct) { au += s_u2[w]; an += s_n2[w]; continue; }
+      if (ct >= 0) { atomicAdd(&normU2[ct], au); atomicAdd(&normNew2[ct], an); }
+      ct = s_t[w]; au = s_u2[w]; an = s_n2[w];
+    }
+    if (ct >= 0) { atomicAdd(&normU2[ct], au); atomicAdd(&normNew2[ct], an); }
   }
 }
 
@@ -648,9 +682,18 @@ sumsq_kernel(const __nv_bfloat16* X, long long numel, float* out) {
   float acc = 0.f;
   const long long base = (long long)blockIdx.x * kChunk;
   const long long end = (base + kChunk < numel) ? base + kChunk : numel;
-  for (long long i = base + threadIdx.x; i < end; i += kThreads) {
-    const float f = __bfloat162float(x[i]);
-    acc += f * f;
+  if ((numel & 7) == 0 && (reinterpret_cast<uintptr_t>(X) & 15) == 0) {
+    // kChunk = 16 elements per thread: two 16-byte loads, both issued before use
+    const long long i0 = base + (long long)threadIdx.x * 8, i1 = i0 + kThreads * 8;
+    const uint4 z = make_uint4(0, 0, 0, 0);
+    const uint4 q0 = i0 < end ? __ldg(reinterpret_cast<const uint4*>(x + i0)) : z;
+    const uint4 q1 = i1 < end ? __ldg(reinterpret_cast<const uint4*>(x + i1)) : z;
+    acc = sumsq8(q0) + sumsq8(q1);
+  } else {
+    for (long long i = base + threadIdx.x; i < end; i += kThreads) {
+      const float f = __bfloat162float(x[i]);
+      acc += f * f;
+    }
   }
   const float s = block_sum(acc);
   if (threadIdx.x == 0) atomicAdd(&out[t], s);

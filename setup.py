@@ -1,7 +1,10 @@
 """Packaging for dion_b200.  The CUDA kernels are compiled for sm_100a into ``dion_b200/_lib``
 at build time when nvcc is available (``python setup.py build_kernels`` or automatically by
 ``build_py``); they are also built on first use.  Extras: ``dev`` (tests), ``train`` (data
-preparation, logging).  There is no ``triton`` extra: nothing here uses it."""
+preparation, logging).  There is no ``triton`` extra: nothing here uses it.  With
+``DION_B200_COMPAT=1`` in the environment the forwarding packages ``dion`` and ``models`` of
+``compat/`` are installed as well, so code written against the reference's import names runs
+unchanged; they are left out by default because they would shadow a real ``dion`` install."""
 import os
 import sys
 
@@ -49,13 +52,20 @@ def _readme() -> str:
     return open(path, encoding="utf-8").read() if os.path.exists(path) else ""
 
 
+_packages = find_packages(include=["dion_b200", "dion_b200.*"])
+_package_dir = {}
+if os.environ.get("DION_B200_COMPAT", "0") == "1":
+    _packages += ["dion", "models"]
+    _package_dir = {"dion": "compat/dion", "models": "compat/models"}
+
 setup(
     name="dion_b200",
     version="0.1.0",
     description="Orthonormal-update optimizers (Muon, Dion, Dion2, NorMuon) with sm_100a kernels",
     long_description=_readme(),
     long_description_content_type="text/markdown",
-    packages=find_packages(include=["dion_b200", "dion_b200.*"]),
+    packages=_packages,
+    package_dir=_package_dir,
     package_data={"dion_b200": ["csrc/*.cu", "csrc/*.cuh", "csrc/*.h", "_lib/*.so"]},
     python_requires=">=3.10",
     install_requires=["torch>=2.7", "numpy"],

@@ -134,9 +134,10 @@ def test_dion2_post(select_dim):
     _close(Xc, Xg, 1e-6)
 
 
-def test_normuon_rowstats_and_apply():
+@pytest.mark.parametrize("shape", [(3, 40, 72), (5, 37, 2056), (4, 13, 75), (2, 9, 1024)])
+def test_normuon_rowstats_and_apply(shape):
     torch.manual_seed(0)
-    N, rows, cols = 3, 40, 72
+    N, rows, cols = shape   # rows not a multiple of 8: blocks span two matrices
     U = torch.randn(N, rows, cols).bfloat16()
     Vc = [torch.rand(rows, 1) for _ in range(N)]
     Vg = [v.clone().cuda() for v in Vc]

@@ -101,3 +101,40 @@ def test_weights_interchange_with_the_reference_model(ref_dion):
     ours2 = _model(7)
     ours2.load_state_dict({k: v for k, v in ref.state_dict().items() if "inv_freq" not in k})
     assert torch.allclose(ours2(x, y, return_logits=True), ours(x, y, return_logits=True), atol=1e-6)
+
+
+def test_reference_import_names_forward_to_this_package():
+    """With ``compat/`` on the path, imports written against the reference package resolve to the
+    classes and functions of this one (and only then: the folder is not on the default path)."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    code = (
+        "import dion, dion_b200\n"
+        "from dion import Muon, Dion2, Dion, NorMuon, NorDion2, Dion3, DionMixedPrecisionConfig\n"
+        "from dion import DionSimple, DionReference, MuonReference\n"
+        "assert Muon is dion_b200.Muon and Dion is dion_b200.Dion and Dion3 is NorDion2\n"
+        "from dion.cuda_graph import CudaGraphOptimizer\n"
+        "from dion.newton_schulz_triton import newton_schulz_triton, ns_line_1, ns_line_2, ns_line_3\n"
+        "from dion.polar_express import polar_express\n"
+        "from dion.opt_utils import AsyncRuntime, AsyncTask, to_local, pad_batch\n"
+        "from dion.scalar_opts import adamw_update_foreach, lion_update_foreach\n"
+        "from dion.megabatch_base import DistributedOrthoBase, megabatch_orthogonalize_async\n"
+        "from dion.dion2_triton import dion2_post_orthogonalize_triton\n"
+        "from models.gpt_model import GPT, GPTConfig, parallelize_gpt_model\n"
+        "from models.gpt_utils import DistributedDataLoader\n"
+        "import torch\n"
+        "p = torch.nn.Parameter(torch.randn(8, 16)); p.grad = torch.randn(8, 16)\n"
+        "Muon([p], lr=0.01).step()\n"
+        "print('forwarded', dion.__file__)\n")
+    env = dict(os.environ, PYTHONPATH=os.pathsep.join([os.path.join(root, "compat"), root]))
+    out = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True,
+                         timeout=300)
+    assert out.returncode == 0, out.stderr[-2000:]
+    assert os.path.join("compat", "dion") in out.stdout
+    # Without the opt-in nothing named ``dion`` comes from this repository.
+    plain = subprocess.run([sys.executable, "-c", "import dion_b200, sys; print('dion' in sys.modules)"],
+                           env=dict(os.environ, PYTHONPATH=root), capture_output=True, text=True,
+                           timeout=300)
+    assert plain.stdout.strip() == "False"
