@@ -112,3 +112,47 @@ def test_dion2_scope_default_is_local_and_full_fraction_makes_scopes_equal():
 
     for a, b in zip(run("local"), run("global")):
         assert torch.allclose(a, b, atol=1e-6)
+
+
+class _DeviceLookalike(torch.Tensor):
+    """A wrapper-subclass tensor that reports a CUDA device while its data lives elsewhere - what
+    DTensor-like wrappers look like to code that is about to hand a raw address to a kernel (the
+    reference tests the same guard with a mock ``__torch_dispatch__`` tensor,
+    tests/test_dion2_post_ortho_triton.py:95-159)."""
+
+    @staticmethod
+    def __new__(cls, inner):
+        return torch.Tensor._make_wrapper_subclass(
+            cls, inner.shape, dtype=inner.dtype, device="cuda", strides=inner.stride())
+
+    def __init__(self, inner):
+        self.inner = inner
+
+    @classmethod
+    def __torch_dispatch__(cls, func, types, args=(), kwargs=None):
+        from torch.utils._pytree import tree_map
+        strip = lambda t: t.inner if isinstance(t, _DeviceLookalike) else t  # noqa: E731
+        out = func(*tree_map(strip, args), **tree_map(strip, kwargs or {}))
+        return tree_map(lambda t: _DeviceLookalike(t) if isinstance(t, torch.Tensor) else t, out)
+
+
+def test_wrapper_subclass_tensors_never_reach_a_raw_pointer_kernel():
+    from dion_b200.ops import foreach as F
+    from dion_b200.utils.tensors import is_plain_tensor
+    torch.manual_seed(0)
+    x0 = torch.randn(6, 8)
+    u = torch.randn(3, 8).bfloat16()
+    idx = torch.tensor([4, 0, 2])
+    wrapped = _DeviceLookalike(x0.clone())
+    assert wrapped.is_cuda and not is_plain_tensor(wrapped)
+    assert not F._kernel_ok([wrapped], [u])
+    # The update goes through tensor arithmetic (dispatched to the wrapper) and matches the
+    # plain-tensor result exactly.
+    plain = x0.clone()
+    maps = [torch.full((6,), -1, dtype=torch.int32)]
+    maps[0][idx] = torch.arange(3, dtype=torch.int32)
+    F.dion2_post([plain], [u], [idx], maps, 0.1, 0.01, 1.5, -2)
+    F.dion2_post([wrapped], [u], [idx], maps, 0.1, 0.01, 1.5, -2)
+    assert torch.equal(wrapped.inner, plain)
+    untouched = [r for r in range(6) if r not in idx.tolist()]
+    assert torch.equal(plain[untouched], x0[untouched] * (1 - 0.1 * 0.01))
