@@ -156,3 +156,38 @@ def test_wrapper_subclass_tensors_never_reach_a_raw_pointer_kernel():
     assert torch.equal(wrapped.inner, plain)
     untouched = [r for r in range(6) if r not in idx.tolist()]
     assert torch.equal(plain[untouched], x0[untouched] * (1 - 0.1 * 0.01))
+
+
+def _public_overrides(cls):
+    return sorted(n for n, a in vars(cls).items()
+                  if callable(a) and not n.startswith("_") and hasattr(torch.optim.Optimizer, n))
+
+
+def test_graph_wrapper_is_call_compatible_with_torch_optimizer():
+    """The CUDA-graph wrapper stands in for a ``torch.optim.Optimizer``: every method it
+    overrides keeps torch's parameter names and kinds (distributed checkpointing calls
+    ``load_state_dict(state_dict=...)`` by keyword), found by reflection so that a method
+    overridden later is checked too (reference: tests/test_cuda_graph.py:818-872)."""
+    import inspect
+    from dion_b200 import CudaGraphOptimizer, Dion2
+    names = _public_overrides(CudaGraphOptimizer)
+    assert {"load_state_dict", "state_dict", "zero_grad", "step", "add_param_group"} <= set(names)
+    for name in names:
+        ours = inspect.signature(getattr(CudaGraphOptimizer, name))
+        base = inspect.signature(getattr(torch.optim.Optimizer, name))
+        assert [(p.name, p.kind) for p in ours.parameters.values()] == \
+            [(p.name, p.kind) for p in base.parameters.values()], name
+    # and the keyword call really loads: the step counter of a saved run arrives
+    torch.manual_seed(0)
+    ps = [torch.nn.Parameter(torch.randn(8, 16)) for _ in range(2)]
+    src = Dion2([dict(params=ps)], lr=0.01)
+    for _ in range(2):
+        for p in ps:
+            p.grad = torch.randn_like(p)
+        src.step()
+    saved = src.state_dict()
+    qs = [torch.nn.Parameter(torch.randn(8, 16)) for _ in range(2)]
+    wrap = CudaGraphOptimizer(Dion2([dict(params=qs)], lr=0.01), warmup_steps=1)
+    before = wrap.param_groups[0]["step"]
+    wrap.load_state_dict(state_dict=saved)
+    assert wrap.param_groups[0]["step"] == src.param_groups[0]["step"] != before
