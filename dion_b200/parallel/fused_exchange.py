@@ -53,7 +53,7 @@ def get_exchange(cache: dict, key, pg, n: int, rows_local: int, cols: int,
 def eligible(local_shape: Sequence[int], comm_dim: Optional[int], global_rows: Optional[int],
              world: int, pg: Optional[ProcessGroup], ns_func, flatten: bool,
              split_sizes) -> bool:
-    """All ranks must reach the same verdict, so only rank-independent facts are used."""
+    """All ranks must reach the same decision, so only rank-independent facts are used."""
     if not fused_exchange_enabled() or pg is None or comm_dim != -2 or len(local_shape) != 2:
         return False
     if flatten or split_sizes is not None or world < 2 or world > 8:
