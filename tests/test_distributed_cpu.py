@@ -196,3 +196,34 @@ def _wrapper_tensor_worker(rank, world):
 
 def test_functional_collective_results_are_unwrapped(tmp_path):
     run_ranks(_wrapper_tensor_worker, 2)
+
+
+def _hsdp_worker(rank, world, cases):
+    """Hybrid sharding: parameters replicated over ``dp`` and row-sharded over ``fs``; the
+    optimizer is given the ``fs`` sub-mesh (as the trainer does), replicas compute redundantly."""
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.tensor import Replicate, Shard, distribute_tensor
+    mesh = init_device_mesh("cpu", (2, world // 2), mesh_dim_names=("dp", "fs"))
+    placements = [Replicate(), Shard(0)]
+    outs = []
+    for name, kw, _ in cases:
+        shapes = _case_shapes(name, 0)
+        ps = [torch.nn.Parameter(distribute_tensor(w, mesh, placements)) for w in _weights(shapes)]
+        opt = getattr(dion_b200, name)([dict(params=ps)], distributed_mesh=mesh["fs"], lr=0.1, **kw)
+        for s in range(2):
+            for p, g in zip(ps, _grads(s, shapes)):
+                p.grad = distribute_tensor(g, mesh, placements)
+            opt.step()
+        outs.append([p.detach().full_tensor().clone() for p in ps])  # collective: on every rank
+    return outs if rank == 0 else None
+
+
+HSDP_CASES = [("Muon", {}, 1e-6), ("NorMuon", {}, 2e-2),
+              ("Dion2", dict(selection_scope="global"), 5e-4)]
+
+
+def test_hybrid_sharded_mesh_matches_single_process(tmp_path):
+    outs = run_ranks(_hsdp_worker, 4, "gloo", (HSDP_CASES,), str(tmp_path))[0]
+    for (name, kw, tol), out in zip(HSDP_CASES, outs):
+        for a, b in zip(_single(name, kw, _case_shapes(name, 0)), out):
+            assert (a - b).abs().max().item() <= tol, name
