@@ -109,6 +109,21 @@ def test_trainer_ddp_and_fsdp_resume(tmp_path):
     assert "Resumed from step 1" in out and "Step 2:" in out and "Step 0:" not in out
 
 
+def test_trainer_hybrid_meshes():
+    """Four ranks as dp x fs (hybrid sharding, Muon and legacy Dion with compressed data-parallel
+    sync) and as fs x tp (legacy Dion with tensor parallelism): the losses fall."""
+    def losses(out):
+        return [float(tok.split("=")[1].rstrip(",")) for tok in out.split()
+                if tok.startswith("train_loss=")]
+    big = ["--batch_size", "16", "--num_iterations", "3"]
+    for extra in (["--optimizer", "muon", "--dp_size", "2", "--fs_size", "2"],
+                  ["--optimizer", "dion", "--dp_size", "2", "--fs_size", "2",
+                   "--replicate_mesh_grad_sync"],
+                  ["--optimizer", "dion", "--fs_size", "2", "--tp_size", "2"]):
+        ls = losses(_torchrun(extra + big, nproc=4))
+        assert len(ls) == 3 and ls[-1] < ls[0], (extra, ls)
+
+
 def test_trace_spans_and_profile_helper():
     from dion_b200.utils import trace
     with trace.span("idle"):          # disabled (or no GPU): nothing happens
