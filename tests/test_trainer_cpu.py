@@ -148,3 +148,41 @@ def test_sectioned_and_flat_config_files_load_alike(tmp_path):
     for name in os.listdir(os.path.join(ROOT, "configs")):
         args = parse_cli_args(["--config", os.path.join(ROOT, "configs", name)])
         assert args.optimizer and args.model_dim
+
+
+def test_optimizer_factory_covers_every_choice():
+    """``init_optimizer`` builds each optimizer the command line offers on a stub-free tiny model
+    (no mesh, no DDP), with the matrix group first and embedding / head as scalar groups; one
+    step changes the weights (reference: tests/test_dion3_alias.py:46-120 checks the alias)."""
+    import argparse
+    from dion_b200 import trainer
+    from dion_b200.models.gpt import GPT, GPTConfig
+    import dion_b200
+    expected = {"muon": dion_b200.Muon, "dion2": dion_b200.Dion2, "normuon": dion_b200.NorMuon,
+                "nordion2": dion_b200.NorDion2, "dion3": dion_b200.NorDion2,
+                "dion": dion_b200.Dion, "dion_reference": dion_b200.DionReference,
+                "dion_simple": dion_b200.DionSimple, "muon_reference": dion_b200.MuonReference,
+                "adamw": torch.optim.AdamW}
+    cli = argparse.Namespace()
+    for name, cls in expected.items():
+        torch.manual_seed(0)
+        model = GPT(GPTConfig(vocab_size=64, n_layer=1, n_head=2, n_embd=16, sequence_len=8))
+        model.init_weights()
+        hp = trainer.Hyperparameters(optimizer=name, model_dim=16, n_layer=1, n_head=2,
+                                     scalar_opt="lion" if name == "muon" else "adamw")
+        opt = trainer.init_optimizer(model, None, None, hp, cli)
+        assert type(opt) is cls, name
+        assert len(opt.param_groups) == 3
+        if name != "adamw":
+            assert [g.get("algorithm") for g in opt.param_groups][1:] == [hp.scalar_opt] * 2
+        idx = torch.randint(0, 64, (2, 8))
+        before = [p.detach().clone() for p in model.parameters()]
+        model(idx, idx).backward()
+        opt.step()
+        assert any(not torch.equal(a, b) for a, b in zip(before, model.parameters())), name
+    with pytest.raises(ValueError):
+        trainer.init_optimizer(model, None, None,
+                               trainer.Hyperparameters(optimizer="sgd", model_dim=16), cli)
+    with pytest.raises(ValueError):
+        trainer.init_optimizer(model, None, None, trainer.Hyperparameters(
+            optimizer="muon", model_dim=16, replicate_mesh_grad_sync=True), cli)
