@@ -227,3 +227,26 @@ def test_hybrid_sharded_mesh_matches_single_process(tmp_path):
     for (name, kw, tol), out in zip(HSDP_CASES, outs):
         for a, b in zip(_single(name, kw, _case_shapes(name, 0)), out):
             assert (a - b).abs().max().item() <= tol, name
+
+
+def _flattened_mesh_worker(rank, world):
+    """Several mesh dimensions (data x context parallel) flattened into the one sharding mesh
+    that the optimizer is given (the reference documents this use, README.md:317-337)."""
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.tensor import Shard, distribute_tensor
+    mesh = init_device_mesh("cpu", (2, world // 2), mesh_dim_names=("dp", "cp"))
+    flat = mesh["dp", "cp"]._flatten("dp_cp")
+    ps = [torch.nn.Parameter(distribute_tensor(w, flat, [Shard(0)])) for w in _weights(SHAPES)]
+    opt = dion_b200.Muon([dict(params=ps)], distributed_mesh=flat, lr=0.1)
+    for s in range(2):
+        for p, g in zip(ps, _grads(s, SHAPES)):
+            p.grad = distribute_tensor(g, flat, [Shard(0)])
+        opt.step()
+    full = [p.detach().full_tensor().clone() for p in ps]
+    return full if rank == 0 else None
+
+
+def test_flattened_mesh_matches_single_process(tmp_path):
+    out = run_ranks(_flattened_mesh_worker, 4, "gloo", (), str(tmp_path))[0]
+    for a, b in zip(_single("Muon", {}), out):
+        assert (a - b).abs().max().item() <= 1e-6
