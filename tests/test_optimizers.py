@@ -93,6 +93,39 @@ def test_dion_parity_with_reference(ref_dion, name, kw):
         assert (x - y).abs().max().item() < 1e-5
 
 
+def test_dion_mixed_precision_states_and_parity(ref_dion):
+    """``DionMixedPrecisionConfig``: bf16 momentum and Q, fp32 AdamW variance on fp32 weights -
+    the state tensors take the configured types and the run follows the reference's with the
+    same configuration (reference README: "Mixed Precision Dion")."""
+    shapes = ((64, 128), (128, 64), (96, 96))
+
+    def run(pkg, scalar):
+        mp = pkg.DionMixedPrecisionConfig(momentum_dtype=torch.bfloat16, Q_dtype=torch.bfloat16,
+                                          variance_dtype=torch.float32)
+        return _run(pkg.Dion, dict(rank_fraction=0.25, mixed_precision_config=mp), shapes=shapes,
+                    steps=4, scalar=scalar, pre=_same_q_init)
+
+    # The reference's AdamW path rejects momentum and variance of different types, so the
+    # side-by-side run uses Lion for the vector; AdamW with mixed types is checked on ours alone.
+    ours, opt = run(dion_b200, "lion")
+    theirs, _ = run(ref_dion, "lion")
+    matrix, vector = opt.param_groups[0]["params"][0], opt.param_groups[1]["params"][0]
+    assert opt.state[matrix]["momentum"].dtype == torch.bfloat16
+    assert opt.state[matrix]["Q"].dtype == torch.bfloat16
+    assert opt.state[vector]["momentum"].dtype == torch.bfloat16
+    for x, y in zip(ours, theirs):
+        assert (x - y).abs().max().item() < 2e-3     # bf16 state: rounding order differs slightly
+    full, _ = _run(dion_b200.Dion, dict(rank_fraction=0.25), shapes=shapes, steps=4,
+                   scalar="lion", pre=_same_q_init)
+    for x, y in zip(ours, full):
+        assert (x - y).abs().max().item() < 5e-2     # and stays close to the fp32-state run
+    adam, opt = run(dion_b200, "adamw")
+    vector = opt.param_groups[1]["params"][0]
+    assert opt.state[vector]["variance"].dtype == torch.float32
+    assert opt.state[vector]["momentum"].dtype == torch.bfloat16
+    assert all(torch.isfinite(t).all() for t in adam)
+
+
 def test_simple_and_muon_reference_parity(ref_dion):
     shapes = ((64, 128), (128, 64))
     for name, kw in (("DionSimple", dict(rank=16)), ("MuonReference", dict())):
