@@ -250,3 +250,59 @@ def test_flattened_mesh_matches_single_process(tmp_path):
     out = run_ranks(_flattened_mesh_worker, 4, "gloo", (), str(tmp_path))[0]
     for a, b in zip(_single("Muon", {}), out):
         assert (a - b).abs().max().item() <= 1e-6
+
+
+def _compressed_sync_worker(rank, world, steps):
+    """Data-parallel ranks with different gradients: (a) Dion synchronizes only the low-rank
+    factors (decoupled momentum), (b) gradients are averaged first and Dion synchronizes nothing.
+    The weights agree up to rounding; (a)'s momenta differ between ranks until
+    ``synchronize_for_checkpoint`` averages them (reference README, "Compressed Data-Parallel
+    Gradient Sync for Dion")."""
+    shapes = ((32, 64), (64, 32), (48, 48))   # rank 24 of 48 x 48 saves nothing: not compressed
+    outs = {}
+    for mode in ("compressed", "averaged"):
+        ps = [torch.nn.Parameter(w) for w in _weights(shapes)]
+        torch.manual_seed(0)   # same random Q on every rank and in both runs
+        opt = dion_b200.Dion([dict(params=ps)], replicate_mesh=dist.group.WORLD,
+                             replicate_mesh_grad_sync=(mode == "compressed"),
+                             rank_fraction=0.5, lr=0.05)
+        for s in range(steps):
+            g = torch.Generator().manual_seed(1000 * s + rank)
+            for p in ps:
+                p.grad = torch.randn(p.shape, generator=g)
+                if mode == "averaged":
+                    dist.all_reduce(p.grad)
+                    p.grad /= world
+            opt.step()
+        moms = [opt.state[p]["momentum"].clone() for p in ps]
+        spread = []
+        for m in moms:
+            lo, hi = m.clone(), m.clone()
+            dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+            dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+            spread.append((hi - lo).abs().max().item())
+        opt.synchronize_for_checkpoint()
+        after = []
+        for p in ps:
+            m = opt.state[p]["momentum"]
+            lo, hi = m.clone(), m.clone()
+            dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+            dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+            after.append((hi - lo).abs().max().item())
+        outs[mode] = ([p.detach().clone() for p in ps], spread, after,
+                      [opt.state[p]["momentum"].clone() for p in ps])
+    return outs if rank == 0 else None
+
+
+def test_compressed_data_parallel_sync_equals_gradient_averaging(tmp_path):
+    outs = run_ranks(_compressed_sync_worker, 2, "gloo", (3,), str(tmp_path))[0]
+    wa, spread_a, after_a, mom_a = outs["compressed"]
+    wb, spread_b, after_b, mom_b = outs["averaged"]
+    for a, b in zip(wa, wb):
+        assert (a - b).abs().max().item() < 1e-5
+    assert min(spread_a[:2]) > 1e-3      # decoupled momentum really differs between ranks
+    assert spread_a[2] == 0.0            # (m + n) r >= m n: that gradient is all-reduced in full
+    assert max(spread_b) == 0.0          # with averaged gradients it never does
+    assert max(after_a) < 1e-6           # and the checkpoint synchronization removes the spread
+    for a, b in zip(mom_a, mom_b):       # the averaged decoupled momentum is the coupled one
+        assert (a - b).abs().max().item() < 1e-5
