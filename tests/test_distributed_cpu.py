@@ -306,3 +306,37 @@ def test_compressed_data_parallel_sync_equals_gradient_averaging(tmp_path):
     assert max(after_a) < 1e-6           # and the checkpoint synchronization removes the spread
     for a, b in zip(mom_a, mom_b):       # the averaged decoupled momentum is the coupled one
         assert (a - b).abs().max().item() < 1e-5
+
+
+def _bad_sharding_worker(rank, world):
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.tensor import Shard, distribute_tensor
+    mesh = init_device_mesh("cpu", (2, 2), mesh_dim_names=("fs", "tp"))
+    w = torch.randn(32, 64)
+    seen = []
+    # Dion: FSDP and TP must shard different matrix dimensions.
+    p = torch.nn.Parameter(distribute_tensor(w, mesh, [Shard(0), Shard(0)]))
+    try:
+        opt = dion_b200.Dion([dict(params=[p])], outer_shard_mesh=mesh["fs"],
+                             inner_shard_mesh=mesh["tp"], lr=0.1)
+        p.grad = distribute_tensor(torch.randn(32, 64), mesh, [Shard(0), Shard(0)])
+        opt.step()
+        seen.append("accepted")
+    except RuntimeError as exc:
+        seen.append(str(exc))
+    # Megabatch optimizers: one sharded matrix dimension at most.
+    q = torch.nn.Parameter(distribute_tensor(w, mesh, [Shard(0), Shard(1)]))
+    try:
+        opt = dion_b200.Muon([dict(params=[q])], distributed_mesh=mesh["fs"], lr=0.1)
+        q.grad = distribute_tensor(torch.randn(32, 64), mesh, [Shard(0), Shard(1)])
+        opt.step()
+        seen.append("accepted")
+    except NotImplementedError as exc:
+        seen.append(str(exc))
+    return seen if rank == 0 else None
+
+
+def test_unsupported_shardings_are_rejected_on_every_rank(tmp_path):
+    dion_msg, muon_msg = run_ranks(_bad_sharding_worker, 4, "gloo", (), str(tmp_path))[0]
+    assert "double-sharded" in dion_msg
+    assert "multiple sharded dimensions" in muon_msg
