@@ -182,7 +182,13 @@ def init_distributed(dp_size, fs_size, tp_size, device_type: str = "cuda") -> Op
     """Initialise the process group (plain DDP when no mesh size is given) or a 3-D
     ``("dp", "fs", "tp")`` device mesh.  Expects torchrun's RANK / LOCAL_RANK / WORLD_SIZE."""
     global _MASTER
-    if not all(v in os.environ for v in ("RANK", "LOCAL_RANK", "WORLD_SIZE")):
+    launcher_vars = ("RANK", "LOCAL_RANK", "WORLD_SIZE")
+    if not any(v in os.environ for v in launcher_vars):
+        # Started as a plain ``python train.py``: a one-process job on the local machine.
+        os.environ.update(RANK="0", LOCAL_RANK="0", WORLD_SIZE="1")
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29511")
+    elif not all(v in os.environ for v in launcher_vars):
         raise RuntimeError("This script must be launched using the 'torchrun' command.")
     rank, local_rank = int(os.environ["RANK"]), int(os.environ["LOCAL_RANK"])
     world = int(os.environ["WORLD_SIZE"])

@@ -186,3 +186,20 @@ def test_optimizer_factory_covers_every_choice():
     with pytest.raises(ValueError):
         trainer.init_optimizer(model, None, None, trainer.Hyperparameters(
             optimizer="muon", model_dim=16, replicate_mesh_grad_sync=True), cli)
+
+
+def test_trainer_runs_as_a_plain_single_process():
+    """``python train.py`` without a launcher is a one-process job; validation and the
+    optimizer timer report at the validation steps."""
+    env = {k: v for k, v in os.environ.items()
+           if k not in ("RANK", "LOCAL_RANK", "WORLD_SIZE", "MASTER_ADDR", "MASTER_PORT")}
+    env["OMP_NUM_THREADS"] = "2"
+    cmd = [sys.executable, os.path.join(ROOT, "train.py"), "--device", "cpu", "--synthetic",
+           "--no_wandb", "--debug", "--model_dim", "64", "--n_layer", "2", "--n_head", "2",
+           "--sequence_length", "32", "--batch_size", "8", "--device_batch_size", "4",
+           "--val_loss_every", "2", "--val_tokens", "512", "--scalar_opt", "lion",
+           "--num_iterations", "4", "--optimizer", "dion2", "--time_optimizer"]
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=ROOT)
+    assert res.returncode == 0, res.stdout[-1500:] + res.stderr[-1500:]
+    assert res.stdout.count("train_loss=") == 4
+    assert res.stdout.count("val_loss:") == 3 and "opt_avg:" in res.stdout
