@@ -299,6 +299,10 @@ class CheckpointManager:
         self.model, self.optimizer = model, optimizer
         self.train_loader, self.val_loader = train_loader, val_loader
         self.wandb_id = wandb_id
+        # Position of the training loader before it prefetched the batch of the following step;
+        # saved instead of the live position so that a resumed run reads the same batches as an
+        # uninterrupted one.
+        self.train_loader_state: Optional[dict] = None
 
     def _path(self, step: int) -> str:
         return os.path.join(self.checkpoint_dir, f"step_{step:08d}")
@@ -313,7 +317,8 @@ class CheckpointManager:
     def _state(self, step: int) -> Dict[str, Any]:
         model_sd, optim_sd = get_state_dict(self.model, self.optimizer)
         return {"model": model_sd, "optimizer": optim_sd,
-                "train_loader": self.train_loader.state_dict() if self.train_loader else {},
+                "train_loader": (self.train_loader_state if self.train_loader_state is not None
+                                 else self.train_loader.state_dict() if self.train_loader else {}),
                 "val_loader": self.val_loader.state_dict() if self.val_loader else {},
                 "step": step, "wandb_id": self.wandb_id or ""}
 
@@ -488,8 +493,13 @@ def main(argv: Optional[List[str]] = None) -> None:
     if hp.checkpoint_dir:
         ckpt = CheckpointManager(hp.checkpoint_dir, raw_model, optimizer, train_loader, val_loader)
         if ckpt.latest_step() is not None:
-            start_step = ckpt.load()
-            print0(f"Resumed from step {start_step}")
+            done = ckpt.load()
+            start_step = done + 1     # the checkpoint was written after step ``done`` completed
+            scheduler.last_epoch = start_step
+            for g, base in zip(optimizer.param_groups, scheduler.base_lrs):
+                g["lr"] = base * lr_multiplier(start_step, hp.num_iterations, hp.warmup_ratio,
+                                               hp.warmdown_ratio)
+            print0(f"Resumed from step {done}")
 
     wandb = None
     if not args.no_wandb and not args.debug and rank == 0:
@@ -584,6 +594,8 @@ def main(argv: Optional[List[str]] = None) -> None:
                     ys.append(y)
                 train_loss = gstep(torch.stack(xs), torch.stack(ys)).clone()
             scheduler.step()
+            if ckpt:
+                ckpt.train_loader_state = train_loader.state_dict()
             x, y = train_loader.next_batch()
             if args.time_optimizer:
                 tot_all += max_over_ranks(timer_all.stop(), device)
@@ -604,8 +616,10 @@ def main(argv: Optional[List[str]] = None) -> None:
                 loss = model(x, y)
             train_loss = loss.detach()
             loss = loss / grad_accum
-            x, y = train_loader.next_batch()
             final = micro == grad_accum
+            if final and ckpt:
+                ckpt.train_loader_state = train_loader.state_dict()
+            x, y = train_loader.next_batch()
             if ddp is not None and (not final or hp.replicate_mesh_grad_sync):
                 with ddp.no_sync():
                     loss.backward()

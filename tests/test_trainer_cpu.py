@@ -2,6 +2,7 @@
 reference Muon) on the small configuration, the data loaders, and the trainer under torchrun with
 gloo (DDP and FSDP2 + checkpoint resume)."""
 import os
+import shutil
 import subprocess
 import sys
 
@@ -101,12 +102,17 @@ def test_trainer_ddp_and_fsdp_resume(tmp_path):
     out = _torchrun(["--optimizer", "muon", "--num_iterations", "3"])
     assert out.count("train_loss=") == 3
     ck = str(tmp_path / "ckpt")
-    out = _torchrun(["--optimizer", "normuon", "--fs_size", "2", "--num_iterations", "2",
-                     "--checkpoint_dir", ck, "--checkpoint_freq", "1"])
+    fsdp = ["--optimizer", "normuon", "--fs_size", "2", "--checkpoint_dir", ck]
+    full = _torchrun(fsdp + ["--num_iterations", "3", "--checkpoint_freq", "1"])
     assert os.path.isdir(os.path.join(ck, "step_00000001"))
-    out = _torchrun(["--optimizer", "normuon", "--fs_size", "2", "--num_iterations", "3",
-                     "--checkpoint_dir", ck])
-    assert "Resumed from step 1" in out and "Step 2:" in out and "Step 0:" not in out
+    for later in ("step_00000002", "step_00000003"):
+        shutil.rmtree(os.path.join(ck, later), ignore_errors=True)
+    out = _torchrun(fsdp + ["--num_iterations", "3"])
+    assert "Resumed from step 1" in out and "Step 0:" not in out and "Step 1:" not in out
+    # The resumed run continues with the following step, on the same batches, schedule position
+    # and optimizer state: its log lines repeat those of the uninterrupted run.
+    line = [ln for ln in full.splitlines() if ln.startswith("Step 2:")]
+    assert line and line[0] in out
 
 
 def test_trainer_hybrid_meshes():
