@@ -100,6 +100,12 @@ class CudaGraphOptimizer(torch.optim.Optimizer):
             torch.cuda.synchronize()
             old.reset()
 
+    def _on_cuda(self) -> bool:
+        for group in self.param_groups:
+            for p in group["params"]:
+                return p.is_cuda
+        return False
+
     def _count_live_tensors(self) -> int:
         return len(getattr(self.optimizer, "_hyperparam_tensors", None) or ())
 
@@ -144,8 +150,8 @@ class CudaGraphOptimizer(torch.optim.Optimizer):
         if closure is not None:
             with torch.enable_grad():
                 loss = closure()
-        if self._steps_taken < self.warmup_steps:
-            self.optimizer.step()
+        if self._steps_taken < self.warmup_steps or not self._on_cuda():
+            self.optimizer.step()      # warm-up, or nothing to record: parameters live on the host
         else:
             _call_if_present(self.optimizer, "_sync_hyperparam_tensors")
             if self._graph is None:

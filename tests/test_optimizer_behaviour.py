@@ -191,3 +191,23 @@ def test_graph_wrapper_is_call_compatible_with_torch_optimizer():
     before = wrap.param_groups[0]["step"]
     wrap.load_state_dict(state_dict=saved)
     assert wrap.param_groups[0]["step"] == src.param_groups[0]["step"] != before
+
+
+def test_graph_wrapper_steps_eagerly_for_host_parameters():
+    """With parameters on the CPU there is nothing to record: every step is an ordinary step and
+    matches the unwrapped optimizer."""
+    from dion_b200 import CudaGraphOptimizer, Muon
+    torch.manual_seed(0)
+    w0 = torch.randn(8, 16)
+    grads = [torch.randn(8, 16) for _ in range(4)]
+    out = []
+    for wrap in (False, True):
+        p = torch.nn.Parameter(w0.clone())
+        opt = Muon([dict(params=[p])], lr=0.01)
+        opt = CudaGraphOptimizer(opt, warmup_steps=1) if wrap else opt
+        for g in grads:
+            p.grad = g.clone()
+            opt.step()
+            opt.zero_grad()
+        out.append(p.detach().clone())
+    assert torch.equal(out[0], out[1])
