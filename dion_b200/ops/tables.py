@@ -16,6 +16,14 @@ CHUNK = 4096  # must match kChunk in csrc/foreach_ops.cu
 
 _cache: Dict[Tuple, "TensorTable"] = {}
 _CACHE_LIMIT = 4096
+# Tables that a CUDA graph recorded: replays read their device memory, so they must outlive the
+# cache (which is dropped wholesale when it grows past its limit).
+_recorded: Dict[Tuple, "TensorTable"] = {}
+
+
+def _remember_if_capturing(key: Tuple, tb: "TensorTable") -> None:
+    if tb.device_tensor.is_cuda and torch.cuda.is_current_stream_capturing():
+        _recorded.setdefault(key, tb)
 
 # Pinned staging memory for the host->device copies of tables.  Eager rebuilds take slices of a
 # ring; rebuilds that happen while a CUDA graph is being captured take slices that are never
@@ -55,6 +63,9 @@ def _upload(host: Tensor, device: torch.device) -> Tensor:
         if n > _RING_WORDS:
             return host.pin_memory().to(device, non_blocking=True)
         if _ring_pos + n > _RING_WORDS:
+            # About to overwrite staging words whose copies were queued long ago; make sure the
+            # stream has drained them (once per ~2 MB of tables, so the wait is rare and short).
+            torch.cuda.current_stream(device).synchronize()
             _ring_pos = 0
         stage = _ring[_ring_pos:_ring_pos + n]
         _ring_pos += n
@@ -107,6 +118,7 @@ def build_table(
     key = (tag, chunk, tuple(numels)) + tuple(tuple(_ptr(t) for t in lst) for lst in lists)
     hit = _cache.get(key)
     if hit is not None:
+        _remember_if_capturing(key, hit)
         return hit
     device = next(t.device for lst in lists for t in lst if isinstance(t, Tensor))
     prefix = [0]
@@ -124,6 +136,7 @@ def build_table(
     # fresh table is built; nothing is kept alive here (that would pin freed gradients).
     tb = TensorTable(dev, n, prefix[-1], None)
     _cache[key] = tb
+    _remember_if_capturing(key, tb)
     return tb
 
 
@@ -132,6 +145,7 @@ def build_ptr_array(lists: Sequence[Sequence[Optional[Tensor]]], tag: str = "") 
     key = ("ptrs", tag) + tuple(tuple(_ptr(t) for t in lst) for lst in lists)
     hit = _cache.get(key)
     if hit is not None:
+        _remember_if_capturing(key, hit)
         return hit.device_tensor
     device = next((t.device for lst in lists for t in lst if isinstance(t, Tensor)), None)
     if device is None:  # only raw addresses: they belong to the current CUDA device
@@ -140,9 +154,11 @@ def build_ptr_array(lists: Sequence[Sequence[Optional[Tensor]]], tag: str = "") 
     dev = _upload(host, device) if device.type == "cuda" else host
     if len(_cache) > _CACHE_LIMIT:
         _cache.clear()
-    _cache[key] = TensorTable(dev, len(lists[0]), 0, None)
+    tb = _cache[key] = TensorTable(dev, len(lists[0]), 0, None)
+    _remember_if_capturing(key, tb)
     return dev
 
 
 def clear_cache() -> None:
+    """Drop cached tables (those recorded by CUDA graphs stay alive)."""
     _cache.clear()
