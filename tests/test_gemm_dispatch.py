@@ -33,3 +33,26 @@ def test_config_choice_fills_the_machine(monkeypatch):
     # thin outputs never go to the pair kernel
     assert gemm._choose_config(128, 4096, 512, 8, False, True, dev)[0] is False
     gemm._config_cache.clear()
+
+
+def test_pointer_tables_layout_and_cache():
+    """Host-side construction of the multi-tensor tables: ``[n, chunk prefix, numels, pointers]``,
+    cached by the addresses they hold."""
+    import torch
+    from dion_b200.ops import tables
+    tables.clear_cache()
+    a, b = torch.zeros(5000), torch.zeros(10)
+    g, h = torch.zeros(5000), torch.zeros(10)
+    tb = tables.build_table([[a, b], [g, h], [None, tables.RawPointer(4096)]], tag="t")
+    flat = tb.device_tensor.tolist()
+    assert tb.n == 2 and tb.n_chunks == 3            # ceil(5000 / 4096) + ceil(10 / 4096)
+    assert flat[0] == 2 and flat[1:4] == [0, 2, 3] and flat[4:6] == [5000, 10]
+    assert flat[6:8] == [a.data_ptr(), b.data_ptr()] and flat[8:10] == [g.data_ptr(), h.data_ptr()]
+    assert flat[10:12] == [0, 4096]
+    assert tables.build_table([[a, b], [g, h], [None, tables.RawPointer(4096)]], tag="t") is tb
+    g2 = torch.zeros(5000)                            # a gradient buffer that moved
+    tb2 = tables.build_table([[a, b], [g2, h], [None, tables.RawPointer(4096)]], tag="t")
+    assert tb2 is not tb and tb2.device_tensor.tolist()[8] == g2.data_ptr()
+    arr = tables.build_ptr_array([[a, b], [g, h]], tag="p")
+    assert arr.tolist() == [[a.data_ptr(), b.data_ptr()], [g.data_ptr(), h.data_ptr()]]
+    assert tables.build_ptr_array([[a, b], [g, h]], tag="p") is arr
