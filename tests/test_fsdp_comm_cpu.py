@@ -74,3 +74,45 @@ def test_in_place_gather_launches_on_the_owning_ring():
     out2 = comm.allocate((64,), dtype=torch.float32, device=torch.device("cpu"))
     comm(out2, torch.full((32,), 7.0), None)
     assert torch.all(out2[32:] == 7.0) and comm.rings[1].gathers == [128]
+
+
+def test_all_reduce_slices_partition_the_buffer():
+    """Each rank reduces one slice of 16-byte vectors; over all ranks the slices cover the data
+    exactly once, for sizes that do not divide evenly too (host arithmetic of
+    ``SymmetricAllReduce.all_reduce_`` / ``all_gather_``, no GPU needed)."""
+    import torch
+    from dion_b200.parallel.symm import SymmetricAllReduce
+    for world in (2, 3, 4, 8):
+        for numel, dtype in ((1, torch.float32), (5, torch.bfloat16), (4096, torch.float32),
+                             (1000003, torch.bfloat16), (7 * world * 4, torch.float32)):
+            covered = []
+            for rank in range(world):
+                red = object.__new__(SymmetricAllReduce)
+                red.world, red.rank, red.capacity = world, rank, 1 << 30
+                calls = []
+                red._launch = lambda b, e, dt, sc, gather, calls=calls: calls.append((b, e, dt, sc, gather))
+                red.all_reduce_(numel, dtype, op="avg")
+                (b, e, dt, sc, gather), = calls
+                assert dt == (0 if dtype == torch.float32 else 1) and not gather
+                assert abs(sc - 1.0 / world) < 1e-12
+                covered.append((b, max(b, e)))
+            esize = 4 if dtype == torch.float32 else 2
+            nvec = (numel * esize + 15) // 16
+            pos = 0
+            for b, e in covered:            # ranks in order: contiguous, disjoint, complete
+                assert b == min(pos, b) or b >= pos
+                if e > b:
+                    assert b == pos
+                    pos = e
+            assert pos == nvec
+    red = object.__new__(SymmetricAllReduce)
+    red.world, red.rank, red.capacity = 4, 2, 1 << 20
+    calls = []
+    red._launch = lambda b, e, dt, sc, gather: calls.append((b, e, gather))
+    red.all_gather_(4096)
+    assert calls == [(2 * 256, 3 * 256, True)]
+    import pytest
+    with pytest.raises(ValueError):
+        red.all_gather_(24)                 # slots are whole 16-byte vectors
+    with pytest.raises(ValueError):
+        red.all_gather_(1 << 20)            # world * slot must fit
