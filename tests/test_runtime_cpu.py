@@ -72,3 +72,36 @@ def test_arena_hands_out_the_same_addresses_every_step():
     assert arena.alloc((4, 8), torch.float32, dev).data_ptr() == big.data_ptr()
     plain = alloc(None, (2, 2), torch.float32, dev, zero=True)
     assert plain.shape == (2, 2) and float(plain.sum()) == 0.0
+
+
+def test_fused_exchange_eligibility_uses_only_rank_independent_facts(monkeypatch):
+    """Which buckets take the peer-memory exchange: evenly row-sharded 2-D matrices with a column
+    count the TMA rules allow, a built-in Newton-Schulz driver and 2-8 ranks on one node; anything
+    else keeps the collective path.  The decision reads no local shard size, so every rank of an
+    uneven layout decides alike."""
+    from dion_b200.ops import newton_schulz as NS
+    from dion_b200.parallel import fused_exchange as FX
+    monkeypatch.setattr(FX.symm, "symmetric_memory_available", lambda pg: True)
+    monkeypatch.delenv("DION_B200_FUSED_EXCHANGE", raising=False)
+    pg = object()
+    ok = dict(local_shape=(256, 1024), comm_dim=-2, global_rows=1024, world=4, pg=pg,
+              ns_func=NS.polar_express, flatten=False, split_sizes=None)
+    assert FX.eligible(**ok)
+    for change in (dict(comm_dim=-1),                      # column shards
+                   dict(local_shape=(3, 256, 1024)),       # batched parameter
+                   dict(global_rows=1022),                 # uneven row shards
+                   dict(global_rows=None),
+                   dict(local_shape=(256, 1020)),          # row length not a multiple of 8
+                   dict(world=1), dict(world=16),
+                   dict(pg=None),
+                   dict(flatten=True), dict(split_sizes=(512, 512)),
+                   dict(ns_func=lambda X, epsilon: X),      # user driver: iteration unknown
+                   dict(ns_func=NS.gram_newton_schulz)):
+        assert not FX.eligible(**{**ok, **change}), change
+    # the local shard size itself plays no part (an empty shard on one rank changes nothing)
+    assert FX.eligible(**{**ok, "local_shape": (0, 1024)})
+    monkeypatch.setenv("DION_B200_FUSED_EXCHANGE", "0")
+    assert not FX.eligible(**ok)
+    monkeypatch.delenv("DION_B200_FUSED_EXCHANGE")
+    monkeypatch.setattr(FX.symm, "symmetric_memory_available", lambda pg: False)
+    assert not FX.eligible(**ok)
