@@ -105,3 +105,45 @@ def test_fused_exchange_eligibility_uses_only_rank_independent_facts(monkeypatch
     monkeypatch.delenv("DION_B200_FUSED_EXCHANGE")
     monkeypatch.setattr(FX.symm, "symmetric_memory_available", lambda pg: False)
     assert not FX.eligible(**ok)
+
+
+def test_megabatch_plan_modes_padding_and_argument_errors():
+    """Layout decisions of one megabatch round, without communication: mode, per-rank counts,
+    padded shard sizes, where each input is written, and the argument errors (the reference checks
+    the missing ``global_comm_dim_size`` error with a one-rank gloo group,
+    tests/test_megabatch_empty_shard.py:116-143)."""
+    from dion_b200.ops import newton_schulz as NS
+    from dion_b200.parallel.megabatch import MegabatchPlan
+    dev = torch.device("cpu")
+    pg = object()                                            # never used for communication here
+    single = MegabatchPlan((8, 16), 3, dev, None, 0, 1, None)
+    assert (single.mode, single.per_rank, single.n_total) == ("single", 3, 3)
+    views = single.input_views()
+    for i, v in enumerate(views):
+        v.copy_(torch.randn(8, 16))
+    out = run_to_completion(single.run(NS.polar_express, False, 1e-6))
+    assert out.shape == (3, 8, 16) and torch.isfinite(out.float()).all()
+
+    rep = MegabatchPlan((8, 16), 5, dev, None, 1, 4, pg)    # DDP: 5 matrices over 4 ranks
+    assert (rep.mode, rep.per_rank, rep.n_total) == ("replicated", 2, 8)
+    owned = [i for i, v in enumerate(rep.input_views()) if v is not None]
+    assert owned == [2, 3]                                   # rank 1 owns matrices 2 and 3
+
+    sh = MegabatchPlan((3, 16), 6, dev, -2, 0, 4, pg, global_comm_dim_size=10)
+    assert sh.mode == "sharded" and sh.padded_local == 3 and sh.padded_shape == (3, 16)
+    short = MegabatchPlan((1, 16), 6, dev, -2, 3, 4, pg, global_comm_dim_size=10)   # last rank
+    assert short.padded_shape == (3, 16) and short.input_views()[0].shape == (1, 16)
+    empty = MegabatchPlan((0, 16), 2, dev, -2, 3, 4, pg, global_comm_dim_size=3)
+    assert empty.padded_shape == (1, 16) and empty.input_views()[1].shape == (0, 16)
+
+    with pytest.raises(ValueError, match="global_comm_dim_size"):
+        MegabatchPlan((4, 16), 2, dev, -2, 0, 2, pg)
+    with pytest.raises(ValueError, match="negative"):
+        MegabatchPlan((4, 16), 2, dev, 0, 0, 2, pg, global_comm_dim_size=8)
+    with pytest.raises(RuntimeError, match="padded_local_size"):
+        MegabatchPlan((9, 16), 2, dev, -2, 0, 2, pg, global_comm_dim_size=10)
+    with pytest.raises(NotImplementedError, match="divisible"):
+        MegabatchPlan((5, 16), 2, dev, -2, 0, 2, pg, global_comm_dim_size=9, split_sizes=(4, 5))
+    with pytest.raises(NotImplementedError, match="local_comm_size"):
+        MegabatchPlan((4, 16), 2, dev, -2, 0, 2, pg, global_comm_dim_size=8, local_comm_size=2,
+                      split_sizes=(4, 4))
