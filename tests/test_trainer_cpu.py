@@ -209,3 +209,22 @@ def test_trainer_runs_as_a_plain_single_process():
     assert res.returncode == 0, res.stdout[-1500:] + res.stderr[-1500:]
     assert res.stdout.count("train_loss=") == 4
     assert res.stdout.count("val_loss:") == 3 and "opt_avg:" in res.stdout
+
+
+def test_token_shard_loader_reads_what_the_reference_loader_reads(ref_dion, tmp_path, monkeypatch):
+    """Same files, same ranks: identical batches and identical checkpoint state, across shard
+    boundaries and the wrap-around to the first shard (reference: models/gpt_utils.py:40-104;
+    its ``.cuda()`` calls are made no-ops so that it runs here)."""
+    from models.gpt_utils import DistributedDataLoader as RefLoader   # from baseline/_ref
+    monkeypatch.setattr(torch.Tensor, "cuda", lambda self, *a, **k: self)
+    rng = np.random.default_rng(0)
+    for i, n in enumerate((700, 450, 620)):
+        write_datafile(str(tmp_path / f"fineweb_train_{i:06d}.bin"), rng.integers(0, 50000, n))
+    pattern = str(tmp_path / "fineweb_train_*.bin")
+    for rank in (0, 1):
+        ours = DistributedDataLoader(pattern, 2, 16, rank, 2, device=torch.device("cpu"))
+        ref = RefLoader(pattern, 2, 16, rank, 2)
+        for step in range(40):
+            (x, y), (rx, ry) = ours.next_batch(), ref.next_batch()
+            assert torch.equal(x.cpu(), rx) and torch.equal(y.cpu(), ry), (rank, step)
+            assert ours.state_dict() == ref.state_dict(), (rank, step)
