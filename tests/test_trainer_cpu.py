@@ -228,3 +228,30 @@ def test_token_shard_loader_reads_what_the_reference_loader_reads(ref_dion, tmp_
             (x, y), (rx, ry) = ours.next_batch(), ref.next_batch()
             assert torch.equal(x.cpu(), rx) and torch.equal(y.cpu(), ry), (rank, step)
             assert ours.state_dict() == ref.state_dict(), (rank, step)
+
+
+def test_arithmetic_loader_reads_what_the_reference_loader_reads(ref_dion, tmp_path, monkeypatch):
+    """Header-less uint16 files: circular strided reading (with wrap-around) and, for a file
+    shorter than one batch, random windows drawn from numpy's global generator - both as the
+    reference does (models/gpt_utils.py:107-168)."""
+    from models.gpt_utils import ArithmeticDistributedDataLoader as RefLoader
+    from dion_b200.models.data import ArithmeticDistributedDataLoader
+    monkeypatch.setattr(torch.Tensor, "cuda", lambda self, *a, **k: self)
+    rng = np.random.default_rng(1)
+    rng.integers(0, 60000, 1000).astype(np.uint16).tofile(str(tmp_path / "train.bin"))
+    rng.integers(0, 60000, 40).astype(np.uint16).tofile(str(tmp_path / "val.bin"))
+    for rank in (0, 1, 2):
+        ours = ArithmeticDistributedDataLoader(str(tmp_path), 2, 16, rank, 3,
+                                               device=torch.device("cpu"))
+        ref = RefLoader(str(tmp_path), 2, 16, rank, 3)
+        for step in range(30):                                   # 30 * 96 tokens: wraps 2-3 times
+            (x, y), (rx, ry) = ours.next_batch(), ref.next_batch()
+            assert torch.equal(x.cpu(), rx) and torch.equal(y.cpu(), ry), (rank, step)
+    ours = ArithmeticDistributedDataLoader(str(tmp_path), 4, 16, 0, 1, split="val",
+                                           device=torch.device("cpu"))
+    ref = RefLoader(str(tmp_path), 4, 16, 0, 1, split="val")
+    np.random.seed(5)
+    x, y = ours.next_batch()
+    np.random.seed(5)
+    rx, ry = ref.next_batch()
+    assert torch.equal(x.cpu(), rx) and torch.equal(y.cpu(), ry)
