@@ -255,3 +255,27 @@ def test_arithmetic_loader_reads_what_the_reference_loader_reads(ref_dion, tmp_p
     np.random.seed(5)
     rx, ry = ref.next_batch()
     assert torch.equal(x.cpu(), rx) and torch.equal(y.cpu(), ry)
+
+
+def test_hyperparameter_defaults_and_flags_match_the_reference_trainer(ref_dion):
+    """Field names and default values of ``Hyperparameters`` and the set of command-line flags are
+    those of the reference trainer (read from its source text, train.py:35-213, not imported)."""
+    import ast
+    import dataclasses
+    import re
+    from dion_b200 import trainer
+    path = os.path.join(ROOT, "baseline", "_ref", "train.py")
+    if not os.path.exists(path):
+        pytest.skip("reference trainer not copied beside the reference package")
+    source = open(path).read()
+    theirs = {}
+    for node in ast.parse(source).body:
+        if isinstance(node, ast.ClassDef) and node.name == "Hyperparameters":
+            for st in node.body:
+                if isinstance(st, ast.AnnAssign) and st.value is not None:
+                    theirs[st.target.id] = eval(compile(ast.Expression(st.value), "<ref>", "eval"))
+    ours = {f.name: f.default for f in dataclasses.fields(trainer.Hyperparameters)}
+    assert theirs and ours == theirs
+    ref_flags = set(re.findall(r'"--([a-z_0-9]+)"', source))
+    our_flags = set(re.findall(r'"--([a-z_0-9]+)"', open(trainer.__file__).read()))
+    assert ref_flags <= our_flags, sorted(ref_flags - our_flags)
