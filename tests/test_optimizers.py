@@ -275,3 +275,24 @@ def test_cuda_matches_cpu(name, kw):
     check_status()
     for x, y in zip(a, b):
         assert (x - y).abs().max().item() < 5e-3  # lr * bf16 Newton-Schulz differences
+
+
+@pytest.mark.parametrize("name", ["Muon", "NorMuon", "Dion2", "NorDion2", "Dion3", "Dion",
+                                  "DionReference", "DionSimple", "MuonReference",
+                                  "CudaGraphOptimizer"])
+def test_constructor_signatures_match_the_reference(ref_dion, name):
+    """Same argument names, order and default values, so call sites written for the reference
+    construct these classes unchanged."""
+    import inspect
+    if name == "CudaGraphOptimizer":
+        from dion.cuda_graph import CudaGraphOptimizer as theirs
+    else:
+        theirs = getattr(ref_dion, name)
+    ours = getattr(dion_b200, name)
+    a = inspect.signature(theirs.__init__).parameters
+    b = inspect.signature(ours.__init__).parameters
+    assert list(a) == list(b)
+    for key in a:
+        if not callable(a[key].default):
+            assert a[key].default == b[key].default, key
+        assert a[key].kind == b[key].kind, key
