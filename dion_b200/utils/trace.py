@@ -11,7 +11,6 @@ string.
 """
 from __future__ import annotations
 
-import contextlib
 import os
 from typing import Callable, Optional
 
