@@ -340,3 +340,25 @@ def test_unsupported_shardings_are_rejected_on_every_rank(tmp_path):
     dion_msg, muon_msg = run_ranks(_bad_sharding_worker, 4, "gloo", (), str(tmp_path))[0]
     assert "double-sharded" in dion_msg
     assert "multiple sharded dimensions" in muon_msg
+
+
+def _muon_reference_worker(rank, world):
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.tensor import Shard, distribute_tensor
+    mesh = init_device_mesh("cpu", (world,))
+    ps = [torch.nn.Parameter(distribute_tensor(w, mesh, [Shard(0)])) for w in _weights(SHAPES)]
+    opt = dion_b200.MuonReference([dict(params=ps)], lr=0.1)
+    for s in range(2):
+        for p, g in zip(ps, _grads(s, SHAPES)):
+            p.grad = distribute_tensor(g, mesh, [Shard(0)])
+        opt.step()
+    full = [p.detach().full_tensor().clone() for p in ps]
+    return full if rank == 0 else None
+
+
+def test_muon_reference_on_sharded_parameters_matches_single_process(tmp_path):
+    """The all-gather variant (every rank assembles each full matrix) gives the single-process
+    result on row-sharded DTensor parameters."""
+    out = run_ranks(_muon_reference_worker, 2, "gloo", (), str(tmp_path))[0]
+    for a, b in zip(_single("MuonReference", {}), out):
+        assert (a - b).abs().max().item() <= 1e-6
