@@ -362,3 +362,69 @@ def test_muon_reference_on_sharded_parameters_matches_single_process(tmp_path):
     out = run_ranks(_muon_reference_worker, 2, "gloo", (), str(tmp_path))[0]
     for a, b in zip(_single("MuonReference", {}), out):
         assert (a - b).abs().max().item() <= 1e-6
+
+
+DION_SHAPES = ((32, 64), (32, 64), (64, 32), (64, 32))
+
+
+def _dion_common_q(opt, ps, distribute=None):
+    """Create Dion's state now and replace every ``Q`` by (the shards of) one fixed full matrix,
+    so that runs with different layouts start from the same point."""
+    group = opt.param_groups[0]
+    gen = torch.Generator().manual_seed(11)
+    for p in ps:
+        opt._init_opt_state_dion(p, opt.state[p], group["rank_fraction"], group["rank_multiple_of"])
+        q = opt.state[p]["Q"]
+        full = torch.randn(tuple(q.shape), generator=gen)
+        opt.state[p]["Q"] = full if distribute is None else distribute(full, q)
+
+
+def _dion_single(transposed, steps=3):
+    ps = [torch.nn.Parameter(w) for w in _weights(DION_SHAPES)]
+    opt = dion_b200.Dion([dict(params=ps)], rank_fraction=0.25, lr=0.1)
+    for p, t in zip(ps, transposed):     # iterate on the side the sharded layout iterates on
+        opt._get_dion_param_config(p).is_transposed = t
+    _dion_common_q(opt, ps)
+    for s in range(steps):
+        for p, g in zip(ps, _grads(s, DION_SHAPES)):
+            p.grad = g
+        opt.step()
+    return [p.detach().clone() for p in ps]
+
+
+def _dion_layout_worker(rank, world, mode, steps):
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.tensor import Shard, distribute_tensor
+    if mode == "fsdp":
+        mesh = init_device_mesh("cpu", (world,), mesh_dim_names=("fs",))
+        kw, place = dict(outer_shard_mesh=mesh["fs"]), lambda i: [Shard(0)]  # noqa: E731
+    elif mode == "tp":
+        mesh = init_device_mesh("cpu", (world,), mesh_dim_names=("tp",))
+        kw = dict(inner_shard_mesh=mesh["tp"])
+        place = lambda i: [Shard(0)] if i < 2 else [Shard(1)]  # noqa: E731
+    else:
+        mesh = init_device_mesh("cpu", (2, 2), mesh_dim_names=("fs", "tp"))
+        kw = dict(outer_shard_mesh=mesh["fs"], inner_shard_mesh=mesh["tp"])
+        place = lambda i: [Shard(1), Shard(0)] if i < 2 else [Shard(0), Shard(1)]  # noqa: E731
+    ps = [torch.nn.Parameter(distribute_tensor(w, mesh, place(i)))
+          for i, w in enumerate(_weights(DION_SHAPES))]
+    opt = dion_b200.Dion([dict(params=ps)], rank_fraction=0.25, lr=0.1, **kw)
+    _dion_common_q(opt, ps, lambda full, q: distribute_tensor(full, q.device_mesh, q.placements))
+    for s in range(steps):
+        for p, g in zip(ps, _grads(s, DION_SHAPES)):
+            p.grad = distribute_tensor(g, p.device_mesh, p.placements)
+        opt.step()
+    full = [p.detach().full_tensor().clone() for p in ps]
+    transposed = [opt._get_dion_param_config(p).is_transposed for p in ps]
+    return (full, transposed) if rank == 0 else None
+
+
+@pytest.mark.parametrize("mode,world", [("fsdp", 2), ("tp", 2), ("fsdp_tp", 4)])
+def test_dion_sharded_layouts_equal_the_single_process_run(tmp_path, mode, world):
+    """Legacy Dion on FSDP, tensor-parallel and FSDP x TP shards follows the single-process
+    trajectory when both start from the same ``Q`` and iterate on the same side of the matrix
+    (a sharded layout fixes that side by which dimension it shards; the sketch of the randomized
+    QR differs between the runs and must not matter)."""
+    out, transposed = run_ranks(_dion_layout_worker, world, "gloo", (mode, 3), str(tmp_path))[0]
+    for a, b in zip(_dion_single(transposed), out):
+        assert (a - b).abs().max().item() < 1e-4, mode
