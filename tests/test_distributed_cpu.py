@@ -379,9 +379,9 @@ def _dion_common_q(opt, ps, distribute=None):
         opt.state[p]["Q"] = full if distribute is None else distribute(full, q)
 
 
-def _dion_single(transposed, steps=3):
+def _dion_single(transposed, steps=3, cls="Dion"):
     ps = [torch.nn.Parameter(w) for w in _weights(DION_SHAPES)]
-    opt = dion_b200.Dion([dict(params=ps)], rank_fraction=0.25, lr=0.1)
+    opt = getattr(dion_b200, cls)([dict(params=ps)], rank_fraction=0.25, lr=0.1)
     for p, t in zip(ps, transposed):     # iterate on the side the sharded layout iterates on
         opt._get_dion_param_config(p).is_transposed = t
     _dion_common_q(opt, ps)
@@ -392,7 +392,7 @@ def _dion_single(transposed, steps=3):
     return [p.detach().clone() for p in ps]
 
 
-def _dion_layout_worker(rank, world, mode, steps):
+def _dion_layout_worker(rank, world, mode, steps, cls="Dion"):
     from torch.distributed.device_mesh import init_device_mesh
     from torch.distributed.tensor import Shard, distribute_tensor
     if mode == "fsdp":
@@ -408,7 +408,7 @@ def _dion_layout_worker(rank, world, mode, steps):
         place = lambda i: [Shard(1), Shard(0)] if i < 2 else [Shard(0), Shard(1)]  # noqa: E731
     ps = [torch.nn.Parameter(distribute_tensor(w, mesh, place(i)))
           for i, w in enumerate(_weights(DION_SHAPES))]
-    opt = dion_b200.Dion([dict(params=ps)], rank_fraction=0.25, lr=0.1, **kw)
+    opt = getattr(dion_b200, cls)([dict(params=ps)], rank_fraction=0.25, lr=0.1, **kw)
     _dion_common_q(opt, ps, lambda full, q: distribute_tensor(full, q.device_mesh, q.placements))
     for s in range(steps):
         for p, g in zip(ps, _grads(s, DION_SHAPES)):
@@ -419,12 +419,14 @@ def _dion_layout_worker(rank, world, mode, steps):
     return (full, transposed) if rank == 0 else None
 
 
+@pytest.mark.parametrize("cls", ["Dion", "DionReference"])
 @pytest.mark.parametrize("mode,world", [("fsdp", 2), ("tp", 2), ("fsdp_tp", 4)])
-def test_dion_sharded_layouts_equal_the_single_process_run(tmp_path, mode, world):
+def test_dion_sharded_layouts_equal_the_single_process_run(tmp_path, mode, world, cls):
     """Legacy Dion on FSDP, tensor-parallel and FSDP x TP shards follows the single-process
     trajectory when both start from the same ``Q`` and iterate on the same side of the matrix
     (a sharded layout fixes that side by which dimension it shards; the sketch of the randomized
     QR differs between the runs and must not matter)."""
-    out, transposed = run_ranks(_dion_layout_worker, world, "gloo", (mode, 3), str(tmp_path))[0]
-    for a, b in zip(_dion_single(transposed), out):
+    out, transposed = run_ranks(_dion_layout_worker, world, "gloo", (mode, 3, cls),
+                                str(tmp_path))[0]
+    for a, b in zip(_dion_single(transposed, cls=cls), out):
         assert (a - b).abs().max().item() < 1e-4, mode
