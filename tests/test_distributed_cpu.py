@@ -430,3 +430,14 @@ def test_dion_sharded_layouts_equal_the_single_process_run(tmp_path, mode, world
                                 str(tmp_path))[0]
     for a, b in zip(_dion_single(transposed, cls=cls), out):
         assert (a - b).abs().max().item() < 1e-4, mode
+
+
+def test_batched_and_unbatched_dion_agree_from_a_common_start():
+    """The batched optimizer and the one-matrix-at-a-time variant are the same algorithm: from a
+    common ``Q`` (and on the same side of each matrix) their weights agree to rounding, although
+    their randomized sketches differ."""
+    for sides in ([False] * 4, [True, True, False, False]):
+        a = _dion_single(sides, cls="Dion")
+        b = _dion_single(sides, cls="DionReference")
+        for x, y in zip(a, b):
+            assert (x - y).abs().max().item() < 1e-5
