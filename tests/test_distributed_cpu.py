@@ -61,6 +61,8 @@ SHARDED_CASES = [
     ("Dion2", dict(selection_scope="global"), 0, 5e-4),    # exact whole-matrix top-k
     ("Dion2", dict(selection_scope="global"), 1, 5e-4),
     ("NorDion2", dict(selection_scope="global", fraction=1.0), 0, 2e-2),
+    ("Dion2", dict(fraction=1.0), 0, 5e-4),              # local scope, everything selected
+    ("Dion2", dict(fraction=1.0), 1, 5e-4),
 ]
 
 
