@@ -443,3 +443,34 @@ def test_batched_and_unbatched_dion_agree_from_a_common_start():
         b = _dion_single(sides, cls="DionReference")
         for x, y in zip(a, b):
             assert (x - y).abs().max().item() < 1e-5
+
+
+def _submatrix_exchange_worker(rank, world):
+    """Local-scope Dion2 exchanges only the ``k`` selected rows of each shard.  Forcing the
+    exchange to carry whole (zero-padded) shards instead must give the same update (the reference
+    makes this comparison by patching its exchange function,
+    tests/test_dion2_selection_scope.py:243-256)."""
+    import dion_b200.optim.dion2 as d2
+    kw = dict(fraction=0.5)
+    lean = _sharded_worker(rank, world, "Dion2", kw, WIDE, 2, 0)
+    real_plan = d2.MegabatchPlan
+    seen = []
+
+    def whole_shards(*args, **kwargs):
+        seen.append(kwargs.get("local_comm_size"))
+        kwargs["local_comm_size"] = None
+        return real_plan(*args, **kwargs)
+
+    d2.MegabatchPlan = whole_shards
+    try:
+        padded = _sharded_worker(rank, world, "Dion2", kw, WIDE, 2, 0)
+    finally:
+        d2.MegabatchPlan = real_plan
+    return (lean, padded, seen) if rank == 0 else None
+
+
+def test_dion2_submatrix_exchange_equals_whole_shard_exchange(tmp_path):
+    lean, padded, seen = run_ranks(_submatrix_exchange_worker, 2, "gloo", (), str(tmp_path))[0]
+    assert seen and all(k == 4 for k in seen)          # 8 local rows, half of them selected
+    for a, b in zip(lean, padded):
+        assert (a - b).abs().max().item() <= 1e-3
