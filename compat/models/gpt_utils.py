@@ -5,3 +5,5 @@ from dion_b200.models.data import *  # noqa: F401,F403
 
 def __getattr__(name):
     return getattr(_m, name)
+
+_load_data_shard = _m._read_shard      # the reference's name of the shard reader
