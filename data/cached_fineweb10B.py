@@ -1,0 +1,12 @@
+#!/usr/bin/env python
+"""`python data/cached_fineweb10B.py [num_train_chunks]`: fetch the pre-tokenized fineweb10B shards (the command
+line of the reference's script of the same name); the work is done by download_cached.fetch."""
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+from download_cached import fetch  # noqa: E402
+
+if __name__ == "__main__":
+    fetch("fineweb10B", int(sys.argv[1]) if len(sys.argv) > 1 else None)
