@@ -76,3 +76,18 @@ def test_newton_schulz_benchmark_curve_writer(tmp_path, capsys):
     assert open(path).read().splitlines() == ["dim,a,b", "128,10.0,5.0", "256,30.0,"]
     assert "#" * 50 in capsys.readouterr().out
     assert mod.ns_flops(2, 8, 4) == 2 * 5 * (4.0 * 16 * 8 + 2.0 * 64)
+
+
+def test_reference_benchmark_command_line_is_translated():
+    import importlib.util
+    import os
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    spec = importlib.util.spec_from_file_location(
+        "benchmark_newton_shultz", os.path.join(root, "benchmark", "benchmark_newton_shultz.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    assert mod.translate(["--single", "--m", "1024"]) == ["--batch", "1", "--single", "1024", "1024"]
+    assert mod.translate(["--single", "--m", "768", "--n", "3072", "--batch_size", "4"]) == \
+        ["--batch", "4", "--single", "768", "3072"]
+    assert mod.translate(["--grid", "--expansion", "4"]) == ["--batch", "1", "--sweep", "--expansion", "4"]
+    assert mod.translate(["--plot", "--batch_size", "2"]) == ["--batch", "2", "--curve"]
