@@ -474,3 +474,50 @@ def test_dion2_submatrix_exchange_equals_whole_shard_exchange(tmp_path):
     assert seen and all(k == 4 for k in seen)          # 8 local rows, half of them selected
     for a, b in zip(lean, padded):
         assert (a - b).abs().max().item() <= 1e-3
+
+
+def _keller_jordan_worker(rank, world):
+    from dion_b200 import MuonKellerJordan
+    ps = [torch.nn.Parameter(w) for w in _weights(SHAPES)]
+    opt = MuonKellerJordan(ps, lr=0.05)
+    for s in range(2):
+        for p, g in zip(ps, _grads(s, SHAPES)):
+            p.grad = g
+        opt.step()
+    return [p.detach().clone() for p in ps] if rank == 0 else None
+
+
+def test_keller_jordan_muon_by_formula_and_across_ranks(tmp_path, monkeypatch):
+    """``MuonKellerJordan``: momentum, Nesterov look-ahead, five fixed-coefficient Newton-Schulz
+    steps, update scaled by ``sqrt(rows / cols)``; with several ranks the parameters are dealt
+    round-robin and one all-reduce shares the updates, which changes nothing in the result."""
+    from dion_b200 import MuonKellerJordan
+    from dion_b200.optim.muon_reference import zeropower_via_newtonschulz5
+    monkeypatch.setenv("WORLD_SIZE", "1")
+    monkeypatch.setenv("RANK", "0")
+    ps = [torch.nn.Parameter(w) for w in _weights(SHAPES)]
+    want = [w.clone() for w in _weights(SHAPES)]
+    bufs = [torch.zeros_like(w) for w in want]
+    opt = MuonKellerJordan(ps, lr=0.05, momentum=0.9)
+    for s in range(2):
+        for i, (p, g) in enumerate(zip(ps, _grads(s, SHAPES))):
+            p.grad = g
+            bufs[i].mul_(0.9).add_(g)
+            look = g + 0.9 * bufs[i]
+            u = zeropower_via_newtonschulz5(look, steps=5) * (g.size(0) / g.size(1)) ** 0.5
+            want[i] -= 0.05 * u.bfloat16().float()      # updates travel as bf16
+        opt.step()
+    for a, b in zip(want, ps):
+        assert torch.allclose(a, b.detach(), atol=1e-6)
+    single = [p.detach().clone() for p in ps]
+    # two ranks with default momentum against one process with the same settings
+    ps1 = [torch.nn.Parameter(w) for w in _weights(SHAPES)]
+    opt1 = MuonKellerJordan(ps1, lr=0.05)
+    for s in range(2):
+        for p, g in zip(ps1, _grads(s, SHAPES)):
+            p.grad = g
+        opt1.step()
+    out = run_ranks(_keller_jordan_worker, 2, "gloo", (), str(tmp_path))[0]
+    for a, b in zip(ps1, out):
+        assert torch.equal(a.detach(), b)
+    assert any(not torch.equal(a, b.detach()) for a, b in zip(single, ps1))   # momentum matters
