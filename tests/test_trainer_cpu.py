@@ -279,3 +279,21 @@ def test_hyperparameter_defaults_and_flags_match_the_reference_trainer(ref_dion)
     ref_flags = set(re.findall(r'"--([a-z_0-9]+)"', source))
     our_flags = set(re.findall(r'"--([a-z_0-9]+)"', open(trainer.__file__).read()))
     assert ref_flags <= our_flags, sorted(ref_flags - our_flags)
+
+
+def test_every_shipped_configuration_uses_known_flags():
+    """Each key of every file under ``configs/`` is a flag of the trainer (a misspelt key would
+    be ignored silently), and the files parse into usable hyper-parameters."""
+    import glob
+    import yaml
+    from dion_b200 import trainer
+    files = sorted(glob.glob(os.path.join(ROOT, "configs", "*.yaml")))
+    assert len(files) >= 4
+    for path in files:
+        flat = trainer.flatten_config(yaml.safe_load(open(path)))
+        args = trainer.parse_cli_args(["--config", path])
+        unknown = [k for k in flat if not hasattr(args, k)]
+        assert not unknown, (os.path.basename(path), unknown)
+        hp = trainer.override_args_from_cli(trainer.Hyperparameters(), args)
+        assert hp.optimizer in ("dion", "dion2", "muon", "normuon", "nordion2", "dion3")
+        assert hp.batch_size % hp.device_batch_size == 0 and hp.model_dim % hp.n_head == 0
