@@ -21,6 +21,7 @@
 // are bounded; the epilogue threads meet at a barrier that also ANDs their wait results, so a
 // timeout makes all of them leave together.
 #include "common.cuh"
+#include "tmap_cache.h"
 
 namespace dion {
 
@@ -548,11 +549,7 @@ static int make_map2(CUtensorMap* map, const void* ptr, int batch, int rows, int
   cuuint64_t strides[2] = {(cuuint64_t)ld * 2, (cuuint64_t)batch_stride * 2};
   if (batch == 1) strides[1] = (cuuint64_t)ld * 2 * (cuuint64_t)rows;
   cuuint32_t box[3] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows, 1};
-  cuuint32_t estr[3] = {1, 1, 1};
-  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides,
-                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? 0 : -2;
+  return encode_bf16_3d(enc, map, ptr, dims, strides, box);  // cached when opted in
 }
 
 template <bool A_MN, bool B_MN, int STAGES>

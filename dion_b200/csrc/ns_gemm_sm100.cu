@@ -17,6 +17,7 @@
 // warps 2-5 drain TMEM with tcgen05.ld, apply the epilogue and store.  While the
 // epilogue drains slot k the MMA warp already fills slot k^1.
 #include "common.cuh"
+#include "tmap_cache.h"
 
 namespace dion {
 
@@ -477,11 +478,7 @@ static int make_map_3d(CUtensorMap* map, const void* ptr, int batch, int rows, i
   cuuint64_t strides[2] = {(cuuint64_t)ld * 2, (cuuint64_t)batch_stride * 2};
   if (batch == 1) strides[1] = (cuuint64_t)ld * 2 * (cuuint64_t)rows;
   cuuint32_t box[3] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows, 1};
-  cuuint32_t estr[3] = {1, 1, 1};
-  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides,
-                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? 0 : -2;
+  return encode_bf16_3d(enc, map, ptr, dims, strides, box);  // cached when opted in
 }
 
 template <int BN, bool A_MN, bool B_MN>

@@ -53,7 +53,7 @@ def nvcc_path() -> Optional[str]:
 def _needs_build(src: Path, out: Path) -> bool:
     if not out.exists():
         return True
-    newest = max([src.stat().st_mtime] + [h.stat().st_mtime for h in CSRC.glob("*.cuh")])
+    newest = max([src.stat().st_mtime] + [h.stat().st_mtime for pat in ("*.cuh", "*.h") for h in CSRC.glob(pat)])
     return out.stat().st_mtime < newest
 
 

@@ -56,3 +56,29 @@ def test_pointer_tables_layout_and_cache():
     arr = tables.build_ptr_array([[a, b], [g, h]], tag="p")
     assert arr.tolist() == [[a.data_ptr(), b.data_ptr()], [g.data_ptr(), h.data_ptr()]]
     assert tables.build_ptr_array([[a, b], [g, h]], tag="p") is arr
+
+
+def test_tensor_map_cache_hits_only_on_identical_keys(tmp_path):
+    """The host-side cache of encoded tensor maps (csrc/tmap_cache.h, opt-in) checked with a
+    counting stand-in for the driver's encoder: off by default, and when on, a map is reused only
+    for the same address, extents, strides and box."""
+    import os
+    import shutil
+    import subprocess
+    import pytest
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cuda_inc = os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"), "include")
+    gxx = shutil.which("g++")
+    if gxx is None or not os.path.exists(os.path.join(cuda_inc, "cuda.h")):
+        pytest.skip("needs g++ and the CUDA headers")
+    exe = str(tmp_path / "tmap_cache_check")
+    subprocess.run([gxx, "-std=c++17", "-O1", "-I" + cuda_inc,
+                    "-I" + os.path.join(root, "dion_b200", "csrc"),
+                    os.path.join(root, "tests", "native", "tmap_cache_check.cpp"), "-o", exe,
+                    "-lpthread"], check=True, timeout=300)
+    env = {k: v for k, v in os.environ.items() if k != "DION_B200_TMAP_CACHE"}
+    off = subprocess.run([exe], env=env, capture_output=True, text=True, check=True).stdout.split()
+    on = subprocess.run([exe], env=dict(env, DION_B200_TMAP_CACHE="1"), capture_output=True,
+                        text=True, check=True).stdout.split()
+    assert off == ["3", "6", "0", "1", "1"]      # every call encodes
+    assert on == ["1", "3", "1", "1", "1"]       # repeats hit, other box / address miss
