@@ -297,3 +297,77 @@ def test_every_shipped_configuration_uses_known_flags():
         hp = trainer.override_args_from_cli(trainer.Hyperparameters(), args)
         assert hp.optimizer in ("dion", "dion2", "muon", "normuon", "nordion2", "dion3")
         assert hp.batch_size % hp.device_batch_size == 0 and hp.model_dim % hp.n_head == 0
+
+
+HEADLINE_CPU = dict(sequence_len=256, vocab_size=50304, n_layer=4, n_head=4, n_embd=256)
+
+
+def _muon_adamw(muon_cls, model, **kw):
+    return muon_cls(
+        [dict(params=list(model.transformer.h.parameters())),
+         dict(params=list(model.transformer.wte.parameters()) + list(model.lm_head.parameters()),
+              algorithm="adamw", lr=3e-3, betas=(0.9, 0.95))],
+        lr=0.02, mu=0.95, nesterov=True, weight_decay=0.01, use_polar_express=False, **kw)
+
+
+def _small_gpt_curve(gpt_cls, cfg_cls, muon_cls, steps=20):
+    """4 layers, d_model 256, 4 heads, vocabulary 50304, sequence 256, batch 8; fp32 weights from
+    seed 0, uniform-random tokens from seed 0; Muon (momentum 0.95, Nesterov, quintic
+    coefficients, lr 0.02, wd 0.01) + AdamW (lr 3e-3, betas 0.9 / 0.95) on embedding and head."""
+    torch.manual_seed(0)
+    model = gpt_cls(cfg_cls(**HEADLINE_CPU))
+    model.init_weights()
+    opt = _muon_adamw(muon_cls, model)
+    g = torch.Generator().manual_seed(0)
+    losses = []
+    for _ in range(steps):
+        x = torch.randint(0, 50304, (8, 256), generator=g)
+        y = torch.randint(0, 50304, (8, 256), generator=g)
+        loss = model(x, y)
+        loss.backward()
+        opt.step()
+        model.zero_grad(set_to_none=True)
+        losses.append(float(loss.detach()))
+    return losses
+
+
+def test_small_gpt_twenty_step_curve_matches_reference(ref_dion):
+    from models.gpt_model import GPT as RefGPT, GPTConfig as RefConfig
+    ours = _small_gpt_curve(GPT, GPTConfig, dion_b200.Muon)
+    ref = _small_gpt_curve(RefGPT, RefConfig, ref_dion.Muon)
+    assert len(ours) == 20 and ours[0] == pytest.approx(ref[0], abs=1e-5)
+    assert max(abs(a - b) for a, b in zip(ours, ref)) < 2e-3
+
+
+def _small_gpt_ddp_worker(rank, world, steps):
+    from torch.nn.parallel import DistributedDataParallel
+    import torch.distributed as dist
+    torch.manual_seed(0)
+    model = GPT(GPTConfig(**HEADLINE_CPU))
+    model.init_weights()
+    ddp = DistributedDataParallel(model)
+    opt = _muon_adamw(dion_b200.Muon, model, distributed_mesh=ddp.process_group)
+    g = torch.Generator().manual_seed(0)
+    per = 8 // world
+    losses = []
+    for _ in range(steps):
+        x = torch.randint(0, 50304, (8, 256), generator=g)
+        y = torch.randint(0, 50304, (8, 256), generator=g)
+        loss = ddp(x[rank * per:(rank + 1) * per], y[rank * per:(rank + 1) * per])
+        loss.backward()
+        opt.step()
+        model.zero_grad(set_to_none=True)
+        mean = loss.detach().clone()
+        dist.all_reduce(mean)
+        losses.append(float(mean) / world)
+    return losses if rank == 0 else None
+
+
+def test_small_gpt_curve_under_ddp_on_two_gloo_ranks(tmp_path):
+    """The same run as two data-parallel ranks (each half of every batch, Muon given the DDP
+    process group) follows the single-process curve."""
+    from tests.dist_utils import run_ranks
+    steps = 8
+    ddp = run_ranks(_small_gpt_ddp_worker, 2, "gloo", (steps,), str(tmp_path))[0]
+    single = _small_gpt_curve(GPT, GPTConfig, dion_b200.Muon, steps=steps)
+    assert max(abs(a - b) for a, b in zip(ddp, single)) < 2e-3
