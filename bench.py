@@ -12,6 +12,14 @@ batch from pinned host memory, runs forward/backward/optimizer through the publi
 the loss back to the host.  ``--impl reference`` runs the unmodified reference package from
 ``baseline/_ref`` (its GPT model, its Dion2 with its Triton kernels, torch DDP) on the same
 configuration and prints the same line with ``"impl": "reference"``.
+
+After the headline both arms time a second block, printed under the key ``aux`` of the same line:
+the optimizer step alone of GPT-1B (24 layers, d_model 2048) under Muon on the model's block
+matrices (96 x 2048^2, 24 x 8192x2048, 24 x 2048x8192) held the way FSDP2 holds them: fp32
+``Shard(0)`` DTensors over the N ranks (plain tensors for N = 1), with fixed random gradients.
+Ours runs it twice, with the all-to-all carried by the compute kernels over peer memory
+(``fused_ms``) and with NCCL ``all_to_all_single`` (``nccl_ms``); the reference runs its own
+``dion.Muon`` (Triton Newton-Schulz, NCCL all-to-all).  ``--no-aux`` skips the block.
 """
 from __future__ import annotations
 
@@ -29,6 +37,7 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 MODEL = dict(n_layer=12, n_embd=768, n_head=12, vocab_size=50304, sequence_len=1024)
 DEVICE_BATCH = 32
 SEQ = 1024
+PRIME_STEPS = 3   # untimed steps both arms take before the warm-up (compile / capture)
 LR, FRACTION, MU, WD = 0.02, 0.25, 0.95, 0.01
 
 
@@ -41,6 +50,10 @@ def parse() -> argparse.Namespace:
     p.add_argument("--optimizer", type=str, default="dion2",
                    choices=["dion2", "muon", "normuon", "nordion2", "dion"])
     p.add_argument("--no-e2e", action="store_true")
+    p.add_argument("--no-aux", action="store_true",
+                   help="skip the GPT-1B Muon optimizer-step block")
+    p.add_argument("--aux-steps", type=int, default=20)
+    p.add_argument("--aux-warmup", type=int, default=5)
     p.add_argument("--eager", action="store_true",
                    help="ours: launch every kernel from Python (torch DDP for N>1) instead of "
                         "replaying the whole step as one CUDA graph")
@@ -202,6 +215,153 @@ def emit(args, impl, ms, e2e_ms, clocks, launches, world, extra=None):
 
 
 # ------------------------------------------------------------------------------------------------
+# second block: GPT-1B Muon optimizer step on FSDP-style shards
+# ------------------------------------------------------------------------------------------------
+AUX_D, AUX_LAYERS = 2048, 24
+NVLINK_BYTES_PER_S = 770e9     # measured peer copy per direction per GPU on this kind of box
+
+
+def aux_shapes():
+    d, n = AUX_D, AUX_LAYERS
+    return [(d, d)] * (4 * n) + [(4 * d, d)] * n + [(d, 4 * d)] * n
+
+
+def measured_peak_tflops() -> float:
+    """Sustained cuBLAS bf16 rate of this pool's GPUs when a measurement file lies beside this
+    script, else a typical sustained figure for a B200 under its power cap."""
+    try:
+        return float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+                     ["bf16_tflops_sustained"])
+    except Exception:  # noqa: BLE001
+        return 1400.0
+
+
+def aux_bounds(world: int) -> dict:
+    """Work of one Muon step on ``aux_shapes()`` per rank: Newton-Schulz FLOPs by the reference's
+    cost model (5 x (4 m^2 n + 2 m^3), benchmark/benchmark_newton_shultz.py:40-45), the
+    multiply-adds actually needed when the two symmetric products are computed as half
+    (5 x (3 m^2 n + m^3)), and the bf16 bytes each rank sends (shards out, results back)."""
+    nominal = real = elems = 0.0
+    for r, c in aux_shapes():
+        m, n = min(r, c), max(r, c)
+        nominal += 5 * (4.0 * m * m * n + 2.0 * m ** 3)
+        real += 5 * (3.0 * m * m * n + 1.0 * m ** 3)
+        elems += r * c
+    sent = 2 * (elems * 2 / world) * (world - 1) / world if world > 1 else 0.0
+    peak = measured_peak_tflops() * 1e12
+    compute_ms = real / world / peak * 1e3
+    link_ms = sent / NVLINK_BYTES_PER_S * 1e3
+    return {"ns_tflop_nominal_per_gpu": nominal / world / 1e12,
+            "ns_tflop_needed_per_gpu": real / world / 1e12,
+            "nvlink_mb_sent_per_gpu": sent / 1e6,
+            "compute_bound_ms": compute_ms, "nvlink_bound_ms": link_ms,
+            "roofline_ms": max(compute_ms, link_ms), "peak_tflops_used": peak / 1e12}
+
+
+def aux_tensors(world: int, rank: int, device):
+    """Parameters and gradients of the block matrices: fp32 (as FSDP2 keeps sharded parameters
+    under its bf16 mixed-precision policy), gradient values representable in bf16, seed 0.
+    -> (params, grads, mesh)"""
+    import torch
+
+    gen = torch.Generator(device=device).manual_seed(0)
+
+    def make(shape, scale):
+        t = torch.randn(*shape, device=device, dtype=torch.float32, generator=gen) * scale
+        return t.bfloat16().float()
+
+    if world == 1:
+        params = [torch.nn.Parameter(make(s, 0.02)) for s in aux_shapes()]
+        grads = [make(s, 1.0) for s in aux_shapes()]
+        return params, grads, None
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.tensor import DTensor, Shard
+
+    mesh = init_device_mesh("cuda", (world,))
+
+    def shard(shape, scale):
+        return DTensor.from_local(make((shape[0] // world, shape[1]), scale), mesh, [Shard(0)],
+                                  run_check=False)
+
+    params = [torch.nn.Parameter(shard(s, 0.02)) for s in aux_shapes()]
+    grads = [shard(s, 1.0) for s in aux_shapes()]
+    return params, grads, mesh
+
+
+def aux_time(opt, params, grads, steps: int, warmup: int, world: int, device) -> float:
+    """ms per optimizer step, CUDA events, max over ranks."""
+    def step():
+        for p, g in zip(params, grads):
+            p.grad = g
+        opt.step()
+
+    ms, _ = time_loop(step, steps, warmup, world, device)
+    return ms / steps
+
+
+def run_aux_ours(args, rank: int, world: int, device) -> dict:
+    import torch
+
+    import dion_b200
+    from dion_b200.ops.gemm import check_status
+
+    out = {"what": "GPT-1B Muon optimizer step on the block matrices (96x2048^2, 24x8192x2048, "
+                   "24x2048x8192), fp32 Shard(0) over N ranks, nesterov, quintic Newton-Schulz",
+           "steps": args.aux_steps, "warmup": args.aux_warmup, "n_gpus": world}
+    out.update(aux_bounds(world))
+    params, grads, mesh = aux_tensors(world, rank, device)
+    variants = [("fused", "1"), ("nccl", "0")] if world > 1 else [("single", "1")]
+    old = os.environ.get("DION_B200_FUSED_EXCHANGE")
+    try:
+        for label, env in variants:
+            os.environ["DION_B200_FUSED_EXCHANGE"] = env
+            opt = dion_b200.Muon([dict(params=params)], distributed_mesh=mesh, lr=LR, mu=MU,
+                                 weight_decay=WD, nesterov=True, use_polar_express=False)
+            ms = aux_time(opt, params, grads, args.aux_steps, args.aux_warmup, world, device)
+            out[f"{label}_ms"] = ms
+            out[f"{label}_fraction_of_roofline"] = out["roofline_ms"] / ms
+            if label == "fused":
+                out["n_fused_exchanges"] = len(opt._fused_exchanges)
+            try:
+                check_status()
+                out[f"{label}_status"] = "ok"
+            except RuntimeError as exc:
+                out[f"{label}_status"] = str(exc)
+            del opt
+            torch.cuda.empty_cache()
+    finally:
+        if old is None:
+            os.environ.pop("DION_B200_FUSED_EXCHANGE", None)
+        else:
+            os.environ["DION_B200_FUSED_EXCHANGE"] = old
+    return out
+
+
+def run_aux_reference(args, ref_dion, rank: int, world: int, device) -> dict:
+    out = {"what": "GPT-1B Muon optimizer step, unmodified reference dion.Muon (Triton "
+                   "Newton-Schulz, NCCL all-to-all) on the same tensors",
+           "steps": args.aux_steps, "warmup": args.aux_warmup, "n_gpus": world}
+    out.update(aux_bounds(world))
+    params, grads, mesh = aux_tensors(world, rank, device)
+    # Arguments as the reference trainer builds them (train.py:421-446).
+    opt = ref_dion.Muon([dict(params=params)], distributed_mesh=mesh, lr=LR, mu=MU,
+                        weight_decay=WD, nesterov=True, adjust_lr="spectral_norm",
+                        use_triton=True, use_polar_express=False)
+    ms = aux_time(opt, params, grads, args.aux_steps, args.aux_warmup, world, device)
+    out["reference_ms"] = ms
+    out["reference_fraction_of_roofline"] = out["roofline_ms"] / ms
+    return out
+
+
+def guarded_aux(fn, *a) -> dict:
+    """The second block must never cost the headline: report its failure instead."""
+    try:
+        return fn(*a)
+    except Exception as exc:  # noqa: BLE001
+        return {"error": f"{type(exc).__name__}: {str(exc)[:300]}"}
+
+
+# ------------------------------------------------------------------------------------------------
 # our arm
 # ------------------------------------------------------------------------------------------------
 def run_ours(args) -> None:
@@ -219,7 +379,8 @@ def run_ours(args) -> None:
     torch.manual_seed(0)
     model = GPT(GPTConfig(**MODEL)).to(device)
     model.init_weights()
-    graphed = not args.eager
+    # Legacy Dion hands its learning rate to the kernels as a host number: no graph replay.
+    graphed = not args.eager and args.optimizer != "dion"
     if graphed:
         # Same seed on every rank, so the replicas start identical; gradients are averaged by
         # the step object's own bucketed all-reduce.
@@ -231,9 +392,9 @@ def run_ours(args) -> None:
 
     groups = [dict(params=list(model.transformer.h.parameters())),
               dict(params=list(model.transformer.wte.parameters()), algorithm="adamw", lr=LR,
-                   weight_decay=0),
+                   betas=(0.95, 0.98), weight_decay=0),
               dict(params=list(model.lm_head.parameters()), algorithm="adamw", lr=LR,
-                   weight_decay=0)]
+                   betas=(0.95, 0.98), weight_decay=0)]
     name = args.optimizer
     if name == "dion2":
         opt = dion_b200.Dion2(groups, distributed_mesh=pg, lr=LR, fraction=FRACTION, ef_decay=MU,
@@ -262,13 +423,15 @@ def run_ours(args) -> None:
         gstep = GraphedTrainStep(lambda x, y: model(x, y), list(model.parameters()), opt,
                                  [dev_batches[0][0], dev_batches[0][1]], device=device,
                                  process_group=pg, warmup=2)
-        # Prime: two eager steps, then the capture; count the kernels one replay launches.
+        # Prime (PRIME_STEPS calls): two eager steps, then the capture; count the kernels one
+        # replay launches.
         for i in range(2):
             gstep(dev_batches[i][0], dev_batches[i][1])
         _backend.reset_launch_count()
         gstep(dev_batches[2][0], dev_batches[2][1])
         launches_per_step = _backend.launch_count()
         torch.cuda.synchronize()
+        state["i"] = PRIME_STEPS
 
         def step_device():
             xy = dev_batches[state["i"] % len(dev_batches)]
@@ -292,6 +455,9 @@ def run_ours(args) -> None:
             call.zero_grad(set_to_none=True)
             state["loss"] = loss.detach()
 
+        for _ in range(PRIME_STEPS):
+            step_device()
+
         def step_e2e():
             xy = host[state["i"] % len(host)].to(device, non_blocking=True)
             state["i"] += 1
@@ -310,17 +476,23 @@ def run_ours(args) -> None:
     from dion_b200.ops.gemm import check_status
 
     check_status()
+    # Loss of the last device-timed step: the same step index, on the same batches, in both arms.
+    loss_after = float(state["loss"].item())
     e2e_ms = None
     if not args.no_e2e:
         e2e_ms, _ = time_loop(step_e2e, args.steps, 2, world, device, None)
+    if graphed:
+        gstep.release()
+    torch.cuda.empty_cache()
+    aux = None if args.no_aux else guarded_aux(run_aux_ours, args, rank, world, device)
     if rank == 0:
         emit(args, "ours", ms, e2e_ms, clocks, launches, world,
-             {"final_loss": float(state["loss"].item()),
+             {"final_loss": loss_after,
+              "final_loss_after_steps": PRIME_STEPS + args.warmup + args.steps,
+              "aux": aux,
               "launch_mode": "one CUDA graph per step (forward, backward, gradient all-reduce, "
                              "optimizer); gpu_launches counts the kernels of this package "
                              "recorded in the graph x steps" if graphed else "eager"})
-    if graphed:
-        gstep.release()
     if world > 1:
         dist.destroy_process_group()
 
@@ -422,7 +594,8 @@ def run_reference(args) -> None:
         state["loss_host"] = loss.item()
 
     try:
-        step_device()  # first call compiles / autotunes; failures here fall back to eager
+        for _ in range(PRIME_STEPS):
+            step_device()  # the first call compiles / autotunes
     except Exception as exc:  # noqa: BLE001
         if rank == 0:
             print(json.dumps({"impl": "reference",
@@ -433,12 +606,18 @@ def run_reference(args) -> None:
         return
     sampler = ClockSampler(local_rank) if rank == 0 else None
     ms, clocks = time_loop(step_device, args.steps, args.warmup, world, device, sampler)
+    loss_after = float(state["loss"].item())
     e2e_ms = None
     if not args.no_e2e:
         e2e_ms, _ = time_loop(step_e2e, args.steps, 2, world, device, None)
+    torch.cuda.empty_cache()
+    aux = None if args.no_aux else guarded_aux(run_aux_reference, args, ref_dion, rank, world,
+                                               device)
     if rank == 0:
         emit(args, "reference", ms, e2e_ms, clocks, 0, world,
-             {"final_loss": float(state["loss"].item()), "model_compiled": compiled})
+             {"final_loss": loss_after,
+              "final_loss_after_steps": PRIME_STEPS + args.warmup + args.steps,
+              "aux": aux, "model_compiled": compiled})
     if world > 1:
         dist.destroy_process_group()
 

@@ -25,17 +25,6 @@ __device__ __forceinline__ void st_release_sys_i32(int* p, int v) {
   asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
-constexpr unsigned kMaxFlagPolls = 1u << 22;
-
-// status[0] = error code, [1] = index of the flag (source rank) that did not arrive,
-// [2] = sequence number waited for, [3] = value found.  The first reporter wins.
-__device__ __forceinline__ void report_peer_timeout(int* status, int who, int want, int found) {
-  if (atomicCAS(status, 0, kStatusTimeoutPeer) == 0) {
-    status[1] = who;
-    status[2] = want;
-    status[3] = found;
-  }
-}
 
 __global__ void bump_seq_kernel(int* seq) {
   if (threadIdx.x == 0 && blockIdx.x == 0) *seq += 1;
@@ -54,10 +43,7 @@ __global__ void wait_flags_kernel(const int* flags, int n, const int* seq, int d
   const int i = threadIdx.x;
   if (i >= n) return;
   const int want = *seq + delta;
-  for (unsigned k = 0; k < kMaxFlagPolls; ++k) {
-    if (ld_acquire_sys_i32(flags + i) >= want) return;
-    __nanosleep(64);
-  }
+  if (flag_wait_bounded(flags + i, want)) return;
   report_peer_timeout(status, i, want, ld_acquire_sys_i32(flags + i));
 }
 
@@ -158,11 +144,7 @@ allreduce_fused_kernel(const AllReduceArgs a) {
     st_release_sys_i32(reinterpret_cast<int*>(a.peer_in[threadIdx.x]) + a.rank, seq);
   }
   if (threadIdx.x < a.world) {
-    bool got = false;
-    for (unsigned k = 0; k < kMaxFlagPolls; ++k) {
-      if (ld_acquire_sys_i32(a.flags_in + threadIdx.x) >= seq) { got = true; break; }
-      __nanosleep(32);
-    }
+    const bool got = flag_wait_bounded(a.flags_in + threadIdx.x, seq);
     if (!got) {
       report_peer_timeout(a.status, threadIdx.x, seq, ld_acquire_sys_i32(a.flags_in + threadIdx.x));
       s_ok = 0;
@@ -237,11 +219,7 @@ allreduce_fused_kernel(const AllReduceArgs a) {
   __threadfence_system();
   if (threadIdx.x < a.world) {
     st_release_sys_i32(reinterpret_cast<int*>(a.peer_out[threadIdx.x]) + a.rank, seq);
-    bool got = false;
-    for (unsigned k = 0; k < kMaxFlagPolls; ++k) {
-      if (ld_acquire_sys_i32(a.flags_out + threadIdx.x) >= seq) { got = true; break; }
-      __nanosleep(32);
-    }
+    const bool got = flag_wait_bounded(a.flags_out + threadIdx.x, seq);
     if (!got)
       report_peer_timeout(a.status, threadIdx.x, seq,
                           ld_acquire_sys_i32(a.flags_out + threadIdx.x));

@@ -59,16 +59,78 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Poll limit for on-chip barriers. try_wait suspends for a hardware-chosen
-// interval per poll, so this is on the order of a second.
-constexpr uint32_t kMaxPolls = 1u << 24;
+// ---- bounded waits ------------------------------------------------------------------------
+// Every spin in this library gives up after a time budget measured on the GPU's nanosecond
+// timer (the same for on-chip barriers and for flags written by other GPUs), records a code in
+// the status word and lets the caller unwind.  The budget is a per-library device variable that
+// the host may change with dion_set_wait_budget_ns() on the device that is current; the Python
+// loader does so when DION_B200_WAIT_BUDGET_MS is set.
+__device__ unsigned long long g_wait_budget_ns = 2000000000ull;  // 2 s
 
-// Waits for the barrier phase; returns false after kMaxPolls unsuccessful polls.
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
-  for (uint32_t i = 0; i < kMaxPolls; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+// Polls that run before the clock is consulted at all (the common case ends well inside them).
+constexpr uint32_t kFreePolls = 2048;
+// The timer is read once per this many further polls.
+constexpr uint32_t kPollsPerClockRead = 64;
+
+struct WaitBudget {
+  unsigned long long t0 = 0;
+  uint32_t polls = 0;
+  // Call after every unsuccessful poll; true once the budget is spent.
+  __device__ __forceinline__ bool spent() {
+    ++polls;
+    if (polls < kFreePolls) return false;
+    if (polls == kFreePolls) {
+      t0 = global_timer_ns();
+      return false;
+    }
+    if ((polls & (kPollsPerClockRead - 1)) != 0) return false;
+    return global_timer_ns() - t0 > g_wait_budget_ns;
   }
-  return false;
+};
+
+// Waits for the barrier phase; returns false once the time budget is spent.
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
+  WaitBudget budget;
+  for (;;) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (budget.spent()) return false;
+  }
+}
+
+// status[0] = error code, [1] = index of the flag (source rank) that did not arrive,
+// [2] = sequence number waited for, [3] = value found.  The first reporter wins.
+__device__ __forceinline__ void report_peer_timeout(int* status, int who, int want, int found) {
+  if (status != nullptr && atomicCAS(status, 0, kStatusTimeoutPeer) == 0) {
+    status[1] = who;
+    status[2] = want;
+    status[3] = found;
+  }
+}
+
+// True when a kernel has already recorded an error in the status word.
+__device__ __forceinline__ bool status_is_set(const int* status) {
+  if (status == nullptr) return false;
+  int v;
+  asm volatile("ld.volatile.global.s32 %0, [%1];" : "=r"(v) : "l"(status) : "memory");
+  return v != 0;
+}
+
+// Waits until *flag >= want (flag written by another GPU, or by the host); false on timeout.
+__device__ __forceinline__ bool flag_wait_bounded(const int* flag, int want) {
+  WaitBudget budget;
+  for (;;) {
+    int v;
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+    if (v >= want) return true;
+    if (budget.spent()) return false;
+    __nanosleep(64);
+  }
 }
 
 __device__ __forceinline__ void fence_barrier_init() {
@@ -188,3 +250,8 @@ __device__ __forceinline__ float2 unpack_bf16x2(uint32_t u) {
 }
 
 }  // namespace dion
+
+// One definition per library (each .cu includes this header once).
+DION_EXPORT int dion_set_wait_budget_ns(unsigned long long ns) {
+  return cudaMemcpyToSymbol(dion::g_wait_budget_ns, &ns, sizeof(ns)) == cudaSuccess ? 0 : -1;
+}

@@ -259,14 +259,7 @@ struct ApplyArgs {
 __device__ __forceinline__ bool wait_flag_block(const int* flag, int want) {
   __shared__ int ok;
   if (threadIdx.x == 0) {
-    int good = 0;
-    for (unsigned k = 0; k < (1u << 22); ++k) {
-      int v;
-      asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
-      if (v >= want) { good = 1; break; }
-      __nanosleep(64);
-    }
-    ok = good;
+    ok = flag_wait_bounded(flag, want) ? 1 : 0;
   }
   __syncthreads();
   return ok != 0;
@@ -276,9 +269,13 @@ __global__ void __launch_bounds__(kThreads)
 muon_post_kernel(const long long* raw, const ApplyArgs a) {
   Table tb{raw};
   if (a.wait_flags) {
+    // An earlier kernel of this step (or this kernel's wait below) gave up on a peer: the update
+    // buffer may be incomplete, so the weights are left exactly as they are.
+    if (status_is_set(a.status)) return;
     const int t0 = find_tensor(tb, blockIdx.x);
-    if (!wait_flag_block(a.wait_flags + t0 / a.per_rank, *a.seq_ptr)) {
-      if (threadIdx.x == 0) atomicExch(a.status, kStatusTimeoutPeer);
+    const int src = t0 / a.per_rank;
+    if (!wait_flag_block(a.wait_flags + src, *a.seq_ptr)) {
+      if (threadIdx.x == 0) report_peer_timeout(a.status, src, *a.seq_ptr, a.wait_flags[src]);
       return;
     }
   }
@@ -513,11 +510,25 @@ struct Dion2PostArgs {
   int select_rows;
   const float* normU2;    // optional NorDion2 rescale (per tensor)
   const float* normNew2;
+  // As in ApplyArgs: U of tensor t was stored here by rank t / per_rank (optional).
+  const int* wait_flags;
+  const int* seq_ptr;
+  int per_rank;
+  int* status;
 };
 
 __global__ void __launch_bounds__(kThreads)
 dion2_post_kernel(const long long* raw, const Dion2PostArgs a) {
   Table tb{raw};
+  if (a.wait_flags) {
+    if (status_is_set(a.status)) return;  // see muon_post_kernel
+    const int t0 = find_tensor(tb, blockIdx.x);
+    const int src = t0 / a.per_rank;
+    if (!wait_flag_block(a.wait_flags + src, *a.seq_ptr)) {
+      if (threadIdx.x == 0) report_peer_timeout(a.status, src, *a.seq_ptr, a.wait_flags[src]);
+      return;
+    }
+  }
   void* X; const __nv_bfloat16* U; const int* map; const float* rs;
   int tt;
   {
@@ -594,6 +605,93 @@ dion2_post_kernel(const long long* raw, const Dion2PostArgs a) {
 }
 
 // ---------------------------------------------------------------------------------------------
+// Dion2 with global selection scope: the update U comes back full-size and exactly zero off the
+// selected slices (orthonormal slices have unit norm, so "selected" == "has a non-zero").
+//   pass 1  flags[t][slice] = 1 for every slice of U_t that holds a non-zero
+//   pass 2  X = (1 - lr*wd)*X - lr*ratio*U ;  M[selected slices] *= ef_decay
+// Table pointers: 0=X, 1=M, 2=U(bf16).  Replaces the per-parameter compiled function
+// dion/dion2.py:621-659 of the reference with two launches for all parameters.
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kThreads)
+slice_flags_kernel(const long long* raw, int cols, int select_rows, int num_select, int* flags) {
+  Table tb{raw};
+  const __nv_bfloat16* U;
+  {
+    const int t0 = find_tensor(tb, blockIdx.x);
+    U = reinterpret_cast<const __nv_bfloat16*>(tb.ptr(2, t0));
+  }
+  const bool vu = aligned4(U, DT_BF16);
+  DION_CHUNK_LOOP(tb, {
+    float u[4];
+    if (full) ld4(U, DT_BF16, i, vu, u);
+    else for (int k = 0; k < 4; ++k) u[k] = (i + k < end) ? ld(U, DT_BF16, i + k) : 0.f;
+    int* f = flags + (long long)t * num_select;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      if (u[k] != 0.f) {   // every writer stores the same value: the race is benign
+        const long long e = i + k;
+        const int r = (int)(e / cols);
+        f[select_rows ? r : (int)(e - (long long)r * cols)] = 1;
+      }
+    }
+  })
+}
+
+struct MaskedPostArgs {
+  const float* lr;
+  const float* wd_ptr;
+  float wd, ratio, ef_decay;
+  int x_dt, m_dt, cols, select_rows, num_select;
+  const int* flags;
+};
+
+__global__ void __launch_bounds__(kThreads)
+dion2_post_masked_kernel(const long long* raw, const MaskedPostArgs a) {
+  Table tb{raw};
+  void* X; void* M; const __nv_bfloat16* U;
+  {
+    const int t0 = find_tensor(tb, blockIdx.x);
+    X = tb.ptr(0, t0); M = tb.ptr(1, t0);
+    U = reinterpret_cast<const __nv_bfloat16*>(tb.ptr(2, t0));
+  }
+  const float lr = *a.lr;
+  const float wd = a.wd_ptr ? *a.wd_ptr : a.wd;
+  const float ca = 1.f - lr * wd, cb = lr * a.ratio;
+  const bool vx = aligned4(X, a.x_dt), vm = aligned4(M, a.m_dt), vu = aligned4(U, DT_BF16);
+  DION_CHUNK_LOOP(tb, {
+    const int* f = a.flags + (long long)t * a.num_select;
+    float x[4], m[4], u[4];
+    if (full) {
+      ld4(X, a.x_dt, i, vx, x); ld4(M, a.m_dt, i, vm, m); ld4(U, DT_BF16, i, vu, u);
+    } else {
+      for (int k = 0; k < 4; ++k) {
+        const bool in = i + k < end;
+        x[k] = in ? ld(X, a.x_dt, i + k) : 0.f;
+        m[k] = in ? ld(M, a.m_dt, i + k) : 0.f;
+        u[k] = in ? ld(U, DT_BF16, i + k) : 0.f;
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const long long e = i + k;
+      if (e < end) {
+        const int r = (int)(e / a.cols);
+        const int slice = a.select_rows ? r : (int)(e - (long long)r * a.cols);
+        if (f[slice]) m[k] *= a.ef_decay;
+      }
+      x[k] = ca * x[k] - cb * u[k];
+    }
+    if (full) {
+      st4(X, a.x_dt, i, vx, x); st4(M, a.m_dt, i, vm, m);
+    } else {
+      for (int k = 0; k < 4 && i + k < end; ++k) {
+        st(X, a.x_dt, i + k, x[k]); st(M, a.m_dt, i + k, m[k]);
+      }
+    }
+  })
+}
+
+// ---------------------------------------------------------------------------------------------
 // NorMuon row statistics over a stacked bf16 update U[n_mats][rows][cols]:
 //   rowms = mean(u^2); V = lerp(V, rowms, 1-beta2); rinv[r] = 1/(sqrt(V)+1e-8);
 //   normU2[t] += sum(u^2); normNew2[t] += sum(u^2)*rinv^2.
@@ -611,7 +709,10 @@ __device__ __forceinline__ float sumsq8(const uint4 q) {
 
 __global__ void __launch_bounds__(kThreads)
 normuon_rowstats_kernel(const long long* raw, const __nv_bfloat16* U, int rows, int cols, int v_dt,
-                        float beta2, float* rinv, float* normU2, float* normNew2, int n_mats) {
+                        float beta2, float* rinv, float* normU2, float* normNew2, int n_mats,
+                        const int* guard_status) {
+  // U came from other GPUs and a wait on them gave up: keep the second-moment state as it is.
+  if (status_is_set(guard_status)) return;
   constexpr int kWarps = kThreads / 32;
   __shared__ int s_t[kWarps];
   __shared__ float s_u2[kWarps], s_n2[kWarps];
@@ -765,23 +866,43 @@ DION_EXPORT int dion_lion(const void* table, long long n_chunks, const float* lr
 DION_EXPORT int dion_dion2_post(const void* table, long long n_chunks, const float* lr,
                                 const float* wd_ptr, float wd, float ratio, int x_dt, int cols,
                                 int k, int select_rows, const float* normU2, const float* normNew2,
-                                void* stream) {
+                                const int* wait_flags, const int* seq_ptr, int per_rank,
+                                int* status, void* stream) {
   if (n_chunks <= 0) return 0;
-  Dion2PostArgs a{lr, wd_ptr, wd, ratio, x_dt, cols, k, select_rows, normU2, normNew2};
+  Dion2PostArgs a{lr, wd_ptr, wd, ratio, x_dt, cols, k, select_rows, normU2, normNew2,
+                  wait_flags, seq_ptr, per_rank > 0 ? per_rank : 1, status};
   dion2_post_kernel<<<(unsigned)n_chunks, kThreads, 0, S(stream)>>>(
+      static_cast<const long long*>(table), a);
+  return rc();
+}
+
+// `flags` is an int32 array [n_tensors, num_select] that this call zeroes and fills.
+DION_EXPORT int dion_dion2_post_masked(const void* table, long long n_chunks, int n_tensors,
+                                       const float* lr, const float* wd_ptr, float wd, float ratio,
+                                       float ef_decay, int x_dt, int m_dt, int cols,
+                                       int select_rows, int num_select, int* flags, void* stream) {
+  if (n_chunks <= 0) return 0;
+  if (cudaMemsetAsync(flags, 0, sizeof(int) * (size_t)n_tensors * num_select, S(stream)) !=
+      cudaSuccess)
+    return -1;
+  slice_flags_kernel<<<(unsigned)n_chunks, kThreads, 0, S(stream)>>>(
+      static_cast<const long long*>(table), cols, select_rows, num_select, flags);
+  MaskedPostArgs a{lr, wd_ptr, wd, ratio, ef_decay, x_dt, m_dt, cols, select_rows, num_select,
+                   flags};
+  dion2_post_masked_kernel<<<(unsigned)n_chunks, kThreads, 0, S(stream)>>>(
       static_cast<const long long*>(table), a);
   return rc();
 }
 
 DION_EXPORT int dion_normuon_rowstats(const void* table, const void* U, int n_mats, int rows,
                                       int cols, int v_dt, float beta2, float* rinv, float* normU2,
-                                      float* normNew2, void* stream) {
+                                      float* normNew2, const int* guard_status, void* stream) {
   const long long total_rows = (long long)n_mats * rows;
   if (total_rows <= 0) return 0;
   const int wpb = kThreads / 32;
   normuon_rowstats_kernel<<<(unsigned)((total_rows + wpb - 1) / wpb), kThreads, 0, S(stream)>>>(
       static_cast<const long long*>(table), static_cast<const __nv_bfloat16*>(U), rows, cols, v_dt,
-      beta2, rinv, normU2, normNew2, n_mats);
+      beta2, rinv, normU2, normNew2, n_mats, guard_status);
   return rc();
 }
 

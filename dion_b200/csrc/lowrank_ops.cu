@@ -241,6 +241,115 @@ cholesky_upper_kernel(const float* __restrict__ G, float* U, int r) {
   }
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// Inverse of upper-triangular matrices (fp32), one CTA per matrix, r <= 1024.
+//
+// The randomized Cholesky-QR needs P R^-1 twice per step.  With R^-1 in hand that product is an
+// ordinary tall GEMM for the tensor cores (lowrank_gemm_sm100.cu) instead of a triangular solve,
+// which the reference leaves to cuBLAS trsm (dion/dion.py:1290-1300).
+//
+// The matrix is cut into 32 x 32 blocks (padded with the identity), warp I owns block row I.
+// First every warp inverts its diagonal block (lane l solves for column l by back substitution,
+// the column in registers) and keeps it in shared memory.  Then the block super-diagonals are
+// filled one after the other: X[I,J] = -inv(U[I,I]) * sum_{K=I+1..J} U[I,K] X[K,J], where every
+// X[K,J] on the right lies on an earlier super-diagonal of block column J.  Blocks of one
+// super-diagonal are independent (one per warp); a block barrier separates the super-diagonals.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ float triu_elem(const float* __restrict__ U, int r, int i, int k) {
+  if (i < r && k < r) return __ldg(U + (size_t)i * r + k);
+  return i == k ? 1.f : 0.f;
+}
+
+template <int kMaxThreads>
+__global__ void __launch_bounds__(kMaxThreads)
+triu_inverse_kernel(const float* __restrict__ Uall, float* Xall, int r) {
+  extern __shared__ float ti_smem[];            // [NB][32][32] inverses of the diagonal blocks
+  const int NB = blockDim.x >> 5;
+  const int I = threadIdx.x >> 5, l = threadIdx.x & 31;
+  const float* U = Uall + (size_t)blockIdx.x * r * r;
+  float* X = Xall + (size_t)blockIdx.x * r * r;
+  float* Ys = ti_smem + (size_t)I * 1024;
+  const bool fast = (r & 3) == 0 && (reinterpret_cast<uintptr_t>(U) & 15) == 0;
+  const int i0 = I * 32;
+
+  // ---- diagonal block: lane l solves U[I,I] y = e_l ----
+  {
+    // Stage the block so that row reads below are shared-memory broadcasts.
+    for (int i = 0; i < 32; ++i) Ys[i * 32 + l] = triu_elem(U, r, i0 + i, i0 + l);
+    __syncwarp();
+    float y[32];
+#pragma unroll
+    for (int i = 31; i >= 0; --i) {
+      float s = (i == l) ? 1.f : 0.f;
+#pragma unroll
+      for (int k = i + 1; k < 32; ++k) s -= Ys[i * 32 + k] * y[k];
+      y[i] = s / Ys[i * 32 + i];
+    }
+    __syncwarp();
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      Ys[i * 32 + l] = y[i];
+      if (i0 + i < r && i0 + l < r) X[(size_t)(i0 + i) * r + i0 + l] = y[i];
+    }
+    // Blocks below the diagonal are zero.
+    for (int J = 0; J < I; ++J)
+      for (int i = 0; i < 32; ++i)
+        if (i0 + i < r) X[(size_t)(i0 + i) * r + J * 32 + l] = 0.f;
+  }
+
+  for (int d = 1; d < NB; ++d) {
+    __syncthreads();   // the previous super-diagonal (and the diagonal blocks) are in memory
+    if (I >= NB - d) continue;
+    const int J = I + d, j0 = J * 32;
+    float acc[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) acc[i] = 0.f;
+    for (int K = I + 1; K <= J; ++K) {
+      const int k0 = K * 32;
+      float xk[32];
+#pragma unroll
+      for (int k = 0; k < 32; ++k)
+        xk[k] = (k0 + k < r && j0 + l < r) ? X[(size_t)(k0 + k) * r + j0 + l] : 0.f;
+      if (fast && k0 + 32 <= r && i0 + 32 <= r) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const float4* urow = reinterpret_cast<const float4*>(U + (size_t)(i0 + i) * r + k0);
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            const float4 u = __ldg(urow + q);
+            acc[i] += u.x * xk[q * 4] + u.y * xk[q * 4 + 1] + u.z * xk[q * 4 + 2] +
+                      u.w * xk[q * 4 + 3];
+          }
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+#pragma unroll 4
+          for (int k = 0; k < 32; ++k) {
+            const float u = (i0 + i < r && k0 + k < r) ? __ldg(U + (size_t)(i0 + i) * r + k0 + k)
+                                                       : 0.f;
+            acc[i] += u * xk[k];
+          }
+        }
+      }
+    }
+    // X[I,J] = -inv(U[I,I]) * acc
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      float s = 0.f;
+      const float4* yrow = reinterpret_cast<const float4*>(Ys + i * 32);
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        const float4 yv = yrow[q];
+        s += yv.x * acc[q * 4] + yv.y * acc[q * 4 + 1] + yv.z * acc[q * 4 + 2] +
+             yv.w * acc[q * 4 + 3];
+      }
+      if (i0 + i < r && j0 + l < r) X[(size_t)(i0 + i) * r + j0 + l] = -s;
+    }
+  }
+}
+
 }  // namespace dion
 
 using namespace dion;
@@ -294,4 +403,29 @@ DION_EXPORT int dion_cholesky_upper(const void* G, void* U, int n, int r, void* 
   if (r <= 512) return launch_chol<16>(g, u, n, r, S(stream));
   if (r <= 768) return launch_chol<24>(g, u, n, r, S(stream));
   return launch_chol<32>(g, u, n, r, S(stream));
+}
+
+// X[b] = U[b]^-1 for a batch of upper-triangular r x r fp32 matrices (r <= 1024); the strictly
+// lower triangle of X is written as zero.  X must not alias U.
+DION_EXPORT int dion_triu_inverse(const void* U, void* X, int n, int r, void* stream) {
+  if (n <= 0 || r <= 0) return 0;
+  if (r > 1024 || U == X) return -2;
+  const int nb = (r + 31) / 32;
+  const int smem = nb * 4096;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(dion::triu_inverse_kernel<512>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, 16 * 4096) != cudaSuccess ||
+        cudaFuncSetAttribute(dion::triu_inverse_kernel<1024>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, 32 * 4096) != cudaSuccess)
+      return -3;
+    configured = true;
+  }
+  const float* u = static_cast<const float*>(U);
+  float* x = static_cast<float*>(X);
+  if (nb <= 16)   // up to 512 threads: twice the registers per thread
+    dion::triu_inverse_kernel<512><<<n, nb * 32, smem, S(stream)>>>(u, x, r);
+  else
+    dion::triu_inverse_kernel<1024><<<n, nb * 32, smem, S(stream)>>>(u, x, r);
+  return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }

@@ -138,7 +138,8 @@ __device__ __forceinline__ void tc_mma_bf16_pair(uint32_t d_tmem, uint64_t a_des
 
 // Bounded wait with cluster-scope acquire (the arrivals come from both CTAs of the pair).
 __device__ __forceinline__ bool mbar_wait_bounded_cluster(uint64_t* bar, uint32_t parity) {
-  for (uint32_t i = 0; i < kMaxPolls; ++i) {
+  WaitBudget budget;
+  for (;;) {
     uint32_t ok;
     asm volatile(
         "{\n"
@@ -150,8 +151,8 @@ __device__ __forceinline__ bool mbar_wait_bounded_cluster(uint64_t* bar, uint32_
         : "r"(smem_u32(bar)), "r"(parity)
         : "memory");
     if (ok) return true;
+    if (budget.spent()) return false;
   }
-  return false;
 }
 
 // TMA store of one box from shared memory (bulk-group completion).

@@ -72,15 +72,9 @@ __device__ __forceinline__ float ld_volatile_f32(const float* p) {
   asm volatile("ld.volatile.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
   return v;
 }
-constexpr uint32_t kMaxFlagPolls = 1u << 22;  // ~ a second or two of polling a local flag
-
-// Waits until flag >= seq; false after kMaxFlagPolls polls.
+// Waits until flag >= seq; false once the wait budget is spent.
 __device__ __forceinline__ bool wait_flag_bounded(const int* flag, int seq) {
-  for (uint32_t i = 0; i < kMaxFlagPolls; ++i) {
-    if (ld_acquire_sys(flag) >= seq) return true;
-    __nanosleep(64);
-  }
-  return false;
+  return flag_wait_bounded(flag, seq);
 }
 
 template <int BN>
@@ -166,7 +160,7 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             for (int src = r0 / p.rows_per_src; src <= r1 / p.rows_per_src && src < p.n_src; ++src) {
               if (ready_mask & (1u << src)) continue;
               if (!wait_flag_bounded(p.wait_flags + src, seq)) {
-                atomicExch(p.status, kStatusTimeoutPeer);
+                report_peer_timeout(p.status, src, seq, ld_acquire_sys(p.wait_flags + src));
                 abort_flag = 1;
                 ok = false;
                 break;
@@ -196,7 +190,7 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                  ++src) {
               if (ready_mask & (1u << src)) continue;
               if (!wait_flag_bounded(p.wait_flags + src, seq)) {
-                atomicExch(p.status, kStatusTimeoutPeer);
+                report_peer_timeout(p.status, src, seq, ld_acquire_sys(p.wait_flags + src));
                 abort_flag = 1;
                 ok = false;
                 break;
@@ -296,9 +290,11 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           bool fine = true;
           if (lane == 0) {
             const int seq = *p.seq_ptr;
-            for (int src = 0; src < p.n_src && fine; ++src)
+            int src = 0;
+            for (; src < p.n_src && fine; ++src)
               fine = wait_flag_bounded(p.wait_flags + src, seq);
-            if (!fine) atomicExch(p.status, kStatusTimeoutPeer);
+            if (!fine)
+              report_peer_timeout(p.status, src - 1, seq, ld_acquire_sys(p.wait_flags + src - 1));
           }
           fine = __shfl_sync(0xffffffffu, fine ? 1 : 0, 0) != 0;
           if (!fine) break;

@@ -11,6 +11,7 @@ a GPU run never silently falls back to eager PyTorch.
 from __future__ import annotations
 
 import ctypes
+import fcntl
 import os
 import shutil
 import subprocess
@@ -38,6 +39,7 @@ SOURCES = {
     "model_ops": "libdion_model.so",
     "comm_ops": "libdion_comm.so",
     "lowrank_ops": "libdion_lowrank.so",
+    "lowrank_gemm_sm100": "libdion_lowrank_gemm.so",
     "no_alloc": "libdion_noalloc.so",
 }
 
@@ -58,6 +60,11 @@ def _needs_build(src: Path, out: Path) -> bool:
 
 
 def _compile(stem: str, force: bool, verbose: bool) -> Optional[str]:
+    """Compile one library.  Several processes may get here at once (every rank of a multi-GPU
+    launch sees a missing or stale library on the first run after a checkout or a header edit),
+    so the build happens under an exclusive file lock, the need to build is re-checked once the
+    lock is held, and the result is written beside its final place and renamed into it: nobody
+    can load a half-written library."""
     src = CSRC / f"{stem}.cu"
     if not src.exists():
         return None
@@ -67,11 +74,23 @@ def _compile(stem: str, force: bool, verbose: bool) -> Optional[str]:
     nvcc = nvcc_path()
     if nvcc is None:
         raise RuntimeError("nvcc not found; cannot build dion_b200 kernels")
-    cmd = [nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-o", str(out), str(src)]
-    res = subprocess.run(cmd, capture_output=True, text=True)
-    if res.returncode != 0:
-        raise RuntimeError(f"nvcc failed for {src.name}:\n{res.stdout}\n{res.stderr}")
-    return res.stderr
+    LIBDIR.mkdir(exist_ok=True)
+    with open(LIBDIR / f".{stem}.lock", "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        try:
+            if not force and not _needs_build(src, out):
+                return None  # another process built it while this one waited
+            tmp = LIBDIR / f".{SOURCES[stem]}.{os.getpid()}.tmp"
+            cmd = ([nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else [])
+                   + ["-o", str(tmp), str(src)])
+            res = subprocess.run(cmd, capture_output=True, text=True)
+            if res.returncode != 0:
+                tmp.unlink(missing_ok=True)
+                raise RuntimeError(f"nvcc failed for {src.name}:\n{res.stdout}\n{res.stderr}")
+            os.replace(tmp, out)
+            return res.stderr
+        finally:
+            fcntl.flock(lock, fcntl.LOCK_UN)
 
 
 def build(force: bool = False, verbose: bool = False) -> List[str]:
@@ -86,7 +105,8 @@ def build(force: bool = False, verbose: bool = False) -> List[str]:
 
 
 # Kernels launched per exported entry point (default 1); used for the launch counter.
-_KERNELS_PER_CALL = {"dion_adamw": 2, "dion_ns_iterate2": 0}  # the latter counts itself
+_KERNELS_PER_CALL = {"dion_adamw": 2, "dion_dion2_post_masked": 2,
+                     "dion_ns_iterate2": 0}  # the last one counts itself
 _launches = 0
 
 
@@ -141,12 +161,52 @@ def lib(stem: str) -> "_CountingLib":
             _compile(stem, False, False)
         if not out.exists():
             raise RuntimeError(
-                f"kernel library {out} is missing; run `python -c 'import __graft_entry__ as g; "
-                f"g.build()'` (needs nvcc)"
+                f"kernel library {out} is missing; build it with "
+                f"`python -c 'from dion_b200.ops import _backend; _backend.build()'` (needs nvcc)"
             )
-        h = _CountingLib(ctypes.CDLL(str(out)))
+        dll = ctypes.CDLL(str(out))
+        _apply_wait_budget(dll)
+        h = _CountingLib(dll)
         _loaded[stem] = h
         return h
+
+
+_wait_budget_ms: Optional[float] = None
+
+
+def _apply_wait_budget(dll: ctypes.CDLL) -> None:
+    ms = _wait_budget_ms
+    if ms is None:
+        env = os.environ.get("DION_B200_WAIT_BUDGET_MS")
+        ms = float(env) if env else None
+    if ms is None:
+        return
+    setter = getattr(dll, "dion_set_wait_budget_ns", None)
+    if setter is None:
+        return
+    try:
+        import torch
+
+        if not torch.cuda.is_available():
+            return
+        torch.cuda.current_device()  # makes sure the context exists
+    except Exception:  # noqa: BLE001
+        return
+    setter.argtypes = [ctypes.c_ulonglong]
+    if setter(ctypes.c_ulonglong(int(ms * 1e6))) != 0:
+        raise RuntimeError("could not set the kernels' wait budget")
+
+
+def set_wait_budget_ms(ms: float) -> None:
+    """How long a kernel may wait for a peer GPU (or for one of its own pipeline stages) before
+    it records a timeout and unwinds; 2000 by default, ``DION_B200_WAIT_BUDGET_MS`` at start-up.
+    The value is written into each library's device variable on the GPU that is current at the
+    time (one process drives one GPU) and applies to libraries loaded later as well."""
+    global _wait_budget_ms
+    _wait_budget_ms = float(ms)
+    with _lock:
+        for h in _loaded.values():
+            _apply_wait_budget(h._dll)
 
 
 def available(stem: str) -> bool:

@@ -91,11 +91,14 @@ def muon_pre(
 ) -> List[Tensor]:
     """``M = mu*M + G`` (or ``M += G`` with ``add_only``); returns the bf16 orthogonalization
     input ``U`` (``mu*M + G`` with Nesterov, else ``M``), written into ``out`` when given.
+    ``out=False`` skips the bf16 output altogether.
     ``sumsq[i]`` (optional, fp32, pre-zeroed) receives ``sum(U_i**2)``.  ``out`` entries may be
     :class:`RawPointer` addresses of peer-GPU memory; ``sumsq_targets[i]`` (raw addresses of fp32
     accumulators, possibly on a peer) then receive the sums instead of ``sumsq``."""
     if not G:
         return []
+    if out is False:      # momentum update only: no bf16 copy is wanted
+        out = [None] * len(M)
     if out is None:
         out = [torch.empty_like(m, dtype=torch.bfloat16) for m in M]
     if _kernel_ok(G, M, out) and _same_dtype(G) and _same_dtype(M) and M[0].numel():
@@ -345,10 +348,12 @@ def dion2_post(
     rowscale: Optional[List[Tensor]] = None,
     normU2: Optional[Tensor] = None,
     normNew2: Optional[Tensor] = None,
+    wait: Optional[tuple] = None,
 ) -> None:
     """``x = (1 - lr*wd)*x - lr*ratio*u`` on the selected rows/columns and plain decay elsewhere,
     rounded once.  ``indices[i]`` lists the selected slices of ``X[i]`` in the order of ``U[i]``;
-    ``maps[i]`` (int32, slice -> position or -1) is the inverse the kernel reads."""
+    ``maps[i]`` (int32, slice -> position or -1) is the inverse the kernel reads.  ``wait`` as
+    in :func:`muon_post` (kernel path only)."""
     if not X:
         return
     k = U[0].size(select_dim) if U[0].numel() else 0
@@ -366,9 +371,15 @@ def dion2_post(
                 ctypes.c_float(wd_f), ctypes.c_float(float(ratio)), _DT[X[0].dtype],
                 int(X[0].size(-1)), int(k), int(select_dim == -2),
                 _c(normU2.data_ptr() if normU2 is not None else 0),
-                _c(normNew2.data_ptr() if normNew2 is not None else 0), _stream(dev)),
+                _c(normNew2.data_ptr() if normNew2 is not None else 0),
+                _c(wait[0].data_ptr() if wait else 0), _c(wait[1].data_ptr() if wait else 0),
+                int(wait[2]) if wait else 1, _c(wait[3].data_ptr() if wait else 0),
+                _stream(dev)),
             "dion_dion2_post")
         return
+    if wait is not None:
+        raise RuntimeError("dion2_post(wait=...) needs the CUDA kernel path (2-D bf16 updates "
+                           "with an index map)")
     # PyTorch path: decay in place, then overwrite the selected slices with the fused value.
     a = 1 - lr * weight_decay
     b = lr * ratio
@@ -387,6 +398,41 @@ def dion2_post(
         x.scatter_(select_dim, idx_exp, sel.to(x.dtype))
 
 
+def dion2_post_masked(X: List[Tensor], M: List[Tensor], U: List[Tensor], lr: Scalar,
+                      weight_decay: Scalar, ratio: float, ef_decay: float, select_dim: int) -> None:
+    """Post step of Dion2's global selection scope (reference: dion/dion2.py:621-659): ``U[i]``
+    is full-size and zero off the selected slices, which are recognised by holding a non-zero.
+    ``X = (1 - lr*wd)*X - lr*ratio*U`` and the selected slices of ``M`` are scaled by
+    ``ef_decay``; on a GPU two launches cover every parameter."""
+    if not X:
+        return
+    if (X[0].ndim == 2 and _kernel_ok(X, M, U) and _same_dtype(X) and _same_dtype(M)
+            and all(u.dtype == torch.bfloat16 for u in U)
+            and all(x.shape == X[0].shape for x in X)):
+        dev = X[0].device
+        lr_t = device_scalar(lr, dev)
+        wd_t, wd_f = _wd_args(weight_decay, dev)
+        num_select = X[0].size(select_dim)
+        flags = torch.empty((len(X), num_select), dtype=torch.int32, device=dev)
+        tb = build_table([X, M, U], [x.numel() for x in X], tag="d2mask")
+        _check(
+            _backend.lib("foreach_ops").dion_dion2_post_masked(
+                _c(tb.device_tensor.data_ptr()), ctypes.c_longlong(tb.n_chunks), len(X),
+                _c(lr_t.data_ptr()), _c(wd_t.data_ptr() if wd_t is not None else 0),
+                ctypes.c_float(wd_f), ctypes.c_float(float(ratio)), ctypes.c_float(float(ef_decay)),
+                _DT[X[0].dtype], _DT[M[0].dtype], int(X[0].size(-1)), int(select_dim == -2),
+                int(num_select), _c(flags.data_ptr()), _stream(dev)),
+            "dion_dion2_post_masked")
+        return
+    norm_dim = -1 if select_dim == -2 else -2
+    torch._foreach_mul_(X, 1 - lr * weight_decay)
+    step = lr * ratio
+    for x, m, u in zip(X, M, U):
+        sel = u.to(torch.float32).abs().sum(dim=norm_dim, keepdim=True) > 0
+        m.mul_(torch.where(sel, ef_decay, 1.0).to(m.dtype))
+        x.sub_((step * u).to(x.dtype))
+
+
 # ------------------------------------------------------------------------------------------------
 # NorMuon statistics
 # ------------------------------------------------------------------------------------------------
@@ -395,13 +441,15 @@ def normuon_rowstats(
     V: List[Tensor],
     beta2: float,
     vmaps: Optional[List[Tensor]] = None,
+    guard: Optional[Tensor] = None,
 ):
     """Per-row second-moment update for a stacked update ``U`` of shape ``[N, rows, cols]``.
 
     ``V[i]`` (shape ``[R, 1]``) is updated in place as ``lerp(V, mean(U_i**2, -1), 1-beta2)`` at
     rows ``vmaps[i]`` (all rows when ``vmaps`` is None).  Returns ``(rinv, normU2, normNew2)``:
     ``rinv[N, rows] = 1/(sqrt(V)+1e-8)``, and the squared Frobenius norms of ``U_i`` and of
-    ``U_i * rinv_i``."""
+    ``U_i * rinv_i``.  ``guard`` (the device status word) makes the kernel leave ``V`` untouched
+    when an earlier kernel reported that ``U`` may be incomplete."""
     N, rows, cols = U.shape
     dev = U.device
     rinv = torch.empty((N, rows), dtype=torch.float32, device=dev)
@@ -417,7 +465,8 @@ def normuon_rowstats(
             _backend.lib("foreach_ops").dion_normuon_rowstats(
                 _c(tb.device_tensor.data_ptr()), _c(U.data_ptr()), N, rows, cols,
                 _DT[V[0].dtype], ctypes.c_float(float(beta2)), _c(rinv.data_ptr()),
-                _c(normU2.data_ptr()), _c(normNew2.data_ptr()), _stream(dev)),
+                _c(normU2.data_ptr()), _c(normNew2.data_ptr()),
+                _c(guard.data_ptr() if guard is not None else 0), _stream(dev)),
             "dion_normuon_rowstats")
         return rinv, normU2, normNew2
     Uf = U.to(torch.float32)

@@ -41,6 +41,18 @@ def status_tensor(device: torch.device) -> Tensor:
     return t
 
 
+def _raise_for(idx: int, record) -> None:
+    code, who, want, found = (int(v) for v in record)
+    if code == 0:
+        return
+    detail = ""
+    if code == 5 and (who or want or found):
+        detail = (f" (flag of source rank {who}: waited for sequence {want}, found {found})")
+    raise RuntimeError(
+        f"dion_b200 kernel error on cuda:{idx}: {STATUS_MESSAGES.get(code, code)}{detail}; "
+        f"updates that depended on the missing data were skipped")
+
+
 def check_status(device: Optional[torch.device] = None) -> None:
     """Read the device status word (synchronizes) and raise if a kernel reported a timeout."""
     devs = list(_status) if device is None else [device.index or 0]
@@ -48,17 +60,48 @@ def check_status(device: Optional[torch.device] = None) -> None:
         t = _status.get(idx)
         if t is None:
             continue
-        code = int(t[0].item())
-        if code != 0:
-            who, want, found = (int(v) for v in t[1:4].tolist())
+        record = t.tolist()
+        if record[0] != 0:
             t.zero_()
-            detail = ""
-            if code == 5 and (who or want or found):
-                detail = (f" (flag of source rank {who}: waited for sequence {want}, "
-                          f"found {found})")
-            raise RuntimeError(
-                f"dion_b200 kernel error on cuda:{idx}: {STATUS_MESSAGES.get(code, code)}{detail}"
-            )
+            _snapshots.pop(idx, None)
+            _raise_for(idx, record)
+
+
+# Non-blocking watch: a copy of the status record in pinned host memory, refreshed by an
+# asynchronous copy at the end of each step, read once that copy has completed.
+_snapshots: Dict[int, Tuple[Tensor, "torch.cuda.Event"]] = {}
+
+
+def snapshot_status(device: torch.device) -> None:
+    """Queue a copy of the device status record to the host on the current stream (nothing is
+    queued while the stream is being captured)."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    t = _status.get(idx)
+    if t is None or torch.cuda.is_current_stream_capturing():
+        return
+    snap = _snapshots.get(idx)
+    if snap is None:
+        host = torch.zeros(4, dtype=torch.int32).pin_memory()
+        snap = _snapshots[idx] = (host, torch.cuda.Event())
+    host, event = snap
+    host.copy_(t, non_blocking=True)
+    event.record(torch.cuda.current_stream(t.device))
+
+
+def poll_status(device: torch.device) -> None:
+    """Raise if the last completed snapshot shows an error; never waits for the GPU."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    snap = _snapshots.get(idx)
+    if snap is None or torch.cuda.is_current_stream_capturing():
+        return
+    host, event = snap
+    if not event.query():
+        return
+    record = host.tolist()
+    if record[0] != 0:
+        host.zero_()
+        _status[idx].zero_()
+        _raise_for(idx, record)
 
 
 def sm_count(device: torch.device) -> int:

@@ -27,6 +27,169 @@ def _stream(dev) -> ctypes.c_void_p:
     return ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
 
 
+class _LrOperand(ctypes.Structure):
+    _fields_ = [("ptr", ctypes.c_void_p), ("ld", ctypes.c_longlong), ("stride", ctypes.c_longlong)]
+
+
+class _LrExtra(ctypes.Structure):
+    _fields_ = [("c_table", ctypes.c_void_p), ("d_table", ctypes.c_void_p),
+                ("red_targets", ctypes.c_longlong * 8), ("n_red", ctypes.c_int),
+                ("colsq", ctypes.c_void_p)]
+
+
+_pointer_tables: dict = {}
+
+
+def _pointer_table(tensors: List[Tensor]) -> Tensor:
+    """int64 device tensor of the data pointers of ``tensors`` (cached by those pointers)."""
+    key = tuple(t.data_ptr() for t in tensors)
+    tab = _pointer_tables.get(key)
+    if tab is None:
+        if len(_pointer_tables) > 256:
+            _pointer_tables.clear()
+        tab = torch.tensor(key, dtype=torch.int64).to(tensors[0].device)
+        _pointer_tables[key] = tab
+    return tab
+
+
+def _ld_stride3(t: Tensor) -> Tuple[int, int]:
+    ld = t.stride(1) if t.size(1) > 1 else max(t.stride(1), t.size(2))
+    bs = t.stride(0) if t.size(0) > 1 else t.size(1) * ld
+    return ld, bs
+
+
+def lr_gemm_ok(*ts: Tensor) -> bool:
+    """Operands the tensor-core kernel can read in place: CUDA, fp32 or bf16 (all alike), 3-D,
+    innermost dimension contiguous, 16-byte aligned base / leading dimension / batch stride."""
+    from ..utils.tensors import is_plain_tensor
+
+    dt = ts[0].dtype
+    if dt not in (torch.float32, torch.bfloat16):
+        return False
+    per16 = 16 // ts[0].element_size()
+    for t in ts:
+        if not (t.is_cuda and t.dtype == dt and t.ndim == 3 and is_plain_tensor(t)):
+            return False
+        if t.numel() == 0 or t.stride(2) != 1 or t.data_ptr() % 16:
+            return False
+        ld, bs = _ld_stride3(t)
+        if ld % per16 or bs % per16:
+            return False
+    return True
+
+
+def split_lo(x: Tensor) -> Tensor:
+    """``x - tf32(x)``: the part of an fp32 tensor that a tf32 instruction does not see."""
+    x = x.contiguous()
+    lo = torch.empty_like(x)
+    rc = _backend.lib("lowrank_gemm_sm100").dion_split_lo(
+        _ptr(x), _ptr(lo), ctypes.c_longlong(x.numel()), _stream(x.device))
+    if rc != 0:
+        raise RuntimeError(f"dion_split_lo launch failed (code {rc})")
+    return lo
+
+
+def lr_gemm(A: Tensor, B: Tensor, *, a_mn: bool = False, b_mn: bool = False,
+            out: Optional[Tensor] = None, out_dtype: Optional[torch.dtype] = None,
+            out_list: Optional[List[Tensor]] = None, D: Optional[Tensor] = None,
+            d_list: Optional[List[Tensor]] = None, alpha: float = 1.0, beta: float = 0.0,
+            precise: bool = False, colsq: Optional[Tensor] = None,
+            red_targets: Optional[List[int]] = None, red_ld: int = 0, red_stride: int = 0,
+            bn: Optional[int] = None) -> Optional[Tensor]:
+    """``out[b] = alpha * A[b] @ op(B[b]) + beta * D[b]`` on the tensor cores (tf32 for fp32
+    operands, bf16 otherwise; fp32 accumulation), see csrc/lowrank_gemm_sm100.cu.
+
+    ``A`` is ``[batch, M, K]`` (``a_mn``: ``[batch, K, M]``), ``B`` is ``[batch, N, K]``
+    (``b_mn``: ``[batch, K, N]``).  ``out`` / ``D`` are strided batches, ``out_list`` / ``d_list``
+    lists of per-matrix tensors (separately allocated weights); ``D`` may be ``out``.
+    ``precise`` (fp32 operands): three tf32 products recover fp32-level accuracy.
+    ``colsq [batch, N]`` (fp32, zeroed by the caller) receives the column sums of squares of the
+    result.  ``red_targets``: raw addresses of fp32 buffers (same layout ``red_ld`` /
+    ``red_stride``) to which the result is added instead of being stored."""
+    from . import gemm
+
+    assert lr_gemm_ok(A, B), "operands violate the kernel's layout rules; see lr_gemm_ok()"
+    batch = A.size(0)
+    M, K = (A.size(2), A.size(1)) if a_mn else (A.size(1), A.size(2))
+    N, Kb = (B.size(2), B.size(1)) if b_mn else (B.size(1), B.size(2))
+    assert K == Kb and B.size(0) == batch
+    dev = A.device
+    eb = A.element_size()
+    segs = [(A, B)]
+    if precise and eb == 4:
+        Ac = A if A.is_contiguous() else A.contiguous()
+        Bc = B if B.is_contiguous() else B.contiguous()
+        segs = [(Ac, Bc), (split_lo(Ac), Bc), (Ac, split_lo(Bc))]
+    a_ops = (_LrOperand * 3)()
+    b_ops = (_LrOperand * 3)()
+    for i, (a, b) in enumerate(segs):
+        lda, sa = _ld_stride3(a)
+        ldb, sb = _ld_stride3(b)
+        a_ops[i] = _LrOperand(a.data_ptr(), lda, sa)
+        b_ops[i] = _LrOperand(b.data_ptr(), ldb, sb)
+    ex = _LrExtra()
+    use_ex = False
+    c_ptr, ldc, sc, c_dt = 0, N, M * N, 0
+    if red_targets is not None:
+        for i, addr in enumerate(red_targets):
+            ex.red_targets[i] = addr
+        ex.n_red = len(red_targets)
+        ldc, sc = red_ld or N, red_stride or M * N
+        use_ex = True
+    elif out_list is not None:
+        assert len(out_list) == batch
+        ex.c_table = _pointer_table(out_list).data_ptr()
+        ldc = out_list[0].stride(0)
+        c_dt = 0 if out_list[0].dtype == torch.float32 else 1
+        use_ex = True
+    else:
+        if out is None:
+            out = torch.empty((batch, M, N), dtype=out_dtype or A.dtype, device=dev)
+        assert out.ndim == 3 and out.stride(2) == 1
+        ldc, sc = _ld_stride3(out)
+        c_ptr, c_dt = out.data_ptr(), (0 if out.dtype == torch.float32 else 1)
+    d_ptr, ldd, sd, d_dt = 0, 0, 0, 0
+    if d_list is not None:
+        ex.d_table = _pointer_table(d_list).data_ptr()
+        ldd = d_list[0].stride(0)
+        d_dt = 0 if d_list[0].dtype == torch.float32 else 1
+        d_ptr = d_list[0].data_ptr()
+        use_ex = True
+    elif D is not None:
+        ldd, sd = _ld_stride3(D)
+        d_ptr, d_dt = D.data_ptr(), (0 if D.dtype == torch.float32 else 1)
+    if colsq is not None:
+        assert colsq.dtype == torch.float32 and colsq.numel() >= batch * N
+        ex.colsq = colsq.data_ptr()
+        use_ex = True
+    if bn is None:
+        bn = 256 if N > 128 else 128
+    st = gemm.status_tensor(dev)
+    rc = _backend.lib("lowrank_gemm_sm100").dion_lr_gemm(
+        eb, len(segs), a_ops, b_ops, int(a_mn), int(b_mn),
+        ctypes.c_void_p(c_ptr), ctypes.c_longlong(ldc), ctypes.c_longlong(sc), c_dt,
+        ctypes.c_void_p(d_ptr), ctypes.c_longlong(ldd), ctypes.c_longlong(sd), d_dt,
+        batch, M, N, K, ctypes.c_float(alpha), ctypes.c_float(beta), bn, gemm.sm_count(dev),
+        _ptr(st), _stream(dev), ctypes.byref(ex) if use_ex else None)
+    if rc != 0:
+        raise RuntimeError(f"dion_lr_gemm launch failed (code {rc})")
+    return out
+
+
+def triu_inverse(U: Tensor) -> Tensor:
+    """Inverse of every upper-triangular ``U[b]`` (``[B, r, r]`` fp32)."""
+    if U.is_cuda and U.dtype == torch.float32 and U.ndim == 3 and U.size(-1) <= _MAX_FACTOR_DIM:
+        Uc = U.contiguous()
+        X = torch.empty_like(Uc)
+        rc = _backend.lib("lowrank_ops").dion_triu_inverse(
+            _ptr(Uc), _ptr(X), Uc.size(0), Uc.size(-1), _stream(Uc.device))
+        if rc != 0:
+            raise RuntimeError(f"dion_triu_inverse launch failed (code {rc})")
+        return X
+    eye = torch.eye(U.size(-1), dtype=U.dtype, device=U.device).expand_as(U)
+    return torch.linalg.solve_triangular(U, eye, upper=True)
+
+
 def sketch_rows(r: int, oversample: float) -> int:
     """Number of sketch rows: ``oversample * r`` rounded up to a multiple of 128."""
     return int(math.ceil(oversample * r / 128.0) * 128)
@@ -81,8 +244,27 @@ def cholesky_upper(G: Tensor) -> Tensor:
 
 
 def right_solve_upper(R: Tensor, P: Tensor) -> Tensor:
-    """``P @ R^-1`` for upper-triangular ``R``."""
+    """``P @ R^-1`` for upper-triangular ``R`` (``[B, r, r]`` fp32) and ``P [B, m, r]`` fp32.  On
+    a GPU: ``R^-1`` from the batched inversion kernel, then a tensor-core product with split
+    operands (fp32-level accuracy); elsewhere a triangular solve."""
+    if (P.is_cuda and P.dtype == torch.float32 and R.dtype == torch.float32 and P.ndim == 3
+            and R.size(-1) <= _MAX_FACTOR_DIM and lr_gemm_ok(P, R.contiguous())):
+        return lr_gemm(P, triu_inverse(R), b_mn=True, precise=True)
     return torch.linalg.solve_triangular(R, P, upper=True, left=False)
+
+
+def gram(P: Tensor) -> Tensor:
+    """``P^T P`` in fp32 for ``P [B, m, r]`` fp32 (tensor cores with split operands on a GPU)."""
+    if P.is_cuda and P.dtype == torch.float32 and P.ndim == 3 and lr_gemm_ok(P):
+        return lr_gemm(P, P, a_mn=True, b_mn=True, precise=True)
+    return P.mT @ P
+
+
+def sketch_product(S: Tensor, P: Tensor) -> Tensor:
+    """``S P`` for the sketch ``S [B, k, m]`` and ``P [B, m, r]`` (same dtype), fp32 result."""
+    if lr_gemm_ok(S, P):
+        return lr_gemm(S, P, b_mn=True, out_dtype=torch.float32)
+    return (S @ P).to(torch.float32)
 
 
 def orthogonalize(P: Tensor, oversample: float = 1.25,
@@ -91,7 +273,10 @@ def orthogonalize(P: Tensor, oversample: float = 1.25,
     """Orthonormalize the columns of every ``P[b]`` (``[B, m, r]``), result in ``P.dtype``.
 
     ``m <= r``: Householder QR.  Otherwise randomized Cholesky-QR: ``R1 = qr(S P).R``,
-    ``P <- P R1^-1`` (well conditioned), then ``R2 = chol(P^T P)``, ``P <- P R2^-1``."""
+    ``P <- P R1^-1`` (well conditioned), then ``R2 = chol(P^T P)``, ``P <- P R2^-1``
+    (reference: dion/dion.py:1265-1305).  On a GPU every product runs on this package's
+    tensor-core kernel and the triangular solves are products with explicitly inverted
+    factors."""
     assert P.ndim >= 3, "expected a batch dimension"
     dtype = P.dtype
     m, r = P.shape[-2], P.shape[-1]
@@ -99,9 +284,9 @@ def orthogonalize(P: Tensor, oversample: float = 1.25,
         return householder_q(P).to(dtype).contiguous()
     if sketch is None:
         sketch = random_sketch(P.size(0), sketch_rows(r, oversample), m, dtype, P.device, generator)
-    R1 = qr_r_factor(sketch @ P)
+    R1 = qr_r_factor(sketch_product(sketch, P))
     P32 = right_solve_upper(R1, P.to(torch.float32))
-    R2 = cholesky_upper(P32.mT @ P32)
+    R2 = cholesky_upper(gram(P32))
     return right_solve_upper(R2, P32).to(dtype).contiguous()
 
 
@@ -134,8 +319,9 @@ def column_normalize(X: Tensor, full_column_sum_sq: Optional[Tensor] = None,
 def foreach_baddbmm_(X: List[Tensor], A: Tensor, B: Tensor, alpha=1.0, beta=1.0,
                      transpose: bool = False) -> None:
     """``X[i] = beta*X[i] + alpha*(A[i] @ B[i]^T)`` (or ``B[i] @ A[i]^T`` when ``transpose``).
-    One fused GEMM-with-epilogue per matrix: the rank-r product is never materialized at full
-    size and every ``X[i]`` is read and written once."""
+    One fused GEMM-with-epilogue launch for all matrices on a GPU (the rank-r product is never
+    materialized at full size and every ``X[i]`` is read and written once, in place, by the
+    epilogue of the tensor-core kernel); one ``addmm`` per matrix elsewhere."""
     assert A.size(0) == B.size(0) == len(X)
     if isinstance(alpha, Tensor) or isinstance(beta, Tensor):
         # Device-resident scalars (no host read): scale with multi-tensor ops instead.
@@ -145,44 +331,71 @@ def foreach_baddbmm_(X: List[Tensor], A: Tensor, B: Tensor, alpha=1.0, beta=1.0,
         torch._foreach_add_(X, [u.to(x.dtype) for u, x in zip(upd, X)])
         return
     alpha, beta = float(alpha), float(beta)
+    a3, b3 = (B, A) if transpose else (A, B)
+    if _rank_update_ok(X, a3, b3):
+        lr_gemm(a3, b3, out_list=X, d_list=X, alpha=alpha, beta=beta)
+        return
     for i, x in enumerate(X):
-        a, b = (B[i], A[i]) if transpose else (A[i], B[i])
+        a, b = a3[i], b3[i]
         if a.dtype != x.dtype:
             a, b = a.to(x.dtype), b.to(x.dtype)
         torch.addmm(x, a, b.mT, beta=beta, alpha=alpha, out=x)
 
 
-def _tcgen05_ok(A: Tensor, B: Tensor) -> bool:
-    from . import gemm
+def _rank_update_ok(X: List[Tensor], a3: Tensor, b3: Tensor) -> bool:
     from ..utils.tensors import is_plain_tensor
 
-    return (A.is_cuda and A.dtype == torch.bfloat16 and B.dtype == torch.bfloat16
-            and A.ndim == 3 and B.ndim == 3 and is_plain_tensor(A) and is_plain_tensor(B)
-            and A.is_contiguous() and B.is_contiguous() and gemm.supported(A, B)
-            and B.size(-1) % 8 == 0 and min(A.shape[-2:]) >= 64 and B.size(-1) >= 64)
+    if not (a3.dtype == b3.dtype and lr_gemm_ok(a3, b3)):
+        return False
+    x0 = X[0]
+    if x0.dtype not in (torch.float32, torch.bfloat16) or x0.ndim != 2:
+        return False
+    for x in X:
+        if not (is_plain_tensor(x) and x.is_cuda and x.dtype == x0.dtype and x.stride(1) == 1
+                and x.stride(0) == x0.stride(0) and x.shape == x0.shape):
+            return False
+    return True
 
 
-def power_iteration_p(Mb: Tensor, Qb: Tensor) -> Tensor:
-    """``P = M Q`` for batches ``Mb [B, m, n]``, ``Qb [B, n, r]`` (reference: dion/dion.py:798).
-    bf16 batches on a GPU run on this package's tcgen05 GEMM (``Q`` read as a [K, N] operand),
-    anything else through ``torch.bmm``."""
-    if _tcgen05_ok(Mb, Qb):
-        from . import gemm
-        return gemm.ns_gemm(Mb, Qb, b_is_kn=True)
-    return Mb @ Qb
+def rank_update_stack_(X3: Tensor, A: Tensor, B: Tensor, alpha: float, beta: float,
+                       transpose: bool = False) -> None:
+    """As :func:`foreach_baddbmm_` for matrices stored as one stack ``X3 [B, m, n]``."""
+    a3, b3 = (B, A) if transpose else (A, B)
+    if a3.dtype == b3.dtype and lr_gemm_ok(a3, b3) and X3.is_cuda and X3.stride(2) == 1 \
+            and X3.dtype in (torch.float32, torch.bfloat16):
+        lr_gemm(a3, b3, out=X3, D=X3, alpha=float(alpha), beta=float(beta))
+        return
+    foreach_baddbmm_(list(X3.unbind(0)), A, B, alpha=alpha, beta=beta, transpose=transpose)
 
 
-def power_iteration_r(Mb: Tensor, P: Tensor) -> Tensor:
-    """``R = M^T P`` for ``Mb [B, m, n]``, ``P [B, m, r]`` (reference: dion/dion.py:836) without
-    a transposed copy of ``M``: both operands are read K-outermost."""
-    if _tcgen05_ok(Mb, P):
-        from . import gemm
-        return gemm.ns_gemm(Mb, P, a_is_km=True, b_is_kn=True)
-    return Mb.mT @ P
+def power_iteration_p(M3: Tensor, Q3: Tensor, transposed: bool = False) -> Tensor:
+    """``P = Mt Q`` with ``Mt = M^T`` when ``transposed`` else ``M``, for the stack ``M3
+    [B, m, n]`` in its row-major storage and ``Q3 [B, n or m, r]`` (reference:
+    dion/dion.py:797-798).  On a GPU both operands are read in place by the tensor-core kernel
+    (``M^T`` as an MN-major operand, ``Q`` as a ``[K, N]`` operand): no transposed copy."""
+    if Q3.dtype != M3.dtype:
+        Q3 = Q3.to(M3.dtype)
+    if lr_gemm_ok(M3, Q3):
+        return lr_gemm(M3, Q3, a_mn=transposed, b_mn=True)
+    return (M3.mT if transposed else M3) @ Q3
+
+
+def power_iteration_r(M3: Tensor, P: Tensor, transposed: bool = False,
+                      colsq: Optional[Tensor] = None) -> Tensor:
+    """``R = Mt^T P`` (reference: dion/dion.py:836); ``colsq`` as in :func:`lr_gemm`."""
+    if P.dtype != M3.dtype:
+        P = P.to(M3.dtype)
+    if lr_gemm_ok(M3, P):
+        return lr_gemm(M3, P, a_mn=not transposed, b_mn=True, colsq=colsq)
+    R = (M3 if transposed else M3.mT) @ P
+    if colsq is not None:
+        colsq.view(R.size(0), R.size(-1)).add_(R.to(torch.float32).square().sum(dim=-2))
+    return R
 
 
 def stack_for_power_iteration(M: List[Tensor], Q: List[Tensor], transposed: bool):
     """``(M_batch, Q_batch)`` with ``M_batch[i] = M[i]^T`` when ``transposed``; ``Q`` is cast to
-    the momentum dtype."""
+    the momentum dtype.  (List form kept for callers that hold separate tensors; the optimizer
+    keeps its momentum as one stack and passes ``transposed`` to the functions above.)"""
     Mb = torch.stack([m.mT for m in M]) if transposed else torch.stack(M)
     return Mb, torch.stack(Q).to(Mb.dtype)

@@ -38,6 +38,26 @@ def _call_if_present(obj, name: str):
     return fn() if fn is not None else None
 
 
+def supports_graph_replay(optimizer) -> bool:
+    """True for optimizers whose step stays correct when replayed from a recording: learning rate
+    in persistent device tensors refreshed through ``_sync_hyperparam_tensors``, AdamW counters
+    on the device, host counters advanced through ``_advance_host_step_counters`` (the megabatch
+    family).  Optimizers that pass ``group["lr"]`` or a step count to their kernels as host
+    numbers (legacy Dion, DionReference, DionSimple, MuonReference, plain torch optimizers)
+    would replay the values of the recorded step for ever."""
+    return (callable(getattr(optimizer, "_sync_hyperparam_tensors", None))
+            and callable(getattr(optimizer, "_advance_host_step_counters", None)))
+
+
+def require_graph_replay_support(optimizer, what: str) -> None:
+    if not supports_graph_replay(optimizer):
+        raise TypeError(
+            f"{what} needs an optimizer that keeps its learning rate and step counters in device "
+            f"tensors (Muon, NorMuon, Dion2, NorDion2); {type(optimizer).__name__} passes them "
+            f"as host numbers, so a replayed step would train at the recorded step's learning "
+            f"rate and bias correction.  Run it without a CUDA graph.")
+
+
 class CudaGraphOptimizer(torch.optim.Optimizer):
     """A ``torch.optim.Optimizer`` face on ``optimizer`` whose steps are recorded once and then
     replayed.  It owns no parameters or state of its own: ``param_groups`` and ``state`` are the
@@ -116,6 +136,7 @@ class CudaGraphOptimizer(torch.optim.Optimizer):
                 if p.requires_grad and p.grad is None]
 
     def _record(self) -> None:
+        require_graph_replay_support(self.optimizer, "CudaGraphOptimizer")
         orphans = self._params_without_grad()
         if orphans:
             listed = ", ".join(orphans[:5])
@@ -142,7 +163,9 @@ class CudaGraphOptimizer(torch.optim.Optimizer):
                 "(assigning a Tensor weight_decay is the way in); the recording holds the old "
                 "host value and cannot see the tensor.  Opt in before the first recording or "
                 "call release() to record again.")
+        _call_if_present(self.optimizer, "_poll_device_status")
         self._graph.replay()
+        _call_if_present(self.optimizer, "_snapshot_device_status")
         _call_if_present(self.optimizer, "_advance_host_step_counters")
 
     def step(self, closure: Optional[Callable] = None):

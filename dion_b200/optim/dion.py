@@ -45,6 +45,7 @@ from ..ops import lowrank as LR
 from ..parallel import collectives as C
 from ..parallel.async_runtime import AsyncRuntime, AsyncTask
 from ..utils.tensors import create_param_batches, group_by_shape, to_local
+from .status import DeviceStatusMixin
 
 
 @dataclass
@@ -83,7 +84,7 @@ def _mesh_check(name: str, mesh, others) -> None:
             raise ValueError(f"{name} shard mesh must be different from {oname}.")
 
 
-class Dion(Optimizer):
+class Dion(DeviceStatusMixin, Optimizer):
     """Distributed Dion.
 
     Args:
@@ -169,6 +170,7 @@ class Dion(Optimizer):
         self._base_seed = self._agree_on_seed()
         self._generators: Dict[torch.device, torch.Generator] = {}
         self._q_counter = 0
+        self._momentum_stacks: Dict[tuple, Tensor] = {}
 
     # ------------------------------------------------------------------ randomness ----------
     def _agree_on_seed(self) -> int:
@@ -201,6 +203,7 @@ class Dion(Optimizer):
         if closure is not None:
             with torch.enable_grad():
                 loss = closure()
+        self._poll_device_status()
         groups = {"dion": [], "lion": [], "adamw": []}
         for group in self.param_groups:
             group["step"] += 1
@@ -212,6 +215,7 @@ class Dion(Optimizer):
                       self._create_lion_tasks(groups["lion"]),
                       self._create_adamw_tasks(groups["adamw"]))
         AsyncRuntime(tasks, max_concurrent_tasks=3).run()
+        self._snapshot_device_status()
         return loss
 
     @torch.no_grad()
@@ -219,6 +223,7 @@ class Dion(Optimizer):
         """Average every state tensor over the replicate mesh.  Compressed synchronization lets
         the momentum drift apart between replicas; call this before saving a checkpoint.  No-op
         without a replicate mesh or when the optimizer does not own the gradient sync."""
+        self.check_device_status()
         if self._replicate_mesh is None or not self._replicate_mesh_grad_sync:
             return
         tensors = [to_local(v) for st in self.state.values() for v in st.values()
@@ -433,6 +438,33 @@ class Dion(Optimizer):
                 out["non_sharded"].append(p)
         return out
 
+    def _momentum_stack(self, params: List[Tensor], batch: int) -> Tensor:
+        """``[batch, rows, cols]`` tensor whose first ``len(params)`` slices ARE the (local)
+        momentum tensors of ``params``: on first use (and again after ``load_state_dict``, which
+        replaces the state tensors) the momentum is moved into one allocation and the state
+        entries are re-pointed at its slices.  Checkpoints are unaffected: ``state_dict()`` still
+        holds one tensor per parameter."""
+        states = [self.state[p] for p in params]
+        local = to_local([st["momentum"] for st in states])
+        key = (id(params[0]), len(params), batch)
+        stack = self._momentum_stacks.get(key)
+        if stack is not None and all(m.data_ptr() == stack[i].data_ptr()
+                                     for i, m in enumerate(local)):
+            return stack
+        stack = torch.zeros((batch,) + tuple(local[0].shape), dtype=local[0].dtype,
+                            device=local[0].device)
+        for i, (st, m) in enumerate(zip(states, local)):
+            stack[i].copy_(m)
+            old = st["momentum"]
+            if isinstance(old, DTensor):
+                st["momentum"] = DTensor.from_local(stack[i], old.device_mesh, old.placements,
+                                                    run_check=False, shape=old.shape,
+                                                    stride=old.stride())
+            else:
+                st["momentum"] = stack[i]
+        self._momentum_stacks[key] = stack
+        return stack
+
     # ------------------------------------------------------------------ the update ----------
     def _dion_update(self, kind: str, batch: int, params, grads, moms, Qs,
                      cfg: _DionParamConfig, group: dict, task_id: int):
@@ -449,24 +481,33 @@ class Dion(Optimizer):
         sync = self._replicate_mesh_grad_sync and rep is not None
         compressed = sync and cfg.compressed_all_reduce
 
-        X, G, M, Q = to_local(params), to_local(grads), to_local(moms), to_local(Qs)
+        X, G, Q = to_local(params), to_local(grads), to_local(Qs)
         n_real = len(X)
-        for lst in (X, G, M, Q):  # pad with inert stand-ins up to the batch size
+        # The momentum of the batch lives in one stack [batch, rows, cols] (slots past n_real are
+        # inert zeros), so the batched kernels read it in place and nothing is copied per step.
+        M3 = self._momentum_stack(params, batch)
+        M = list(M3.unbind(0))
+        for lst in (X, G, Q):  # pad with inert stand-ins up to the batch size
             lst.extend(torch.zeros_like(lst[0]) for _ in range(batch - n_real))
         dev = X[0].device
+        tr = cfg.is_transposed
 
         if sync and not compressed:
             work = C.all_reduce_(G[:n_real], rep, op="avg", async_op=True)
             yield
             work.wait()
-        torch._foreach_add_(M, [g.to(M[0].dtype) for g in G])
+        if G[0].is_cuda and G[0].dtype in (torch.float32, torch.bfloat16) \
+                and M3.dtype in (torch.float32, torch.bfloat16):
+            F.muon_pre(G[:n_real], M[:n_real], 0.0, False, add_only=True, out=False)
+        else:
+            torch._foreach_add_(M[:n_real], [g.to(M3.dtype) for g in G[:n_real]])
 
         if kind == "inner_sharded" and inner_pg is not None:
             Q_full = [C.all_gather_last_dim(q, inner_pg) for q in Q]
         else:
             Q_full = Q
-        Mb, Qb = LR.stack_for_power_iteration(M, Q_full, cfg.is_transposed)
-        P = LR.power_iteration_p(Mb, Qb)  # [B, rows_loc, r]; partial over a sharded outer mesh
+        Qb = torch.stack(Q_full).to(M3.dtype)
+        P = LR.power_iteration_p(M3, Qb, tr)  # [B, rows_loc, r]; partial over a sharded outer mesh
 
         if kind == "non_sharded":
             rank = C.group_rank(rep) if rep is not None else 0
@@ -512,7 +553,7 @@ class Dion(Optimizer):
             gen = self._generator(dev, step, task_id, i_rank)
             P = distributed_orthogonalize(P, oversample, inner_pg, generator=gen)
 
-        R = LR.power_iteration_r(Mb, P)  # [B, cols_loc, r]
+        R = LR.power_iteration_r(M3, P, tr)  # [B, cols_loc, r]
         if kind == "inner_sharded":
             work = C.all_reduce_(R, inner_pg, op="sum", async_op=True)
             yield
@@ -522,8 +563,8 @@ class Dion(Optimizer):
             yield
             work.wait()
 
-        P, R = LR.fix_all_zero_or_nan(P, R, Qb, Mb)
-        LR.foreach_baddbmm_(M, P, R, alpha=-(1 - mu), transpose=cfg.is_transposed)
+        P, R = LR.fix_all_zero_or_nan(P, R, Qb, M3)
+        LR.rank_update_stack_(M3, P, R, alpha=-(1 - mu), beta=1.0, transpose=tr)
 
         if outer_pg is not None:
             ss = LR.local_column_sum_sq(R)
@@ -535,8 +576,8 @@ class Dion(Optimizer):
             Q_new = LR.column_normalize(R, epsilon=eps)
 
         scaled_lr = math.sqrt(fan_out / fan_in) * lr
-        LR.foreach_baddbmm_(X, P, Q_new, alpha=-scaled_lr, beta=1 - lr * wd,
-                            transpose=cfg.is_transposed)
+        LR.foreach_baddbmm_(X[:n_real], P[:n_real], Q_new[:n_real], alpha=-scaled_lr,
+                            beta=1 - lr * wd, transpose=tr)
 
         # Write the new Q back into the (possibly TP-sharded) state.
         if kind == "inner_sharded" and inner_pg is not None:

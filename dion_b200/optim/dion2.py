@@ -197,9 +197,9 @@ def dion2_update_megabatch_async(
         fx.publish()
         NS.iterate_with_exchange(fx.input_matrix(), newton_schulz_func, epsilon, fx)
         fx.finish()
-        fx.wait_results()
         F.dion2_post(Xl, list(fx.result_stack().unbind(0)), list(idx.unbind(0)),
-                     list(maps.unbind(0)), lr, weight_decay, ratio, select_dim)
+                     list(maps.unbind(0)), lr, weight_decay, ratio, select_dim,
+                     wait=fx.result_wait())
         fx.release()
         yield
         return
@@ -248,13 +248,7 @@ def dion2_post_orthogonalize_masked(
     """Global-scope post step: ``U`` is full-size and exactly zero off the selected slices, which
     are recognised by being non-zero (orthonormal slices have unit norm).  Decays ``X``, applies
     ``ef_decay`` to the selected slices of ``M`` and adds the update."""
-    norm_dim = -1 if select_dim == -2 else -2
-    torch._foreach_mul_(X, 1 - lr * weight_decay)
-    step = lr * ratio
-    for x, m, u in zip(X, M, U):
-        sel = u.to(torch.float32).abs().sum(dim=norm_dim, keepdim=True) > 0
-        m.mul_(torch.where(sel, ef_decay, 1.0).to(m.dtype))
-        x.sub_((step * u).to(x.dtype))
+    F.dion2_post_masked(X, M, U, lr, weight_decay, ratio, ef_decay, select_dim)
 
 
 def dion2_pre_orthogonalize(G, M, fraction, ef_decay, select_dim, k_override=None):

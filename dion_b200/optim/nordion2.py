@@ -175,10 +175,11 @@ def nordion2_update_megabatch_async(
         U3 = fx.result_stack()
         idx_list = list(idx.unbind(0))
         rinv, n_u2, n_new2 = F.normuon_rowstats(U3, _matrix_views(Vl, num_select),
-                                                float(muon_beta2), vmaps=idx_list)
+                                                float(muon_beta2), vmaps=idx_list,
+                                                guard=fx.status)
         F.dion2_post(Xl, list(U3.unbind(0)), idx_list, list(maps.unbind(0)), lr, weight_decay,
                      ratio, select_dim, rowscale=list(rinv.unbind(0)), normU2=n_u2,
-                     normNew2=n_new2)
+                     normNew2=n_new2, wait=fx.result_wait())
         fx.release()
         yield
         return

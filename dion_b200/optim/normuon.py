@@ -156,7 +156,8 @@ def normuon_update_megabatch_async(
         fx.finish()
         fx.wait_results()
         normuon_normalize_and_apply(Xl, fx.result_stack(), Vl, float(muon_beta2), lr,
-                                    weight_decay, ratio, cautious_wd, None)
+                                    weight_decay, ratio, cautious_wd, None,
+                                    wait=fx.result_wait())
         fx.release()
         yield
         return
@@ -182,9 +183,11 @@ def normuon_normalize_and_apply(
     ratio: float,
     cautious_wd: bool,
     split_sizes: Optional[Tuple[int, ...]] = None,
+    wait: Optional[tuple] = None,
 ) -> None:
     """Update ``V`` from the stacked orthogonalized update ``U`` (``[N, ..., rows, cols]``) and
-    apply the row-normalized, norm-preserving update to ``X``."""
+    apply the row-normalized, norm-preserving update to ``X``.  ``wait`` (fused exchange, see
+    ``foreach.muon_post``): ``V`` and ``X`` stay untouched once the status word is set."""
     if U.numel() == 0:
         return
     if not U.is_contiguous():
@@ -195,10 +198,11 @@ def normuon_normalize_and_apply(
     if split_sizes is None:
         U3 = U.reshape(N * inner, rows, cols)
         Vm = _matrix_views(V, rows)
-        rinv, n_u2, n_new2 = F.normuon_rowstats(U3, Vm, muon_beta2)
+        rinv, n_u2, n_new2 = F.normuon_rowstats(U3, Vm, muon_beta2,
+                                                guard=wait[3] if wait else None)
         if inner == 1:
             F.muon_post(X, list(U.unbind(0)), lr, weight_decay, ratio, cautious_wd,
-                        rowscale=list(rinv.unbind(0)), normU2=n_u2, normNew2=n_new2)
+                        rowscale=list(rinv.unbind(0)), normU2=n_u2, normNew2=n_new2, wait=wait)
         else:
             Xm = [x.reshape(-1, rows, cols)[j] for x in X for j in range(inner)]
             F.muon_post(Xm, list(U3.unbind(0)), lr, weight_decay, ratio, cautious_wd,

@@ -26,6 +26,7 @@ from ..parallel.async_runtime import AsyncRuntime, AsyncTask
 from ..utils.arena import StepArena
 from ..utils import trace
 from ..utils.tensors import to_local
+from .status import DeviceStatusMixin
 
 MAX_CONCURRENT_TASKS = 3
 
@@ -87,7 +88,7 @@ def _mesh_coordinates(mesh) -> Tuple[int, int, Optional[ProcessGroup]]:
                     f"Expected DeviceMesh or ProcessGroup.")
 
 
-class DistributedOrthoBase(Optimizer):
+class DistributedOrthoBase(DeviceStatusMixin, Optimizer):
     """Base class; subclasses implement ``_create_ortho_tasks(groups)``."""
 
     def __init__(
@@ -170,6 +171,7 @@ class DistributedOrthoBase(Optimizer):
             with torch.enable_grad():
                 loss = closure()
         self._sync_hyperparam_tensors()
+        self._poll_device_status()
         self._arena.reset()
 
         buckets = {"ortho": [], "lion": [], "adamw": []}
@@ -198,6 +200,7 @@ class DistributedOrthoBase(Optimizer):
         tasks = chain(self._create_ortho_tasks(buckets["ortho"]), scalar_tasks())
         with trace.span(f"{self._algo_name}.step"):
             AsyncRuntime(tasks, max_concurrent_tasks=MAX_CONCURRENT_TASKS).run()
+        self._snapshot_device_status()
         return loss
 
     def _create_ortho_tasks(self, param_groups: List[dict]) -> Iterable[AsyncTask]:

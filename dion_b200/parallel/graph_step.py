@@ -174,6 +174,10 @@ class GraphedTrainStep:
         self.autocast_dtype = autocast_dtype
         self.warmup = max(1, warmup)
         self.use_graph = use_graph and device.type == "cuda"
+        if self.use_graph:
+            from ..optim.cuda_graph import require_graph_replay_support
+
+            require_graph_replay_support(optimizer, "GraphedTrainStep(use_graph=True)")
         self.sync = BucketedGradSync(self.params, process_group, bucket_mb)
         self._deferrable = self._scalar_group_params(optimizer)
         if accumulation_steps < 1:
@@ -249,14 +253,16 @@ class GraphedTrainStep:
             dst.copy_(src, non_blocking=True)
 
     def _pre_replay(self) -> None:
-        sync = getattr(self.optimizer, "_sync_hyperparam_tensors", None)
-        if sync is not None:
-            sync()
+        for name in ("_sync_hyperparam_tensors", "_poll_device_status"):
+            fn = getattr(self.optimizer, name, None)
+            if fn is not None:
+                fn()
 
     def _post_replay(self) -> None:
-        advance = getattr(self.optimizer, "_advance_host_step_counters", None)
-        if advance is not None:
-            advance()
+        for name in ("_snapshot_device_status", "_advance_host_step_counters"):
+            fn = getattr(self.optimizer, name, None)
+            if fn is not None:
+                fn()
 
     def __call__(self, *inputs: Tensor) -> Tensor:
         self._load_inputs(inputs)

@@ -19,7 +19,15 @@ from torch.distributed import ProcessGroup
 from ..ops import _backend
 
 
+_capability: Dict[int, bool] = {}
+
+
 def symmetric_memory_available(pg: Optional[ProcessGroup]) -> bool:
+    """Whether kernels may address the memory of every rank of ``pg`` directly: an NCCL group
+    whose ranks all sit on one host, each on a GPU of its own that every other rank's GPU can
+    reach by peer access.  Decided once per group by a collective exchange (host name and device
+    index of every rank) and a MIN-reduction of each rank's verdict, then cached, so that all
+    ranks take the same path; the first call for a group is therefore collective."""
     if pg is None or not torch.cuda.is_available():
         return False
     try:
@@ -30,7 +38,29 @@ def symmetric_memory_available(pg: Optional[ProcessGroup]) -> bool:
         importlib.import_module("torch.distributed._symmetric_memory")
     except Exception:
         return False
-    return True
+    key = id(pg)
+    known = _capability.get(key)
+    if known is not None:
+        return known
+    import socket
+
+    world = dist.get_world_size(pg)
+    me = (socket.gethostname(), torch.cuda.current_device())
+    everyone: List = [None] * world
+    dist.all_gather_object(everyone, me, group=pg)
+    ok = len({h for h, _ in everyone}) == 1 and len({d for _, d in everyone}) == world
+    if ok:
+        for _, d in everyone:
+            if d != me[1]:
+                try:
+                    ok = ok and torch.cuda.can_device_access_peer(me[1], d)
+                except Exception:
+                    ok = False
+    verdict = torch.tensor([1 if ok else 0], dtype=torch.int32,
+                           device=torch.device("cuda", me[1]))
+    dist.all_reduce(verdict, op=dist.ReduceOp.MIN, group=pg)
+    known = _capability[key] = bool(verdict.item())
+    return known
 
 
 class SymmetricBuffer:

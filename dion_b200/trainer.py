@@ -286,6 +286,10 @@ def init_optimizer(model: GPT, device_mesh: Optional[DeviceMesh], ddp_model, hp:
         raise ValueError(f"Unsupported optimizer: {name}")
     if hp.replicate_mesh_grad_sync and name not in ("dion", "dion_reference"):
         raise ValueError("replicate_mesh_grad_sync is set for non-Dion optimizer")
+    if hp.replicate_mesh_grad_sync and replicate_mesh is None and dist.is_initialized() \
+            and dist.get_world_size() > 1:
+        raise ValueError("replicate_mesh_grad_sync needs a replicate mesh or data-parallel "
+                         "process group: nobody would average the gradients")
     return opt
 
 
@@ -294,7 +298,11 @@ class CheckpointManager:
     loaders and step, written to a temporary directory and renamed into place."""
 
     def __init__(self, checkpoint_dir: str, model, optimizer, train_loader, val_loader,
-                 wandb_id: Optional[str] = None):
+                 wandb_id: Optional[str] = None, keep_last: int = 2):
+        """``keep_last``: how many ``step_*`` directories survive a save (0 keeps all).  A
+        directory written by the reference trainer (a single ``checkpoint`` folder that each
+        save replaces, train.py:589-692 there) is recognised on load."""
+        self.keep_last = keep_last
         self.checkpoint_dir = checkpoint_dir
         self.model, self.optimizer = model, optimizer
         self.train_loader, self.val_loader = train_loader, val_loader
@@ -307,12 +315,23 @@ class CheckpointManager:
     def _path(self, step: int) -> str:
         return os.path.join(self.checkpoint_dir, f"step_{step:08d}")
 
-    def latest_step(self) -> Optional[int]:
+    def _steps(self) -> List[int]:
         if not os.path.isdir(self.checkpoint_dir):
-            return None
-        steps = [int(d.split("_")[1]) for d in os.listdir(self.checkpoint_dir)
-                 if d.startswith("step_") and d.split("_")[1].isdigit()]
-        return max(steps) if steps else None
+            return []
+        return sorted(int(d.split("_")[1]) for d in os.listdir(self.checkpoint_dir)
+                      if d.startswith("step_") and d.split("_")[1].isdigit())
+
+    def latest_step(self) -> Optional[int]:
+        steps = self._steps()
+        return steps[-1] if steps else None
+
+    def _single_folder(self) -> Optional[str]:
+        """The reference trainer's layout: one folder named ``checkpoint``."""
+        path = os.path.join(self.checkpoint_dir, "checkpoint")
+        return path if os.path.isdir(path) else None
+
+    def exists(self) -> bool:
+        return self.latest_step() is not None or self._single_folder() is not None
 
     def _state(self, step: int) -> Dict[str, Any]:
         model_sd, optim_sd = get_state_dict(self.model, self.optimizer)
@@ -323,6 +342,10 @@ class CheckpointManager:
                 "step": step, "wandb_id": self.wandb_id or ""}
 
     def save(self, step: int) -> None:
+        # A kernel timeout (peer GPU that never delivered) must not end up in a checkpoint.
+        check = getattr(self.optimizer, "check_device_status", None)
+        if check is not None:
+            check()
         final = self._path(step)
         tmp = final + ".tmp"
         rank = dist.get_rank() if dist.is_initialized() else 0
@@ -337,15 +360,19 @@ class CheckpointManager:
         if rank == 0:
             shutil.rmtree(final, ignore_errors=True)
             os.replace(tmp, final)
+            if self.keep_last > 0:
+                for old in self._steps()[:-self.keep_last]:
+                    shutil.rmtree(self._path(old), ignore_errors=True)
         if dist.is_initialized():
             dist.barrier()
 
     def load(self, step: Optional[int] = None) -> int:
         step = self.latest_step() if step is None else step
-        if step is None:
+        path = self._path(step) if step is not None else self._single_folder()
+        if path is None:
             raise FileNotFoundError(f"no checkpoint under {self.checkpoint_dir}")
         state = self._state(0)
-        dcp.load(state, checkpoint_id=self._path(step))
+        dcp.load(state, checkpoint_id=path)
         set_state_dict(self.model, self.optimizer, model_state_dict=state["model"],
                        optim_state_dict=state["optimizer"])
         if self.train_loader and state["train_loader"]:
@@ -479,7 +506,16 @@ def main(argv: Optional[List[str]] = None) -> None:
         comm = use_symmetric_all_gather(raw_model, mesh["fs"].get_group(), device)
         print0("FSDP all-gather: " + ("symmetric-memory kernel" if comm is not None
                                       else "NCCL (symmetric memory unavailable)"))
-    optimizer = init_optimizer(raw_model, mesh, ddp, hp, args)
+    replicas = ddp
+    if graph_step and world > 1:
+        # No DDP wrapper on this path: the optimizer still has to know the data-parallel group,
+        # to divide the orthogonalization work over the ranks (megabatch family).
+        replicas = argparse.Namespace(process_group=dist.group.WORLD)
+    optimizer = init_optimizer(raw_model, mesh, replicas, hp, args)
+    if (graph_step or args.cuda_graph) and device.type == "cuda":
+        from .optim.cuda_graph import require_graph_replay_support
+
+        require_graph_replay_support(optimizer, "--graph_step / --cuda_graph")
     scheduler = torch.optim.lr_scheduler.LambdaLR(
         optimizer, lambda s: lr_multiplier(s, hp.num_iterations, hp.warmup_ratio, hp.warmdown_ratio))
     stepper = optimizer
@@ -492,7 +528,7 @@ def main(argv: Optional[List[str]] = None) -> None:
     start_step = 0
     if hp.checkpoint_dir:
         ckpt = CheckpointManager(hp.checkpoint_dir, raw_model, optimizer, train_loader, val_loader)
-        if ckpt.latest_step() is not None:
+        if ckpt.exists():
             done = ckpt.load()
             start_step = done + 1     # the checkpoint was written after step ``done`` completed
             scheduler.last_epoch = start_step
@@ -549,6 +585,8 @@ def main(argv: Optional[List[str]] = None) -> None:
                 dist.all_reduce(vl, op=dist.ReduceOp.AVG if device.type == "cuda" else dist.ReduceOp.SUM)
                 if device.type != "cuda":
                     vl /= world
+            if hasattr(optimizer, "check_device_status"):
+                optimizer.check_device_status()   # the host synchronizes here anyway
             msg = f"step:{step}/{hp.num_iterations} val_loss:{vl.item():.4f}"
             if timed:
                 msg += (f" step_avg:{tot_all / timed:.2f}ms fwd_bwd_avg:{tot_fb / timed:.2f}ms "

@@ -91,3 +91,22 @@ def test_reference_benchmark_command_line_is_translated():
         ["--batch", "4", "--single", "768", "3072"]
     assert mod.translate(["--grid", "--expansion", "4"]) == ["--batch", "1", "--sweep", "--expansion", "4"]
     assert mod.translate(["--plot", "--batch_size", "2"]) == ["--batch", "2", "--curve"]
+
+
+def test_aux_block_work_model():
+    """Work of the GPT-1B Muon step used for the roofline fractions of the `aux` block."""
+    bench = _bench()
+    shapes = bench.aux_shapes()
+    assert len(shapes) == 144 and shapes.count((2048, 2048)) == 96
+    one = bench.aux_bounds(1)
+    eight = bench.aux_bounds(8)
+    # 5 x (4 m^2 n + 2 m^3): 96 square matrices + 48 matrices of 2048 x 8192
+    nominal = 5 * (96 * 6 * 2048 ** 3 + 48 * (4 * 2048 ** 2 * 8192 + 2 * 2048 ** 3)) / 1e12
+    assert abs(one["ns_tflop_nominal_per_gpu"] - nominal) < 1e-6
+    assert abs(eight["ns_tflop_nominal_per_gpu"] * 8 - nominal) < 1e-6
+    assert one["ns_tflop_needed_per_gpu"] < one["ns_tflop_nominal_per_gpu"]
+    assert one["nvlink_mb_sent_per_gpu"] == 0 and one["nvlink_bound_ms"] == 0
+    # every rank sends 7/8 of its 1/8 of all bf16 elements, once out and once back
+    elems = 96 * 2048 ** 2 + 48 * 2048 * 8192
+    assert abs(eight["nvlink_mb_sent_per_gpu"] - 2 * elems * 2 / 8 * 7 / 8 / 1e6) < 1e-6
+    assert eight["roofline_ms"] == max(eight["compute_bound_ms"], eight["nvlink_bound_ms"])

@@ -152,3 +152,41 @@ def test_normuon_rowstats_and_apply(shape):
     F.muon_post(Xg, list(U.cuda().unbind(0)), torch.tensor(0.02).cuda(), 0.01, 1.2, False,
                 rowscale=list(rg.unbind(0)), normU2=ug, normNew2=ng)
     _close(Xc, Xg, 1e-5)
+
+
+@pytest.mark.parametrize("select_dim", [-2, -1])
+@pytest.mark.parametrize("m_dtype", [torch.float32, torch.bfloat16])
+def test_dion2_post_masked_matches_torch(select_dim, m_dtype):
+    """Global-scope post step: the kernels and the PyTorch form agree; slices of the momentum
+    that were not selected are bit-identical."""
+    from dion_b200.ops import foreach as F
+    torch.manual_seed(0)
+    n, rows, cols = 3, 72, 200
+    X = [torch.randn(rows, cols) for _ in range(n)]
+    M = [torch.randn(rows, cols).to(m_dtype) for _ in range(n)]
+    U = []
+    for _ in range(n):
+        u = torch.zeros(rows, cols)
+        num = rows if select_dim == -2 else cols
+        pick = torch.randperm(num)[: num // 4]
+        if select_dim == -2:
+            u[pick] = torch.randn(len(pick), cols)
+        else:
+            u[:, pick] = torch.randn(rows, len(pick))
+        U.append(u.bfloat16())
+    Xc, Mc = [x.clone() for x in X], [m.clone() for m in M]
+    F.dion2_post_masked(Xc, Mc, U, 0.02, 0.01, 1.7, 0.9, select_dim)          # PyTorch form
+    Xg, Mg, Ug = [x.cuda() for x in X], [m.cuda() for m in M], [u.cuda() for u in U]
+    lr = torch.tensor(0.02, device="cuda")
+    F.dion2_post_masked(Xg, Mg, Ug, lr, 0.01, 1.7, 0.9, select_dim)           # kernels
+    torch.cuda.synchronize()
+    for t in range(n):
+        assert (Xc[t] - Xg[t].cpu()).abs().max().item() < 1e-5
+        assert (Mc[t].float() - Mg[t].cpu().float()).abs().max().item() <= (
+            1e-6 if m_dtype == torch.float32 else 1e-2)
+        untouched = (U[t].float().abs().sum(dim=-1 if select_dim == -2 else -2) == 0)
+        a, b = M[t], Mg[t].cpu()
+        if select_dim == -2:
+            assert torch.equal(a[untouched], b[untouched])
+        else:
+            assert torch.equal(a[:, untouched], b[:, untouched])

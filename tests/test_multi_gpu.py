@@ -112,6 +112,53 @@ def test_wait_on_flag_nobody_sets_times_out_cleanly():
     gemm.check_status()                       # status was cleared
 
 
+def test_update_is_refused_after_a_timeout_and_the_next_step_raises():
+    """The apply kernel waits for a producer that never signals: the wait runs out, the weights
+    stay bit-identical, the status names the silent rank, and the optimizer's next step raises
+    without anybody having synchronized on its behalf."""
+    from dion_b200.ops import _backend, foreach, gemm
+    dev = torch.device("cuda")
+    _backend.lib("foreach_ops")
+    _backend.set_wait_budget_ms(50)
+    try:
+        gemm.status_tensor(dev).zero_()
+        g = torch.Generator(device=dev).manual_seed(0)
+        X = [torch.randn(64, 128, device=dev, generator=g) for _ in range(4)]
+        U = [torch.randn(64, 128, device=dev, generator=g).bfloat16() for _ in range(4)]
+        before = [x.clone() for x in X]
+        flags = torch.zeros(2, dtype=torch.int32, device=dev)   # producers 0 and 1: never raised
+        seq = torch.ones((), dtype=torch.int32, device=dev)
+        wait = (flags, seq, 2, gemm.status_tensor(dev))
+        foreach.muon_post(X, U, 0.1, 0.01, 1.0, wait=wait)
+        torch.cuda.synchronize()
+        for x, b in zip(X, before):
+            assert torch.equal(x, b)
+        # Once the status word is set, later kernels of the same kind refuse as well, even if
+        # their own producer has signalled.
+        flags.fill_(1)
+        foreach.muon_post(X, U, 0.1, 0.01, 1.0, wait=wait)
+        V = [torch.ones(64, 1, device=dev) for _ in range(4)]
+        foreach.normuon_rowstats(torch.stack(U), V, 0.95, guard=gemm.status_tensor(dev))
+        torch.cuda.synchronize()
+        for x, b in zip(X, before):
+            assert torch.equal(x, b)
+        assert all(bool((v == 1).all()) for v in V)
+        # An optimizer notices at its next step (snapshot taken after a step, read before one).
+        p = torch.nn.Parameter(torch.randn(64, 128, device=dev))
+        opt = dion_b200.Muon([dict(params=[p])], lr=0.01)
+        opt._snapshot_device_status()
+        torch.cuda.synchronize()
+        p.grad = torch.randn_like(p)
+        with pytest.raises(RuntimeError, match="flag of source rank") as err:
+            opt.step()
+        assert "waited for sequence 1, found 0" in str(err.value)
+        opt.step()                       # status cleared: the run can go on
+        gemm.check_status()
+    finally:
+        _backend.set_wait_budget_ms(2000)
+        gemm.status_tensor(dev).zero_()
+
+
 @pytest.mark.parametrize("name,kw", [("NorMuon", dict(use_polar_express=False)),
                                      ("Dion2", dict(fraction=0.25)),
                                      ("NorDion2", dict(fraction=0.5))])

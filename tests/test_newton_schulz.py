@@ -59,8 +59,13 @@ def test_cuda_vs_torch(variant, shape):
     check_status()
     ref = NS.torch_reference(variant)(G)
     assert got.shape == G.shape and got.dtype == torch.bfloat16
-    # bf16 iterations amplify rounding differences; the reference's own Triton-vs-torch test
-    # allows 0.02 (entries are O(1/sqrt(n))), Gram-NS keeps less precision in the small matrix.
-    tol = 0.06 if variant == "gram" else 0.03
-    assert (got.float() - ref.float()).abs().max().item() < tol
+    # Entries of an orthogonalized matrix are O(1/sqrt(n)), so a bound on the largest absolute
+    # difference says little: compare every matrix by its relative Frobenius error.  Two bf16
+    # evaluations of the same five iterations differ by a few percent (different accumulation
+    # order and rounding points); a wrong coefficient or operand gives errors of order one.
+    # Gram-NS keeps less precision in the small matrix it iterates on.
+    g3 = got.float().reshape(-1, *got.shape[-2:])
+    r3 = ref.float().reshape(-1, *ref.shape[-2:])
+    rel = (g3 - r3).flatten(1).norm(dim=1) / r3.flatten(1).norm(dim=1)
+    assert rel.max().item() < (0.2 if variant == "gram" else 0.1), rel.tolist()
     assert _orth_err(got) < 0.4

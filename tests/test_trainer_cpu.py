@@ -113,6 +113,13 @@ def test_trainer_ddp_and_fsdp_resume(tmp_path):
     # and optimizer state: its log lines repeat those of the uninterrupted run.
     line = [ln for ln in full.splitlines() if ln.startswith("Step 2:")]
     assert line and line[0] in out
+    # A directory in the reference trainer's layout (one folder named "checkpoint") resumes too.
+    for name in os.listdir(ck):
+        if name != "step_00000001":
+            shutil.rmtree(os.path.join(ck, name), ignore_errors=True)
+    os.rename(os.path.join(ck, "step_00000001"), os.path.join(ck, "checkpoint"))
+    out = _torchrun(fsdp + ["--num_iterations", "3"])
+    assert "Resumed from step 1" in out and line[0] in out
 
 
 def test_trainer_hybrid_meshes():
