@@ -45,15 +45,24 @@ struct LrGemmArgs {
   int tiles_per_mat;
   int total_tiles;
   int* status;
-  // Optional reduction instead of a store (fp32 C only): every value is added to the same
-  // position of up to 8 targets (symmetric buffers of the ranks of a group, this rank's
-  // included), so that after all ranks have run the kernel each target holds the sum.
-  long long red_targets[8];
-  int n_red;
+  // How the result leaves (fp32 C only for the last two):
+  //   kOutStore      plain store into C / c_table[b]
+  //   kOutReduce     red.add into C / c_table[b]: with c_table[b] pointing into the buffer of
+  //                  the rank that owns matrix b (peer-mapped memory), every rank's launch adds
+  //                  its contribution there - a reduce-scatter over the batch carried by the
+  //                  epilogue
+  //   kOutBroadcast  store into each of n_targets buffers at matrix slot (slot0 + b): an
+  //                  all-gather carried by the epilogue
+  int out_mode;
+  long long targets[8];
+  int n_targets;
+  int slot0;
   // Optional: column sums of squares of the stored values, accumulated per matrix into
   // colsq[b * N + c] (fp32, pre-zeroed).
   float* colsq;
 };
+
+enum : int { kOutStore = 0, kOutReduce = 1, kOutBroadcast = 2 };
 
 struct LrMaps {
   CUtensorMap a[3];
@@ -68,6 +77,27 @@ __host__ __device__ constexpr uint32_t make_idesc(int fmt, int m, int n, int a_m
          | (static_cast<uint32_t>(b_mn) << 16)
          | (static_cast<uint32_t>(n >> 3) << 17)
          | (static_cast<uint32_t>(m >> 4) << 24);
+}
+
+// Shared-memory descriptor of an MN-major operand.  16-bit elements use the plain 128-byte
+// swizzle (16-byte chunks XORed with the row, 8-row atoms 1024 bytes apart).  For 32-bit (tf32)
+// elements the tensor core only accepts the "128-byte swizzle with 32-byte atoms" layout: 32-byte
+// chunks XORed with the row, 4-row atoms 512 bytes apart - the layout TMA produces with
+// CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B.  `lead_bytes` is the distance between consecutive
+// 128-byte-wide blocks along MN.
+template <int EB>
+__device__ __forceinline__ uint64_t make_mn_desc(uint32_t saddr, uint32_t lead_bytes) {
+  if constexpr (EB == 4) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((saddr & 0x3FFFF) >> 4);
+    d |= static_cast<uint64_t>((lead_bytes >> 4) & 0x3FFF) << 16;
+    d |= static_cast<uint64_t>((512u >> 4) & 0x3FFF) << 32;
+    d |= static_cast<uint64_t>(1) << 46;  // descriptor version for sm_100
+    d |= static_cast<uint64_t>(1) << 61;  // SWIZZLE_128B with 32-byte atoms
+    return d;
+  } else {
+    return make_smem_desc(saddr, lead_bytes, 1024);
+  }
 }
 
 template <int EB>
@@ -217,9 +247,9 @@ lr_gemm_kernel(const __grid_constant__ LrMaps maps, const LrGemmArgs p) {
           const uint32_t sb = sa + kABytes;
 #pragma unroll
           for (int k = 0; k < BK / UK; ++k) {
-            const uint64_t da = A_MN ? make_smem_desc(sa + k * kStepMN, kBoxBytes, 1024)
+            const uint64_t da = A_MN ? make_mn_desc<EB>(sa + k * kStepMN, kBoxBytes)
                                      : make_smem_desc(sa + k * 32, 16, 1024);
-            const uint64_t db = B_MN ? make_smem_desc(sb + k * kStepMN, kBoxBytes, 1024)
+            const uint64_t db = B_MN ? make_mn_desc<EB>(sb + k * kStepMN, kBoxBytes)
                                      : make_smem_desc(sb + k * 32, 16, 1024);
             tc_mma<EB>(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
           }
@@ -320,19 +350,31 @@ lr_gemm_kernel(const __grid_constant__ LrMaps maps, const LrGemmArgs p) {
             for (int j = 0; j < 32; ++j) v[j] *= p.alpha;
           }
           // ---- store / reduce ----
-          if (p.n_red > 0) {
-            for (int tgt = 0; tgt < p.n_red; ++tgt) {
-              float* crow = reinterpret_cast<float*>(p.red_targets[tgt]) +
-                            (long long)b * p.strideC + (long long)r * p.ldc + c0;
-              if (c_vec && full) {
+          if (p.out_mode == kOutReduce) {
+            float* crow = reinterpret_cast<float*>(Cb) + (long long)r * p.ldc + c0;
+            if (c_vec && full) {
+#pragma unroll
+              for (int q = 0; q < 8; ++q)
+                red_add_f32x4(crow + q * 4,
+                              make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]));
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (c0 + j < p.N) atomicAdd(crow + j, v[j]);
+            }
+          } else if (p.out_mode == kOutBroadcast) {
+            for (int tgt = 0; tgt < p.n_targets; ++tgt) {
+              float* crow = reinterpret_cast<float*>(p.targets[tgt]) +
+                            (long long)(p.slot0 + b) * p.strideC + (long long)r * p.ldc + c0;
+              if ((p.ldc & 3) == 0 && (p.strideC & 3) == 0 && full) {
 #pragma unroll
                 for (int q = 0; q < 8; ++q)
-                  red_add_f32x4(crow + q * 4,
-                                make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]));
+                  *reinterpret_cast<float4*>(crow + q * 4) =
+                      make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
               } else {
 #pragma unroll
                 for (int j = 0; j < 32; ++j)
-                  if (c0 + j < p.N) atomicAdd(crow + j, v[j]);
+                  if (c0 + j < p.N) crow[j] = v[j];
               }
             }
           } else if (p.c_dt == 0) {
@@ -437,9 +479,11 @@ static EncodeTiledFnLr get_encode_fn_lr() {
 }
 
 // 3-D map over [batch, rows, cols] (cols contiguous) of 2- or 4-byte elements, box
-// {box_cols, box_rows, 1}, 128-byte swizzle (box_cols * elem_bytes == 128).
+// {box_cols, box_rows, 1}, 128-byte swizzle (box_cols * elem_bytes == 128); `atom32` selects the
+// variant with 32-byte atoms that MN-major tf32 operands need (see make_mn_desc).
 static int make_map_lr(CUtensorMap* map, const void* ptr, int eb, int batch, int rows, int cols,
-                       long long ld, long long batch_stride, int box_cols, int box_rows) {
+                       long long ld, long long batch_stride, int box_cols, int box_rows,
+                       bool atom32 = false) {
   EncodeTiledFnLr enc = get_encode_fn_lr();
   if (!enc) return -1;
   cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)batch};
@@ -449,7 +493,8 @@ static int make_map_lr(CUtensorMap* map, const void* ptr, int eb, int batch, int
   cuuint32_t estr[3] = {1, 1, 1};
   CUresult r = enc(map, eb == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
                    3, const_cast<void*>(ptr), dims, strides, box, estr,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : -2;
 }
@@ -494,8 +539,10 @@ struct DionLrOperand {
 struct DionLrExtra {
   const long long* c_table;   // per-matrix output pointers (C must then be null)
   const long long* d_table;   // per-matrix addend pointers
-  long long red_targets[8];   // add into these buffers instead of storing (fp32 C)
-  int n_red;
+  int out_mode;               // 0 store, 1 red.add into C / c_table[b], 2 store to all targets
+  long long targets[8];       // mode 2: bases of fp32 buffers [slots, M, N] (ldc, strideC apply)
+  int n_targets;
+  int slot0;                  // mode 2: matrix b goes to slot slot0 + b
   float* colsq;               // [batch, N] column sums of squares of the result
 };
 
@@ -529,10 +576,12 @@ DION_EXPORT int dion_lr_gemm(int elem_bytes, int nseg, const DionLrOperand* A,
       return -12;
     int rc;
     if (!a_mn) rc = make_map_lr(&maps.a[s], a.ptr, elem_bytes, batch, M, K, a.ld, a.stride, bk, LBM);
-    else rc = make_map_lr(&maps.a[s], a.ptr, elem_bytes, batch, K, M, a.ld, a.stride, box_mn, bk);
+    else rc = make_map_lr(&maps.a[s], a.ptr, elem_bytes, batch, K, M, a.ld, a.stride, box_mn, bk,
+                          elem_bytes == 4);
     if (rc != 0) return -13;
     if (!b_mn) rc = make_map_lr(&maps.b[s], b.ptr, elem_bytes, batch, N, K, b.ld, b.stride, bk, bn);
-    else rc = make_map_lr(&maps.b[s], b.ptr, elem_bytes, batch, K, N, b.ld, b.stride, box_mn, bk);
+    else rc = make_map_lr(&maps.b[s], b.ptr, elem_bytes, batch, K, N, b.ld, b.stride, box_mn, bk,
+                          elem_bytes == 4);
     if (rc != 0) return -14;
   }
   LrGemmArgs g;
@@ -548,13 +597,16 @@ DION_EXPORT int dion_lr_gemm(int elem_bytes, int nseg, const DionLrOperand* A,
   if (ex != nullptr) {
     g.c_table = ex->c_table;
     g.d_table = ex->d_table;
-    g.n_red = ex->n_red;
-    for (int i = 0; i < 8; ++i) g.red_targets[i] = ex->red_targets[i];
+    g.out_mode = ex->out_mode;
+    g.n_targets = ex->n_targets;
+    g.slot0 = ex->slot0;
+    for (int i = 0; i < 8; ++i) g.targets[i] = ex->targets[i];
     g.colsq = ex->colsq;
-    if (g.n_red < 0 || g.n_red > 8) return -15;
-    if (g.n_red > 0 && c_dt != 0) return -15;
+    if (g.out_mode < 0 || g.out_mode > 2 || g.n_targets < 0 || g.n_targets > 8) return -15;
+    if (g.out_mode != 0 && c_dt != 0) return -15;
+    if (g.out_mode == 2 && g.n_targets == 0) return -15;
   }
-  if (g.c_table == nullptr && g.C == nullptr && g.n_red == 0) return -16;
+  if (g.c_table == nullptr && g.C == nullptr && g.out_mode != 2) return -16;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (elem_bytes == 4) {
     return bn == 256 ? dispatch_lr<4, 256>(a_mn, b_mn, maps, g, num_sms, s)

@@ -350,6 +350,54 @@ triu_inverse_kernel(const float* __restrict__ Uall, float* Xall, int r) {
   }
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// Gaussian sketch: out[i] = std * N(0,1), a pure function of (seed, i) - Philox4x32-10 with the
+// element index / 4 as counter and Box-Muller on the four outputs - so every replica that derives
+// the same seed generates the same sketch without any communication and without a generator
+// state (the reference draws it from the framework generator, dion/dion.py:1218-1260).
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void philox4x32_10(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3,
+                                              uint32_t k0, uint32_t k1, uint32_t (&out)[4]) {
+#pragma unroll
+  for (int round = 0; round < 10; ++round) {
+    const uint32_t hi0 = __umulhi(0xD2511F53u, c0), lo0 = 0xD2511F53u * c0;
+    const uint32_t hi1 = __umulhi(0xCD9E8D57u, c2), lo1 = 0xCD9E8D57u * c2;
+    c0 = hi1 ^ c1 ^ k0;
+    c1 = lo1;
+    c2 = hi0 ^ c3 ^ k1;
+    c3 = lo0;
+    k0 += 0x9E3779B9u;
+    k1 += 0xBB67AE85u;
+  }
+  out[0] = c0; out[1] = c1; out[2] = c2; out[3] = c3;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+philox_normal_kernel(T* out, long long n, unsigned long long seed, float std_dev) {
+  const long long q = (long long)blockIdx.x * blockDim.x + threadIdx.x;   // group of 4 elements
+  const long long i = q * 4;
+  if (i >= n) return;
+  uint32_t r[4];
+  philox4x32_10((uint32_t)q, (uint32_t)(q >> 32), 0u, 0u, (uint32_t)seed, (uint32_t)(seed >> 32),
+                r);
+  // uniforms in (0, 1]: never zero, so the logarithm is finite
+  const float u0 = ((float)(r[0] >> 8) + 1.0f) * (1.0f / 16777216.0f);
+  const float u1 = ((float)(r[1] >> 8) + 1.0f) * (1.0f / 16777216.0f);
+  const float u2 = ((float)(r[2] >> 8) + 1.0f) * (1.0f / 16777216.0f);
+  const float u3 = ((float)(r[3] >> 8) + 1.0f) * (1.0f / 16777216.0f);
+  const float ra = std_dev * sqrtf(-2.0f * __logf(u0));
+  const float rb = std_dev * sqrtf(-2.0f * __logf(u2));
+  float sa, ca, sb, cb;
+  __sincosf(6.283185307179586f * u1, &sa, &ca);
+  __sincosf(6.283185307179586f * u3, &sb, &cb);
+  const float v[4] = {ra * ca, ra * sa, rb * cb, rb * sb};
+#pragma unroll
+  for (int k = 0; k < 4; ++k)
+    if (i + k < n) out[i + k] = static_cast<T>(v[k]);
+}
+
 }  // namespace dion
 
 using namespace dion;
@@ -427,5 +475,20 @@ DION_EXPORT int dion_triu_inverse(const void* U, void* X, int n, int r, void* st
     dion::triu_inverse_kernel<512><<<n, nb * 32, smem, S(stream)>>>(u, x, r);
   else
     dion::triu_inverse_kernel<1024><<<n, nb * 32, smem, S(stream)>>>(u, x, r);
+  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+// out[i] = std_dev * N(0,1) from (seed, i); dt: 0 = fp32, 1 = bf16.
+DION_EXPORT int dion_philox_normal(void* out, long long n, unsigned long long seed, float std_dev,
+                                   int dt, void* stream) {
+  if (n <= 0) return 0;
+  const long long groups = (n + 3) / 4;
+  const unsigned blocks = (unsigned)((groups + 255) / 256);
+  if (dt == 0)
+    dion::philox_normal_kernel<float><<<blocks, 256, 0, S(stream)>>>(
+        static_cast<float*>(out), n, seed, std_dev);
+  else
+    dion::philox_normal_kernel<__nv_bfloat16><<<blocks, 256, 0, S(stream)>>>(
+        static_cast<__nv_bfloat16*>(out), n, seed, std_dev);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }

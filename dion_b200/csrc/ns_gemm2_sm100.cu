@@ -61,7 +61,38 @@ struct Gemm2Args {
   int total_tiles;
   int* status;
   int epi;      // kEpi*
+  // ---- optional coupling to other GPUs (same meaning as in GemmArgs of ns_gemm_sm100.cu) ----
+  // Gating: rows [s*rows_per_src, (s+1)*rows_per_src) of the gated operands were stored into
+  // this GPU's memory by rank s, which then raised wait_flags[s] to *seq_ptr.
+  const int* wait_flags;
+  const int* seq_ptr;
+  int n_src;
+  int rows_per_src;
+  int wait_a, wait_b, wait_k;
+  // scale = 1 / (sqrt(sum_s scale_partials[b*n_src + s]) * scale_mult + scale_eps)
+  const float* scale_partials;
+  float scale_mult, scale_eps;
+  // Output rows go to their owners instead of C: row r of matrix b is stored at
+  // remote_c[r / rows_per_dst] + ((remote_slot + b) * rows_per_dst + r % rows_per_dst) * ldc.
+  long long remote_c[8];
+  int rows_per_dst;
+  int remote_slot;
 };
+
+__device__ __forceinline__ int ld_acquire_sys2(const int* p) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ float ld_volatile_f32_2(const float* p) {
+  float v;
+  asm volatile("ld.volatile.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
+  return v;
+}
+// Barrier over the 128 epilogue threads without a predicate (barrier 2).
+__device__ __forceinline__ void epi_barrier_plain() {
+  asm volatile("barrier.cta.sync.aligned 2, 128;" ::: "memory");
+}
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
@@ -249,16 +280,52 @@ ns_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     if (lane == 0) {
       uint32_t stage = 0, phase = 0;
       bool ok = true;
+      uint32_t ready_mask = 0;
+      const int seq = p.wait_flags ? *p.seq_ptr : 0;
+      // Waits (bounded) until every source rank owning rows [r0, r1] has delivered.
+      auto sources_ready = [&](int r0, int r1) -> bool {
+        for (int src = r0 / p.rows_per_src; src <= r1 / p.rows_per_src && src < p.n_src; ++src) {
+          if (ready_mask & (1u << src)) continue;
+          if (!flag_wait_bounded(p.wait_flags + src, seq)) {
+            report_peer_timeout(p.status, src, seq, ld_acquire_sys2(p.wait_flags + src));
+            return false;
+          }
+          ready_mask |= 1u << src;
+          // peer stores (generic proxy) must be visible to the TMA reads (async proxy)
+          asm volatile("fence.proxy.async;" ::: "memory");
+        }
+        return true;
+      };
       for (int t = first_tile; t < p.total_tiles && ok; t += tile_step) {
         const int b = t / p.tiles_per_mat;
         const int2 tt = p.tiles[t - b * p.tiles_per_mat];
         const int row0 = tt.x * 256 + (int)cta * BM2;          // this CTA's rows of A
         const int col0 = tt.y * BN2 + (int)cta * (BN2 / 2);    // this CTA's columns of B
+        if (p.wait_flags) {
+          // Gate this CTA's share of the tile on the ranks that own its operand rows.
+          if (p.wait_a && row0 < p.M) {
+            const int r1 = row0 + BM2 - 1 < p.M ? row0 + BM2 - 1 : p.M - 1;
+            ok = sources_ready(row0, r1);
+          }
+          if (ok && p.wait_b && col0 < p.N) {
+            const int r1 = col0 + BN2 / 2 - 1 < p.N ? col0 + BN2 / 2 - 1 : p.N - 1;
+            ok = sources_ready(col0, r1);
+          }
+          if (!ok) break;
+        }
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1)) {
             atomicExch(p.status, kStatusTimeoutEmpty);
             ok = false;
             break;
+          }
+          if (p.wait_flags && p.wait_k) {
+            // K-slab gating: rows [kb*BK2, +BK2) of MN-major operands belong to these sources.
+            const int k1 = kb * BK2 + BK2 - 1 < p.K ? kb * BK2 + BK2 - 1 : p.K - 1;
+            if (!sources_ready(kb * BK2, k1)) {
+              ok = false;
+              break;
+            }
           }
           uint8_t* sa = smem + stage * kStageBytes2;
           uint8_t* sb = sa + kABytes2;
@@ -383,6 +450,9 @@ ns_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     uint32_t aslot = 0, aphase = 0;
     uint32_t g = 0;  // running sub-tile count
     bool ok = true;
+    bool all_sources_ready = false;
+    const bool remote = p.remote_c[0] != 0;
+    const int epi_tid = (warp - 2) * 32 + lane;   // 0..127
     for (int t = first_tile; t < p.total_tiles && ok; t += tile_step) {
       const int b = t / p.tiles_per_mat;
       const int2 tt = p.tiles[t - b * p.tiles_per_mat];
@@ -391,6 +461,28 @@ ns_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       tc_fence_after();
       float sc = 1.f;
       if (p.scale != nullptr) sc = p.scale[b];
+      if (p.scale_partials != nullptr && mine_ok) {
+        // The norm needs every source's partial sum: wait for all of them once.
+        if (!all_sources_ready) {
+          int fine = 1;
+          if (lane == 0) {
+            const int seq = *p.seq_ptr;
+            for (int src = 0; src < p.n_src && fine; ++src) {
+              if (!flag_wait_bounded(p.wait_flags + src, seq)) {
+                report_peer_timeout(p.status, src, seq, ld_acquire_sys2(p.wait_flags + src));
+                fine = 0;
+              }
+            }
+          }
+          fine = __shfl_sync(0xffffffffu, fine, 0);
+          if (!fine) mine_ok = false;
+          all_sources_ready = true;
+        }
+        float ss = 0.f;
+        for (int src = 0; src < p.n_src; ++src)
+          ss += ld_volatile_f32_2(p.scale_partials + (long long)b * p.n_src + src);
+        sc = 1.f / (sqrtf(ss) * p.scale_mult + p.scale_eps);
+      }
       const float alpha = p.alpha * ipow2(sc, p.alpha_pow);
       const float beta = p.beta * ipow2(sc, p.beta_pow);
       const int row0 = tt.x * 256 + (int)cta * BM2;
@@ -479,6 +571,33 @@ ns_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         // tells whether any of them gave up.
         ok = epi_barrier_and(mine_ok);
         if (!ok) break;
+        if (remote) {
+          // Rows leave for the ranks that own them: 16-byte stores over NVLink, eight
+          // consecutive threads per 128-byte row segment of the (swizzled) sub-tile.
+          const int chunk = epi_tid & 7;
+          if (c0 + chunk * 8 < p.N) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int rr = (epi_tid >> 3) + 16 * i;     // row of the 128-row half-tile
+              const int grow = row0 + rr;
+              if (grow < p.M) {
+                const uint8_t* src = dc + (uint32_t)(rr >> 6) * 8192u + (uint32_t)(rr & 63) * 128u +
+                                     (((uint32_t)chunk ^ (uint32_t)(rr & 7)) << 4);
+                const int dst = grow / p.rows_per_dst;
+                __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.remote_c[dst]) +
+                    ((long long)(p.remote_slot + b) * p.rows_per_dst +
+                     (grow - dst * p.rows_per_dst)) * p.ldc + c0 + chunk * 8;
+                *reinterpret_cast<uint4*>(out) = *reinterpret_cast<const uint4*>(src);
+              }
+            }
+          }
+          epi_barrier_plain();   // the buffer has been read: it may take the next D sub-tile
+          if (elected && has_d && pf_valid()) {
+            issue_d(g + 2);
+            pf_advance();
+          }
+          continue;
+        }
         if (elected) {
           if (row0 < p.M) tma_store_3d(&map_c, dc, c0, row0, b);
           if (row0 + 64 < p.M) tma_store_3d(&map_c, dc + 8192, c0, row0 + 64, b);
@@ -606,20 +725,35 @@ static int launch2(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorM
 
 }  // namespace dion
 
-// Same contract as dion_ns_gemm (ns_gemm_sm100.cu) for the features it has: bf16 output, optional
-// D, per-batch scale, symmetric mode; `tiles` holds (tile_m, tile_n) pairs in units of 256 x 256.
-DION_EXPORT int dion_ns_gemm2(const void* A, long long lda, long long strideA, int a_mn,
-                              const void* B, long long ldb, long long strideB, int b_mn, void* C,
-                              long long ldc, long long strideC, const void* D, long long ldd,
-                              long long strideD, int batch, int M, int N, int K, float alpha,
-                              float beta, const float* scale, int alpha_pow, int beta_pow, int sym,
-                              const void* tiles, int tiles_per_mat, int epi, int* status,
-                              void* stream) {
+// Optional cross-GPU coupling of one launch; see the matching fields of Gemm2Args (the layout is
+// shared with DionGemmExtra of ns_gemm_sm100.cu so that one host structure serves both kernels).
+struct DionGemm2Extra {
+  const int* wait_flags;
+  const int* seq_ptr;
+  int n_src, rows_per_src, wait_a, wait_b, wait_k;
+  const float* scale_partials;
+  float scale_mult, scale_eps;
+  long long remote_c[8];
+  int rows_per_dst, remote_slot;
+};
+
+// Same contract as dion_ns_gemm_ex (ns_gemm_sm100.cu) for the features it has: bf16 output,
+// optional D, per-batch scale, symmetric mode, gating on peer flags, norm from partial sums and
+// rows stored to their owners (then C may be null); `tiles` holds (tile_m, tile_n) pairs in units
+// of 256 x 256.
+DION_EXPORT int dion_ns_gemm2_ex(const void* A, long long lda, long long strideA, int a_mn,
+                                 const void* B, long long ldb, long long strideB, int b_mn, void* C,
+                                 long long ldc, long long strideC, const void* D, long long ldd,
+                                 long long strideD, int batch, int M, int N, int K, float alpha,
+                                 float beta, const float* scale, int alpha_pow, int beta_pow,
+                                 int sym, const void* tiles, int tiles_per_mat, int epi,
+                                 int* status, void* stream, const DionGemm2Extra* ex) {
   using namespace dion;
   if (batch <= 0 || M <= 0 || N <= 0 || K <= 0) return 0;
+  const bool remote = ex != nullptr && ex->remote_c[0] != 0;
   if ((lda & 7) || (ldb & 7) || (strideA & 7) || (strideB & 7) ||
       (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) ||
-      C == nullptr)
+      (C == nullptr && !remote))
     return -10;
   CUtensorMap ma, mb;
   if (!a_mn) {
@@ -633,10 +767,15 @@ DION_EXPORT int dion_ns_gemm2(const void* A, long long lda, long long strideA, i
     if (make_map2(&mb, B, batch, K, N, ldb, strideB, 64, BK2) != 0) return -13;
   }
   // C leaves (and D arrives) through TMA in 64 x 64 boxes.
-  if ((ldc & 7) || (strideC & 7) || (reinterpret_cast<uintptr_t>(C) & 15)) return -11;
+  if (C && ((ldc & 7) || (strideC & 7) || (reinterpret_cast<uintptr_t>(C) & 15))) return -11;
   if (D && ((ldd & 7) || (strideD & 7) || (reinterpret_cast<uintptr_t>(D) & 15))) return -11;
+  if (remote && (sym || (ldc & 7) || (N & 7) || (D == nullptr && C == nullptr))) return -15;
   CUtensorMap mc, md;
-  if (make_map2(&mc, C, batch, M, N, ldc, strideC, kSubCols, 64) != 0) return -14;
+  // A map needs some valid tensor even where the kernel never uses it (no D / remote output).
+  const void* c_for_map = C ? C : D;
+  if (make_map2(&mc, c_for_map, batch, M, N, C ? ldc : ldd, C ? strideC : strideD, kSubCols,
+                64) != 0)
+    return -14;
   if (make_map2(&md, D ? D : C, batch, M, N, D ? ldd : ldc, D ? strideD : strideC, kSubCols,
                 64) != 0)
     return -14;
@@ -649,6 +788,25 @@ DION_EXPORT int dion_ns_gemm2(const void* A, long long lda, long long strideA, i
   a.tiles = static_cast<const int2*>(tiles); a.tiles_per_mat = tiles_per_mat;
   a.total_tiles = tiles_per_mat * batch;
   a.status = status;
+  a.wait_flags = nullptr; a.seq_ptr = nullptr; a.n_src = 0; a.rows_per_src = 1;
+  a.wait_a = a.wait_b = a.wait_k = 0;
+  a.scale_partials = nullptr; a.scale_mult = 1.f; a.scale_eps = 0.f;
+  for (int i = 0; i < 8; ++i) a.remote_c[i] = 0;
+  a.rows_per_dst = 1; a.remote_slot = 0;
+  if (ex != nullptr) {
+    if (ex->n_src > 8 || ex->n_src < 0) return -14;
+    if ((ex->wait_flags != nullptr || ex->scale_partials != nullptr) &&
+        (ex->seq_ptr == nullptr || ex->rows_per_src <= 0))
+      return -16;
+    a.wait_flags = ex->wait_flags; a.seq_ptr = ex->seq_ptr; a.n_src = ex->n_src;
+    a.rows_per_src = ex->rows_per_src; a.wait_a = ex->wait_a; a.wait_b = ex->wait_b;
+    a.wait_k = ex->wait_k;
+    a.scale_partials = ex->scale_partials; a.scale_mult = ex->scale_mult;
+    a.scale_eps = ex->scale_eps;
+    for (int i = 0; i < 8; ++i) a.remote_c[i] = ex->remote_c[i];
+    a.rows_per_dst = ex->rows_per_dst > 0 ? ex->rows_per_dst : 1;
+    a.remote_slot = ex->remote_slot;
+  }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   a.epi = epi;
   if (epi == kEpiMul2Sqrt && D == nullptr) return -16;
@@ -668,6 +826,18 @@ DION_EXPORT int dion_ns_gemm2(const void* A, long long lda, long long strideA, i
     case 2: return launch2<true, false, kStagesPlain>(ma, mb, mc, md, a, s);
     default: return launch2<true, true, kStagesPlain>(ma, mb, mc, md, a, s);
   }
+}
+
+DION_EXPORT int dion_ns_gemm2(const void* A, long long lda, long long strideA, int a_mn,
+                              const void* B, long long ldb, long long strideB, int b_mn, void* C,
+                              long long ldc, long long strideC, const void* D, long long ldd,
+                              long long strideD, int batch, int M, int N, int K, float alpha,
+                              float beta, const float* scale, int alpha_pow, int beta_pow, int sym,
+                              const void* tiles, int tiles_per_mat, int epi, int* status,
+                              void* stream) {
+  return dion_ns_gemm2_ex(A, lda, strideA, a_mn, B, ldb, strideB, b_mn, C, ldc, strideC, D, ldd,
+                          strideD, batch, M, N, K, alpha, beta, scale, alpha_pow, beta_pow, sym,
+                          tiles, tiles_per_mat, epi, status, stream, nullptr);
 }
 
 // Whole Newton-Schulz iteration from one host call: for every coefficient triple (a, b, c)

@@ -183,6 +183,12 @@ def pair_default() -> bool:
     return os.environ.get("DION_B200_PAIR_GEMM", "1") != "0"
 
 
+def pair_exchange() -> bool:
+    """Whether launches coupled to other GPUs (flag-gated loads, rows stored to their owners) may
+    use the two-CTA kernel (``DION_B200_PAIR_EXCHANGE``, default on)."""
+    return os.environ.get("DION_B200_PAIR_EXCHANGE", "1") != "0"
+
+
 def _num_tiles(M: int, N: int, bm: int, bn: int, sym: bool) -> int:
     tm_n, tn_n = -(-M // bm), -(-N // bn)
     if not sym:
@@ -279,8 +285,10 @@ def ns_gemm(
     if epi != 0:
         pair = True
     if pair is None:
-        pair_ok = pair_default() and bn is None and extra is None and out_t is None \
-            and out_f32 is None
+        pair_ok = pair_default() and bn is None and out_t is None and out_f32 is None \
+            and (extra is None or pair_exchange())
+        if remote and (sym or N % 8 or D3 is None):
+            pair_ok = False
         # The two-CTA kernel moves C and D by TMA: 16-byte aligned bases, strides multiples of 8.
         for t3, ld_, bs_ in ((C3, ldc, sc), (D3, ldd, sd)):
             if t3 is not None and (t3.data_ptr() % 16 or ld_ % 8 or bs_ % 8):
@@ -292,10 +300,10 @@ def ns_gemm(
         else:
             pair = False
     if pair:
-        if extra is not None or out_t is not None or out_f32 is not None:
-            raise ValueError("the two-CTA kernel has no transposed/fp32/cross-GPU outputs")
+        if out_t is not None or out_f32 is not None:
+            raise ValueError("the two-CTA kernel has no transposed/fp32 outputs")
         tiles = tile_table(M, N, 256, sym, dev, bm=256)
-        rc = _backend.lib("ns_gemm2_sm100").dion_ns_gemm2(
+        rc = _backend.lib("ns_gemm2_sm100").dion_ns_gemm2_ex(
             _p(A3), ctypes.c_longlong(lda), ctypes.c_longlong(sa),
             ctypes.c_int(1 if a_is_km else 0),
             _p(B3), ctypes.c_longlong(ldb), ctypes.c_longlong(sb),
@@ -307,6 +315,7 @@ def ns_gemm(
             ctypes.c_int(alpha_pow), ctypes.c_int(beta_pow), ctypes.c_int(1 if sym else 0),
             _p(tiles), ctypes.c_int(tiles.size(0)), ctypes.c_int(epi), _p(st),
             ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream),
+            ctypes.byref(extra) if extra is not None else None,
         )
         if rc != 0:
             raise RuntimeError(f"dion_ns_gemm2 launch failed with code {rc}")

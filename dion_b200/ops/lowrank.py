@@ -33,7 +33,8 @@ class _LrOperand(ctypes.Structure):
 
 class _LrExtra(ctypes.Structure):
     _fields_ = [("c_table", ctypes.c_void_p), ("d_table", ctypes.c_void_p),
-                ("red_targets", ctypes.c_longlong * 8), ("n_red", ctypes.c_int),
+                ("out_mode", ctypes.c_int), ("targets", ctypes.c_longlong * 8),
+                ("n_targets", ctypes.c_int), ("slot0", ctypes.c_int),
                 ("colsq", ctypes.c_void_p)]
 
 
@@ -94,8 +95,9 @@ def lr_gemm(A: Tensor, B: Tensor, *, a_mn: bool = False, b_mn: bool = False,
             out_list: Optional[List[Tensor]] = None, D: Optional[Tensor] = None,
             d_list: Optional[List[Tensor]] = None, alpha: float = 1.0, beta: float = 0.0,
             precise: bool = False, colsq: Optional[Tensor] = None,
-            red_targets: Optional[List[int]] = None, red_ld: int = 0, red_stride: int = 0,
-            bn: Optional[int] = None) -> Optional[Tensor]:
+            reduce_into: Optional[Tensor] = None, reduce_ld: int = 0,
+            broadcast_to: Optional[List[int]] = None, slot0: int = 0, out_ld: int = 0,
+            out_stride: int = 0, bn: Optional[int] = None) -> Optional[Tensor]:
     """``out[b] = alpha * A[b] @ op(B[b]) + beta * D[b]`` on the tensor cores (tf32 for fp32
     operands, bf16 otherwise; fp32 accumulation), see csrc/lowrank_gemm_sm100.cu.
 
@@ -104,8 +106,15 @@ def lr_gemm(A: Tensor, B: Tensor, *, a_mn: bool = False, b_mn: bool = False,
     lists of per-matrix tensors (separately allocated weights); ``D`` may be ``out``.
     ``precise`` (fp32 operands): three tf32 products recover fp32-level accuracy.
     ``colsq [batch, N]`` (fp32, zeroed by the caller) receives the column sums of squares of the
-    result.  ``red_targets``: raw addresses of fp32 buffers (same layout ``red_ld`` /
-    ``red_stride``) to which the result is added instead of being stored."""
+    result.
+
+    Two ways for the result to leave over NVLink instead of being stored locally (fp32):
+    ``reduce_into``: int64 device tensor of one address per matrix (row length ``reduce_ld``);
+    the result is added there with ``red.add`` - with each address inside the buffer of the rank
+    that owns the matrix, the launches of all ranks together perform a reduce-scatter.
+    ``broadcast_to``: raw base addresses of buffers ``[slots, M, N]`` (``out_ld``,
+    ``out_stride``) on every rank; matrix ``b`` is stored into slot ``slot0 + b`` of each - an
+    all-gather."""
     from . import gemm
 
     assert lr_gemm_ok(A, B), "operands violate the kernel's layout rules; see lr_gemm_ok()"
@@ -130,11 +139,17 @@ def lr_gemm(A: Tensor, B: Tensor, *, a_mn: bool = False, b_mn: bool = False,
     ex = _LrExtra()
     use_ex = False
     c_ptr, ldc, sc, c_dt = 0, N, M * N, 0
-    if red_targets is not None:
-        for i, addr in enumerate(red_targets):
-            ex.red_targets[i] = addr
-        ex.n_red = len(red_targets)
-        ldc, sc = red_ld or N, red_stride or M * N
+    if reduce_into is not None:
+        assert reduce_into.dtype == torch.int64 and reduce_into.numel() >= batch
+        ex.c_table = reduce_into.data_ptr()
+        ex.out_mode = 1
+        ldc = reduce_ld or N
+        use_ex = True
+    elif broadcast_to is not None:
+        for i, addr in enumerate(broadcast_to):
+            ex.targets[i] = addr
+        ex.n_targets, ex.slot0, ex.out_mode = len(broadcast_to), slot0, 2
+        ldc, sc = out_ld or N, out_stride or M * N
         use_ex = True
     elif out_list is not None:
         assert len(out_list) == batch
@@ -195,11 +210,31 @@ def sketch_rows(r: int, oversample: float) -> int:
     return int(math.ceil(oversample * r / 128.0) * 128)
 
 
+_sketch_calls = 0
+
+
 def random_sketch(batch: int, k: int, m: int, dtype: torch.dtype, device: torch.device,
                   generator: Optional[torch.Generator] = None) -> Tensor:
-    """Gaussian sketch ``S ~ N(0, 1/k)`` of shape ``[batch, k, m]``."""
+    """Gaussian sketch ``S ~ N(0, 1/k)`` of shape ``[batch, k, m]``.  On a GPU the values are a
+    pure function of the generator's seed and the element index (Philox counter kernel of this
+    package): replicas that derive the same seed draw the same sketch.  Without a generator the
+    seed is the framework's default seed combined with a call counter."""
     S = torch.empty((batch, k, m), dtype=dtype, device=device)
-    S.normal_(std=math.sqrt(1.0 / k), generator=generator)
+    std = math.sqrt(1.0 / k)
+    if S.is_cuda and dtype in (torch.float32, torch.bfloat16) and S.numel():
+        global _sketch_calls
+        if generator is not None:
+            seed = generator.initial_seed()
+        else:
+            _sketch_calls += 1
+            seed = (torch.initial_seed() * 1000003 + _sketch_calls) % (1 << 63)
+        rc = _backend.lib("lowrank_ops").dion_philox_normal(
+            _ptr(S), ctypes.c_longlong(S.numel()), ctypes.c_ulonglong(seed & ((1 << 64) - 1)),
+            ctypes.c_float(std), 0 if dtype == torch.float32 else 1, _stream(device))
+        if rc != 0:
+            raise RuntimeError(f"dion_philox_normal launch failed (code {rc})")
+        return S
+    S.normal_(std=std, generator=generator)
     return S
 
 
@@ -290,13 +325,19 @@ def orthogonalize(P: Tensor, oversample: float = 1.25,
     return right_solve_upper(R2, P32).to(dtype).contiguous()
 
 
-def fix_all_zero_or_nan(P: Tensor, R: Tensor, Q_init: Tensor, B: Tensor) -> Tuple[Tensor, Tensor]:
+def fix_all_zero_or_nan(P: Tensor, R: Tensor, Q_init: Tensor, B: Optional[Tensor],
+                        sum_sq: Optional[Tensor] = None) -> Tuple[Tensor, Tensor]:
     """Branch-free guard: where the (local) momentum ``B[b]`` is entirely zero, return ``P = 0``
     and ``R = Q_init``; elsewhere replace NaNs by zero.  Shards are judged independently so no
     communication is needed.  "Entirely zero" is read off the max-norm (one pass over ``B`` with
     no full-size temporary; a NaN in ``B`` makes the norm NaN, which is not zero, exactly as an
-    element-wise comparison would decide)."""
-    zero = (torch.linalg.vector_norm(B, ord=float("inf"), dim=(-2, -1), keepdim=True) == 0)
+    element-wise comparison would decide).  ``sum_sq`` (one value per matrix, e.g. the sum of
+    squares the momentum kernel accumulates anyway) replaces the pass over ``B``: it is zero, NaN
+    or positive exactly when the max-norm is."""
+    if sum_sq is not None:
+        zero = (sum_sq.reshape(-1, 1, 1) == 0)
+    else:
+        zero = (torch.linalg.vector_norm(B, ord=float("inf"), dim=(-2, -1), keepdim=True) == 0)
     keep = ~zero
     return P.nan_to_num() * keep, R.nan_to_num() * keep + Q_init * zero
 
@@ -368,23 +409,36 @@ def rank_update_stack_(X3: Tensor, A: Tensor, B: Tensor, alpha: float, beta: flo
     foreach_baddbmm_(list(X3.unbind(0)), A, B, alpha=alpha, beta=beta, transpose=transpose)
 
 
-def power_iteration_p(M3: Tensor, Q3: Tensor, transposed: bool = False) -> Tensor:
+def power_iteration_p(M3: Tensor, Q3: Tensor, transposed: bool = False,
+                      reduce_into: Optional[Tensor] = None, alpha: float = 1.0
+                      ) -> Optional[Tensor]:
     """``P = Mt Q`` with ``Mt = M^T`` when ``transposed`` else ``M``, for the stack ``M3
     [B, m, n]`` in its row-major storage and ``Q3 [B, n or m, r]`` (reference:
     dion/dion.py:797-798).  On a GPU both operands are read in place by the tensor-core kernel
-    (``M^T`` as an MN-major operand, ``Q`` as a ``[K, N]`` operand): no transposed copy."""
+    (``M^T`` as an MN-major operand, ``Q`` as a ``[K, N]`` operand): no transposed copy.
+    ``reduce_into`` / ``alpha``: the product (scaled) leaves through ``red.add`` instead of being
+    returned, see :func:`lr_gemm`."""
     if Q3.dtype != M3.dtype:
         Q3 = Q3.to(M3.dtype)
+    if reduce_into is not None:
+        lr_gemm(M3, Q3, a_mn=transposed, b_mn=True, reduce_into=reduce_into, alpha=alpha)
+        return None
     if lr_gemm_ok(M3, Q3):
-        return lr_gemm(M3, Q3, a_mn=transposed, b_mn=True)
-    return (M3.mT if transposed else M3) @ Q3
+        return lr_gemm(M3, Q3, a_mn=transposed, b_mn=True, alpha=alpha)
+    return ((M3.mT if transposed else M3) @ Q3) * alpha if alpha != 1.0 else \
+        (M3.mT if transposed else M3) @ Q3
 
 
 def power_iteration_r(M3: Tensor, P: Tensor, transposed: bool = False,
-                      colsq: Optional[Tensor] = None) -> Tensor:
-    """``R = Mt^T P`` (reference: dion/dion.py:836); ``colsq`` as in :func:`lr_gemm`."""
+                      colsq: Optional[Tensor] = None, reduce_into: Optional[Tensor] = None,
+                      alpha: float = 1.0) -> Optional[Tensor]:
+    """``R = Mt^T P`` (reference: dion/dion.py:836); ``colsq``, ``reduce_into`` and ``alpha`` as
+    in :func:`lr_gemm`."""
     if P.dtype != M3.dtype:
         P = P.to(M3.dtype)
+    if reduce_into is not None:
+        lr_gemm(M3, P, a_mn=not transposed, b_mn=True, reduce_into=reduce_into, alpha=alpha)
+        return None
     if lr_gemm_ok(M3, P):
         return lr_gemm(M3, P, a_mn=not transposed, b_mn=True, colsq=colsq)
     R = (M3 if transposed else M3.mT) @ P

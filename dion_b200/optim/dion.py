@@ -43,6 +43,7 @@ except ImportError:  # pragma: no cover
 from ..ops import foreach as F
 from ..ops import lowrank as LR
 from ..parallel import collectives as C
+from ..parallel import lowrank_sync as LS
 from ..parallel.async_runtime import AsyncRuntime, AsyncTask
 from ..utils.tensors import create_param_batches, group_by_shape, to_local
 from .status import DeviceStatusMixin
@@ -171,6 +172,7 @@ class Dion(DeviceStatusMixin, Optimizer):
         self._generators: Dict[torch.device, torch.Generator] = {}
         self._q_counter = 0
         self._momentum_stacks: Dict[tuple, Tensor] = {}
+        self._lowrank_sync: Dict[tuple, tuple] = {}
 
     # ------------------------------------------------------------------ randomness ----------
     def _agree_on_seed(self) -> int:
@@ -438,6 +440,30 @@ class Dion(DeviceStatusMixin, Optimizer):
                 out["non_sharded"].append(p)
         return out
 
+    def _sync_workspaces(self, first_param: Tensor, pg: ProcessGroup, batch: int, M3: Tensor,
+                         Qb: Tensor, transposed: bool):
+        """(workspace for P, workspace for R or None) of one batch, created collectively on
+        first use.  R needs one only where it is averaged over ``pg`` (unsharded parameters)."""
+        key = (id(first_param), batch, id(pg))
+        ws = self._lowrank_sync.get(key)
+        if ws is None:
+            W = dist.get_world_size(pg)
+            rows_p = M3.size(2) if transposed else M3.size(1)
+            rows_r = M3.size(1) if transposed else M3.size(2)
+            r = Qb.size(-1)
+            dev = M3.device
+            wp = LS.FusedReduceGather(pg, batch // W, rows_p, r, dev)
+            wr = LS.FusedReduceGather(pg, batch // W, rows_r, r, dev) \
+                if self._split_kind(first_param) == "non_sharded" else None
+            ws = self._lowrank_sync[key] = (wp, wr)
+        return ws
+
+    def _split_kind(self, p: Tensor) -> str:
+        cfg = self._get_dion_param_config(p)
+        if cfg.inner_shard_mesh_dim is not None:
+            return "inner_sharded"
+        return "outer_sharded" if cfg.outer_shard_mesh_dim is not None else "non_sharded"
+
     def _momentum_stack(self, params: List[Tensor], batch: int) -> Tensor:
         """``[batch, rows, cols]`` tensor whose first ``len(params)`` slices ARE the (local)
         momentum tensors of ``params``: on first use (and again after ``load_state_dict``, which
@@ -496,9 +522,12 @@ class Dion(DeviceStatusMixin, Optimizer):
             work = C.all_reduce_(G[:n_real], rep, op="avg", async_op=True)
             yield
             work.wait()
+        m_sq = None   # per-matrix sum of squares of the new momentum ("is it all zero?")
         if G[0].is_cuda and G[0].dtype in (torch.float32, torch.bfloat16) \
                 and M3.dtype in (torch.float32, torch.bfloat16):
-            F.muon_pre(G[:n_real], M[:n_real], 0.0, False, add_only=True, out=False)
+            m_sq = torch.zeros(batch, dtype=torch.float32, device=dev)
+            F.muon_pre(G[:n_real], M[:n_real], 0.0, False, add_only=True, out=False,
+                       sumsq=m_sq)
         else:
             torch._foreach_add_(M[:n_real], [g.to(M3.dtype) for g in G[:n_real]])
 
@@ -507,40 +536,71 @@ class Dion(DeviceStatusMixin, Optimizer):
         else:
             Q_full = Q
         Qb = torch.stack(Q_full).to(M3.dtype)
-        P = LR.power_iteration_p(M3, Qb, tr)  # [B, rows_loc, r]; partial over a sharded outer mesh
+        # Reduce-scatter of P (and of R below) inside the GEMM epilogue over peer memory where
+        # the group allows it (see parallel/lowrank_sync.py); otherwise product + collective.
+        rep_pg = C.as_groups(rep)[0] if rep is not None else None
+        sync_pg = rep_pg if (kind == "non_sharded" and compressed) else \
+            (outer_pg if kind == "outer_sharded" else None)
+        fx = None
+        if sync_pg is not None and LR.lr_gemm_ok(M3, Qb) and LS.eligible(sync_pg, dev):
+            fx = self._sync_workspaces(params[0], sync_pg, batch, M3, Qb, tr)
 
         if kind == "non_sharded":
             rank = C.group_rank(rep) if rep is not None else 0
-            if compressed:
-                P1, work = C.reduce_scatter_dim0(P, C.as_groups(rep)[0], op="avg", async_op=True)
-                yield
-                work.wait()
+            if fx is not None:
+                fxP = fx[0]
+                fxP.begin()
+                LR.power_iteration_p(M3, Qb, tr, reduce_into=fxP.targets,
+                                     alpha=1.0 / self._replicate_world_size)
+                fxP.after_gemm()
+                gen = self._generator(dev, step, task_id, rank)
+                fxP.own().copy_(LR.orthogonalize(fxP.own(), oversample, generator=gen))
+                P = fxP.gather()
             else:
-                per_rank = batch // self._replicate_world_size
-                P1 = P[rank * per_rank:(rank + 1) * per_rank]
-            gen = self._generator(dev, step, task_id, rank)
-            P1 = LR.orthogonalize(P1, oversample, generator=gen)
-            if rep is not None:
-                P, work = C.all_gather_dim0(P1, C.as_groups(rep)[0], async_op=True)
-                yield
-                work.wait()
-            else:
-                P = P1
+                P = LR.power_iteration_p(M3, Qb, tr)  # [B, rows_loc, r]
+                if compressed:
+                    P1, work = C.reduce_scatter_dim0(P, rep_pg, op="avg", async_op=True)
+                    yield
+                    work.wait()
+                else:
+                    per_rank = batch // self._replicate_world_size
+                    P1 = P[rank * per_rank:(rank + 1) * per_rank]
+                gen = self._generator(dev, step, task_id, rank)
+                P1 = LR.orthogonalize(P1, oversample, generator=gen)
+                if rep is not None:
+                    P, work = C.all_gather_dim0(P1, rep_pg, async_op=True)
+                    yield
+                    work.wait()
+                else:
+                    P = P1
         elif kind == "outer_sharded":
             o_rank = dist.get_rank(outer_pg)
-            P1, work = C.reduce_scatter_dim0(P, outer_pg, op="sum", async_op=True)
-            yield
-            work.wait()
+            if fx is not None:
+                fxP = fx[0]
+                fxP.begin()
+                LR.power_iteration_p(M3, Qb, tr, reduce_into=fxP.targets)  # partial sums
+                fxP.after_gemm()
+                P1 = fxP.own()
+            else:
+                P = LR.power_iteration_p(M3, Qb, tr)  # partial over the sharded outer mesh
+                P1, work = C.reduce_scatter_dim0(P, outer_pg, op="sum", async_op=True)
+                yield
+                work.wait()
             if compressed:
                 work = C.all_reduce_(P1, rep, op="avg", async_op=True)
                 yield
                 work.wait()
             gen = self._generator(dev, step, task_id, o_rank)
             P1 = LR.orthogonalize(P1, oversample, generator=gen)
-            P, work = C.all_gather_dim0(P1, outer_pg, async_op=True)
-            yield
-            work.wait()
+            if fx is not None:
+                fxP.own().copy_(P1)
+                P = fxP.gather()
+            else:
+                P, work = C.all_gather_dim0(P1, outer_pg, async_op=True)
+                yield
+                work.wait()
         else:  # inner_sharded
+            P = LR.power_iteration_p(M3, Qb, tr)
             if outer_pg is not None:
                 work = C.all_reduce_(P, outer_pg, op="sum", async_op=True)
                 yield
@@ -553,17 +613,29 @@ class Dion(DeviceStatusMixin, Optimizer):
             gen = self._generator(dev, step, task_id, i_rank)
             P = distributed_orthogonalize(P, oversample, inner_pg, generator=gen)
 
-        R = LR.power_iteration_r(M3, P, tr)  # [B, cols_loc, r]
-        if kind == "inner_sharded":
-            work = C.all_reduce_(R, inner_pg, op="sum", async_op=True)
-            yield
-            work.wait()
-        if compressed:
-            work = C.all_reduce_(R, rep, op="avg", async_op=True)
-            yield
-            work.wait()
+        if fx is not None and kind == "non_sharded":
+            fxR = fx[1]     # average of R over the replicas, again inside the epilogue
+            fxR.begin()
+            LR.power_iteration_r(M3, P, tr, reduce_into=fxR.targets,
+                                 alpha=1.0 / self._replicate_world_size)
+            fxR.after_gemm()
+            R = fxR.gather()
+        else:
+            R = LR.power_iteration_r(M3, P, tr)  # [B, cols_loc, r]
+            if kind == "inner_sharded":
+                work = C.all_reduce_(R, inner_pg, op="sum", async_op=True)
+                yield
+                work.wait()
+            if compressed:
+                work = C.all_reduce_(R, rep, op="avg", async_op=True)
+                yield
+                work.wait()
 
-        P, R = LR.fix_all_zero_or_nan(P, R, Qb, M3)
+        P, R = LR.fix_all_zero_or_nan(P, R, Qb, M3, sum_sq=m_sq)
+        if fx is not None:   # the symmetric stacks have been read for the last time
+            for w in fx:
+                if w is not None and w.seq_open:
+                    w.release()
         LR.rank_update_stack_(M3, P, R, alpha=-(1 - mu), beta=1.0, transpose=tr)
 
         if outer_pg is not None:

@@ -166,21 +166,27 @@ def muon_update_megabatch_async(
     global_rows = global_comm_size(X[0], comm_dim)
     if fused_cache is not None and FX.eligible(Ml[0].shape, comm_dim, global_rows, world_size,
                                                process_group, newton_schulz_func, flatten,
-                                               split_sizes):
-        # Row-sharded matrices: the exchange is carried by the kernels themselves.
-        key = (id(X[0]), len(X), tuple(Ml[0].shape))
+                                               split_sizes, allow_uneven=True):
+        # Row-sharded matrices: the exchange is carried by the kernels themselves.  Every
+        # rank's slice of an assembled matrix is `pl` rows high; a rank with fewer rows (or
+        # none) fills only what it has, the rest of its slice stays zero.
+        pl = (global_rows + world_size - 1) // world_size
+        rows, cols = Ml[0].shape
+        key = (id(X[0]), len(X), pl, cols)
         fx = fused_cache.get(key)
         if fx is None:
-            fx = fused_cache[key] = FX.FusedRowExchange(process_group, len(X), Ml[0].shape[0],
-                                                        Ml[0].shape[1], Ml[0].device)
+            fx = fused_cache[key] = FX.FusedRowExchange(process_group, len(X), pl, cols,
+                                                        Ml[0].device)
         fx.begin()
-        outs, sums = fx.push_targets()
-        F.muon_pre(Gl, Ml, float(momentum), nesterov, out=outs, sumsq_targets=sums)
+        if rows > 0:
+            outs, sums = fx.push_targets()
+            F.muon_pre(Gl, Ml, float(momentum), nesterov, out=outs, sumsq_targets=sums)
         fx.publish()
         NS.iterate_with_exchange(fx.input_matrix(), newton_schulz_func, epsilon, fx)
         fx.finish()
-        F.muon_post(Xl, fx.result_views(), lr, weight_decay, ratio, cautious_wd,
-                    wait=fx.result_wait())
+        if rows > 0:
+            F.muon_post(Xl, fx.result_views(rows), lr, weight_decay, ratio, cautious_wd,
+                        wait=fx.result_wait())
         fx.release()
         yield
         return

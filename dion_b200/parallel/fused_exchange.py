@@ -52,15 +52,24 @@ def get_exchange(cache: dict, key, pg, n: int, rows_local: int, cols: int,
 
 def eligible(local_shape: Sequence[int], comm_dim: Optional[int], global_rows: Optional[int],
              world: int, pg: Optional[ProcessGroup], ns_func, flatten: bool,
-             split_sizes) -> bool:
-    """All ranks must reach the same decision, so only rank-independent facts are used."""
+             split_sizes, allow_uneven: bool = False) -> bool:
+    """All ranks must reach the same decision, so only rank-independent facts are used (the
+    number of local rows is not one of them).  ``allow_uneven``: the caller copes with ranks that
+    hold fewer than ``ceil(global_rows / world)`` rows, or none; every rank's slice of the
+    assembled matrix then has that padded height, the missing rows staying zero as in the
+    collective path (reference: dion/megabatch_base.py:740-782)."""
     if not fused_exchange_enabled() or pg is None or comm_dim != -2 or len(local_shape) != 2:
         return False
     if flatten or split_sizes is not None or world < 2 or world > 8:
         return False
     if getattr(ns_func, "ns_spec", None) is None:
         return False
-    if global_rows is None or global_rows % world != 0:
+    if global_rows is None or global_rows < 1:
+        return False
+    if global_rows % world != 0 and not allow_uneven:
+        return False
+    padded = -(-global_rows // world) * world
+    if padded % 8:      # the Gram matrix of the assembled rows is itself a TMA operand
         return False
     if local_shape[1] % 8:
         return False
@@ -160,8 +169,11 @@ class FusedRowExchange:
         symm.signal_peers(self.peer_flag_tables["ret"], self.rank, self.seq)
 
     # -- consumer side ------------------------------------------------------------------------
-    def result_views(self) -> List[Tensor]:
-        return [self.ret[i] for i in range(self.n)]
+    def result_views(self, rows: Optional[int] = None) -> List[Tensor]:
+        """Updates of this rank's shards; ``rows`` < padded height when the shard is ragged."""
+        if rows is None or rows == self.pl:
+            return [self.ret[i] for i in range(self.n)]
+        return [self.ret[i][:rows] for i in range(self.n)]
 
     def result_wait(self):
         """Argument for ``foreach.muon_post(wait=...)``: matrix ``i`` was produced by rank

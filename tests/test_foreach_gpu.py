@@ -181,9 +181,11 @@ def test_dion2_post_masked_matches_torch(select_dim, m_dtype):
     F.dion2_post_masked(Xg, Mg, Ug, lr, 0.01, 1.7, 0.9, select_dim)           # kernels
     torch.cuda.synchronize()
     for t in range(n):
-        assert (Xc[t] - Xg[t].cpu()).abs().max().item() < 1e-5
+        # the PyTorch form rounds lr*ratio*u to bf16 before the subtraction (as the reference's
+        # function does); the kernel keeps the product in fp32
+        assert (Xc[t] - Xg[t].cpu()).abs().max().item() < 5e-4
         assert (Mc[t].float() - Mg[t].cpu().float()).abs().max().item() <= (
-            1e-6 if m_dtype == torch.float32 else 1e-2)
+            1e-6 if m_dtype == torch.float32 else 2e-2)   # one bf16 step at |m| ~ 4
         untouched = (U[t].float().abs().sum(dim=-1 if select_dim == -2 else -2) == 0)
         a, b = M[t], Mg[t].cpu()
         if select_dim == -2:

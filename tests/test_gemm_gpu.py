@@ -201,3 +201,58 @@ def test_batch_offsets_beyond_32_bits(pair):
         ref = Bm[i].float() @ X[i].float() + 0.5 * X[i].float()
         assert _rel_err(out[i], ref) < 1e-2
         assert _rel_err(A[i], X[i].float() @ X[i].float().T) < 1e-2
+
+
+@pytest.mark.parametrize("pair", [False, True])
+@pytest.mark.parametrize("tall", [False, True])
+def test_exchange_coupling_on_one_gpu(pair, tall):
+    """The cross-GPU coupling of the GEMM kernels with this GPU standing in for every peer: the
+    first Gram waits on (already raised) arrival flags and builds its scale from per-source
+    partial sums; the update GEMM stores each output row into the buffer of its owner."""
+    from dion_b200.ops import gemm
+    torch.manual_seed(0)
+    dev = torch.device("cuda")
+    W, batch = 4, 3
+    m, n = (1024, 512) if tall else (512, 1024)
+    X = torch.randn(batch, m, n, device=dev).bfloat16()
+    flags = torch.full((W,), 7, dtype=torch.int32, device=dev)
+    seq = torch.full((), 7, dtype=torch.int32, device=dev)
+    # per-source partial sums of squares (row blocks of m / W rows each)
+    parts = X.float().reshape(batch, W, m // W, n).square().sum(dim=(2, 3)).contiguous()
+    g = n if tall else m
+    ex = gemm.GemmExtra()
+    ex.wait_flags, ex.seq_ptr = flags.data_ptr(), seq.data_ptr()
+    ex.n_src, ex.rows_per_src = W, m // W
+    ex.wait_a = ex.wait_b = 0 if tall else 1
+    ex.wait_k = 1 if tall else 0
+    ex.scale_partials = parts.data_ptr()
+    ex.scale_mult, ex.scale_eps = 1.0, 1e-7
+    A = torch.empty(batch, g, g, device=dev, dtype=torch.bfloat16)
+    gemm.ns_gemm(X, X, out=A, sym=True, a_is_km=tall, b_is_kn=tall, alpha_pow=2, extra=ex,
+                 pair=pair)
+    scale = 1.0 / (X.float().flatten(1).norm(dim=1) + 1e-7)
+    Xs = X.float() * scale.view(-1, 1, 1)
+    ref = (Xs.mT @ Xs) if tall else (Xs @ Xs.mT)
+    torch.cuda.synchronize()
+    gemm.check_status()
+    assert (A.float() - ref).abs().max().item() < 2e-2 * ref.abs().max().item()
+    # update GEMM with rows scattered to W owners: owner d gets rows [d*m/W, (d+1)*m/W)
+    Bm = torch.randn(batch, g, g, device=dev).bfloat16()
+    slots = 5
+    bufs = [torch.zeros(slots, m // W, n, device=dev, dtype=torch.bfloat16) for _ in range(W)]
+    ex2 = gemm.GemmExtra()
+    for d in range(W):
+        ex2.remote_c[d] = bufs[d].data_ptr()
+    ex2.rows_per_dst, ex2.remote_slot = m // W, 1
+    if tall:
+        gemm.ns_gemm(X, Bm, out=None, D=X, alpha=1.0, beta=0.5, extra=ex2, pair=pair)
+        want = 0.5 * X.float() + X.float() @ Bm.float().mT
+    else:
+        gemm.ns_gemm(Bm, X, out=None, b_is_kn=True, D=X, alpha=1.0, beta=0.5, extra=ex2, pair=pair)
+        want = 0.5 * X.float() + Bm.float() @ X.float()
+    torch.cuda.synchronize()
+    gemm.check_status()
+    got = torch.cat([b_[1:1 + batch] for b_ in bufs], dim=1)        # [batch, m, n]
+    assert (got.float() - want).abs().max().item() < 2e-2 * want.abs().max().item()
+    for b_ in bufs:
+        assert float(b_[0].abs().max()) == 0 and float(b_[4].abs().max()) == 0

@@ -220,9 +220,10 @@ def test_symmetric_all_reduce_matches_nccl(tmp_path, use_nvls):
         assert not any(r["multimem"] for r in res)
 
 
-def _dion_ddp_worker(rank, world, symmetric):
+def _dion_ddp_worker(rank, world, mode):
     import os
-    os.environ["DION_B200_SYMM_ALLREDUCE"] = "1" if symmetric else "0"
+    os.environ["DION_B200_SYMM_ALLREDUCE"] = "1" if mode == "symmetric" else "0"
+    os.environ["DION_B200_FUSED_LOWRANK"] = "1" if mode == "fused" else "0"
     from dion_b200.ops.gemm import check_status
     dev = torch.device("cuda", rank)
     torch.manual_seed(3)
@@ -238,23 +239,68 @@ def _dion_ddp_worker(rank, world, symmetric):
     opt.synchronize_for_checkpoint()
     torch.cuda.synchronize()
     check_status()
-    return [p.detach().cpu() for p in params]
+    out = [p.detach().cpu() for p in params]
+    out.append(torch.tensor(float(len(opt._lowrank_sync))))
+    return out
 
 
-def test_dion_compressed_sync_through_symmetric_all_reduce(tmp_path):
-    """Legacy Dion under DDP with compressed P/R synchronization: the NVLS / peer-memory
-    all-reduce gives the result of the NCCL path, and replicas stay identical."""
-    _need(2)
+@pytest.mark.parametrize("world", [2, 4])
+def test_dion_compressed_sync_paths_agree(tmp_path, world):
+    """Legacy Dion under DDP with compressed P/R synchronization, three ways: NCCL collectives,
+    the symmetric-memory all-reduce kernel, and the reduce-scatter carried by the GEMM epilogue
+    (with the all-gather kernel).  All give the same weights, and replicas stay identical."""
+    _need(world)
     out = {}
-    for symmetric in (False, True):
-        d = tmp_path / str(symmetric)
+    for mode in ("nccl", "symmetric", "fused"):
+        d = tmp_path / mode
         d.mkdir()
-        out[symmetric] = run_ranks(_dion_ddp_worker, 2, backend="nccl", args=(symmetric,),
-                                   result_dir=str(d))
+        out[mode] = run_ranks(_dion_ddp_worker, world, backend="nccl", args=(mode,),
+                              result_dir=str(d))
+    assert out["fused"][0][-1].item() > 0 and out["nccl"][0][-1].item() == 0  # the path really ran
     for res in out.values():
-        for a, b in zip(res[0], res[1]):
-            assert torch.allclose(a, b, atol=1e-5)
-    for a, b in zip(out[False][0], out[True][0]):
+        for other in res[1:]:
+            for a, b in zip(res[0][:-1], other[:-1]):
+                assert torch.allclose(a, b, atol=1e-5)
+    for mode in ("symmetric", "fused"):
+        for a, b in zip(out["nccl"][0][:-1], out[mode][0][:-1]):
+            assert torch.allclose(a, b, atol=2e-3, rtol=1e-2), mode
+
+
+def _dion_fsdp_worker(rank, world, fused):
+    import os
+    os.environ["DION_B200_FUSED_LOWRANK"] = "1" if fused else "0"
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.tensor import Shard, distribute_tensor
+    from dion_b200.ops.gemm import check_status
+    mesh = init_device_mesh("cuda", (world,), mesh_dim_names=("fs",))
+    g = torch.Generator().manual_seed(11)
+    shapes = ((256, 128),) * 3 + ((128, 512),) * 2
+    ws = [torch.randn(*s, generator=g) * 0.1 for s in shapes]
+    ps = [torch.nn.Parameter(distribute_tensor(w.cuda(), mesh, [Shard(0)])) for w in ws]
+    opt = dion_b200.Dion([dict(params=ps)], outer_shard_mesh=mesh, rank_fraction=0.25, lr=0.02)
+    for s in range(3):
+        for p, shape in zip(ps, shapes):
+            grad = torch.randn(*shape, generator=g)
+            p.grad = distribute_tensor(grad.cuda(), mesh, [Shard(0)])
+        opt.step()
+    torch.cuda.synchronize()
+    check_status()
+    full = [p.detach().full_tensor().cpu() for p in ps]
+    return (full, len(opt._lowrank_sync)) if rank == 0 else None
+
+
+def test_dion_fsdp_reduce_scatter_in_the_gemm_epilogue_matches_nccl(tmp_path):
+    """Row-sharded (FSDP) legacy Dion: the partial sums of P are reduce-scattered by the GEMM
+    epilogue over peer memory instead of by NCCL; same weights."""
+    _need(2)
+    res = {}
+    for fused in (False, True):
+        d = tmp_path / str(fused)
+        d.mkdir()
+        res[fused] = run_ranks(_dion_fsdp_worker, 2, backend="nccl", args=(fused,),
+                               result_dir=str(d))[0]
+    assert res[False][1] == 0 and res[True][1] > 0
+    for a, b in zip(res[False][0], res[True][0]):
         assert torch.allclose(a, b, atol=2e-3, rtol=1e-2)
 
 
@@ -377,3 +423,130 @@ def test_fsdp_all_gather_through_symmetric_memory_matches_nccl(tmp_path):
         # average rather than element by element.)
         diff = (out[True][r]["params"] - out[False][r]["params"]).abs()
         assert diff.mean().item() < 1e-4 and (diff > 5e-3).float().mean().item() < 1e-3
+
+
+def _sharded_graph_worker(rank, world, name, mode):
+    """Sharded optimizer step, eager or replayed by CudaGraphOptimizer, with an LR that a
+    scheduler would change in place between steps."""
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.tensor import Shard, distribute_tensor
+    from dion_b200 import CudaGraphOptimizer
+    from dion_b200.ops.gemm import check_status
+    dev = torch.device("cuda", rank)
+    mesh = init_device_mesh("cuda", (world,))
+    gen = torch.Generator(device=dev).manual_seed(1234)
+    shapes = ((128, 256),) * 3 + ((256, 128),) * 2
+    ps = [torch.nn.Parameter(distribute_tensor(torch.randn(*s, generator=gen, device=dev), mesh,
+                                               [Shard(0)])) for s in shapes]
+    for p, s in zip(ps, shapes):
+        p.grad = distribute_tensor(torch.zeros(*s, device=dev), mesh, [Shard(0)])
+    opt = getattr(dion_b200, name)([dict(params=ps)], distributed_mesh=mesh, lr=0.1)
+    wrap = None if mode == "eager" else CudaGraphOptimizer(opt, warmup_steps=2)
+    step = opt.step if wrap is None else wrap.step
+    steps = 6
+    grads = [[distribute_tensor(torch.randn(*s, generator=gen, device=dev), mesh, [Shard(0)])
+              for s in shapes] for _ in range(steps)]
+    try:
+        for t in range(steps):
+            for p, g in zip(ps, grads[t]):
+                p.grad.copy_(g)
+            for group in opt.param_groups:
+                group["lr"].fill_(0.1 * (0.25 + t / steps))
+            step()
+        torch.cuda.synchronize()
+        check_status()
+        full = [p.detach().full_tensor().cpu() for p in ps]
+        used = len(opt._fused_exchanges)
+    finally:
+        if wrap is not None:
+            wrap.release()
+    return (full, used) if rank == 0 else None
+
+
+@pytest.mark.parametrize("name", ["NorDion2", "Muon"])
+def test_captured_sharded_step_matches_eager_with_the_fused_exchange(tmp_path, name):
+    """Two ranks, row-sharded parameters: the step replayed from a CUDA graph (which then holds
+    the peer-memory exchange: flag waits, remote stores, sequence numbers kept on the device)
+    gives the weights of the eager run while the learning rate changes between replays."""
+    _need(2)
+    out = {}
+    for mode in ("eager", "graph"):
+        d = tmp_path / mode
+        d.mkdir()
+        out[mode] = run_ranks(_sharded_graph_worker, 2, "nccl", (name, mode), str(d))[0]
+    assert out["graph"][1] > 0      # the fused exchange was part of the recording
+    for a, b in zip(out["eager"][0], out["graph"][0]):
+        assert (a - b).abs().max().item() <= 1e-5
+
+
+def _dion2_empty_shard_worker(rank, world, global_rows, cols):
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.tensor import Shard, distribute_tensor
+    from dion_b200.ops.gemm import check_status
+    dev = torch.device("cuda", rank)
+    mesh = init_device_mesh("cuda", (world,))
+    torch.manual_seed(0)
+    full = torch.randn(global_rows, cols, device=dev)
+    param = torch.nn.Parameter(distribute_tensor(full, mesh, [Shard(0)]))
+    before = param.to_local().clone()
+    opt = dion_b200.Dion2([param], distributed_mesh=mesh, lr=0.01)
+    for step in range(3):
+        torch.manual_seed(step + 1)
+        g = torch.randn(global_rows, cols, device=dev)
+        param.grad = distribute_tensor(g, mesh, [Shard(0)])
+        opt.step()
+    torch.cuda.synchronize()
+    check_status()
+    after = param.to_local()
+    if after.shape[0] > 0:
+        assert not torch.equal(after, before), f"rank {rank}: weights did not update"
+    else:
+        assert torch.equal(after, before), f"rank {rank}: empty shard mutated"
+    return None
+
+
+@pytest.mark.parametrize("world,global_rows", [(2, 1), (4, 2), (4, 5)])
+def test_dion2_step_with_empty_shards_over_nccl(world, global_rows):
+    """Fewer rows than ranks (or a ragged split): ranks with an empty local shard take part in
+    the exchange and leave their (empty) weights alone; the others update."""
+    _need(world)
+    run_ranks(_dion2_empty_shard_worker, world, "nccl", (global_rows, 16))
+
+
+def _ragged_worker(rank, world, shapes, fused):
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.tensor import Shard, distribute_tensor
+    from dion_b200.ops.gemm import check_status
+    os.environ["DION_B200_FUSED_EXCHANGE"] = "1" if fused else "0"
+    mesh = init_device_mesh("cuda", (world,))
+    ps = [torch.nn.Parameter(distribute_tensor(w.cuda(), mesh, [Shard(0)]))
+          for w in _weights(shapes)]
+    opt = dion_b200.Muon([dict(params=ps)], distributed_mesh=mesh, lr=0.05, nesterov=True,
+                         use_polar_express=False)
+    for s in range(3):
+        for p, g in zip(ps, _weights(shapes, 100 + s)):
+            p.grad = distribute_tensor(g.cuda(), mesh, [Shard(0)])
+        opt.step()
+    torch.cuda.synchronize()
+    check_status()
+    full = [p.detach().full_tensor().cpu() for p in ps]
+    return (full, len(opt._fused_exchanges)) if rank == 0 else None
+
+
+@pytest.mark.parametrize("world,shapes", [
+    (2, ((255, 128),) * 3),                            # 128 + 127 rows
+    (4, ((125, 256),) * 5 + ((5, 64),) * 3),           # 32,32,32,29 rows; 2,2,1,0 rows
+])
+def test_fused_exchange_with_ragged_and_empty_shards(tmp_path, world, shapes):
+    """Rows that do not divide by the number of ranks, and fewer rows than ranks: the fused
+    exchange pads every rank's slice to the same height (as the collective path does) and gives
+    the collective path's weights."""
+    _need(world)
+    res = {}
+    for fused in (False, True):
+        d = tmp_path / str(fused)
+        d.mkdir()
+        res[fused] = run_ranks(_ragged_worker, world, "nccl", (shapes, fused), str(d))[0]
+    assert res[False][1] == 0 and res[True][1] > 0
+    for a, b in zip(res[False][0], res[True][0]):
+        assert (a - b).abs().max().item() < 2e-3
