@@ -211,6 +211,82 @@ def _():
     return (lambda: LR.cholesky_upper(Gm)), Gm.numel() * 8
 
 
+# ---- low-rank (Dion) kernels: 24 matrices of 2048 x 2048 in fp32, rank 512 -----------------------
+LR_B, LR_D, LR_R = 24, 2048, 512
+FLOPS = {}   # kernel name -> floating-point operations per call (reported as TFLOP/s)
+
+
+def _lr_inputs():
+    g = torch.Generator(device=DEV).manual_seed(0)
+    M = torch.randn(LR_B, LR_D, LR_D, device=DEV, generator=g)
+    Q = torch.randn(LR_B, LR_D, LR_R, device=DEV, generator=g) / LR_D ** 0.5
+    return M, Q
+
+
+@case("lowrank_p_gemm_tf32")
+def _():
+    """P = M Q: M read once in fp32 (K-major), Q as a [K, N] operand."""
+    M, Q = _lr_inputs()
+    FLOPS["lowrank_p_gemm_tf32"] = 2.0 * LR_B * LR_D * LR_D * LR_R
+    return (lambda: LR.power_iteration_p(M, Q, False)), \
+        LR_B * (LR_D * LR_D + 2 * LR_D * LR_R) * 4
+
+
+@case("lowrank_r_gemm_tf32")
+def _():
+    """R = M^T P: M read in place as an MN-major tf32 operand."""
+    M, Q = _lr_inputs()
+    FLOPS["lowrank_r_gemm_tf32"] = 2.0 * LR_B * LR_D * LR_D * LR_R
+    return (lambda: LR.power_iteration_r(M, Q, False)), \
+        LR_B * (LR_D * LR_D + 2 * LR_D * LR_R) * 4
+
+
+@case("lowrank_p_gemm_reduce")
+def _():
+    """P = M Q with the epilogue adding every tile into per-matrix accumulators (the local form
+    of the reduce-scatter over peer memory: the same red.add instructions, targets in this
+    GPU's memory)."""
+    M, Q = _lr_inputs()
+    acc = torch.zeros(LR_B, LR_D, LR_R, device=DEV)
+    where = torch.tensor([acc[b].data_ptr() for b in range(LR_B)], dtype=torch.int64).to(DEV)
+    FLOPS["lowrank_p_gemm_reduce"] = 2.0 * LR_B * LR_D * LR_D * LR_R
+    return (lambda: LR.power_iteration_p(M, Q, False, reduce_into=where, alpha=0.5)), \
+        LR_B * (LR_D * LR_D + 3 * LR_D * LR_R) * 4
+
+
+@case("lowrank_rank_update_inplace")
+def _():
+    """M -= c P R^T in place: the fp32 matrix is read and written once by the GEMM epilogue."""
+    M, Q = _lr_inputs()
+    P = torch.randn(LR_B, LR_D, LR_R, device=DEV) / LR_R ** 0.5
+    FLOPS["lowrank_rank_update_inplace"] = 2.0 * LR_B * LR_D * LR_D * LR_R
+    return (lambda: LR.rank_update_stack_(M, P, Q, -0.05, 1.0)), \
+        LR_B * (2 * LR_D * LR_D + 2 * LR_D * LR_R) * 4
+
+
+@case("lowrank_triu_inverse_96x512")
+def _():
+    A = torch.randn(96, 640, 512, device=DEV)
+    U = torch.linalg.qr(A, mode="r")[1].contiguous()
+    FLOPS["lowrank_triu_inverse_96x512"] = 96 * 512 ** 3 / 3.0
+    return (lambda: LR.triu_inverse(U)), U.numel() * 8
+
+
+@case("lowrank_orthogonalize_96x2048x512")
+def _():
+    """The whole randomized Cholesky-QR of 96 factors [2048, 512] (sketch, QR, two inversions,
+    Gram, Cholesky, split-precision products)."""
+    P = torch.randn(96, 2048, 512, device=DEV)
+    return (lambda: LR.orthogonalize(P, 1.25)), P.numel() * 8
+
+
+@case("philox_sketch_96x640x2048")
+def _():
+    dev = torch.device(DEV)
+    gen = torch.Generator(device=dev).manual_seed(1)
+    return (lambda: LR.random_sketch(96, 640, 2048, F32, dev, gen)), 96 * 640 * 2048 * 4
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--only", default=None)
@@ -225,9 +301,11 @@ def main() -> None:
         fn, nbytes = builder()
         ms = timed(fn, iters=args.iters)
         gbs = nbytes / ms / 1e6
-        print(json.dumps({"kernel": name, "ms": round(ms, 4), "algorithmic_MB": round(nbytes / 1e6, 1),
-                          "GBs": round(gbs, 1), "frac_of_measured_hbm": round(gbs / peak, 3)}),
-              flush=True)
+        line = {"kernel": name, "ms": round(ms, 4), "algorithmic_MB": round(nbytes / 1e6, 1),
+                "GBs": round(gbs, 1), "frac_of_measured_hbm": round(gbs / peak, 3)}
+        if name in FLOPS:
+            line["TFLOPs"] = round(FLOPS[name] / ms / 1e9, 1)
+        print(json.dumps(line), flush=True)
 
 
 if __name__ == "__main__":

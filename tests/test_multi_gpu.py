@@ -66,7 +66,7 @@ def _replicated(rank, world, name, kw, steps):
     return [p.detach().cpu() for p in ps] if rank == 0 else None
 
 
-@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("world", [2, 4, 8])
 def test_muon_fused_exchange_matches_collective_and_single(tmp_path, world):
     _need(world)
     kw = dict(nesterov=True, use_polar_express=False)
@@ -244,7 +244,7 @@ def _dion_ddp_worker(rank, world, mode):
     return out
 
 
-@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("world", [2, 4, 8])
 def test_dion_compressed_sync_paths_agree(tmp_path, world):
     """Legacy Dion under DDP with compressed P/R synchronization, three ways: NCCL collectives,
     the symmetric-memory all-reduce kernel, and the reduce-scatter carried by the GEMM epilogue
@@ -273,6 +273,7 @@ def _dion_fsdp_worker(rank, world, fused):
     from torch.distributed.tensor import Shard, distribute_tensor
     from dion_b200.ops.gemm import check_status
     mesh = init_device_mesh("cuda", (world,), mesh_dim_names=("fs",))
+    torch.manual_seed(5)      # the optimizer derives the seeds of Q and of the sketches from it
     g = torch.Generator().manual_seed(11)
     shapes = ((256, 128),) * 3 + ((128, 512),) * 2
     ws = [torch.randn(*s, generator=g) * 0.1 for s in shapes]
@@ -475,8 +476,12 @@ def test_captured_sharded_step_matches_eager_with_the_fused_exchange(tmp_path, n
         d.mkdir()
         out[mode] = run_ranks(_sharded_graph_worker, 2, "nccl", (name, mode), str(d))[0]
     assert out["graph"][1] > 0      # the fused exchange was part of the recording
+    # Not bit-identical: the Frobenius norm travels as partial sums that blocks add with
+    # floating-point atomics, whose order varies from run to run; the last-bit difference in
+    # the scale occasionally flips a bf16 rounding inside the iteration (two eager runs differ
+    # in the same way).  A stale learning rate or a missed exchange would be off by >1e-2.
     for a, b in zip(out["eager"][0], out["graph"][0]):
-        assert (a - b).abs().max().item() <= 1e-5
+        assert (a - b).abs().max().item() <= 1e-3
 
 
 def _dion2_empty_shard_worker(rank, world, global_rows, cols):
