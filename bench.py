@@ -19,7 +19,10 @@ matrices (96 x 2048^2, 24 x 8192x2048, 24 x 2048x8192) held the way FSDP2 holds 
 ``Shard(0)`` DTensors over the N ranks (plain tensors for N = 1), with fixed random gradients.
 Ours runs it twice, with the all-to-all carried by the compute kernels over peer memory
 (``fused_ms``) and with NCCL ``all_to_all_single`` (``nccl_ms``); the reference runs its own
-``dion.Muon`` (Triton Newton-Schulz, NCCL all-to-all).  ``--no-aux`` skips the block.
+``dion.Muon`` (Triton Newton-Schulz, NCCL all-to-all).  ``aux.dion`` times the legacy Dion step
+(rank 1/4) on the same matrices under data parallelism with compressed P/R synchronisation, and
+``aux.newton_schulz`` five iterations on 16 matrices of 4096 x 4096 per GPU.  ``--no-aux`` skips
+the block.
 """
 from __future__ import annotations
 
@@ -337,6 +340,95 @@ def run_aux_ours(args, rank: int, world: int, device) -> dict:
     return out
 
 
+def aux_dion_tensors(world: int, device):
+    """GPT-1B block matrices held the way DDP holds them (every rank a full fp32 copy, equal on
+    all ranks) with gradients that differ per rank; seed 0."""
+    import torch
+
+    gen = torch.Generator(device=device).manual_seed(0)
+    params = [torch.nn.Parameter((torch.randn(*s, device=device, generator=gen) * 0.02)
+                                 .bfloat16().float()) for s in aux_shapes()]
+    rank_gen = torch.Generator(device=device).manual_seed(1 + int(os.environ.get("RANK", "0")))
+    grads = [torch.randn(*s, device=device, generator=rank_gen).bfloat16().float()
+             for s in aux_shapes()]
+    return params, grads
+
+
+def run_aux_dion_ours(args, rank: int, world: int, device) -> dict:
+    """Legacy Dion (rank fraction 1/4) optimizer step on the GPT-1B block matrices under data
+    parallelism with compressed synchronisation (P and R travel instead of the gradients): with
+    the reduce-scatter inside the GEMM epilogue over peer memory, and with NCCL collectives."""
+    import torch
+    import torch.distributed as dist
+
+    import dion_b200
+    from dion_b200.ops.gemm import check_status
+
+    out = {"what": "legacy Dion (rank 1/4, rcQR) optimizer step, GPT-1B block matrices, fp32, "
+                   "data parallel with compressed P/R synchronisation",
+           "steps": args.aux_steps, "warmup": args.aux_warmup, "n_gpus": world}
+    params, grads = aux_dion_tensors(world, device)
+    pg = dist.group.WORLD if world > 1 else None
+    variants = [("fused", "1"), ("nccl", "0")] if world > 1 else [("single", "1")]
+    old = os.environ.get("DION_B200_FUSED_LOWRANK")
+    try:
+        for label, env in variants:
+            os.environ["DION_B200_FUSED_LOWRANK"] = env
+            opt = dion_b200.Dion([dict(params=params)], replicate_mesh=pg,
+                                 replicate_mesh_grad_sync=world > 1, rank_fraction=FRACTION,
+                                 lr=LR, mu=MU, weight_decay=WD)
+            out[f"{label}_ms"] = aux_time(opt, params, grads, args.aux_steps, args.aux_warmup,
+                                          world, device)
+            if label == "fused":
+                out["n_fused_workspaces"] = len(opt._lowrank_sync)
+            try:
+                check_status()
+                out[f"{label}_status"] = "ok"
+            except RuntimeError as exc:
+                out[f"{label}_status"] = str(exc)
+            del opt
+            torch.cuda.empty_cache()
+    finally:
+        if old is None:
+            os.environ.pop("DION_B200_FUSED_LOWRANK", None)
+        else:
+            os.environ["DION_B200_FUSED_LOWRANK"] = old
+    return out
+
+
+def run_aux_dion_reference(args, ref_dion, rank: int, world: int, device) -> dict:
+    import torch.distributed as dist
+
+    out = {"what": "legacy Dion optimizer step, unmodified reference dion.Dion on the same "
+                   "tensors (cuBLAS / cuSOLVER, NCCL)",
+           "steps": args.aux_steps, "warmup": args.aux_warmup, "n_gpus": world}
+    params, grads = aux_dion_tensors(world, device)
+    pg = dist.group.WORLD if world > 1 else None
+    opt = ref_dion.Dion([dict(params=params)], replicate_mesh=pg,
+                        replicate_mesh_grad_sync=world > 1, rank_fraction=FRACTION, lr=LR, mu=MU,
+                        weight_decay=WD)
+    out["reference_ms"] = aux_time(opt, params, grads, min(args.aux_steps, 10), 3, world, device)
+    return out
+
+
+NS_BATCH, NS_DIM = 16, 4096
+
+
+def run_aux_ns(fn, device) -> dict:
+    """Five Newton-Schulz iterations on 16 bf16 matrices of 4096 x 4096 (entries N(0,1)), one
+    GPU's worth of work; ms per call and TFLOP/s by the reference's cost model."""
+    import torch
+
+    gen = torch.Generator(device=device).manual_seed(0)
+    X = torch.randn(NS_BATCH, NS_DIM, NS_DIM, device=device, generator=gen).bfloat16()
+    ms, _ = time_loop(lambda: fn(X), 10, 3, 1, device)
+    ms /= 10
+    flops = NS_BATCH * 5 * 6.0 * NS_DIM ** 3
+    return {"what": "Newton-Schulz, 5 quintic iterations, 16 x 4096 x 4096 bf16, per GPU",
+            "ms": ms, "tflops_reference_cost_model": flops / ms / 1e9,
+            "fraction_of_measured_cublas_sustained": flops / ms / 1e9 / measured_peak_tflops()}
+
+
 def run_aux_reference(args, ref_dion, rank: int, world: int, device) -> dict:
     out = {"what": "GPT-1B Muon optimizer step, unmodified reference dion.Muon (Triton "
                    "Newton-Schulz, NCCL all-to-all) on the same tensors",
@@ -484,7 +576,15 @@ def run_ours(args) -> None:
     if graphed:
         gstep.release()
     torch.cuda.empty_cache()
-    aux = None if args.no_aux else guarded_aux(run_aux_ours, args, rank, world, device)
+    aux = None
+    if not args.no_aux:
+        from dion_b200.ops.newton_schulz import newton_schulz_quintic
+
+        aux = guarded_aux(run_aux_ours, args, rank, world, device)
+        torch.cuda.empty_cache()
+        aux["dion"] = guarded_aux(run_aux_dion_ours, args, rank, world, device)
+        torch.cuda.empty_cache()
+        aux["newton_schulz"] = guarded_aux(run_aux_ns, newton_schulz_quintic, device)
     if rank == 0:
         emit(args, "ours", ms, e2e_ms, clocks, launches, world,
              {"final_loss": loss_after,
@@ -611,8 +711,19 @@ def run_reference(args) -> None:
     if not args.no_e2e:
         e2e_ms, _ = time_loop(step_e2e, args.steps, 2, world, device, None)
     torch.cuda.empty_cache()
-    aux = None if args.no_aux else guarded_aux(run_aux_reference, args, ref_dion, rank, world,
-                                               device)
+    aux = None
+    if not args.no_aux:
+        aux = guarded_aux(run_aux_reference, args, ref_dion, rank, world, device)
+        torch.cuda.empty_cache()
+        aux["dion"] = guarded_aux(run_aux_dion_reference, args, ref_dion, rank, world, device)
+        torch.cuda.empty_cache()
+
+        def ref_ns(X):   # the reference's Triton driver, as its trainer selects it
+            from dion.newton_schulz_triton import newton_schulz_triton
+
+            return newton_schulz_triton(X, epsilon=1e-7)
+
+        aux["newton_schulz"] = guarded_aux(run_aux_ns, ref_ns, device)
     if rank == 0:
         emit(args, "reference", ms, e2e_ms, clocks, 0, world,
              {"final_loss": loss_after,

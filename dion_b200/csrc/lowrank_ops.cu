@@ -243,113 +243,127 @@ cholesky_upper_kernel(const float* __restrict__ G, float* U, int r) {
 
 
 // ---------------------------------------------------------------------------------------------
-// Inverse of upper-triangular matrices (fp32), one CTA per matrix, r <= 1024.
+// Inverse of upper-triangular matrices (fp32), r <= 1024.
 //
 // The randomized Cholesky-QR needs P R^-1 twice per step.  With R^-1 in hand that product is an
 // ordinary tall GEMM for the tensor cores (lowrank_gemm_sm100.cu) instead of a triangular solve,
 // which the reference leaves to cuBLAS trsm (dion/dion.py:1290-1300).
 //
-// The matrix is cut into 32 x 32 blocks (padded with the identity), warp I owns block row I.
-// First every warp inverts its diagonal block (lane l solves for column l by back substitution,
-// the column in registers) and keeps it in shared memory.  Then the block super-diagonals are
-// filled one after the other: X[I,J] = -inv(U[I,I]) * sum_{K=I+1..J} U[I,K] X[K,J], where every
-// X[K,J] on the right lies on an earlier super-diagonal of block column J.  Blocks of one
-// super-diagonal are independent (one per warp); a block barrier separates the super-diagonals.
+// The matrix is cut into 32 x 32 blocks (padded with the identity).  Block column J of the
+// inverse depends on U and on itself only: X[J,J] = inv(U[J,J]) and, going up,
+//     X[I,J] = -inv(U[I,I]) * sum_{K=I+1..J} U[I,K] X[K,J].
+// Kernel 1 inverts the diagonal blocks (one warp each: lane l solves for column l by back
+// substitution, the column in registers) and clears the blocks below the diagonal.  Kernel 2
+// runs one CTA of 8 or 16 warps per block column: as soon as X[K,J] is known, every warp adds
+// U[I,K] X[K,J] to the sums of the block rows I < K it owns, then the owner of row K-1 finishes
+// X[K-1,J] and publishes it through shared memory.  All block columns of all matrices
+// run side by side, so a batch of a few matrices still fills the GPU.
 // ---------------------------------------------------------------------------------------------
-__device__ __forceinline__ float triu_elem(const float* __restrict__ U, int r, int i, int k) {
-  if (i < r && k < r) return __ldg(U + (size_t)i * r + k);
-  return i == k ? 1.f : 0.f;
-}
-
-template <int kMaxThreads>
-__global__ void __launch_bounds__(kMaxThreads)
-triu_inverse_kernel(const float* __restrict__ Uall, float* Xall, int r) {
-  extern __shared__ float ti_smem[];            // [NB][32][32] inverses of the diagonal blocks
-  const int NB = blockDim.x >> 5;
-  const int I = threadIdx.x >> 5, l = threadIdx.x & 31;
-  const float* U = Uall + (size_t)blockIdx.x * r * r;
-  float* X = Xall + (size_t)blockIdx.x * r * r;
-  float* Ys = ti_smem + (size_t)I * 1024;
-  const bool fast = (r & 3) == 0 && (reinterpret_cast<uintptr_t>(U) & 15) == 0;
+// r is a multiple of 32 here (the host pads other sizes with the identity).
+__global__ void __launch_bounds__(32)
+triu_diag_inverse_kernel(const float* __restrict__ Uall, float* Xall, int r) {
+  __shared__ float D[32 * 32];
+  const int I = blockIdx.x, l = threadIdx.x;
+  const float* U = Uall + (size_t)blockIdx.y * r * r;
+  float* X = Xall + (size_t)blockIdx.y * r * r;
   const int i0 = I * 32;
-
-  // ---- diagonal block: lane l solves U[I,I] y = e_l ----
-  {
-    // Stage the block so that row reads below are shared-memory broadcasts.
-    for (int i = 0; i < 32; ++i) Ys[i * 32 + l] = triu_elem(U, r, i0 + i, i0 + l);
-    __syncwarp();
-    float y[32];
+  for (int i = 0; i < 32; ++i) D[i * 32 + l] = __ldg(U + (size_t)(i0 + i) * r + i0 + l);
+  __syncwarp();
+  float y[32];
 #pragma unroll
-    for (int i = 31; i >= 0; --i) {
-      float s = (i == l) ? 1.f : 0.f;
+  for (int i = 31; i >= 0; --i) {
+    float s = (i == l) ? 1.f : 0.f;
 #pragma unroll
-      for (int k = i + 1; k < 32; ++k) s -= Ys[i * 32 + k] * y[k];
-      y[i] = s / Ys[i * 32 + i];
-    }
-    __syncwarp();
-#pragma unroll
-    for (int i = 0; i < 32; ++i) {
-      Ys[i * 32 + l] = y[i];
-      if (i0 + i < r && i0 + l < r) X[(size_t)(i0 + i) * r + i0 + l] = y[i];
-    }
-    // Blocks below the diagonal are zero.
-    for (int J = 0; J < I; ++J)
-      for (int i = 0; i < 32; ++i)
-        if (i0 + i < r) X[(size_t)(i0 + i) * r + J * 32 + l] = 0.f;
+    for (int k = i + 1; k < 32; ++k) s -= D[i * 32 + k] * y[k];
+    y[i] = s / D[i * 32 + i];
   }
+#pragma unroll
+  for (int i = 0; i < 32; ++i) X[(size_t)(i0 + i) * r + i0 + l] = y[i];
+  for (int J = 0; J < I; ++J)     // blocks below the diagonal are zero
+    for (int i = 0; i < 32; ++i) X[(size_t)(i0 + i) * r + J * 32 + l] = 0.f;
+}
 
-  for (int d = 1; d < NB; ++d) {
-    __syncthreads();   // the previous super-diagonal (and the diagonal blocks) are in memory
-    if (I >= NB - d) continue;
-    const int J = I + d, j0 = J * 32;
-    float acc[32];
+constexpr int kBlkPitch = 36;   // floats per staged block row (16-byte aligned rows)
+
+// acc[i] += sum_k A[i0+i, k0+k] * xk[k] for a 32 x 32 block of the row-major matrix A.  The warp
+// first stages the block in its own shared-memory buffer with 32 independent coalesced loads per
+// lane (one round trip to L2 instead of a chain of dependent broadcast loads), then multiplies
+// from shared memory (16-byte broadcasts).
+__device__ __forceinline__ void block_mac(const float* A, int r, int i0, int k0, float* stage,
+                                          int lane, const float (&xk)[32], float (&acc)[32]) {
+  float tmp[32];
 #pragma unroll
-    for (int i = 0; i < 32; ++i) acc[i] = 0.f;
-    for (int K = I + 1; K <= J; ++K) {
-      const int k0 = K * 32;
-      float xk[32];
+  for (int i = 0; i < 32; ++i) tmp[i] = A[(size_t)(i0 + i) * r + k0 + lane];
+  __syncwarp();                      // earlier reads of the buffer are done
 #pragma unroll
-      for (int k = 0; k < 32; ++k)
-        xk[k] = (k0 + k < r && j0 + l < r) ? X[(size_t)(k0 + k) * r + j0 + l] : 0.f;
-      if (fast && k0 + 32 <= r && i0 + 32 <= r) {
+  for (int i = 0; i < 32; ++i) stage[i * kBlkPitch + lane] = tmp[i];
+  __syncwarp();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float4* urow = reinterpret_cast<const float4*>(U + (size_t)(i0 + i) * r + k0);
+  for (int i = 0; i < 32; ++i) {
+    const float4* row = reinterpret_cast<const float4*>(stage + i * kBlkPitch);
 #pragma unroll
-          for (int q = 0; q < 8; ++q) {
-            const float4 u = __ldg(urow + q);
-            acc[i] += u.x * xk[q * 4] + u.y * xk[q * 4 + 1] + u.z * xk[q * 4 + 2] +
-                      u.w * xk[q * 4 + 3];
-          }
-        }
-      } else {
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-#pragma unroll 4
-          for (int k = 0; k < 32; ++k) {
-            const float u = (i0 + i < r && k0 + k < r) ? __ldg(U + (size_t)(i0 + i) * r + k0 + k)
-                                                       : 0.f;
-            acc[i] += u * xk[k];
-          }
-        }
-      }
-    }
-    // X[I,J] = -inv(U[I,I]) * acc
-#pragma unroll
-    for (int i = 0; i < 32; ++i) {
-      float s = 0.f;
-      const float4* yrow = reinterpret_cast<const float4*>(Ys + i * 32);
-#pragma unroll
-      for (int q = 0; q < 8; ++q) {
-        const float4 yv = yrow[q];
-        s += yv.x * acc[q * 4] + yv.y * acc[q * 4 + 1] + yv.z * acc[q * 4 + 2] +
-             yv.w * acc[q * 4 + 3];
-      }
-      if (i0 + i < r && j0 + l < r) X[(size_t)(i0 + i) * r + j0 + l] = -s;
+    for (int q = 0; q < 8; ++q) {
+      const float4 u = row[q];
+      acc[i] += u.x * xk[q * 4] + u.y * xk[q * 4 + 1] + u.z * xk[q * 4 + 2] + u.w * xk[q * 4 + 3];
     }
   }
 }
 
+// WARPS x ROWS >= number of block rows: block row I belongs to warp I % WARPS, slot I / WARPS.
+// Dynamic shared memory: one 32 x kBlkPitch staging block per warp.
+template <int WARPS, int ROWS>
+__global__ void __launch_bounds__(WARPS * 32, 1)
+triu_column_kernel(const float* __restrict__ Uall, float* Xall, int r) {
+  extern __shared__ __align__(16) float tc_smem[];
+  __shared__ float Xs[32 * 33];                 // X[K,J], row k at Xs[k*33 ..]
+  const int J = blockIdx.x;
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  float* stage = tc_smem + (size_t)w * 32 * kBlkPitch;
+  const float* U = Uall + (size_t)blockIdx.y * r * r;
+  float* X = Xall + (size_t)blockIdx.y * r * r;
+  const int j0 = J * 32;
+  float acc[ROWS][32];
+#pragma unroll
+  for (int s = 0; s < ROWS; ++s)
+#pragma unroll
+    for (int i = 0; i < 32; ++i) acc[s][i] = 0.f;
+
+  // X[J,J] was written by the diagonal kernel.
+  for (int e = threadIdx.x; e < 1024; e += WARPS * 32) {
+    const int k = e >> 5, c = e & 31;
+    Xs[k * 33 + c] = X[(size_t)(j0 + k) * r + j0 + c];
+  }
+  __syncthreads();
+
+  for (int K = J; K >= 1; --K) {
+    float xk[32];
+#pragma unroll
+    for (int k = 0; k < 32; ++k) xk[k] = Xs[k * 33 + l];
+    // sums of my block rows I < K
+#pragma unroll
+    for (int s = 0; s < ROWS; ++s) {
+      const int I = s * WARPS + w;
+      if (I < K) block_mac(U, r, I * 32, K * 32, stage, l, xk, acc[s]);
+    }
+    __syncthreads();                             // everybody has read X[K,J]
+    const int In = K - 1;                        // next block to finish
+    if (In % WARPS == w) {
+      // X[In,J] = -inv(U[In,In]) * acc, the inverse read from the diagonal block of X
+#pragma unroll
+      for (int k = 0; k < 32; ++k) xk[k] = 0.f;  // reused as the output column
+#pragma unroll
+      for (int s = 0; s < ROWS; ++s)
+        if (s == In / WARPS) block_mac(X, r, In * 32, In * 32, stage, l, acc[s], xk);
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        const float v = -xk[i];
+        Xs[i * 33 + l] = v;
+        X[(size_t)(In * 32 + i) * r + j0 + l] = v;
+      }
+    }
+    __syncthreads();
+  }
+}
 
 // ---------------------------------------------------------------------------------------------
 // Gaussian sketch: out[i] = std * N(0,1), a pure function of (seed, i) - Philox4x32-10 with the
@@ -453,28 +467,34 @@ DION_EXPORT int dion_cholesky_upper(const void* G, void* U, int n, int r, void* 
   return launch_chol<32>(g, u, n, r, S(stream));
 }
 
-// X[b] = U[b]^-1 for a batch of upper-triangular r x r fp32 matrices (r <= 1024); the strictly
-// lower triangle of X is written as zero.  X must not alias U.
+// X[b] = U[b]^-1 for a batch of upper-triangular r x r fp32 matrices, r a multiple of 32 up to
+// 1024, 16-byte aligned; the strictly lower triangle of X is written as zero.  X must not alias U.
 DION_EXPORT int dion_triu_inverse(const void* U, void* X, int n, int r, void* stream) {
   if (n <= 0 || r <= 0) return 0;
-  if (r > 1024 || U == X) return -2;
-  const int nb = (r + 31) / 32;
-  const int smem = nb * 4096;
+  if (r > 1024 || (r & 31) || U == X || (reinterpret_cast<uintptr_t>(U) & 15) ||
+      (reinterpret_cast<uintptr_t>(X) & 15))
+    return -2;
+  const int nb = r / 32;
+  const float* u = static_cast<const float*>(U);
+  float* x = static_cast<float*>(X);
+  dim3 grid(nb, n);
+  dion::triu_diag_inverse_kernel<<<grid, 32, 0, S(stream)>>>(u, x, r);
   static bool configured = false;
+  constexpr int kStage16 = 16 * 32 * dion::kBlkPitch * 4;   // 72 KB
   if (!configured) {
-    if (cudaFuncSetAttribute(dion::triu_inverse_kernel<512>,
-                             cudaFuncAttributeMaxDynamicSharedMemorySize, 16 * 4096) != cudaSuccess ||
-        cudaFuncSetAttribute(dion::triu_inverse_kernel<1024>,
-                             cudaFuncAttributeMaxDynamicSharedMemorySize, 32 * 4096) != cudaSuccess)
+    if (cudaFuncSetAttribute(dion::triu_column_kernel<16, 1>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, kStage16) != cudaSuccess ||
+        cudaFuncSetAttribute(dion::triu_column_kernel<16, 2>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, kStage16) != cudaSuccess)
       return -3;
     configured = true;
   }
-  const float* u = static_cast<const float*>(U);
-  float* x = static_cast<float*>(X);
-  if (nb <= 16)   // up to 512 threads: twice the registers per thread
-    dion::triu_inverse_kernel<512><<<n, nb * 32, smem, S(stream)>>>(u, x, r);
+  if (nb <= 8)
+    dion::triu_column_kernel<8, 1><<<grid, 256, kStage16 / 2, S(stream)>>>(u, x, r);
+  else if (nb <= 16)
+    dion::triu_column_kernel<16, 1><<<grid, 512, kStage16, S(stream)>>>(u, x, r);
   else
-    dion::triu_inverse_kernel<1024><<<n, nb * 32, smem, S(stream)>>>(u, x, r);
+    dion::triu_column_kernel<16, 2><<<grid, 512, kStage16, S(stream)>>>(u, x, r);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 

@@ -70,33 +70,18 @@ row_norms_kernel(const long long* ptrs, int n, int rows, int cols, int g_dt, int
   const long long off = (long long)r * cols;
   float s = 0.f;
   if ((cols & 7) == 0 && aligned16(M) && (G == nullptr || aligned16(G))) {
-    // Four independent steps of 8 elements per lane are loaded (M and G) before any is used: a
-    // warp then keeps 4 to 8 KB in flight, which is what hides the DRAM latency at one warp
-    // per row (a single dependent load -> add -> store chain per lane reached about half of
-    // the copy bandwidth).
-    for (int c0 = lane * 8; c0 < cols; c0 += 4 * 256) {
-      float m[4][8], g[4][8];
+    for (int c = lane * 8; c < cols; c += 256) {
+      float m[8];
+      ld8v(M, m_dt, off + c, m);
+      if (G) {
+        float g[8];
+        ld8v(G, g_dt, off + c, g);
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int c = c0 + j * 256;
-        if (c < cols) {
-          ld8v(M, m_dt, off + c, m[j]);
-          if (G) ld8v(G, g_dt, off + c, g[j]);
-        }
+        for (int e = 0; e < 8; ++e) m[e] = rnd(m[e] + rnd(g[e], m_dt), m_dt);
+        st8v(M, m_dt, off + c, m);
       }
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int c = c0 + j * 256;
-        if (c < cols) {
-          if (G) {
-#pragma unroll
-            for (int e = 0; e < 8; ++e) m[j][e] = rnd(m[j][e] + rnd(g[j][e], m_dt), m_dt);
-            st8v(M, m_dt, off + c, m[j]);
-          }
-#pragma unroll
-          for (int e = 0; e < 8; ++e) s += fabsf(m[j][e]);
-        }
-      }
+      for (int e = 0; e < 8; ++e) s += fabsf(m[e]);
     }
   } else {
     for (int c = lane; c < cols; c += 32) {

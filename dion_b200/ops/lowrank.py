@@ -192,16 +192,23 @@ def lr_gemm(A: Tensor, B: Tensor, *, a_mn: bool = False, b_mn: bool = False,
 
 
 def triu_inverse(U: Tensor) -> Tensor:
-    """Inverse of every upper-triangular ``U[b]`` (``[B, r, r]`` fp32)."""
-    if U.is_cuda and U.dtype == torch.float32 and U.ndim == 3 and U.size(-1) <= _MAX_FACTOR_DIM:
-        Uc = U.contiguous()
+    """Inverse of every upper-triangular ``U[b]`` (``[B, r, r]`` fp32).  The kernel works on
+    32 x 32 blocks; other sizes are padded with the identity."""
+    r = U.size(-1)
+    if U.is_cuda and U.dtype == torch.float32 and U.ndim == 3 and r <= _MAX_FACTOR_DIM:
+        rp = (r + 31) // 32 * 32
+        if rp != r:
+            Uc = torch.eye(rp, dtype=U.dtype, device=U.device).repeat(U.size(0), 1, 1)
+            Uc[:, :r, :r] = U
+        else:
+            Uc = U.contiguous()
         X = torch.empty_like(Uc)
         rc = _backend.lib("lowrank_ops").dion_triu_inverse(
-            _ptr(Uc), _ptr(X), Uc.size(0), Uc.size(-1), _stream(Uc.device))
+            _ptr(Uc), _ptr(X), Uc.size(0), rp, _stream(Uc.device))
         if rc != 0:
             raise RuntimeError(f"dion_triu_inverse launch failed (code {rc})")
-        return X
-    eye = torch.eye(U.size(-1), dtype=U.dtype, device=U.device).expand_as(U)
+        return X if rp == r else X[:, :r, :r].contiguous()
+    eye = torch.eye(r, dtype=U.dtype, device=U.device).expand_as(U)
     return torch.linalg.solve_triangular(U, eye, upper=True)
 
 

@@ -172,6 +172,8 @@ class Dion(DeviceStatusMixin, Optimizer):
         self._generators: Dict[torch.device, torch.Generator] = {}
         self._q_counter = 0
         self._momentum_stacks: Dict[tuple, Tensor] = {}
+        self._side_streams: Dict[torch.device, list] = {}
+        self._streams_to_join: set = set()
         self._lowrank_sync: Dict[tuple, tuple] = {}
 
     # ------------------------------------------------------------------ randomness ----------
@@ -217,6 +219,9 @@ class Dion(DeviceStatusMixin, Optimizer):
                       self._create_lion_tasks(groups["lion"]),
                       self._create_adamw_tasks(groups["adamw"]))
         AsyncRuntime(tasks, max_concurrent_tasks=3).run()
+        for side in self._streams_to_join:   # batches ran on side streams (see _on_side_stream)
+            torch.cuda.current_stream(side.device).wait_stream(side)
+        self._streams_to_join.clear()
         self._snapshot_device_status()
         return loss
 
@@ -259,10 +264,39 @@ class Dion(DeviceStatusMixin, Optimizer):
                     states = [self._get_or_initialize_state(p, group) for p in params]
                     cfg = self._get_dion_param_config(params[0])
                     task_id += 1
-                    yield AsyncTask(self._dion_update(
+                    update = self._dion_update(
                         kind, batch, params, [p.grad for p in params],
                         [s["momentum"] for s in states], [s["Q"] for s in states], cfg, group,
-                        task_id))
+                        task_id)
+                    yield AsyncTask(self._on_side_stream(update, task_id, to_local(params[0])))
+
+    # Batches are independent of one another, and the factorization kernels of a batch (one CTA
+    # per matrix, long dependent chains) leave most of the GPU idle when the batch is smaller
+    # than the number of SMs.  Each batch therefore runs on one of a few side streams, so that
+    # the kernels of different batches share the GPU; the side streams start after the work
+    # already queued on the caller's stream and are joined before step() returns.
+    _SIDE_STREAMS = 3
+
+    def _on_side_stream(self, gen, task_id: int, sample: Tensor):
+        if not sample.is_cuda or torch.cuda.is_current_stream_capturing():
+            yield from gen
+            return
+        dev = sample.device
+        pool = self._side_streams.get(dev)
+        if pool is None:
+            pool = self._side_streams[dev] = [torch.cuda.Stream(device=dev)
+                                              for _ in range(self._SIDE_STREAMS)]
+        side = pool[task_id % len(pool)]
+        main = torch.cuda.current_stream(dev)
+        side.wait_stream(main)
+        self._streams_to_join.add(side)
+        while True:
+            with torch.cuda.stream(side):
+                try:
+                    next(gen)
+                except StopIteration:
+                    return
+            yield
 
     # Stacked copies of the momentum of one batch are kept below this many bytes.
     _BATCH_BYTES = 2 << 30
