@@ -25,6 +25,7 @@ enum : int {
   kStatusTimeoutTmemEmpty = 4,  // MMA issuer waited for an accumulator that was never drained
   kStatusTimeoutPeer = 5,       // wait on a flag written by another GPU ran out
   kStatusBadArgs = 6,
+  kStatusTimeoutGrid = 7,       // a grid-wide barrier inside a persistent kernel was not completed
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {

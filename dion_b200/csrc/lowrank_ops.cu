@@ -412,6 +412,90 @@ philox_normal_kernel(T* out, long long n, unsigned long long seed, float std_dev
     if (i + k < n) out[i + k] = static_cast<T>(v[k]);
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// Clean-up of the power-iteration factors and the new Q, two launches for a whole batch
+// (reference: fix_all_zero_or_nan, local_column_sum_sq, column_normalize and update_Q_matrix_,
+// dion/dion.py:1414-1558, a dozen element-wise passes over tensors as large as P and R).
+//
+//   fix_factor_kernel   X <- all-zero momentum ? fallback (or 0) : nan_to_num(X)   in place, and
+//                       optionally the column sums of squares of the result (fp32, atomics)
+//   normalize_q_kernel  Q = R / (sqrt(colsq) + eps), written to a stack and, where given, straight
+//                       into the per-parameter state tensors
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ float nan_to_num_f(float v) {
+  if (v != v) return 0.f;
+  if (v == INFINITY) return 3.4028234663852886e38f;
+  if (v == -INFINITY) return -3.4028234663852886e38f;
+  return v;
+}
+template <typename T> __device__ __forceinline__ float to_f(T v);
+template <> __device__ __forceinline__ float to_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f<__nv_bfloat16>(__nv_bfloat16 v) {
+  return __bfloat162float(v);
+}
+template <typename T> __device__ __forceinline__ T from_f(float v);
+template <> __device__ __forceinline__ float from_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float v) {
+  return __float2bfloat16_rn(v);
+}
+
+constexpr int kFixRows = 32;   // rows per block
+
+// X: [batch, rows, cols]; fallback (optional): same shape; sumsq[b] == 0 marks an all-zero
+// momentum; colsq (optional): [batch, cols], pre-zeroed.  grid = (ceil(rows/32), batch).
+template <typename T>
+__global__ void __launch_bounds__(256)
+fix_factor_kernel(T* X, const T* fallback, const float* sumsq, int rows, int cols, float* colsq) {
+  const int b = blockIdx.y;
+  const int r0 = blockIdx.x * kFixRows;
+  const int r1 = min(rows, r0 + kFixRows);
+  const bool zero = sumsq[b] == 0.f;
+  T* x = X + (size_t)b * rows * cols;
+  const T* f = fallback ? fallback + (size_t)b * rows * cols : nullptr;
+  for (int c = threadIdx.x; c < cols; c += 256) {
+    float s = 0.f;
+#pragma unroll 8
+    for (int r = r0; r < r1; ++r) {
+      const size_t e = (size_t)r * cols + c;
+      float v;
+      if (zero) v = f ? to_f<T>(f[e]) : 0.f;
+      else v = nan_to_num_f(to_f<T>(x[e]));
+      const T t = from_f<T>(v);
+      x[e] = t;
+      const float w = to_f<T>(t);
+      s += w * w;
+    }
+    if (colsq) atomicAdd(colsq + (size_t)b * cols + c, s);
+  }
+}
+
+// q_ptrs (optional): one address per matrix (0 = skip) of a [rows, cols] tensor of dtype q_dt.
+template <typename T>
+__global__ void __launch_bounds__(256)
+normalize_q_kernel(const T* R, const float* colsq, float eps, T* Qstack, const long long* q_ptrs,
+                   int q_dt, int rows, int cols) {
+  const int b = blockIdx.y;
+  const int r0 = blockIdx.x * kFixRows;
+  const int r1 = min(rows, r0 + kFixRows);
+  const T* x = R + (size_t)b * rows * cols;
+  T* q = Qstack + (size_t)b * rows * cols;
+  void* state = q_ptrs ? reinterpret_cast<void*>(q_ptrs[b]) : nullptr;
+  for (int c = threadIdx.x; c < cols; c += 256) {
+    const float inv = 1.f / (sqrtf(colsq[(size_t)b * cols + c]) + eps);
+#pragma unroll 8
+    for (int r = r0; r < r1; ++r) {
+      const size_t e = (size_t)r * cols + c;
+      const T t = from_f<T>(to_f<T>(x[e]) * inv);
+      q[e] = t;
+      if (state) {
+        if (q_dt == 0) static_cast<float*>(state)[e] = to_f<T>(t);
+        else static_cast<__nv_bfloat16*>(state)[e] = __float2bfloat16_rn(to_f<T>(t));
+      }
+    }
+  }
+}
+
 }  // namespace dion
 
 using namespace dion;
@@ -510,5 +594,36 @@ DION_EXPORT int dion_philox_normal(void* out, long long n, unsigned long long se
   else
     dion::philox_normal_kernel<__nv_bfloat16><<<blocks, 256, 0, S(stream)>>>(
         static_cast<__nv_bfloat16*>(out), n, seed, std_dev);
+  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+// dt: 0 = fp32, 1 = bf16 (X, fallback).  See fix_factor_kernel.
+DION_EXPORT int dion_fix_factor(void* X, const void* fallback, const float* sumsq, int batch,
+                                int rows, int cols, float* colsq, int dt, void* stream) {
+  if (batch <= 0 || rows <= 0 || cols <= 0) return 0;
+  dim3 grid((rows + dion::kFixRows - 1) / dion::kFixRows, batch);
+  if (dt == 0)
+    dion::fix_factor_kernel<float><<<grid, 256, 0, S(stream)>>>(
+        static_cast<float*>(X), static_cast<const float*>(fallback), sumsq, rows, cols, colsq);
+  else
+    dion::fix_factor_kernel<__nv_bfloat16><<<grid, 256, 0, S(stream)>>>(
+        static_cast<__nv_bfloat16*>(X), static_cast<const __nv_bfloat16*>(fallback), sumsq, rows,
+        cols, colsq);
+  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+DION_EXPORT int dion_normalize_q(const void* R, const float* colsq, float eps, void* Qstack,
+                                 const void* q_ptrs, int q_dt, int batch, int rows, int cols,
+                                 int dt, void* stream) {
+  if (batch <= 0 || rows <= 0 || cols <= 0) return 0;
+  dim3 grid((rows + dion::kFixRows - 1) / dion::kFixRows, batch);
+  if (dt == 0)
+    dion::normalize_q_kernel<float><<<grid, 256, 0, S(stream)>>>(
+        static_cast<const float*>(R), colsq, eps, static_cast<float*>(Qstack),
+        static_cast<const long long*>(q_ptrs), q_dt, rows, cols);
+  else
+    dion::normalize_q_kernel<__nv_bfloat16><<<grid, 256, 0, S(stream)>>>(
+        static_cast<const __nv_bfloat16*>(R), colsq, eps, static_cast<__nv_bfloat16*>(Qstack),
+        static_cast<const long long*>(q_ptrs), q_dt, rows, cols);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }

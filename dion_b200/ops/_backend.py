@@ -34,6 +34,7 @@ NVCC_FLAGS = [
 SOURCES = {
     "ns_gemm_sm100": "libdion_ns_gemm.so",
     "ns_gemm2_sm100": "libdion_ns_gemm2.so",
+    "ns_persistent_sm100": "libdion_ns_persistent.so",
     "foreach_ops": "libdion_foreach.so",
     "select_ops": "libdion_select.so",
     "model_ops": "libdion_model.so",

@@ -19,6 +19,7 @@ from . import _backend
 
 _BM = 128
 _tile_cache: Dict[Tuple, Tensor] = {}
+_tile_hosts: Dict[Tuple, Tensor] = {}
 _status: Dict[int, Tensor] = {}
 _sm_count: Dict[int, int] = {}
 
@@ -29,6 +30,7 @@ STATUS_MESSAGES = {
     4: "MMA warp timed out waiting for a drained accumulator",
     5: "wait on a peer GPU's flag timed out",
     6: "bad arguments",
+    7: "grid-wide barrier of a persistent kernel timed out",
 }
 
 
@@ -129,7 +131,15 @@ def tile_table(M: int, N: int, bn: int, sym: bool, device: torch.device,
             if sym and (tn + 1) * bn - 1 < tm * bm:
                 continue
             pairs.append((tm, tn))
-    t = torch.tensor(pairs, dtype=torch.int32, device=device).contiguous()
+    host = torch.tensor(pairs, dtype=torch.int32)
+    if torch.cuda.is_current_stream_capturing():
+        # First use of this shape inside a graph capture: the copy is recorded, so it has to
+        # read pinned memory that stays alive as long as the table does.
+        host = host.pin_memory()
+        _tile_hosts[key] = host
+        t = host.to(device, non_blocking=True)
+    else:
+        t = host.to(device)
     _tile_cache[key] = t
     return t
 
@@ -380,4 +390,67 @@ def ns_iterate(X: Tensor, Xalt: Tensor, A: Tensor, Bm: Tensor, coeffs, scale: Op
     if rc != 0:
         raise RuntimeError(f"dion_ns_iterate2 failed with code {rc}")
     _backend.add_launches(3 * len(coeffs))
+    return Xalt if len(coeffs) % 2 else X
+
+
+_persist_tiles: Dict[Tuple, Tensor] = {}
+_persist_counter: Dict[int, Tensor] = {}
+
+
+def persistent_enabled() -> bool:
+    """``DION_B200_PERSISTENT_NS`` (default on): small batches run the whole Newton-Schulz loop
+    in one cooperative launch instead of three launches per iteration."""
+    return os.environ.get("DION_B200_PERSISTENT_NS", "1") != "0"
+
+
+def persistent_in_graphs() -> bool:
+    """Whether the cooperative one-launch loop may be recorded into a CUDA graph
+    (``DION_B200_PERSISTENT_NS=graph``)."""
+    return os.environ.get("DION_B200_PERSISTENT_NS", "1") == "graph"
+
+
+def persistent_fits(X: Tensor, batch: int, m: int, n: int, iters: int) -> bool:
+    """The one-launch form pays when no GEMM of the loop has more 128 x 128 tiles than the GPU
+    has SMs (every phase is then a single wave and launch / fill / drain dominate)."""
+    if not persistent_enabled() or not X.is_contiguous() or X.data_ptr() % 16 or m % 8 or n % 8:
+        return False
+    if iters > 8:
+        return False
+    if torch.cuda.is_current_stream_capturing() and not persistent_in_graphs():
+        return False
+    g = min(m, n)
+    tiles = max(_num_tiles(g, g, _BM, 128, True), _num_tiles(m, n, _BM, 128, False)) * batch
+    return tiles <= sm_count(X.device)
+
+
+def ns_persistent(X: Tensor, Xalt: Tensor, A: Tensor, Bm: Tensor, coeffs,
+                  scale: Optional[Tensor]) -> Optional[Tensor]:
+    """All iterations in one cooperative launch (csrc/ns_persistent_sm100.cu).  Returns the
+    buffer that holds the result, or None when the launch could not be made co-resident (the
+    caller falls back to per-GEMM launches; nothing has been written then)."""
+    batch, m, n = X.shape
+    dev = X.device
+    g = min(m, n)
+    key = (m, n, dev.index)
+    tab = _persist_tiles.get(key)
+    if tab is None:
+        gg = tile_table(g, g, 128, True, dev)
+        mn = tile_table(m, n, 128, False, dev)
+        tab = _persist_tiles[key] = (torch.cat([gg, mn]).contiguous(), gg.size(0), mn.size(0))
+    tiles, n_gg, n_mn = tab
+    idx = dev.index if dev.index is not None else torch.cuda.current_device()
+    counter = _persist_counter.get(idx)
+    if counter is None:
+        counter = _persist_counter[idx] = torch.zeros(2, dtype=torch.int32, device=dev)
+    flat = (ctypes.c_float * (3 * len(coeffs)))(*[float(v) for abc in coeffs for v in abc])
+    st = status_tensor(dev)
+    rc = _backend.lib("ns_persistent_sm100").dion_ns_persistent(
+        _p(X), _p(Xalt), _p(A), _p(Bm), ctypes.c_int(batch), ctypes.c_int(m), ctypes.c_int(n),
+        flat, ctypes.c_int(len(coeffs)), _p(scale), _p(tiles), ctypes.c_int(n_gg),
+        ctypes.c_int(n_mn), _p(counter), ctypes.c_int(sm_count(dev)), _p(st),
+        ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream))
+    if rc == -20:
+        return None
+    if rc != 0:
+        raise RuntimeError(f"dion_ns_persistent failed with code {rc}")
     return Xalt if len(coeffs) % 2 else X

@@ -41,16 +41,22 @@ class _LrExtra(ctypes.Structure):
 _pointer_tables: dict = {}
 
 
-def _pointer_table(tensors: List[Tensor]) -> Tensor:
-    """int64 device tensor of the data pointers of ``tensors`` (cached by those pointers)."""
-    key = tuple(t.data_ptr() for t in tensors)
+def _address_table(addresses: tuple, device: torch.device) -> Tensor:
+    """int64 device tensor holding ``addresses``; cached by value, because building one is a
+    blocking host-to-device copy and the state tensors keep their addresses from step to step."""
+    key = (addresses, device.index)
     tab = _pointer_tables.get(key)
     if tab is None:
-        if len(_pointer_tables) > 256:
+        if len(_pointer_tables) > 512:
             _pointer_tables.clear()
-        tab = torch.tensor(key, dtype=torch.int64).to(tensors[0].device)
+        tab = torch.tensor(addresses, dtype=torch.int64).to(device)
         _pointer_tables[key] = tab
     return tab
+
+
+def _pointer_table(tensors: List[Tensor]) -> Tensor:
+    """int64 device tensor of the data pointers of ``tensors`` (cached by those pointers)."""
+    return _address_table(tuple(t.data_ptr() for t in tensors), tensors[0].device)
 
 
 def _ld_stride3(t: Tensor) -> Tuple[int, int]:
@@ -347,6 +353,57 @@ def fix_all_zero_or_nan(P: Tensor, R: Tensor, Q_init: Tensor, B: Optional[Tensor
         zero = (torch.linalg.vector_norm(B, ord=float("inf"), dim=(-2, -1), keepdim=True) == 0)
     keep = ~zero
     return P.nan_to_num() * keep, R.nan_to_num() * keep + Q_init * zero
+
+
+def _factor_kernel_ok(*ts: Tensor) -> bool:
+    from ..utils.tensors import is_plain_tensor
+
+    dt = ts[0].dtype
+    return dt in (torch.float32, torch.bfloat16) and all(
+        t.is_cuda and t.dtype == dt and t.ndim == 3 and t.is_contiguous() and is_plain_tensor(t)
+        and t.numel() for t in ts)
+
+
+def fix_factors_(P: Tensor, R: Tensor, Q_init: Tensor, sum_sq: Tensor) -> Tensor:
+    """In-place form of :func:`fix_all_zero_or_nan` for GPU batches, one launch per factor:
+    where ``sum_sq[b] == 0`` (all-zero momentum) ``P[b] = 0`` and ``R[b] = Q_init[b]``, elsewhere
+    NaN / infinities are replaced as ``nan_to_num`` does.  Returns the column sums of squares of
+    the cleaned ``R`` (``[B, 1, r]`` fp32), which the second launch accumulates on the way."""
+    assert _factor_kernel_ok(P, R, Q_init) and sum_sq.dtype == torch.float32
+    lib = _backend.lib("lowrank_ops")
+    dt = 0 if P.dtype == torch.float32 else 1
+    B = P.size(0)
+    rc = lib.dion_fix_factor(_ptr(P), ctypes.c_void_p(0), _ptr(sum_sq), B, P.size(1), P.size(2),
+                             ctypes.c_void_p(0), dt, _stream(P.device))
+    colsq = torch.zeros((B, 1, R.size(2)), dtype=torch.float32, device=R.device)
+    rc |= lib.dion_fix_factor(_ptr(R), _ptr(Q_init), _ptr(sum_sq), B, R.size(1), R.size(2),
+                              _ptr(colsq), dt, _stream(R.device))
+    if rc != 0:
+        raise RuntimeError("dion_fix_factor launch failed")
+    return colsq
+
+
+def normalize_columns_into(R: Tensor, colsq: Tensor, epsilon: float,
+                           q_states: Optional[List[Tensor]] = None) -> Tensor:
+    """``Q = R / (sqrt(colsq) + eps)`` in one launch; returns the stack ``Q`` (dtype of ``R``)
+    and, when ``q_states`` is given (one contiguous ``[rows, r]`` tensor per matrix, or None to
+    skip), also writes each matrix into its state tensor (fp32 or bf16)."""
+    assert _factor_kernel_ok(R) and colsq.dtype == torch.float32
+    B, rows, cols = R.shape
+    Q = torch.empty_like(R)
+    q_ptrs, q_dt = 0, 0
+    if q_states is not None:
+        live = [q for q in q_states if q is not None]
+        q_dt = 0 if (live and live[0].dtype == torch.float32) else 1
+        addrs = tuple([q.data_ptr() if q is not None else 0 for q in q_states]
+                      + [0] * (B - len(q_states)))
+        q_ptrs = _address_table(addrs, R.device).data_ptr()
+    rc = _backend.lib("lowrank_ops").dion_normalize_q(
+        _ptr(R), _ptr(colsq), ctypes.c_float(float(epsilon)), _ptr(Q), ctypes.c_void_p(q_ptrs),
+        q_dt, B, rows, cols, 0 if R.dtype == torch.float32 else 1, _stream(R.device))
+    if rc != 0:
+        raise RuntimeError("dion_normalize_q launch failed")
+    return Q
 
 
 def local_column_sum_sq(X: Tensor) -> Tensor:

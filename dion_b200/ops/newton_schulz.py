@@ -183,6 +183,10 @@ def _iterate_cuda(X: Tensor, coeffs: Coeffs, scale: Optional[Tensor], hooks=None
     A = torch.empty((B_, g, g), dtype=torch.bfloat16, device=X.device)
     Bm = torch.empty_like(A)
     C = torch.empty_like(X)
+    if hooks is None and gemm.persistent_fits(X, B_, m, n, len(coeffs)):
+        done = gemm.ns_persistent(X, C, A, Bm, coeffs, scale)
+        if done is not None:
+            return done
     if hooks is None and gemm.iterate_in_one_call(X, B_, m, n):
         return gemm.ns_iterate(X, C, A, Bm, coeffs, scale)
     last = len(coeffs) - 1

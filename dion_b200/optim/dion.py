@@ -665,18 +665,30 @@ class Dion(DeviceStatusMixin, Optimizer):
                 yield
                 work.wait()
 
-        P, R = LR.fix_all_zero_or_nan(P, R, Qb, M3, sum_sq=m_sq)
-        if fx is not None:   # the symmetric stacks have been read for the last time
-            for w in fx:
-                if w is not None and w.seq_open:
-                    w.release()
+        # Clean-up of the factors, column normalization and the write-back of Q: two fused
+        # launches plus one where the kernels apply, PyTorch passes otherwise.
+        fused_tail = (m_sq is not None and P.is_cuda and P.dtype == R.dtype == Qb.dtype
+                      and LR._factor_kernel_ok(P.contiguous(), R.contiguous(), Qb))
+        if fused_tail:
+            P, R = P.contiguous(), R.contiguous()
+            ss = LR.fix_factors_(P, R, Qb, m_sq)
+        else:
+            P, R = LR.fix_all_zero_or_nan(P, R, Qb, M3, sum_sq=m_sq)
+            ss = None
         LR.rank_update_stack_(M3, P, R, alpha=-(1 - mu), beta=1.0, transpose=tr)
 
         if outer_pg is not None:
-            ss = LR.local_column_sum_sq(R)
+            if ss is None:
+                ss = LR.local_column_sum_sq(R)
             work = C.all_reduce_(ss, outer_pg, op="sum", async_op=True)
             yield
             work.wait()
+        direct_q = fused_tail and not (kind == "inner_sharded" and inner_pg is not None) \
+            and all(q.is_contiguous() and q.dtype in (torch.float32, torch.bfloat16)
+                    and q.dtype == Q[0].dtype for q in Q[:n_real])
+        if fused_tail:
+            Q_new = LR.normalize_columns_into(R, ss, eps, Q[:n_real] if direct_q else None)
+        elif ss is not None:
             Q_new = LR.column_normalize(R, full_column_sum_sq=ss, epsilon=eps)
         else:
             Q_new = LR.column_normalize(R, epsilon=eps)
@@ -684,8 +696,14 @@ class Dion(DeviceStatusMixin, Optimizer):
         scaled_lr = math.sqrt(fan_out / fan_in) * lr
         LR.foreach_baddbmm_(X[:n_real], P[:n_real], Q_new[:n_real], alpha=-scaled_lr,
                             beta=1 - lr * wd, transpose=tr)
+        if fx is not None:   # the symmetric stacks have been read for the last time
+            for w in fx:
+                if w is not None and w.seq_open:
+                    w.release()
 
         # Write the new Q back into the (possibly TP-sharded) state.
+        if direct_q:
+            return
         if kind == "inner_sharded" and inner_pg is not None:
             W, i_rank = dist.get_world_size(inner_pg), dist.get_rank(inner_pg)
             c = Q_new.size(-1) // W

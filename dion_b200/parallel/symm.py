@@ -74,8 +74,12 @@ class SymmetricBuffer:
         self.world = dist.get_world_size(pg)
         nbytes = (nbytes + 255) // 256 * 256
         dev = torch.device("cuda", torch.cuda.current_device())
-        try:
-            symm_mem.enable_symm_mem_for_group(pg.group_name)
+        import warnings
+
+        try:   # needed by older releases, a deprecated no-op in newer ones
+            with warnings.catch_warnings():
+                warnings.simplefilter("ignore")
+                symm_mem.enable_symm_mem_for_group(pg.group_name)
         except Exception:
             pass
         self.local = symm_mem.empty(nbytes, dtype=torch.uint8, device=dev)
