@@ -289,14 +289,16 @@ def _():
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--only", default=None)
+    ap.add_argument("--only", default=None, help="one kernel name, or several separated by commas")
     ap.add_argument("--iters", type=int, default=10)
     args = ap.parse_args()
     peak = hbm_peak()
-    if args.only and args.only not in CASES:
-        raise SystemExit(f"unknown kernel {args.only!r}; one of: {', '.join(CASES)}")
+    only = [s for s in args.only.split(",") if s] if args.only else []
+    for name in only:
+        if name not in CASES:
+            raise SystemExit(f"unknown kernel {name!r}; one of: {', '.join(CASES)}")
     for name, builder in CASES.items():
-        if args.only and args.only != name:
+        if only and name not in only:
             continue
         fn, nbytes = builder()
         ms = timed(fn, iters=args.iters)

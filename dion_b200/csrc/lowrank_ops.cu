@@ -496,6 +496,155 @@ normalize_q_kernel(const T* R, const float* colsq, float eps, T* Qstack, const l
   }
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// Blocked upper Cholesky factor (fp32), one CTA of 16 warps per matrix, r a multiple of 32 up to
+// 1024:  G = U^T U.  Right-looking over 32 x 32 blocks, all in the output buffer (which starts as
+// a copy of the upper blocks of G):
+//   for every block row k:  warp 0 factors the diagonal block in registers (lane l owns column
+//                           l; the row being eliminated travels by shuffles) and inverts the
+//                           factor;
+//                           block row:  U[k,j] = inv(U[k,k])^T G[k,j]          one block per warp
+//                           trailing:   G[i,j] -= U[k,i]^T U[k,j], k < i <= j  one block per warp
+// Every product is a 32 x 32 x 32 block operation with the left factor staged in the warp's own
+// shared-memory buffer and the right factor's column in registers.  A non-positive pivot gives
+// NaN, which propagates (the caller's clean-up turns the update into a no-op), as
+// torch.linalg.cholesky_ex does not raise either.
+// ---------------------------------------------------------------------------------------------
+// Copy the 32 x 32 block A[m0.., a0..] of a row-major matrix into the warp's staging buffer
+// (32 independent coalesced loads per lane).
+__device__ __forceinline__ void stage_block(const float* A, int r, int m0, int a0, float* stage,
+                                            int lane) {
+  float tmp[32];
+#pragma unroll
+  for (int m = 0; m < 32; ++m) tmp[m] = A[(size_t)(m0 + m) * r + a0 + lane];
+  __syncwarp();
+#pragma unroll
+  for (int m = 0; m < 32; ++m) stage[m * kBlkPitch + lane] = tmp[m];
+  __syncwarp();
+}
+
+// acc[a] += sum_m S[m][a] * xm[m]  (S^T times a column) for a staged block S: one row of S per
+// m, read as 16-byte broadcasts.
+__device__ __forceinline__ void mac_t_staged(const float* stage, const float (&xm)[32],
+                                             float (&acc)[32]) {
+#pragma unroll
+  for (int m = 0; m < 32; ++m) {
+    const float4* row = reinterpret_cast<const float4*>(stage + m * kBlkPitch);
+    const float x = xm[m];
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      const float4 u = row[q];
+      acc[q * 4] += u.x * x;
+      acc[q * 4 + 1] += u.y * x;
+      acc[q * 4 + 2] += u.z * x;
+      acc[q * 4 + 3] += u.w * x;
+    }
+  }
+}
+
+constexpr int kCholWarps = 16;
+
+__global__ void __launch_bounds__(kCholWarps * 32, 1)
+cholesky_blocked_kernel(const float* __restrict__ Gall, float* Uall, int r) {
+  extern __shared__ __align__(16) float cb_smem[];
+  __shared__ __align__(16) float Yk[32 * kBlkPitch];   // inv(U[k,k]), row-major
+  const int NB = r >> 5;
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  float* stage = cb_smem + (size_t)w * 32 * kBlkPitch;
+  const float* G = Gall + (size_t)blockIdx.x * r * r;
+  float* U = Uall + (size_t)blockIdx.x * r * r;
+
+  // U <- upper blocks of G, zero below.
+  for (int e = threadIdx.x; e < r * (r / 4); e += kCholWarps * 32) {
+    const int row = e / (r / 4), c4 = e - row * (r / 4);
+    const int col = c4 * 4;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if ((col >> 5) >= (row >> 5)) v = *reinterpret_cast<const float4*>(G + (size_t)row * r + col);
+    *reinterpret_cast<float4*>(U + (size_t)row * r + col) = v;
+  }
+  __syncthreads();
+
+  for (int k = 0; k < NB; ++k) {
+    const int k0 = k * 32;
+    if (w == 0) {
+      // ---- factor the diagonal block: lane l owns column l (a[i] = element (i, l)) ----
+      float a[32];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) a[i] = U[(size_t)(k0 + i) * r + k0 + l];
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const float piv = sqrtf(__shfl_sync(0xffffffffu, a[j], j));   // NaN if not positive
+        const float rj = (l >= j) ? a[j] / piv : 0.f;                 // row j of the factor
+        a[j] = rj;
+#pragma unroll
+        for (int i = j + 1; i < 32; ++i) {
+          const float rji = __shfl_sync(0xffffffffu, rj, i);
+          a[i] -= rji * rj;                                           // meaningful for l >= i
+        }
+      }
+      // write the factor (zero below the diagonal) and stage it for the inversion
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        const float v = (l >= i) ? a[i] : 0.f;
+        U[(size_t)(k0 + i) * r + k0 + l] = v;
+        stage[i * kBlkPitch + l] = v;
+      }
+      __syncwarp();
+      // ---- invert it: lane l solves R y = e_l by back substitution ----
+      float y[32];
+      const float* vs = stage;
+#pragma unroll
+      for (int i = 31; i >= 0; --i) {
+        float sacc = (i == l) ? 1.f : 0.f;
+#pragma unroll
+        for (int m = i + 1; m < 32; ++m) sacc -= vs[i * kBlkPitch + m] * y[m];
+        y[i] = sacc / vs[i * kBlkPitch + i];
+      }
+#pragma unroll
+      for (int i = 0; i < 32; ++i) Yk[i * kBlkPitch + l] = y[i];
+    }
+    __syncthreads();
+    // ---- block row: U[k,j] = Yk^T G[k,j] for j > k ----
+    for (int j = k + 1 + w; j < NB; j += kCholWarps) {
+      const int j0 = j * 32;
+      // Without this the 1024 loop-invariant reads of Yk are hoisted out of the loop and spilled.
+      asm volatile("" ::: "memory");
+      float g[32], acc[32];
+#pragma unroll
+      for (int m = 0; m < 32; ++m) {
+        g[m] = U[(size_t)(k0 + m) * r + j0 + l];
+        acc[m] = 0.f;
+      }
+      mac_t_staged(Yk, g, acc);          // acc[a] = sum_m Yk[m][a] * g[m]
+#pragma unroll
+      for (int a = 0; a < 32; ++a) U[(size_t)(k0 + a) * r + j0 + l] = acc[a];
+    }
+    __syncthreads();
+    // ---- trailing update: G[i,j] -= U[k,i]^T U[k,j] for k < i <= j ----
+    const int nt = NB - k - 1;              // trailing blocks per side
+    const int total = nt * (nt + 1) / 2;
+    for (int t = w; t < total; t += kCholWarps) {
+      // t -> (ii, jj) with ii <= jj over the upper triangle, row by row
+      int ii = 0, rem = t;
+      while (rem >= nt - ii) { rem -= nt - ii; ++ii; }
+      const int i = k + 1 + ii, j = i + rem;
+      const int i0 = i * 32, j0 = j * 32;
+      stage_block(U, r, k0, i0, stage, l);       // U[k,i]
+      float xm[32], acc[32];
+#pragma unroll
+      for (int m = 0; m < 32; ++m) {
+        xm[m] = U[(size_t)(k0 + m) * r + j0 + l];
+        acc[m] = 0.f;
+      }
+      mac_t_staged(stage, xm, acc);
+#pragma unroll
+      for (int a = 0; a < 32; ++a) U[(size_t)(i0 + a) * r + j0 + l] -= acc[a];
+    }
+    __syncthreads();
+  }
+}
+
 }  // namespace dion
 
 using namespace dion;
@@ -545,6 +694,20 @@ DION_EXPORT int dion_cholesky_upper(const void* G, void* U, int n, int r, void* 
   if (r > 1024) return -2;
   const float* g = static_cast<const float*>(G);
   float* u = static_cast<float*>(U);
+  if ((r & 31) == 0 && r >= 64 && G != U && (reinterpret_cast<uintptr_t>(G) & 15) == 0 &&
+      (reinterpret_cast<uintptr_t>(U) & 15) == 0) {
+    // blocked kernel (the column-by-column kernel below serves the remaining sizes)
+    static bool configured = false;
+    constexpr int kStage = dion::kCholWarps * 32 * dion::kBlkPitch * 4;
+    if (!configured) {
+      if (cudaFuncSetAttribute(dion::cholesky_blocked_kernel,
+                               cudaFuncAttributeMaxDynamicSharedMemorySize, kStage) != cudaSuccess)
+        return -3;
+      configured = true;
+    }
+    dion::cholesky_blocked_kernel<<<n, dion::kCholWarps * 32, kStage, S(stream)>>>(g, u, r);
+    return cudaGetLastError() == cudaSuccess ? 0 : -1;
+  }
   if (r <= 256) return launch_chol<8>(g, u, n, r, S(stream));
   if (r <= 512) return launch_chol<16>(g, u, n, r, S(stream));
   if (r <= 768) return launch_chol<24>(g, u, n, r, S(stream));

@@ -312,8 +312,9 @@ def qkv_rope(h: Tensor, wq: Tensor, wk: Tensor, wv: Tensor, cos: Tensor, sin: Te
 # Embedding and linear layers with mixed-precision-aware backward passes
 # ------------------------------------------------------------------------------------------------
 class _Embedding(torch.autograd.Function):
-    """``weight[idx]`` whose backward sorts the token ids once and sums the rows of each id in a
-    single kernel (deterministic; replaces the several passes of the stock dense backward)."""
+    """``weight[idx]`` whose backward sorts the token ids once and writes every row of the weight
+    gradient exactly once in a single kernel - the sum of the id's rows, or zeros (deterministic;
+    replaces the zero fill and the several passes of the stock dense backward)."""
 
     @staticmethod
     def forward(ctx, idx: Tensor, weight: Tensor):
@@ -331,7 +332,7 @@ class _Embedding(torch.autograd.Function):
         dy2 = dy.reshape(-1, C)
         if not dy2.is_contiguous():
             dy2 = dy2.contiguous()
-        gw = torch.zeros((V, C), dtype=torch.float32, device=dy.device)
+        gw = torch.empty((V, C), dtype=torch.float32, device=dy.device)   # every row is written
         _check(_lib().dion_embedding_bwd(_c(sorted_idx), _c(perm), _c(dy2), _DT[dy2.dtype], _c(gw),
                                          ctypes.c_longlong(flat.numel()), C, ctypes.c_longlong(V),
                                          _stream(dy.device)), "dion_embedding_bwd")

@@ -132,7 +132,7 @@ def tile_table(M: int, N: int, bn: int, sym: bool, device: torch.device,
                 continue
             pairs.append((tm, tn))
     host = torch.tensor(pairs, dtype=torch.int32)
-    if torch.cuda.is_current_stream_capturing():
+    if device.type == "cuda" and torch.cuda.is_current_stream_capturing():
         # First use of this shape inside a graph capture: the copy is recorded, so it has to
         # read pinned memory that stays alive as long as the table does.
         host = host.pin_memory()
@@ -403,6 +403,16 @@ def persistent_enabled() -> bool:
     return os.environ.get("DION_B200_PERSISTENT_NS", "1") != "0"
 
 
+def persistent_waves() -> float:
+    """Largest GEMM of the loop, in waves of 128 x 128 tiles over the SMs, up to which the
+    one-launch form is used (``DION_B200_PERSISTENT_WAVES``, default 1: beyond that the
+    256 x 256 two-CTA kernel's better efficiency outweighs the saved launches)."""
+    try:
+        return float(os.environ.get("DION_B200_PERSISTENT_WAVES", "1"))
+    except ValueError:
+        return 1.0
+
+
 def persistent_in_graphs() -> bool:
     """Whether the cooperative one-launch loop may be recorded into a CUDA graph
     (``DION_B200_PERSISTENT_NS=graph``)."""
@@ -420,7 +430,7 @@ def persistent_fits(X: Tensor, batch: int, m: int, n: int, iters: int) -> bool:
         return False
     g = min(m, n)
     tiles = max(_num_tiles(g, g, _BM, 128, True), _num_tiles(m, n, _BM, 128, False)) * batch
-    return tiles <= sm_count(X.device)
+    return tiles <= persistent_waves() * sm_count(X.device)
 
 
 def ns_persistent(X: Tensor, Xalt: Tensor, A: Tensor, Bm: Tensor, coeffs,

@@ -40,7 +40,7 @@ def test_qr_r_factor_zero_column_is_finite():
     assert R[1].abs().max().item() == 0.0
 
 
-@pytest.mark.parametrize("shape", [(3, 96), (5, 192), (2, 512), (2, 768), (4, 17)])
+@pytest.mark.parametrize("shape", [(3, 96), (5, 192), (2, 512), (2, 768), (4, 17), (2, 64), (1, 1024)])
 def test_cholesky_upper(shape):
     from dion_b200.ops import lowrank as LR
     B, r = shape

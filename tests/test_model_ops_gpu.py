@@ -110,6 +110,34 @@ def test_embedding_backward_matches_torch():
     assert w.grad[60:V - 1].abs().max().item() == 0.0
 
 
+def test_embedding_backward_long_runs_and_absent_rows():
+    """Ids that occur hundreds of times (split over the block's warps), ids that occur once,
+    rows that never occur (written as zeros, not left as allocated), a row count that is no
+    multiple of the warps per block, and bit-identical results from call to call."""
+    torch.manual_seed(3)
+    V, C, T = 1003, 768, 4096
+    w = torch.randn(V, C, device="cuda", requires_grad=True)
+    idx = torch.randint(0, V, (T,), device="cuda")
+    idx[:900] = 7            # one long run
+    idx[900:1500] = V - 1    # another, in the last (partial) group of rows
+    idx[1500:1565] = 500     # just above the threshold
+    idx[1565:1629] = 501     # exactly at it
+    idx = idx[torch.randperm(T, device="cuda")].reshape(4, T // 4)
+    g = torch.randn(4, T // 4, C, device="cuda")
+    junk = torch.full((V, C), float("nan"), device="cuda")   # what an uninitialised buffer may hold
+    del junk
+    (g1,) = torch.autograd.grad(Fn.embedding(idx, w), w, g)
+    (g2,) = torch.autograd.grad(Fn.embedding(idx, w), w, g)
+    assert torch.equal(g1, g2)
+    ref = torch.zeros(V, C, device="cuda", dtype=torch.float64)
+    ref.index_add_(0, idx.reshape(-1), g.reshape(-1, C).double())
+    assert torch.isfinite(g1).all()
+    assert (g1.double() - ref).abs().max().item() < 1e-3
+    absent = torch.ones(V, dtype=torch.bool, device="cuda")
+    absent[idx.reshape(-1)] = False
+    assert absent.any() and g1[absent].abs().max().item() == 0.0
+
+
 def test_linear_bf16_fp32_weight_grad():
     torch.manual_seed(0)
     x = torch.randn(3, 40, 256, device="cuda").bfloat16().requires_grad_()
