@@ -132,11 +132,19 @@ __device__ __forceinline__ float block_sum(float v) {
 // Muon pre-orthogonalize: M = mu*M + G;  U = nesterov ? mu*M + G : M;  U -> bf16 (+ sum of u^2).
 // Table pointers: 0=G, 1=M, 2=U(bf16 out).  sumsq (optional): one float per tensor.
 // With add_only != 0 computes M += G and U = M (Dion2's accumulate step).
+// u_cols > 0: every tensor is a [rows, u_cols] matrix whose U goes into a wider matrix with row
+// pitch u_ld (a column block of an assembled matrix, possibly in a peer's memory): element i is
+// stored at (i / u_cols) * u_ld + i % u_cols.  u_cols must be a multiple of 8.
 // ---------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(kThreads)
 muon_pre_kernel(const long long* raw, int g_dt, int m_dt, float mu, int nesterov, int add_only,
-                float* sumsq, int sumsq_in_table) {
+                float* sumsq, int sumsq_in_table, long long u_cols, long long u_ld) {
   Table tb{raw};
+  auto u_index = [&](long long i) -> long long {
+    if (u_cols <= 0) return i;
+    const long long row = i / u_cols;
+    return row * u_ld + (i - row * u_cols);
+  };
   float acc = 0.f;
   const void* G;
   void* M;
@@ -175,7 +183,7 @@ muon_pre_kernel(const long long* raw, int g_dt, int m_dt, float mu, int nesterov
           acc += uk * uk;
         }
         st8b(M, i, m);
-        if (U) st8b(U, i, u);
+        if (U) st8b(U, u_index(i), u);
       };
       if (h0) body(g0, m0, i0);
       if (h1) body(g1, m1, i1);
@@ -214,11 +222,11 @@ muon_pre_kernel(const long long* raw, int g_dt, int m_dt, float mu, int nesterov
     }
     if (full) {
       st4(M, m_dt, i, vm, m);
-      if (U) st4(U, DT_BF16, i, vu, u);
+      if (U) st4(U, DT_BF16, u_index(i), vu, u);
     } else {
       for (int k = 0; k < 4 && i + k < end; ++k) {
         st(M, m_dt, i + k, m[k]);
-        if (U) st(U, DT_BF16, i + k, u[k]);
+        if (U) st(U, DT_BF16, u_index(i + k), u[k]);
       }
     }
   })
@@ -816,11 +824,12 @@ static inline int rc() { return cudaGetLastError() == cudaSuccess ? 0 : -1; }
 
 DION_EXPORT int dion_muon_pre(const void* table, long long n_chunks, int g_dt, int m_dt, float mu,
                               int nesterov, int add_only, float* sumsq, int sumsq_in_table,
-                              void* stream) {
+                              long long u_cols, long long u_ld, void* stream) {
   if (n_chunks <= 0) return 0;
+  if (u_cols > 0 && ((u_cols & 7) || (u_ld & 7) || u_ld < u_cols)) return -2;
   muon_pre_kernel<<<(unsigned)n_chunks, kThreads, 0, S(stream)>>>(
       static_cast<const long long*>(table), g_dt, m_dt, mu, nesterov, add_only, sumsq,
-      sumsq_in_table);
+      sumsq_in_table, u_cols, u_ld);
   return rc();
 }
 

@@ -262,115 +262,6 @@ rope_qknorm_bwd_kernel(const __nv_bfloat16* Q, const __nv_bfloat16* K, long long
 }
 
 // ---------------------------------------------------------------------------------------------
-// Embedding backward.  `sorted` holds the token ids in ascending order and `perm` the position
-// each came from.  One warp per row of GW: it finds the row's run of equal ids by a 32-way
-// search over `sorted` (three rounds for 32 K tokens), then either sums the run's rows of DY in
-// fp32 - in position order, so the result is deterministic - or writes zeros.  Every row of GW
-// is written exactly once, so the caller needs no zero fill.  A run longer than kEmbLongRun is
-// split into eight contiguous segments over the block's warps, whose partial sums are added in
-// segment order (still deterministic): real token streams have ids that occur thousands of times
-// per batch, and one warp walking such a run alone would decide the kernel's duration.
-// ---------------------------------------------------------------------------------------------
-constexpr int kEmbWarps = 8;
-constexpr int kEmbLongRun = 64;
-
-// First index in [0, n) whose sorted id is >= v (n if none); all lanes get the same answer.
-__device__ __forceinline__ long long warp_lower_bound(const long long* __restrict__ sorted,
-                                                      long long n, long long v, int lane) {
-  long long lo = 0, hi = n;                     // answer lies in [lo, hi]
-  while (hi - lo >= 32) {
-    const long long step = (hi - lo + 31) / 32;
-    long long p = lo + (long long)(lane + 1) * step - 1;   // last element of this lane's slice
-    if (p > hi - 1) p = hi - 1;
-    const unsigned ge = __ballot_sync(0xffffffffu, sorted[p] >= v);
-    if (ge == 0u) return hi;                    // the slices cover [lo, hi): nothing is >= v
-    const int f = __ffs(ge) - 1;                // first slice whose last element is >= v
-    const long long nlo = lo + (long long)f * step;
-    long long nhi = nlo + step - 1;             // that element is >= v: answer <= its index
-    if (nhi > hi - 1) nhi = hi - 1;
-    lo = nlo;
-    hi = nhi;
-  }
-  const long long q = lo + lane;
-  const unsigned ge = __ballot_sync(0xffffffffu, q < hi ? sorted[q] >= v : true);
-  return lo + (__ffs(ge) - 1);                  // lanes at or past hi vote "true": at most hi
-}
-
-// acc += the rows perm[j] of DY for j in [j0, j1), columns [c8*8, c8*8+8), four loads in flight.
-__device__ __forceinline__ void emb_sum_run(const void* __restrict__ DY, int dy_dt,
-                                            const long long* __restrict__ perm, long long j0,
-                                            long long j1, int C, int c8, float (&acc)[8]) {
-  long long j = j0;
-  for (; j + 4 <= j1; j += 4) {
-    float v[4][8];
-#pragma unroll
-    for (int u = 0; u < 4; ++u) load8(DY, dy_dt, perm[j + u] * C + c8 * 8, v[u]);
-#pragma unroll
-    for (int u = 0; u < 4; ++u)
-#pragma unroll
-      for (int e = 0; e < 8; ++e) acc[e] += v[u][e];
-  }
-  for (; j < j1; ++j) {
-    float v[8];
-    load8(DY, dy_dt, perm[j] * C + c8 * 8, v);
-#pragma unroll
-    for (int e = 0; e < 8; ++e) acc[e] += v[e];
-  }
-}
-
-__global__ void __launch_bounds__(kEmbWarps * 32)
-embedding_bwd_kernel(const long long* __restrict__ sorted, const long long* __restrict__ perm,
-                     const void* __restrict__ DY, int dy_dt, float* __restrict__ GW, long long n,
-                     int C, long long V) {
-  extern __shared__ __align__(16) float emb_part[];          // [kEmbWarps][C]
-  __shared__ long long run_lo[kEmbWarps], run_hi[kEmbWarps];
-  const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int C8 = C / 8;
-  // Every block walks whole groups of kEmbWarps rows so that its barriers stay uniform.
-  for (long long base = (long long)blockIdx.x * kEmbWarps; base < V;
-       base += (long long)gridDim.x * kEmbWarps) {
-    const long long v = base + w;
-    long long s = 0, e = 0;
-    if (v < V) {
-      s = warp_lower_bound(sorted, n, v, lane);
-      e = warp_lower_bound(sorted, n, v + 1, lane);
-    }
-    if (lane == 0) { run_lo[w] = s; run_hi[w] = e; }
-    if (v < V && e - s <= kEmbLongRun) {
-      for (int c8 = lane; c8 < C8; c8 += 32) {
-        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        emb_sum_run(DY, dy_dt, perm, s, e, C, c8, acc);
-        store8(GW, DT_F32, v * C + c8 * 8, acc);
-      }
-    }
-    __syncthreads();
-    for (int ww = 0; ww < kEmbWarps; ++ww) {
-      const long long ls = run_lo[ww], le = run_hi[ww];
-      if (le - ls <= kEmbLongRun) continue;                  // same decision in every thread
-      const long long seg = (le - ls + kEmbWarps - 1) / kEmbWarps;
-      long long j0 = ls + (long long)w * seg, j1 = j0 + seg;
-      if (j0 > le) j0 = le;
-      if (j1 > le) j1 = le;
-      for (int c8 = lane; c8 < C8; c8 += 32) {
-        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        emb_sum_run(DY, dy_dt, perm, j0, j1, C, c8, acc);
-#pragma unroll
-        for (int q = 0; q < 8; ++q) emb_part[(size_t)w * C + c8 * 8 + q] = acc[q];
-      }
-      __syncthreads();
-      for (int c = threadIdx.x; c < C; c += kEmbWarps * 32) {
-        float t = 0.f;
-#pragma unroll
-        for (int q = 0; q < kEmbWarps; ++q) t += emb_part[(size_t)q * C + c];
-        GW[(base + ww) * C + c] = t;
-      }
-      __syncthreads();
-    }
-    __syncthreads();                                          // run_lo / run_hi are rewritten next
-  }
-}
-
-// ---------------------------------------------------------------------------------------------
 // ReLU^2
 // ---------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256)
@@ -594,27 +485,6 @@ DION_EXPORT int dion_rope_qknorm_bwd(const void* Q, const void* K, long long in_
   DION_ROPE_DISPATCH(D, (rope_qknorm_bwd_kernel<DD><<<grid, 256, 0, S(stream)>>>(
                             (CP)Q, (CP)K, in_row_stride, (CP)COS, (CP)SIN, (CP)DQO, (CP)DKO, rstd,
                             (P)DQ, (P)DK, out_row_stride, (CP)DVI, (P)DVO, n_vec, T, H)))
-  return rc();
-}
-
-// GW (fp32 [V, C]) needs no initialisation: every row is written.  Limit: 8*C*4 bytes of shared
-// memory (C <= 7168).
-DION_EXPORT int dion_embedding_bwd(const void* sorted, const void* perm, const void* DY, int dy_dt,
-                                   float* GW, long long n, int C, long long V, void* stream) {
-  if (V <= 0) return 0;
-  if (C % 8 || n < 0) return -2;
-  const size_t smem = (size_t)kEmbWarps * C * sizeof(float);
-  if (smem > 224 * 1024) return -2;
-  if (smem > 48 * 1024 &&
-      cudaFuncSetAttribute(embedding_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                           (int)smem) != cudaSuccess)
-    return -3;
-  const long long groups = (V + kEmbWarps - 1) / kEmbWarps;
-  const long long cap = 148LL * 8;
-  embedding_bwd_kernel<<<(unsigned)(groups < cap ? groups : cap), kEmbWarps * 32, smem,
-                         S(stream)>>>(
-      static_cast<const long long*>(sorted), static_cast<const long long*>(perm), DY, dy_dt, GW,
-      n, C, V);
   return rc();
 }
 

@@ -77,6 +77,10 @@ struct Gemm2Args {
   long long remote_c[8];
   int rows_per_dst;
   int remote_slot;
+  // cols_per_dst > 0: split by columns instead: element (r, c) of matrix b goes to
+  // remote_c[c / cols_per_dst] + ((remote_slot + b) * M + r) * cols_per_dst + c % cols_per_dst
+  // (a multiple of 8 columns, so a 16-byte piece has one destination).
+  int cols_per_dst;
 };
 
 __device__ __forceinline__ int ld_acquire_sys2(const int* p) {
@@ -583,10 +587,19 @@ ns_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
               if (grow < p.M) {
                 const uint8_t* src = dc + (uint32_t)(rr >> 6) * 8192u + (uint32_t)(rr & 63) * 128u +
                                      (((uint32_t)chunk ^ (uint32_t)(rr & 7)) << 4);
-                const int dst = grow / p.rows_per_dst;
-                __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.remote_c[dst]) +
-                    ((long long)(p.remote_slot + b) * p.rows_per_dst +
-                     (grow - dst * p.rows_per_dst)) * p.ldc + c0 + chunk * 8;
+                __nv_bfloat16* out;
+                if (p.cols_per_dst > 0) {
+                  const int col = c0 + chunk * 8;
+                  const int dst = col / p.cols_per_dst;
+                  out = reinterpret_cast<__nv_bfloat16*>(p.remote_c[dst]) +
+                        ((long long)(p.remote_slot + b) * p.M + grow) * p.cols_per_dst +
+                        (col - dst * p.cols_per_dst);
+                } else {
+                  const int dst = grow / p.rows_per_dst;
+                  out = reinterpret_cast<__nv_bfloat16*>(p.remote_c[dst]) +
+                        ((long long)(p.remote_slot + b) * p.rows_per_dst +
+                         (grow - dst * p.rows_per_dst)) * p.ldc + c0 + chunk * 8;
+                }
                 *reinterpret_cast<uint4*>(out) = *reinterpret_cast<const uint4*>(src);
               }
             }
@@ -735,6 +748,7 @@ struct DionGemm2Extra {
   float scale_mult, scale_eps;
   long long remote_c[8];
   int rows_per_dst, remote_slot;
+  int cols_per_dst;
 };
 
 // Same contract as dion_ns_gemm_ex (ns_gemm_sm100.cu) for the features it has: bf16 output,
@@ -792,7 +806,7 @@ DION_EXPORT int dion_ns_gemm2_ex(const void* A, long long lda, long long strideA
   a.wait_a = a.wait_b = a.wait_k = 0;
   a.scale_partials = nullptr; a.scale_mult = 1.f; a.scale_eps = 0.f;
   for (int i = 0; i < 8; ++i) a.remote_c[i] = 0;
-  a.rows_per_dst = 1; a.remote_slot = 0;
+  a.rows_per_dst = 1; a.remote_slot = 0; a.cols_per_dst = 0;
   if (ex != nullptr) {
     if (ex->n_src > 8 || ex->n_src < 0) return -14;
     if ((ex->wait_flags != nullptr || ex->scale_partials != nullptr) &&
@@ -806,6 +820,8 @@ DION_EXPORT int dion_ns_gemm2_ex(const void* A, long long lda, long long strideA
     for (int i = 0; i < 8; ++i) a.remote_c[i] = ex->remote_c[i];
     a.rows_per_dst = ex->rows_per_dst > 0 ? ex->rows_per_dst : 1;
     a.remote_slot = ex->remote_slot;
+    if (ex->cols_per_dst < 0 || (ex->cols_per_dst & 7)) return -16;
+    a.cols_per_dst = ex->remote_c[0] != 0 ? ex->cols_per_dst : 0;
   }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   a.epi = epi;

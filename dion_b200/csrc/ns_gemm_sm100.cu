@@ -60,6 +60,10 @@ struct GemmArgs {
   long long remote_c[8];
   int rows_per_dst;
   int remote_slot;
+  // cols_per_dst > 0: the output is split by columns instead: element (r, c) of matrix b goes to
+  // remote_c[c / cols_per_dst] + ((remote_slot + b) * M + r) * cols_per_dst + c % cols_per_dst
+  // (cols_per_dst a multiple of 32, so a 32-column chunk has one destination).
+  int cols_per_dst;
 };
 
 __device__ __forceinline__ int ld_acquire_sys(const int* p) {
@@ -313,7 +317,7 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       const __nv_bfloat16* Drow =
           p.D ? p.D + (long long)b * p.strideD + (long long)r * p.ldd : nullptr;
       __nv_bfloat16* Crow = p.C ? p.C + (long long)b * p.strideC + (long long)r * p.ldc : nullptr;
-      if (p.remote_c[0] != 0 && row_ok) {
+      if (p.remote_c[0] != 0 && row_ok && p.cols_per_dst == 0) {
         const int dst = r / p.rows_per_dst;
         Crow = reinterpret_cast<__nv_bfloat16*>(p.remote_c[dst]) +
                ((long long)(p.remote_slot + b) * p.rows_per_dst + (r - dst * p.rows_per_dst)) *
@@ -343,6 +347,13 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                       v);
         tmem_ld_wait();
         if (!row_ok) continue;
+        if (p.cols_per_dst > 0) {
+          // Column split: this chunk's destination; biased so that Crow[c] is element (r, c).
+          const int dst = c0 / p.cols_per_dst;
+          Crow = reinterpret_cast<__nv_bfloat16*>(p.remote_c[dst]) +
+                 ((long long)(p.remote_slot + b) * p.M + r) * p.cols_per_dst -
+                 (long long)dst * p.cols_per_dst;
+        }
 
         // acc*alpha + beta*D
         if (p.D) {
@@ -510,6 +521,7 @@ struct DionGemmExtra {
   float scale_mult, scale_eps;
   long long remote_c[8];
   int rows_per_dst, remote_slot;
+  int cols_per_dst;
 };
 
 DION_EXPORT int dion_ns_gemm_ex(const void* A, long long lda, long long strideA, int a_mn,
@@ -554,7 +566,7 @@ DION_EXPORT int dion_ns_gemm_ex(const void* A, long long lda, long long strideA,
   a.wait_a = a.wait_b = a.wait_k = 0;
   a.scale_partials = nullptr; a.scale_mult = 1.f; a.scale_eps = 0.f;
   for (int i = 0; i < 8; ++i) a.remote_c[i] = 0;
-  a.rows_per_dst = 1; a.remote_slot = 0;
+  a.rows_per_dst = 1; a.remote_slot = 0; a.cols_per_dst = 0;
   if (ex != nullptr) {
     if (ex->n_src > 8 || ex->n_src < 0) return -14;
     if (ex->remote_c[0] != 0 && (sym || CT != nullptr || Cf != nullptr)) return -15;
@@ -569,6 +581,8 @@ DION_EXPORT int dion_ns_gemm_ex(const void* A, long long lda, long long strideA,
     for (int i = 0; i < 8; ++i) a.remote_c[i] = ex->remote_c[i];
     a.rows_per_dst = ex->rows_per_dst > 0 ? ex->rows_per_dst : 1;
     a.remote_slot = ex->remote_slot;
+    if (ex->cols_per_dst < 0 || (ex->cols_per_dst & 31)) return -16;
+    a.cols_per_dst = ex->remote_c[0] != 0 ? ex->cols_per_dst : 0;
   }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int mode = (a_mn ? 2 : 0) | (b_mn ? 1 : 0);

@@ -311,10 +311,27 @@ def qkv_rope(h: Tensor, wq: Tensor, wk: Tensor, wv: Tensor, cos: Tensor, sin: Te
 # ------------------------------------------------------------------------------------------------
 # Embedding and linear layers with mixed-precision-aware backward passes
 # ------------------------------------------------------------------------------------------------
+_sort_bytes: dict = {}
+
+
+def _embedding_sort_bytes(n: int, V: int) -> int:
+    key = (n, V)
+    b = _sort_bytes.get(key)
+    if b is None:
+        fn = _backend.lib("embedding_ops")._dll.dion_embedding_sort_bytes
+        fn.restype = ctypes.c_longlong
+        b = int(fn(ctypes.c_longlong(n), ctypes.c_longlong(V)))
+        if b < 0:
+            raise RuntimeError("dion_embedding_sort_bytes failed")
+        _sort_bytes[key] = b
+    return b
+
+
 class _Embedding(torch.autograd.Function):
-    """``weight[idx]`` whose backward sorts the token ids once and writes every row of the weight
-    gradient exactly once in a single kernel - the sum of the id's rows, or zeros (deterministic;
-    replaces the zero fill and the several passes of the stock dense backward)."""
+    """``weight[idx]`` whose backward sorts (id, position) pairs over the bits an id needs and
+    writes every row of the weight gradient exactly once - the sum of the id's rows in position
+    order, or zeros (deterministic; replaces the zero fill, the 64-bit sort and the atomics of the
+    stock dense backward)."""
 
     @staticmethod
     def forward(ctx, idx: Tensor, weight: Tensor):
@@ -328,14 +345,22 @@ class _Embedding(torch.autograd.Function):
         (idx,) = ctx.saved_tensors
         V, C = ctx.wshape
         flat = idx.reshape(-1)
-        sorted_idx, perm = torch.sort(flat, stable=True)
+        if not flat.is_contiguous():
+            flat = flat.contiguous()
+        n = flat.numel()
         dy2 = dy.reshape(-1, C)
         if not dy2.is_contiguous():
             dy2 = dy2.contiguous()
-        gw = torch.empty((V, C), dtype=torch.float32, device=dy.device)   # every row is written
-        _check(_lib().dion_embedding_bwd(_c(sorted_idx), _c(perm), _c(dy2), _DT[dy2.dtype], _c(gw),
-                                         ctypes.c_longlong(flat.numel()), C, ctypes.c_longlong(V),
-                                         _stream(dy.device)), "dion_embedding_bwd")
+        dev = dy.device
+        gw = torch.empty((V, C), dtype=torch.float32, device=dev)   # every row is written
+        scratch = torch.empty(4 * n + V + 1, dtype=torch.int32, device=dev)
+        nbytes = _embedding_sort_bytes(n, V)
+        temp = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=dev)
+        keys, vals, starts = scratch[:2 * n], scratch[2 * n:4 * n], scratch[4 * n:]
+        _check(_backend.lib("embedding_ops").dion_embedding_bwd(
+            _c(flat), _c(dy2), _DT[dy2.dtype], _c(gw), ctypes.c_longlong(n), C,
+            ctypes.c_longlong(V), _c(keys), _c(vals), _c(starts), _c(temp),
+            ctypes.c_longlong(nbytes), _stream(dev)), "dion_embedding_bwd")
         return None, gw
 
 

@@ -38,6 +38,7 @@ SOURCES = {
     "foreach_ops": "libdion_foreach.so",
     "select_ops": "libdion_select.so",
     "model_ops": "libdion_model.so",
+    "embedding_ops": "libdion_embedding.so",
     "comm_ops": "libdion_comm.so",
     "lowrank_ops": "libdion_lowrank.so",
     "lowrank_gemm_sm100": "libdion_lowrank_gemm.so",
@@ -107,6 +108,7 @@ def build(force: bool = False, verbose: bool = False) -> List[str]:
 
 # Kernels launched per exported entry point (default 1); used for the launch counter.
 _KERNELS_PER_CALL = {"dion_adamw": 2, "dion_dion2_post_masked": 2,
+                     "dion_embedding_bwd": 3, "dion_embedding_sort_bytes": 0,  # own kernels only
                      "dion_ns_iterate2": 0}  # the last one counts itself
 _launches = 0
 

@@ -14,7 +14,7 @@ The math follows the reference's compiled helpers: Muon pre/post-orthogonalize
 from __future__ import annotations
 
 import ctypes
-from typing import List, Optional, Sequence, Union
+from typing import List, Optional, Sequence, Tuple, Union
 
 import torch
 from torch import Tensor
@@ -88,13 +88,17 @@ def muon_pre(
     sumsq: Optional[Tensor] = None,
     add_only: bool = False,
     sumsq_targets: Optional[List[int]] = None,
+    out_block: Optional[Tuple[int, int]] = None,
 ) -> List[Tensor]:
     """``M = mu*M + G`` (or ``M += G`` with ``add_only``); returns the bf16 orthogonalization
     input ``U`` (``mu*M + G`` with Nesterov, else ``M``), written into ``out`` when given.
     ``out=False`` skips the bf16 output altogether.
     ``sumsq[i]`` (optional, fp32, pre-zeroed) receives ``sum(U_i**2)``.  ``out`` entries may be
     :class:`RawPointer` addresses of peer-GPU memory; ``sumsq_targets[i]`` (raw addresses of fp32
-    accumulators, possibly on a peer) then receive the sums instead of ``sumsq``."""
+    accumulators, possibly on a peer) then receive the sums instead of ``sumsq``.
+    ``out_block=(cols, pitch)``: every ``M`` is a ``[rows, cols]`` matrix and its ``out`` entry
+    points at a column block of a wider row-major matrix with row pitch ``pitch`` elements
+    (kernel path with raw pointers only)."""
     if not G:
         return []
     if out is False:      # momentum update only: no bf16 copy is wanted
@@ -113,9 +117,13 @@ def muon_pre(
                 _DT[G[0].dtype], _DT[M[0].dtype], ctypes.c_float(float(mu)),
                 int(bool(nesterov)), int(bool(add_only)),
                 _c(sumsq.data_ptr() if sumsq is not None else 0),
-                int(sumsq_targets is not None), _stream(dev)),
+                int(sumsq_targets is not None),
+                ctypes.c_longlong(out_block[0] if out_block else 0),
+                ctypes.c_longlong(out_block[1] if out_block else 0), _stream(dev)),
             "dion_muon_pre")
         return out
+    if out_block is not None:
+        raise RuntimeError("muon_pre(out_block=...) needs the CUDA kernel path")
     # PyTorch path
     dtype = M[0].dtype
     Gc = [g.to(dtype) for g in G]

@@ -182,6 +182,7 @@ class GemmExtra(ctypes.Structure):
         ("scale_mult", ctypes.c_float), ("scale_eps", ctypes.c_float),
         ("remote_c", ctypes.c_longlong * 8),
         ("rows_per_dst", ctypes.c_int), ("remote_slot", ctypes.c_int),
+        ("cols_per_dst", ctypes.c_int),
     ]
 
 

@@ -166,21 +166,22 @@ def muon_update_megabatch_async(
     global_rows = global_comm_size(X[0], comm_dim)
     if fused_cache is not None and FX.eligible(Ml[0].shape, comm_dim, global_rows, world_size,
                                                process_group, newton_schulz_func, flatten,
-                                               split_sizes, allow_uneven=True):
-        # Row-sharded matrices: the exchange is carried by the kernels themselves.  Every
-        # rank's slice of an assembled matrix is `pl` rows high; a rank with fewer rows (or
-        # none) fills only what it has, the rest of its slice stays zero.
-        pl = (global_rows + world_size - 1) // world_size
+                                               split_sizes, allow_uneven=True,
+                                               allow_columns=True):
+        # The exchange is carried by the kernels themselves.  Row shards: every rank's slice of
+        # an assembled matrix is `pl` rows high; a rank with fewer rows (or none) fills only what
+        # it has, the rest of its slice stays zero.  Column shards are even by eligibility.
+        by_cols = comm_dim == -1
         rows, cols = Ml[0].shape
-        key = (id(X[0]), len(X), pl, cols)
-        fx = fused_cache.get(key)
-        if fx is None:
-            fx = fused_cache[key] = FX.FusedRowExchange(process_group, len(X), pl, cols,
-                                                        Ml[0].device)
+        pl = rows if by_cols else (global_rows + world_size - 1) // world_size
+        key = (id(X[0]), len(X), pl, cols, by_cols)
+        fx = FX.get_exchange(fused_cache, key, process_group, len(X), pl, cols, Ml[0].device,
+                             by_columns=by_cols)
         fx.begin()
         if rows > 0:
             outs, sums = fx.push_targets()
-            F.muon_pre(Gl, Ml, float(momentum), nesterov, out=outs, sumsq_targets=sums)
+            F.muon_pre(Gl, Ml, float(momentum), nesterov, out=outs, sumsq_targets=sums,
+                       out_block=fx.push_block())
         fx.publish()
         NS.iterate_with_exchange(fx.input_matrix(), newton_schulz_func, epsilon, fx)
         fx.finish()

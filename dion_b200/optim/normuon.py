@@ -145,7 +145,8 @@ def normuon_update_megabatch_async(
     if fused_cache is not None and FX.eligible(Ml[0].shape, comm_dim, global_rows, world_size,
                                                process_group, newton_schulz_func, flatten,
                                                split_sizes):
-        # Row shards travel through peer-mapped memory inside the kernels (see fused_exchange).
+        # Row shards travel through peer-mapped memory inside the kernels (see fused_exchange;
+        # shards along the last dimension are refused at construction, as in the reference).
         fx = FX.get_exchange(fused_cache, (id(X[0]), len(X), tuple(Ml[0].shape)), process_group,
                              len(X), Ml[0].shape[0], Ml[0].shape[1], Ml[0].device)
         fx.begin()

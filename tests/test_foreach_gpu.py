@@ -40,6 +40,29 @@ def test_muon_pre(m_dtype, nesterov):
     assert torch.allclose(ss.cpu(), ref, rtol=1e-3)
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_muon_pre_stores_into_a_column_block(dtype):
+    """``out_block``: the bf16 output of each ``[rows, cols]`` tensor lands in columns
+    ``[off, off + cols)`` of a wider matrix, the rest of which stays untouched; the dense output
+    of a second call gives the expected values."""
+    from dion_b200.ops.tables import RawPointer
+    torch.manual_seed(4)
+    rows, cols, pitch, off = 40, 64, 256, 128
+    G = [torch.randn(rows, cols, device="cuda").to(dtype) for _ in range(3)]
+    M1 = [torch.randn(rows, cols, device="cuda").to(dtype) for _ in range(3)]
+    M2 = [m.clone() for m in M1]
+    wide = torch.full((3, rows, pitch), 7.0, device="cuda", dtype=torch.bfloat16)
+    outs = [RawPointer(wide[i].data_ptr() + off * 2) for i in range(3)]
+    F.muon_pre(G, M1, 0.9, True, out=outs, out_block=(cols, pitch))
+    dense = F.muon_pre(G, M2, 0.9, True)
+    torch.cuda.synchronize()
+    for i in range(3):
+        assert torch.equal(wide[i, :, off:off + cols], dense[i])
+        assert torch.equal(M1[i], M2[i])
+    rest = torch.cat([wide[:, :, :off], wide[:, :, off + cols:]], dim=2)
+    assert (rest == 7.0).all().item()
+
+
 @pytest.mark.parametrize("x_dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("cautious", [False, True])
 def test_muon_post(x_dtype, cautious):

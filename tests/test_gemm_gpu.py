@@ -256,3 +256,59 @@ def test_exchange_coupling_on_one_gpu(pair, tall):
     assert (got.float() - want).abs().max().item() < 2e-2 * want.abs().max().item()
     for b_ in bufs:
         assert float(b_[0].abs().max()) == 0 and float(b_[4].abs().max()) == 0
+
+
+@pytest.mark.parametrize("pair", [False, True])
+@pytest.mark.parametrize("tall", [False, True])
+def test_exchange_coupling_by_columns_on_one_gpu(pair, tall):
+    """Column-split form of the coupling: with the sharded dimension being the columns, the first
+    Gram gates on K-slabs where the row form gates on tile rows (and the other way round), and the
+    update GEMM sends each 16-byte piece of an output row to the owner of its columns, who holds
+    ``[slots, m, n / W]``."""
+    from dion_b200.ops import gemm
+    torch.manual_seed(1)
+    dev = torch.device("cuda")
+    W, batch = 4, 3
+    m, n = (1024, 512) if tall else (512, 1024)
+    pc = n // W
+    X = torch.randn(batch, m, n, device=dev).bfloat16()
+    flags = torch.full((W,), 3, dtype=torch.int32, device=dev)
+    seq = torch.full((), 3, dtype=torch.int32, device=dev)
+    parts = X.float().reshape(batch, m, W, pc).square().sum(dim=(1, 3)).contiguous()
+    g = n if tall else m
+    ex = gemm.GemmExtra()
+    ex.wait_flags, ex.seq_ptr = flags.data_ptr(), seq.data_ptr()
+    ex.n_src, ex.rows_per_src = W, pc
+    contracted = not tall          # wide: X X^T contracts over the (sharded) columns
+    ex.wait_a = ex.wait_b = 0 if contracted else 1
+    ex.wait_k = 1 if contracted else 0
+    ex.scale_partials = parts.data_ptr()
+    ex.scale_mult, ex.scale_eps = 1.0, 1e-7
+    A = torch.empty(batch, g, g, device=dev, dtype=torch.bfloat16)
+    gemm.ns_gemm(X, X, out=A, sym=True, a_is_km=tall, b_is_kn=tall, alpha_pow=2, extra=ex,
+                 pair=pair)
+    scale = 1.0 / (X.float().flatten(1).norm(dim=1) + 1e-7)
+    Xs = X.float() * scale.view(-1, 1, 1)
+    ref = (Xs.mT @ Xs) if tall else (Xs @ Xs.mT)
+    torch.cuda.synchronize()
+    gemm.check_status()
+    assert (A.float() - ref).abs().max().item() < 2e-2 * ref.abs().max().item()
+    Bm = torch.randn(batch, g, g, device=dev).bfloat16()
+    slots = 5
+    bufs = [torch.zeros(slots, m, pc, device=dev, dtype=torch.bfloat16) for _ in range(W)]
+    ex2 = gemm.GemmExtra()
+    for d in range(W):
+        ex2.remote_c[d] = bufs[d].data_ptr()
+    ex2.rows_per_dst, ex2.cols_per_dst, ex2.remote_slot = m, pc, 1
+    if tall:
+        gemm.ns_gemm(X, Bm, out=None, D=X, alpha=1.0, beta=0.5, extra=ex2, pair=pair)
+        want = 0.5 * X.float() + X.float() @ Bm.float().mT
+    else:
+        gemm.ns_gemm(Bm, X, out=None, b_is_kn=True, D=X, alpha=1.0, beta=0.5, extra=ex2, pair=pair)
+        want = 0.5 * X.float() + Bm.float() @ X.float()
+    torch.cuda.synchronize()
+    gemm.check_status()
+    got = torch.cat([b_[1:1 + batch] for b_ in bufs], dim=2)        # [batch, m, n]
+    assert (got.float() - want).abs().max().item() < 2e-2 * want.abs().max().item()
+    for b_ in bufs:
+        assert float(b_[0].abs().max()) == 0 and float(b_[4].abs().max()) == 0

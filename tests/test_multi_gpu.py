@@ -36,17 +36,18 @@ def _single_gpu(name, kw, steps):
     return [p.detach().cpu() for p in ps]
 
 
-def _sharded(rank, world, name, kw, steps, fused):
+def _sharded(rank, world, name, kw, steps, fused, shard=0):
     from torch.distributed.device_mesh import init_device_mesh
     from torch.distributed.tensor import Shard, distribute_tensor
     from dion_b200.ops.gemm import check_status
     os.environ["DION_B200_FUSED_EXCHANGE"] = "1" if fused else "0"
     mesh = init_device_mesh("cuda", (world,))
-    ps = [torch.nn.Parameter(distribute_tensor(w.cuda(), mesh, [Shard(0)])) for w in _weights(SHAPES)]
+    ps = [torch.nn.Parameter(distribute_tensor(w.cuda(), mesh, [Shard(shard)]))
+          for w in _weights(SHAPES)]
     opt = getattr(dion_b200, name)([dict(params=ps)], distributed_mesh=mesh, lr=0.05, **kw)
     for s in range(steps):
         for p, g in zip(ps, _weights(SHAPES, 100 + s)):
-            p.grad = distribute_tensor(g.cuda(), mesh, [Shard(0)])
+            p.grad = distribute_tensor(g.cuda(), mesh, [Shard(shard)])
         opt.step()
     torch.cuda.synchronize()
     check_status()
@@ -78,6 +79,24 @@ def test_muon_fused_exchange_matches_collective_and_single(tmp_path, world):
     assert used0 == 0 and used1 > 0  # the fused path really ran
     for r, c, f in zip(ref, coll, fused):
         assert (r - c).abs().max().item() < 2e-3
+        assert (r - f).abs().max().item() < 2e-3
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_fused_exchange_of_column_shards_matches_collective_and_single(tmp_path, world):
+    """``Shard(1)`` parameters: the momentum kernel's strided store into the owner's matrix, the
+    Gram GEMM gated by K-slabs (wide) or tile rows (tall), the update GEMM's column-split remote
+    store - against the collective path and an unsharded run."""
+    _need(world)
+    name, kw = "Muon", dict(nesterov=True, use_polar_express=False)
+    ref = _single_gpu(name, kw, 3)
+    (tmp_path / "a").mkdir()
+    (tmp_path / "b").mkdir()
+    coll, used0 = run_ranks(_sharded, world, "nccl", (name, kw, 3, False, 1), str(tmp_path / "a"))[0]
+    fused, used1 = run_ranks(_sharded, world, "nccl", (name, kw, 3, True, 1), str(tmp_path / "b"))[0]
+    assert used0 == 0 and used1 > 0
+    for r, c, f in zip(ref, coll, fused):
+        assert (c - f).abs().max().item() < 2e-3
         assert (r - f).abs().max().item() < 2e-3
 
 
