@@ -815,6 +815,61 @@ __global__ void finalize_scale_kernel(const float* sumsq, float* scale, int n, f
   if (i < n) scale[i] = 1.f / (sqrtf(sumsq[i]) * mult + eps);
 }
 
+// ---------------------------------------------------------------------------------------------
+// AOL rescaling of a Newton-Schulz input (reference: dion/newton_schulz_triton.py:601-612, seven
+// element-wise library passes there): s_i = rsqrt(max(sum_j |A_ij|, eps)) from the Gram matrix
+// A = X X^T, then X <- diag(s) X and A <- diag(s) A diag(s).  Two launches: one warp per row of A
+// for the scales, one warp per row of X or A for the in-place rescale (16-byte accesses; m and n
+// multiples of 8).
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+aol_rowscale_kernel(const __nv_bfloat16* __restrict__ A, int m, long long rows, float eps,
+                    float* __restrict__ s) {
+  const long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int lane = threadIdx.x & 31;
+  const uint4* p = reinterpret_cast<const uint4*>(A + row * m);
+  float acc = 0.f;
+  for (int c = lane; c < m / 8; c += 32) {
+    const uint4 q = __ldg(p + c);
+    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 f = unpack_bf16x2(w[e]);
+      acc += fabsf(f.x) + fabsf(f.y);
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if (lane == 0) s[row] = rsqrtf(fmaxf(acc, eps));
+}
+
+__global__ void __launch_bounds__(256)
+aol_apply_kernel(__nv_bfloat16* X, int n, __nv_bfloat16* A, int m, long long rows,
+                 const float* __restrict__ s) {
+  long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (row >= 2 * rows) return;
+  const int lane = threadIdx.x & 31;
+  const bool gram = row >= rows;          // second half of the grid: rows of A
+  if (gram) row -= rows;
+  const float si = s[row];
+  const float* sj = s + (row / m) * m;    // scales of this matrix's columns
+  uint4* p = reinterpret_cast<uint4*>(gram ? A + row * m : X + row * n);
+  const int vecs = (gram ? m : n) / 8;
+  for (int c = lane; c < vecs; c += 32) {
+    uint4 q = p[c];
+    uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      float2 f = unpack_bf16x2(w[e]);
+      const float c0 = gram ? si * sj[c * 8 + e * 2] : si;
+      const float c1 = gram ? si * sj[c * 8 + e * 2 + 1] : si;
+      w[e] = pack_bf16x2(f.x * c0, f.y * c1);
+    }
+    p[c] = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+}
+
 }  // namespace dion
 
 using namespace dion;
@@ -926,5 +981,18 @@ DION_EXPORT int dion_finalize_scale(const float* sumsq, float* scale, int n, flo
                                     void* stream) {
   if (n <= 0) return 0;
   finalize_scale_kernel<<<(n + 127) / 128, 128, 0, S(stream)>>>(sumsq, scale, n, mult, eps);
+  return rc();
+}
+
+// X: bf16 [B, m, n], A: bf16 [B, m, m] (the Gram matrix of X), s: fp32 scratch [B*m].  In place.
+DION_EXPORT int dion_aol_rescale(void* X, void* A, float* s, long long batch, int m, int n,
+                                 float eps, void* stream) {
+  if (batch <= 0 || m <= 0) return 0;
+  if ((m & 7) || (n & 7)) return -2;
+  const long long rows = batch * m;
+  aol_rowscale_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, S(stream)>>>(
+      static_cast<const __nv_bfloat16*>(A), m, rows, eps, s);
+  aol_apply_kernel<<<(unsigned)((2 * rows + 7) / 8), 256, 0, S(stream)>>>(
+      static_cast<__nv_bfloat16*>(X), n, static_cast<__nv_bfloat16*>(A), m, rows, s);
   return rc();
 }

@@ -236,15 +236,38 @@ topk_select_kernel(const float* norms, int num, int k, long long* idx_out, int* 
       if ((key & hi_mask) == prefix) atomicAdd(&hist[(key >> shift) & 255], 1);
     }
     __syncthreads();
-    if (threadIdx.x == 0) {
-      int rem = s_remaining;
-      int b = 255;
-      for (; b > 0; --b) {
-        if (hist[b] >= rem) break;
-        rem -= hist[b];
+    if (threadIdx.x < 32) {
+      // Find the bin that holds the rem-th largest key, walking from bin 255 down: every lane
+      // owns eight bins, a suffix sum over the lanes tells each how many keys lie in the bins
+      // above its own, and the one lane whose bins contain the target finishes the walk.
+      const int lane = threadIdx.x;
+      int h[8], mine = 0;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { h[j] = hist[lane * 8 + j]; mine += h[j]; }
+      int incl = mine;                       // sum over lanes >= this one
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int y = __shfl_down_sync(0xffffffffu, incl, o);
+        if (lane + o < 32) incl += y;
       }
-      s_prefix = prefix | ((uint32_t)b << shift);
-      s_remaining = rem;
+      const int above = incl - mine;
+      const int rem0 = s_remaining;
+      const bool here = above < rem0 && rem0 <= incl;
+      // No lane qualifies only if fewer than rem keys match the prefix, which the counts of the
+      // previous digit exclude; lane 0 then settles on bin 0 as a serial walk would.
+      const unsigned who = __ballot_sync(0xffffffffu, here);
+      if (here || (who == 0u && lane == 0)) {
+        int rem = rem0 - above, b = lane * 8;
+        if (here) {
+#pragma unroll
+          for (int j = 7; j >= 0; --j) {
+            if (h[j] >= rem) { b = lane * 8 + j; break; }
+            rem -= h[j];
+          }
+        }
+        s_prefix = prefix | ((uint32_t)b << shift);
+        s_remaining = rem;
+      }
     }
     __syncthreads();
   }

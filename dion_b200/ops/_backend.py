@@ -107,7 +107,7 @@ def build(force: bool = False, verbose: bool = False) -> List[str]:
 
 
 # Kernels launched per exported entry point (default 1); used for the launch counter.
-_KERNELS_PER_CALL = {"dion_adamw": 2, "dion_dion2_post_masked": 2,
+_KERNELS_PER_CALL = {"dion_adamw": 2, "dion_dion2_post_masked": 2, "dion_aol_rescale": 2,
                      "dion_embedding_bwd": 3, "dion_embedding_sort_bytes": 0,  # own kernels only
                      "dion_ns_iterate2": 0}  # the last one counts itself
 _launches = 0

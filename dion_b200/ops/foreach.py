@@ -512,6 +512,25 @@ def sumsq(X: Tensor, out: Optional[Tensor] = None) -> Tensor:
     return out
 
 
+def aol_rescale_(X: Tensor, A: Tensor, eps: float) -> None:
+    """AOL rescaling in place: with ``s_i = rsqrt(max(sum_j |A_ij|, eps))`` of the Gram matrix
+    ``A = X X^T`` (``[B, m, m]``), ``X <- diag(s) X`` and ``A <- diag(s) A diag(s)``
+    (reference: dion/newton_schulz_triton.py:601-612)."""
+    B, m, n = X.shape
+    if (X.is_cuda and X.dtype == A.dtype == torch.bfloat16 and X.is_contiguous()
+            and A.is_contiguous() and m % 8 == 0 and n % 8 == 0):
+        s = torch.empty(B * m, dtype=torch.float32, device=X.device)
+        _check(
+            _backend.lib("foreach_ops").dion_aol_rescale(
+                _c(X.data_ptr()), _c(A.data_ptr()), _c(s.data_ptr()), ctypes.c_longlong(B), m, n,
+                ctypes.c_float(float(eps)), _stream(X.device)),
+            "dion_aol_rescale")
+        return
+    s = torch.rsqrt(A.abs().sum(dim=-1, dtype=torch.float32).clamp_min(eps))
+    X.copy_((X * s.unsqueeze(-1)).to(X.dtype))
+    A.copy_((A * s.unsqueeze(-1) * s.unsqueeze(-2)).to(A.dtype))
+
+
 def finalize_scale(sumsq_t: Tensor, mult: float, eps: float, out: Optional[Tensor] = None) -> Tensor:
     """``1 / (sqrt(sumsq)*mult + eps)``: the Newton-Schulz input normalization factor."""
     if out is None:

@@ -232,9 +232,9 @@ def _aol_cuda(G: Tensor, epsilon: float) -> Tensor:
     B_, m, n = X.shape
     A = torch.empty((B_, m, m), dtype=torch.bfloat16, device=X.device)
     gemm.ns_gemm(X, X, out=A, sym=True)
-    s = torch.rsqrt(A.abs().sum(dim=-1, dtype=torch.float32).clamp_min(epsilon))
-    X = (X * s.unsqueeze(-1)).to(torch.bfloat16)
-    A = (A * s.unsqueeze(-1) * s.unsqueeze(-2)).to(torch.bfloat16)
+    # X is private to this call (see _prepare_cuda), so the rescale may work in place: two
+    # launches, the row scales and then X and A rescaled together.
+    F.aol_rescale_(X, A, epsilon)
     a, b, c = AOL_COEFFS[0]
     Bm = torch.empty_like(A)
     C = torch.empty_like(X)

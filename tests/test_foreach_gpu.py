@@ -215,3 +215,16 @@ def test_dion2_post_masked_matches_torch(select_dim, m_dtype):
             assert torch.equal(a[untouched], b[untouched])
         else:
             assert torch.equal(a[:, untouched], b[:, untouched])
+
+
+def test_aol_rescale_matches_torch():
+    torch.manual_seed(6)
+    X = torch.randn(3, 136, 264, device="cuda").bfloat16()
+    A = (X.float() @ X.float().mT).bfloat16()
+    s = torch.rsqrt(A.abs().sum(dim=-1, dtype=torch.float32).clamp_min(1e-7))
+    Xr = (X.float() * s.unsqueeze(-1)).bfloat16()
+    Ar = (A.float() * s.unsqueeze(-1) * s.unsqueeze(-2)).bfloat16()
+    F.aol_rescale_(X, A, 1e-7)
+    torch.cuda.synchronize()
+    assert (X.float() - Xr.float()).abs().max().item() <= 1e-2 * Xr.float().abs().max().item()
+    assert (A.float() - Ar.float()).abs().max().item() <= 1e-2 * Ar.float().abs().max().item()
