@@ -274,11 +274,6 @@ lr_gemm_kernel(const __grid_constant__ LrMaps maps, const LrGemmArgs p) {
       const int b = t / p.tiles_per_mat;
       const int rem = t - b * p.tiles_per_mat;
       const int tm = rem / p.tiles_n, tn = rem - tm * p.tiles_n;
-      if (!mbar_wait_bounded(&tfull_bar[aslot], aphase)) {
-        if (lane == 0) atomicExch(p.status, kStatusTimeoutTmemFull);
-        break;
-      }
-      tc_fence_after();
       const int r = tm * LBM + row_in_tile;
       const bool row_ok = r < p.M;
       char* Cb = p.c_table ? reinterpret_cast<char*>(p.c_table[b])
@@ -294,25 +289,57 @@ lr_gemm_kernel(const __grid_constant__ LrMaps maps, const LrGemmArgs p) {
       const bool d_vec = Db != nullptr && (p.ldd & 7) == 0 &&
                          (reinterpret_cast<uintptr_t>(Db) & 15) == 0 &&
                          (p.d_table != nullptr || (p.strideD & 7) == 0);
+      if (Db != nullptr && row_ok) {
+        // While the tensor cores still work on this tile, pull this thread's row of D towards
+        // L2: with K as short as a rank the epilogue is the longer half of a tile, and most of
+        // it used to be the DRAM latency of one D chunk after the other.
+        const int esz = p.d_dt ? 2 : 4;
+        const char* drow = Db + ((long long)r * p.ldd + (long long)tn * BN) * esz;
+        const int cols_here = (p.N - tn * BN) < BN ? (p.N - tn * BN) : BN;
+        for (int off = 0; off < cols_here * esz; off += 128)
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(drow + off));
+      }
+      if (!mbar_wait_bounded(&tfull_bar[aslot], aphase)) {
+        if (lane == 0) atomicExch(p.status, kStatusTimeoutTmemFull);
+        break;
+      }
+      tc_fence_after();
 #pragma unroll 1
       for (int ch = 0; ch < BN / 32; ++ch) {
         const int c0 = tn * BN + ch * 32;
         if (c0 >= p.N) continue;  // warp-uniform
+        const bool full = c0 + 32 <= p.N;
+        // The vector form of D is requested before the accumulator is read, so that both are
+        // in flight together (fp32: eight 16-byte pieces; bf16: four, carried as raw bits).
+        float4 dpre[8];
+        const bool pre = row_ok && d_vec && full;
+        if (pre) {
+          if (p.d_dt == 0) {
+            const float4* dp = reinterpret_cast<const float4*>(
+                reinterpret_cast<const float*>(Db) + (long long)r * p.ldd + c0);
+#pragma unroll
+            for (int q = 0; q < 8; ++q) dpre[q] = dp[q];
+          } else {
+            const float4* dp = reinterpret_cast<const float4*>(
+                reinterpret_cast<const __nv_bfloat16*>(Db) + (long long)r * p.ldd + c0);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) dpre[q] = dp[q];
+          }
+        }
         float v[32];
         tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(lane_grp * 32) << 16) + aslot * BN +
                           ch * 32,
                       v);
         tmem_ld_wait();
-        const bool full = c0 + 32 <= p.N;
         if (row_ok) {
           // ---- combine with D ----
           if (Db != nullptr) {
             if (p.d_dt == 0) {
               const float* drow = reinterpret_cast<const float*>(Db) + (long long)r * p.ldd + c0;
-              if (d_vec && full) {
+              if (pre) {
 #pragma unroll
                 for (int q = 0; q < 8; ++q) {
-                  const float4 d = *reinterpret_cast<const float4*>(drow + q * 4);
+                  const float4 d = dpre[q];
                   v[q * 4] = p.alpha * v[q * 4] + p.beta * d.x;
                   v[q * 4 + 1] = p.alpha * v[q * 4 + 1] + p.beta * d.y;
                   v[q * 4 + 2] = p.alpha * v[q * 4 + 2] + p.beta * d.z;
@@ -326,10 +353,11 @@ lr_gemm_kernel(const __grid_constant__ LrMaps maps, const LrGemmArgs p) {
             } else {
               const __nv_bfloat16* drow =
                   reinterpret_cast<const __nv_bfloat16*>(Db) + (long long)r * p.ldd + c0;
-              if (d_vec && full) {
+              if (pre) {
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
-                  const uint4 u = *reinterpret_cast<const uint4*>(drow + q * 8);
+                  const uint4 u = make_uint4(__float_as_uint(dpre[q].x), __float_as_uint(dpre[q].y),
+                                             __float_as_uint(dpre[q].z), __float_as_uint(dpre[q].w));
                   const uint32_t w[4] = {u.x, u.y, u.z, u.w};
 #pragma unroll
                   for (int e = 0; e < 4; ++e) {
@@ -455,6 +483,26 @@ __global__ void split_lo_kernel(const float* __restrict__ x, float* __restrict__
     for (long long k = i; k < n && k < i + 4; ++k)
       lo[k] = x[k] - __uint_as_float(__float_as_uint(x[k]) & 0xFFFFE000u);
   }
+}
+
+// The same for a batch of `rows` x `cols` matrices read through a strided view (row pitch ld_x,
+// batch pitch bs_x; cols, pitches and bases multiples of 4 elements / 16 bytes); lo is dense.
+__global__ void split_lo_view_kernel(const float* __restrict__ x, long long ld_x, long long bs_x,
+                                     float* __restrict__ lo, long long total4, int rows,
+                                     int cols4) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total4) return;
+  const long long row_all = i / cols4;
+  const int c = static_cast<int>(i - row_all * cols4) * 4;
+  const long long b = row_all / rows;
+  const long long row = row_all - b * rows;
+  const float4 a = *reinterpret_cast<const float4*>(x + b * bs_x + row * ld_x + c);
+  float4 o;
+  o.x = a.x - __uint_as_float(__float_as_uint(a.x) & 0xFFFFE000u);
+  o.y = a.y - __uint_as_float(__float_as_uint(a.y) & 0xFFFFE000u);
+  o.z = a.z - __uint_as_float(__float_as_uint(a.z) & 0xFFFFE000u);
+  o.w = a.w - __uint_as_float(__float_as_uint(a.w) & 0xFFFFE000u);
+  *reinterpret_cast<float4*>(lo + i * 4) = o;
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -621,5 +669,18 @@ DION_EXPORT int dion_split_lo(const float* x, float* lo, long long n, void* stre
   const long long threads = (n + 3) / 4;
   dion::split_lo_kernel<<<(unsigned)((threads + 255) / 256), 256, 0,
                           static_cast<cudaStream_t>(stream)>>>(x, lo, n);
+  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+DION_EXPORT int dion_split_lo_view(const float* x, long long ld_x, long long bs_x, float* lo,
+                                   long long batch, int rows, int cols, void* stream) {
+  if (batch <= 0 || rows <= 0 || cols <= 0) return 0;
+  if ((cols & 3) || (ld_x & 3) || (bs_x & 3) || (reinterpret_cast<uintptr_t>(x) & 15) ||
+      (reinterpret_cast<uintptr_t>(lo) & 15))
+    return -2;
+  const long long total4 = batch * rows * (cols / 4);
+  dion::split_lo_view_kernel<<<(unsigned)((total4 + 255) / 256), 256, 0,
+                               static_cast<cudaStream_t>(stream)>>>(x, ld_x, bs_x, lo, total4, rows,
+                                                                    cols / 4);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }

@@ -645,6 +645,190 @@ cholesky_blocked_kernel(const float* __restrict__ Gall, float* Uall, int r) {
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Panel step of a blocked Householder QR (compact WY form).  One CTA per matrix factors the
+// 32-column panel A[j:, j:j+32] in shared memory and leaves
+//   * the panel's part of R (upper triangle of its top 32 rows) in A,
+//   * V  [kk, 32]: the reflectors, unit lower trapezoidal (kk = k - j rows),
+//   * VT [kk, 32] = V T^T, with T the 32 x 32 upper-triangular factor of
+//     H_0 ... H_31 = I - V T V^T,
+// so that the caller updates the columns to the right of the panel with two products on the
+// tensor cores:  W = V^T A[j:, j+32:],  A[j:, j+32:] -= VT W.
+// Within a column, lane = panel column: the dot products of column c with the columns to its
+// right are taken by all warps over interleaved rows, reduced through shared memory, and the
+// rank-one update follows; two block barriers per column.
+// ---------------------------------------------------------------------------------------------
+constexpr int kQpWarps = 16;
+constexpr int kQpPitch = 33;
+
+// Reflector entry (i, a) of the panel held in P: zero above the diagonal, one on it.
+__device__ __forceinline__ float qp_v(const float* P, int i, int a) {
+  return i > a ? P[i * kQpPitch + a] : (i == a ? 1.f : 0.f);
+}
+
+__global__ void __launch_bounds__(kQpWarps * 32, 1)
+qr_panel_kernel(float* Aall, long long strideA, int ld, int k, int j, float* Vall, float* VTall,
+                float* Vlo_all, float* VTlo_all) {
+  extern __shared__ __align__(16) float qp_smem[];
+  const int kk = k - j;
+  float* P = qp_smem;                               // [kk][33]
+  float* part = P + (size_t)kk * kQpPitch;          // [16][32]
+  float* wv = part + kQpWarps * 32;                 // [32]  w of the current column
+  float* taus = wv + 32;                            // [32]
+  float* sc = taus + 32;                            // [32]  1 / (alpha - beta) per column
+  float* G = sc + 32;                               // [32][33]  V^T V (strictly upper part used)
+  float* T = G + 32 * kQpPitch;                     // [32][33]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float* A = Aall + (size_t)blockIdx.x * strideA + (size_t)j * ld + j;
+  float* V = Vall + (size_t)blockIdx.x * k * 32;
+  float* VT = VTall + (size_t)blockIdx.x * k * 32;
+  float* Vlo = Vlo_all + (size_t)blockIdx.x * k * 32;
+  float* VTlo = VTlo_all + (size_t)blockIdx.x * k * 32;
+
+  for (int i = warp; i < kk; i += kQpWarps) P[i * kQpPitch + lane] = A[(size_t)i * ld + lane];
+  for (int e = threadIdx.x; e < 32 * kQpPitch; e += kQpWarps * 32) G[e] = 0.f;
+  __syncthreads();
+
+  // Dot products of column 0 with every column, over the rows below the diagonal.
+  {
+    float acc = 0.f;
+    for (int i = 1 + warp; i < kk; i += kQpWarps)
+      acc += P[i * kQpPitch] * P[i * kQpPitch + lane];
+    part[warp * 32 + lane] = acc;
+  }
+  __syncthreads();
+
+  for (int c = 0; c < 32; ++c) {
+    // part holds d[lane] = sum_{i > c} P[i][c] * P[i][lane]  (lane = c: the squared tail norm)
+    if (warp == 0) {
+      float d = 0.f;
+#pragma unroll
+      for (int q = 0; q < kQpWarps; ++q) d += part[q * 32 + lane];
+      const float sigma = __shfl_sync(0xffffffffu, d, c);
+      const float alpha = P[c * kQpPitch + c];
+      float tau = 0.f, scale = 0.f, rcc = alpha;    // tail already zero: H = I (as LAPACK's larfg)
+      if (sigma > 0.f) {
+        const float beta = -copysignf(sqrtf(alpha * alpha + sigma), alpha);
+        tau = (beta - alpha) / beta;
+        scale = 1.f / (alpha - beta);
+        rcc = beta;
+      }
+      // w[lane] = tau * v^T A[:, lane] with v = (1, scale * tail)
+      const float w = lane > c ? tau * (P[c * kQpPitch + lane] + scale * d) : 0.f;
+      wv[lane] = w;
+      if (lane > c) P[c * kQpPitch + lane] -= w;    // row c: v_c = 1
+      if (lane == c) {
+        taus[c] = tau;
+        sc[c] = scale;
+        P[c * kQpPitch + c] = rcc;
+      }
+    }
+    __syncthreads();
+    // Rank-one update of the rows below the diagonal (the reflector's tail stays unscaled in P
+    // until the loop is over, so no lane writes what another reads), and in the same pass the
+    // dot products for the next column, whose updated entry arrives by a shuffle from its lane.
+    const float ws = wv[lane] * sc[c];
+    const int cn = (c + 1) & 31;
+    float a0 = 0.f, a1 = 0.f;
+    int i = c + 1 + warp;
+    for (; i + kQpWarps < kk; i += 2 * kQpWarps) {
+      float* p0 = P + i * kQpPitch;
+      float* p1 = p0 + kQpWarps * kQpPitch;
+      const float x0 = p0[c], x1 = p1[c];
+      float v0 = p0[lane], v1 = p1[lane];
+      if (lane > c) {
+        v0 -= x0 * ws;
+        v1 -= x1 * ws;
+        p0[lane] = v0;
+        p1[lane] = v1;
+      }
+      const float n0 = __shfl_sync(0xffffffffu, v0, cn), n1 = __shfl_sync(0xffffffffu, v1, cn);
+      if (i > c + 1) a0 += n0 * v0;
+      a1 += n1 * v1;
+    }
+    if (i < kk) {
+      float* p0 = P + i * kQpPitch;
+      const float x0 = p0[c];
+      float v0 = p0[lane];
+      if (lane > c) {
+        v0 -= x0 * ws;
+        p0[lane] = v0;
+      }
+      const float n0 = __shfl_sync(0xffffffffu, v0, cn);
+      if (i > c + 1) a0 += n0 * v0;
+    }
+    part[warp * 32 + lane] = a0 + a1;   // read by warp 0 only after the next barrier
+    __syncthreads();
+  }
+  // scale the reflector tails: V[i][a] = P[i][a] * sc[a] for i > a
+  {
+    const float scl = sc[lane];
+    for (int i = 1 + warp; i < kk; i += kQpWarps)
+      if (i > lane) P[i * kQpPitch + lane] *= scl;
+  }
+  __syncthreads();
+
+  // G[a][lane] = sum_i V[i][a] V[i][lane]
+  {
+    float g[32];
+#pragma unroll
+    for (int a = 0; a < 32; ++a) g[a] = 0.f;
+    for (int i = warp; i < kk; i += kQpWarps) {
+      const float vc = qp_v(P, i, lane);
+      if (i < 32) {
+#pragma unroll
+        for (int a = 0; a < 32; ++a) g[a] += qp_v(P, i, a) * vc;
+      } else {
+#pragma unroll
+        for (int a = 0; a < 32; ++a) g[a] += P[i * kQpPitch + a] * vc;
+      }
+    }
+#pragma unroll
+    for (int a = 0; a < 32; ++a) atomicAdd(&G[a * kQpPitch + lane], g[a]);
+  }
+  __syncthreads();
+  // T by columns (lane = row a):  T[a][c] = -tau_c * sum_{b = a}^{c-1} T[a][b] G[b][c],  T[c][c] = tau_c
+  if (warp == 0) {
+    float t[32];
+#pragma unroll
+    for (int c = 0; c < 32; ++c) {
+      float sacc = 0.f;
+#pragma unroll
+      for (int b = 0; b < 32; ++b)
+        if (b < c) sacc += (b >= lane ? t[b] : 0.f) * G[b * kQpPitch + c];
+      const float tc = taus[c];
+      t[c] = lane < c ? -tc * sacc : (lane == c ? tc : 0.f);
+      T[lane * kQpPitch + c] = t[c];
+    }
+  }
+  __syncthreads();
+  // V and VT = V T^T to global memory (lane = column a; row a of T in registers)
+  {
+    float trow[32];
+#pragma unroll
+    for (int c = 0; c < 32; ++c) trow[c] = T[lane * kQpPitch + c];
+    for (int i = warp; i < kk; i += kQpWarps) {
+      float acc = 0.f;
+      if (i < 32) {
+#pragma unroll
+        for (int c = 0; c < 32; ++c) acc += qp_v(P, i, c) * trow[c];
+      } else {
+#pragma unroll
+        for (int c = 0; c < 32; ++c) acc += P[i * kQpPitch + c] * trow[c];
+      }
+      const float vv = qp_v(P, i, lane);
+      V[(size_t)(j + i) * 32 + lane] = vv;
+      VT[(size_t)(j + i) * 32 + lane] = acc;
+      // what a tf32 instruction does not see of them (second and third segment of the products)
+      Vlo[(size_t)(j + i) * 32 + lane] = vv - __uint_as_float(__float_as_uint(vv) & 0xFFFFE000u);
+      VTlo[(size_t)(j + i) * 32 + lane] = acc - __uint_as_float(__float_as_uint(acc) & 0xFFFFE000u);
+    }
+  }
+  // the panel's part of R back into A (reflectors are not kept there)
+  for (int i = warp; i < 32 && i < kk; i += kQpWarps)
+    if (lane >= i) A[(size_t)i * ld + lane] = P[i * kQpPitch + lane];
+}
+
 }  // namespace dion
 
 using namespace dion;
@@ -788,5 +972,26 @@ DION_EXPORT int dion_normalize_q(const void* R, const float* colsq, float eps, v
     dion::normalize_q_kernel<__nv_bfloat16><<<grid, 256, 0, S(stream)>>>(
         static_cast<const __nv_bfloat16*>(R), colsq, eps, static_cast<__nv_bfloat16*>(Qstack),
         static_cast<const long long*>(q_ptrs), q_dt, rows, cols);
+  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+// One panel step of the blocked QR on every matrix of A [n][k][ld-pitched rows] (fp32, in
+// place): columns j .. j+31, rows j .. k-1.  V, VT and their tf32 remainders Vlo, VTlo:
+// [n][k][32] (rows j.. written).
+// Limits: j a multiple of 32, j + 32 <= min(k, columns), (k - j) * 33 * 4 bytes + 17 KB of
+// shared memory (k - j <= 1580).
+DION_EXPORT int dion_qr_panel(void* A, long long strideA, int ld, int n, int k, int j, void* V,
+                              void* VT, void* Vlo, void* VTlo, void* stream) {
+  if (n <= 0) return 0;
+  if (j < 0 || (j & 31) || j + 32 > k || j + 32 > ld) return -2;
+  const size_t smem = ((size_t)(k - j) * kQpPitch + kQpWarps * 32 + 96 + 2 * 32 * kQpPitch) *
+                      sizeof(float);
+  if (smem > 226 * 1024) return -2;
+  if (cudaFuncSetAttribute(dion::qr_panel_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           (int)smem) != cudaSuccess)
+    return -3;
+  dion::qr_panel_kernel<<<n, kQpWarps * 32, smem, S(stream)>>>(
+      static_cast<float*>(A), strideA, ld, k, j, static_cast<float*>(V), static_cast<float*>(VT),
+      static_cast<float*>(Vlo), static_cast<float*>(VTlo));
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }

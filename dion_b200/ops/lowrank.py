@@ -8,6 +8,7 @@ Batched operands are ``[B, rows, cols]``.
 from __future__ import annotations
 
 import ctypes
+import os
 import math
 from typing import List, Optional, Tuple
 
@@ -86,7 +87,18 @@ def lr_gemm_ok(*ts: Tensor) -> bool:
 
 
 def split_lo(x: Tensor) -> Tensor:
-    """``x - tf32(x)``: the part of an fp32 tensor that a tf32 instruction does not see."""
+    """``x - tf32(x)``: the part of an fp32 tensor that a tf32 instruction does not see.  A 3-D
+    strided view (a block of rows and columns of every matrix of a batch) is read in place; the
+    result is contiguous."""
+    if (x.ndim == 3 and not x.is_contiguous() and x.stride(2) == 1 and x.size(2) % 4 == 0
+            and x.stride(1) % 4 == 0 and x.stride(0) % 4 == 0 and x.data_ptr() % 16 == 0):
+        lo = torch.empty(x.shape, dtype=x.dtype, device=x.device)
+        rc = _backend.lib("lowrank_gemm_sm100").dion_split_lo_view(
+            _ptr(x), ctypes.c_longlong(x.stride(1)), ctypes.c_longlong(x.stride(0)), _ptr(lo),
+            ctypes.c_longlong(x.size(0)), x.size(1), x.size(2), _stream(x.device))
+        if rc != 0:
+            raise RuntimeError(f"dion_split_lo_view launch failed (code {rc})")
+        return lo
     x = x.contiguous()
     lo = torch.empty_like(x)
     rc = _backend.lib("lowrank_gemm_sm100").dion_split_lo(
@@ -103,14 +115,16 @@ def lr_gemm(A: Tensor, B: Tensor, *, a_mn: bool = False, b_mn: bool = False,
             precise: bool = False, colsq: Optional[Tensor] = None,
             reduce_into: Optional[Tensor] = None, reduce_ld: int = 0,
             broadcast_to: Optional[List[int]] = None, slot0: int = 0, out_ld: int = 0,
-            out_stride: int = 0, bn: Optional[int] = None) -> Optional[Tensor]:
+            out_stride: int = 0, bn: Optional[int] = None,
+            a_lo: Optional[Tensor] = None) -> Optional[Tensor]:
     """``out[b] = alpha * A[b] @ op(B[b]) + beta * D[b]`` on the tensor cores (tf32 for fp32
     operands, bf16 otherwise; fp32 accumulation), see csrc/lowrank_gemm_sm100.cu.
 
     ``A`` is ``[batch, M, K]`` (``a_mn``: ``[batch, K, M]``), ``B`` is ``[batch, N, K]``
     (``b_mn``: ``[batch, K, N]``).  ``out`` / ``D`` are strided batches, ``out_list`` / ``d_list``
     lists of per-matrix tensors (separately allocated weights); ``D`` may be ``out``.
-    ``precise`` (fp32 operands): three tf32 products recover fp32-level accuracy.
+    ``precise`` (fp32 operands): three tf32 products recover fp32-level accuracy (``a_lo``: the
+    tf32 remainder of ``A`` if the caller has it already).
     ``colsq [batch, N]`` (fp32, zeroed by the caller) receives the column sums of squares of the
     result.
 
@@ -132,9 +146,7 @@ def lr_gemm(A: Tensor, B: Tensor, *, a_mn: bool = False, b_mn: bool = False,
     eb = A.element_size()
     segs = [(A, B)]
     if precise and eb == 4:
-        Ac = A if A.is_contiguous() else A.contiguous()
-        Bc = B if B.is_contiguous() else B.contiguous()
-        segs = [(Ac, Bc), (split_lo(Ac), Bc), (Ac, split_lo(Bc))]
+        segs = [(A, B), (a_lo if a_lo is not None else split_lo(A), B), (A, split_lo(B))]
     a_ops = (_LrOperand * 3)()
     b_ops = (_LrOperand * 3)()
     for i, (a, b) in enumerate(segs):
@@ -257,22 +269,69 @@ def householder_q(P: Tensor) -> Tensor:
     return Q
 
 
-def qr_r_factor(A: Tensor) -> Tensor:
-    """Upper-triangular factor of every ``A[b]`` (``[B, k, r]``, ``k >= r``) in fp32.  On a GPU
-    all matrices of the batch are factored at once by one kernel (Householder reflections, one
-    CTA per matrix); the sign of a row of ``R`` may differ from LAPACK's."""
-    A32 = A.to(torch.float32)
-    if A32.is_cuda and A32.ndim == 3 and A32.size(-1) <= A32.size(-2) <= _MAX_FACTOR_DIM:
-        A32 = A32.contiguous()
-        B, k, r = A32.shape
-        V = torch.empty((B, r, k), dtype=torch.float32, device=A32.device)
-        tau = torch.empty((B, r), dtype=torch.float32, device=A32.device)
-        R = torch.empty((B, r, r), dtype=torch.float32, device=A32.device)
-        rc = _backend.lib("lowrank_ops").dion_qr_r_factor(
-            _ptr(A32), _ptr(V), _ptr(tau), _ptr(R), B, k, r, _stream(A32.device))
+_QR_PANEL = 32
+_QR_PANEL_MAX_ROWS = 1580      # shared memory of the panel kernel: (rows * 33 + ...) * 4 bytes
+_QR_BLOCKED_MIN_COLS = 256     # below this the single-kernel form wins (five launches per panel)
+
+
+def blocked_qr_enabled() -> bool:
+    return os.environ.get("DION_B200_BLOCKED_QR", "1") != "0"
+
+
+def _qr_r_blocked(A32: Tensor) -> Tensor:
+    """Blocked Householder QR of a private fp32 batch ``[B, k, r]`` (overwritten): per 32-column
+    panel one kernel factors the panel in shared memory (one CTA per matrix) and emits the
+    reflectors ``V`` and ``V T^T`` of the compact WY form; the columns to the right are then
+    updated by two tensor-core products over the whole batch, ``W = V^T A_right`` and
+    ``A_right -= (V T^T) W`` (split operands: the factor is only as good as these)."""
+    B, k, r = A32.shape
+    dev = A32.device
+    V, VT, Vlo, VTlo = torch.empty((4, B, k, _QR_PANEL), dtype=torch.float32, device=dev).unbind(0)
+    W = torch.empty((B, _QR_PANEL, r), dtype=torch.float32, device=dev)
+    lib = _backend.lib("lowrank_ops")
+    for j in range(0, r, _QR_PANEL):
+        rc = lib.dion_qr_panel(_ptr(A32), ctypes.c_longlong(k * r), r, B, k, j, _ptr(V), _ptr(VT),
+                               _ptr(Vlo), _ptr(VTlo), _stream(dev))
         if rc != 0:
-            raise RuntimeError(f"dion_qr_r_factor launch failed (code {rc})")
-        return R
+            raise RuntimeError(f"dion_qr_panel launch failed (code {rc})")
+        nt = r - j - _QR_PANEL
+        if nt <= 0:
+            break
+        right = A32[:, j:, j + _QR_PANEL:]
+        Wv = W[:, :, :nt]
+        lr_gemm(V[:, j:, :], right, a_mn=True, b_mn=True, out=Wv, precise=True,
+                a_lo=Vlo[:, j:, :])
+        lr_gemm(VT[:, j:, :], Wv, b_mn=True, D=right, out=right, alpha=-1.0, beta=1.0,
+                precise=True, a_lo=VTlo[:, j:, :])
+    return torch.triu(A32[:, :r, :r])
+
+
+def qr_r_factor(A: Tensor, overwrite: bool = False) -> Tensor:
+    """Upper-triangular factor of every ``A[b]`` (``[B, k, r]``, ``k >= r``) in fp32.  On a GPU
+    all matrices of the batch are factored together: blocked Householder with the trailing
+    updates on the tensor cores when ``r`` is a multiple of 32 (at least 256), else one kernel
+    with one CTA per matrix (up to 1024 rows).  The sign of a row of ``R`` may differ from
+    LAPACK's.  ``overwrite``: ``A`` is a temporary of the caller and may be destroyed."""
+    A32 = A.to(torch.float32)
+    if A32.is_cuda and A32.ndim == 3 and A32.size(-1) <= A32.size(-2):
+        B, k, r = A32.shape
+        if (blocked_qr_enabled() and r % _QR_PANEL == 0 and r >= _QR_BLOCKED_MIN_COLS
+                and k <= _QR_PANEL_MAX_ROWS and k % 4 == 0 and B > 0):
+            if not A32.is_contiguous():
+                A32 = A32.contiguous()
+            elif A32.data_ptr() == A.data_ptr() and not overwrite:
+                A32 = A32.clone()
+            return _qr_r_blocked(A32)
+        if k <= _MAX_FACTOR_DIM:
+            A32 = A32.contiguous()
+            V = torch.empty((B, r, k), dtype=torch.float32, device=A32.device)
+            tau = torch.empty((B, r), dtype=torch.float32, device=A32.device)
+            R = torch.empty((B, r, r), dtype=torch.float32, device=A32.device)
+            rc = _backend.lib("lowrank_ops").dion_qr_r_factor(
+                _ptr(A32), _ptr(V), _ptr(tau), _ptr(R), B, k, r, _stream(A32.device))
+            if rc != 0:
+                raise RuntimeError(f"dion_qr_r_factor launch failed (code {rc})")
+            return R
     return torch.linalg.qr(A32, mode="r")[1]
 
 
@@ -332,7 +391,7 @@ def orthogonalize(P: Tensor, oversample: float = 1.25,
         return householder_q(P).to(dtype).contiguous()
     if sketch is None:
         sketch = random_sketch(P.size(0), sketch_rows(r, oversample), m, dtype, P.device, generator)
-    R1 = qr_r_factor(sketch_product(sketch, P))
+    R1 = qr_r_factor(sketch_product(sketch, P), overwrite=True)
     P32 = right_solve_upper(R1, P.to(torch.float32))
     R2 = cholesky_upper(gram(P32))
     return right_solve_upper(R2, P32).to(dtype).contiguous()
