@@ -19,7 +19,7 @@
 //
 // This replaces cuBLAS bmm / addmm / trsm in the reference's dion/dion.py:797-869, 1218-1305,
 // 1491-1527.  Structure as in ns_gemm_sm100.cu: persistent CTAs, warp 0 = TMA producer (128-byte
-// swizzle, no multicast), warp 1 = MMA issuer, warps 2-5 = epilogue; every wait is bounded.
+// swizzle, no multicast), warp 1 = MMA issuer, then four epilogue warps per kEpiGroups; every wait is bounded.
 #include <string.h>
 
 #include "common.cuh"
@@ -27,7 +27,10 @@
 namespace dion {
 
 constexpr int LBM = 128;          // tile rows
-constexpr int kLrThreads = 192;
+constexpr int kEpiGroups = 1;      // epilogue warps per TMEM lane quarter: each takes every
+                                   // kEpiGroups-th 32-column chunk
+constexpr int kEpiPitch = 33;      // floats per row of an epilogue warp's 32 x 32 staging block
+constexpr int kLrThreads = 64 + 128 * kEpiGroups;
 constexpr int kRowBytes = 128;    // one swizzle row = one K slab of a K-major operand row
 
 struct LrGemmArgs {
@@ -146,6 +149,7 @@ lr_gemm_kernel(const __grid_constant__ LrMaps maps, const LrGemmArgs p) {
   __shared__ __align__(8) uint64_t tfull_bar[2];
   __shared__ __align__(8) uint64_t tempty_bar[2];
   __shared__ uint32_t tmem_base_slot;
+  __shared__ float epi_stage[4 * kEpiGroups][32 * kEpiPitch];
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -158,7 +162,7 @@ lr_gemm_kernel(const __grid_constant__ LrMaps maps, const LrGemmArgs p) {
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tfull_bar[a], 1);
-      mbar_init(&tempty_bar[a], 4);
+      mbar_init(&tempty_bar[a], 4 * kEpiGroups);
     }
     fence_barrier_init();
     fence_proxy_async();
@@ -267,7 +271,8 @@ lr_gemm_kernel(const __grid_constant__ LrMaps maps, const LrGemmArgs p) {
     }
   } else {
     // ------------------------------ epilogue ----------------------------------
-    const int lane_grp = warp & 3;
+    const int lane_grp = warp & 3;     // TMEM lanes this warp may read: 32 * (warp % 4) ...
+    const int epi_grp = (warp - 2) >> 2;
     const int row_in_tile = lane_grp * 32 + lane;
     uint32_t aslot = 0, aphase = 0;
     for (int t = blockIdx.x; t < p.total_tiles; t += gridDim.x) {
@@ -289,7 +294,7 @@ lr_gemm_kernel(const __grid_constant__ LrMaps maps, const LrGemmArgs p) {
       const bool d_vec = Db != nullptr && (p.ldd & 7) == 0 &&
                          (reinterpret_cast<uintptr_t>(Db) & 15) == 0 &&
                          (p.d_table != nullptr || (p.strideD & 7) == 0);
-      if (Db != nullptr && row_ok) {
+      if (Db != nullptr && row_ok && epi_grp == 0) {
         // While the tensor cores still work on this tile, pull this thread's row of D towards
         // L2: with K as short as a rank the epilogue is the longer half of a tile, and most of
         // it used to be the DRAM latency of one D chunk after the other.
@@ -305,12 +310,107 @@ lr_gemm_kernel(const __grid_constant__ LrMaps maps, const LrGemmArgs p) {
       }
       tc_fence_after();
 #pragma unroll 1
-      for (int ch = 0; ch < BN / 32; ++ch) {
+      for (int ch = epi_grp; ch < BN / 32; ch += kEpiGroups) {
         const int c0 = tn * BN + ch * 32;
         if (c0 >= p.N) continue;  // warp-uniform
         const bool full = c0 + 32 <= p.N;
         // The vector form of D is requested before the accumulator is read, so that both are
         // in flight together (fp32: eight 16-byte pieces; bf16: four, carried as raw bits).
+        if (p.out_mode == kOutStore && p.colsq == nullptr && c_vec && full &&
+            (Db == nullptr || (d_vec && p.d_dt == p.c_dt))) {
+          // Plain store, possibly in place over D.  A thread of the accumulator owns a row, so
+          // row-wise accesses would touch 32 different lines per instruction, 16 bytes of each:
+          // request slots between L1 and L2, not bytes, then bound the kernel.  The block is
+          // turned through shared memory instead: per instruction the warp covers four rows of
+          // 128 bytes (fp32; eight rows of 64 bytes for bf16), whole lines or sectors, and all
+          // loads of D are issued before the accumulator is read.
+          float* st = epi_stage[warp - 2];
+          const int wrow0 = tm * LBM + lane_grp * 32;
+          if (p.c_dt == 0) {
+            const int rsub = lane >> 3, cq = (lane & 7) * 4;
+            float4 d[8];
+            if (Db != nullptr) {
+#pragma unroll
+              for (int it = 0; it < 8; ++it) {
+                const int rr = wrow0 + it * 4 + rsub;
+                if (rr < p.M)
+                  d[it] = *reinterpret_cast<const float4*>(
+                      reinterpret_cast<const float*>(Db) + (long long)rr * p.ldd + c0 + cq);
+              }
+            }
+            float v[32];
+            tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(lane_grp * 32) << 16) + aslot * BN +
+                              ch * 32,
+                          v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) st[lane * kEpiPitch + j] = p.alpha * v[j];
+            __syncwarp();
+#pragma unroll
+            for (int it = 0; it < 8; ++it) {
+              const int rl = it * 4 + rsub;
+              const int rr = wrow0 + rl;
+              if (rr < p.M) {
+                const float* sp = st + rl * kEpiPitch + cq;
+                float4 x = make_float4(sp[0], sp[1], sp[2], sp[3]);
+                if (Db != nullptr) {
+                  x.x += p.beta * d[it].x;
+                  x.y += p.beta * d[it].y;
+                  x.z += p.beta * d[it].z;
+                  x.w += p.beta * d[it].w;
+                }
+                *reinterpret_cast<float4*>(reinterpret_cast<float*>(Cb) + (long long)rr * p.ldc +
+                                           c0 + cq) = x;
+              }
+            }
+          } else {
+            const int rsub = lane >> 2, cq = (lane & 3) * 8;
+            uint4 d[4];
+            if (Db != nullptr) {
+#pragma unroll
+              for (int it = 0; it < 4; ++it) {
+                const int rr = wrow0 + it * 8 + rsub;
+                if (rr < p.M)
+                  d[it] = *reinterpret_cast<const uint4*>(
+                      reinterpret_cast<const __nv_bfloat16*>(Db) + (long long)rr * p.ldd + c0 + cq);
+              }
+            }
+            float v[32];
+            tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(lane_grp * 32) << 16) + aslot * BN +
+                              ch * 32,
+                          v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) st[lane * kEpiPitch + j] = p.alpha * v[j];
+            __syncwarp();
+#pragma unroll
+            for (int it = 0; it < 4; ++it) {
+              const int rl = it * 8 + rsub;
+              const int rr = wrow0 + rl;
+              if (rr < p.M) {
+                const float* sp = st + rl * kEpiPitch + cq;
+                float x[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) x[e] = sp[e];
+                if (Db != nullptr) {
+                  const uint32_t w[4] = {d[it].x, d[it].y, d[it].z, d[it].w};
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) {
+                    const float2 f = unpack_bf16x2(w[e]);
+                    x[2 * e] += p.beta * f.x;
+                    x[2 * e + 1] += p.beta * f.y;
+                  }
+                }
+                *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(Cb) +
+                                          (long long)rr * p.ldc + c0 + cq) =
+                    make_uint4(pack_bf16x2(x[0], x[1]), pack_bf16x2(x[2], x[3]),
+                               pack_bf16x2(x[4], x[5]), pack_bf16x2(x[6], x[7]));
+              }
+            }
+          }
+          __syncwarp();     // the staging block is reused by the next chunk
+          continue;
+        }
         float4 dpre[8];
         const bool pre = row_ok && d_vec && full;
         if (pre) {
