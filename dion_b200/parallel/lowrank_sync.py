@@ -38,7 +38,12 @@ from . import symm
 
 
 def fused_lowrank_enabled() -> bool:
-    return os.environ.get("DION_B200_FUSED_LOWRANK", "1") != "0"
+    """``DION_B200_FUSED_LOWRANK=1`` turns this path on.  It is off by default: measured on the
+    GPT-1B block matrices it ties with the NCCL reduce-scatter / all-gather at 2 GPUs (29.3
+    against 29.0 ms per step) and loses at 4 (30.0 against 26.8 ms) - the factors are large
+    (0.8 GB per step) against the 0.2 ms product that produces them, so there is little to
+    overlap, and 16-byte reductions use an NVLink far less well than NCCL's bulk copies."""
+    return os.environ.get("DION_B200_FUSED_LOWRANK", "0") == "1"
 
 
 def eligible(pg: Optional[ProcessGroup], device: torch.device) -> bool:
