@@ -29,6 +29,7 @@ namespace dion {
 constexpr int LBM = 128;          // tile rows
 constexpr int kEpiGroups = 1;      // epilogue warps per TMEM lane quarter: each takes every
                                    // kEpiGroups-th 32-column chunk
+constexpr int kRing = 4;           // tile numbers in flight between the producer and the others
 constexpr int kEpiPitch = 33;      // floats per row of an epilogue warp's 32 x 32 staging block
 constexpr int kLrThreads = 64 + 128 * kEpiGroups;
 constexpr int kRowBytes = 128;    // one swizzle row = one K slab of a K-major operand row
@@ -48,6 +49,11 @@ struct LrGemmArgs {
   int tiles_per_mat;
   int total_tiles;
   int* status;
+  // Optional dynamic tile order: sched[0] hands out tile numbers, sched[1] counts finished CTAs
+  // (the last one zeroes both, so launches that follow one another on a stream can share the
+  // pair).  CTAs that start late - their SM was still held by another stream's kernel - then
+  // find the tiles taken instead of making everybody wait for their fixed share.
+  int* sched;
   // How the result leaves (fp32 C only for the last two):
   //   kOutStore      plain store into C / c_table[b]
   //   kOutReduce     red.add into C / c_table[b]: with c_table[b] pointing into the buffer of
@@ -150,6 +156,9 @@ lr_gemm_kernel(const __grid_constant__ LrMaps maps, const LrGemmArgs p) {
   __shared__ __align__(8) uint64_t tempty_bar[2];
   __shared__ uint32_t tmem_base_slot;
   __shared__ float epi_stage[4 * kEpiGroups][32 * kEpiPitch];
+  __shared__ __align__(8) uint64_t ring_full[kRing];
+  __shared__ __align__(8) uint64_t ring_empty[kRing];
+  __shared__ int tile_ring[kRing];
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -163,6 +172,10 @@ lr_gemm_kernel(const __grid_constant__ LrMaps maps, const LrGemmArgs p) {
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tfull_bar[a], 1);
       mbar_init(&tempty_bar[a], 4 * kEpiGroups);
+    }
+    for (int q = 0; q < kRing; ++q) {
+      mbar_init(&ring_full[q], 1);
+      mbar_init(&ring_empty[q], 1 + 4 * kEpiGroups);   // MMA thread + one lane per epilogue warp
     }
     fence_barrier_init();
     fence_proxy_async();
@@ -180,12 +193,45 @@ lr_gemm_kernel(const __grid_constant__ LrMaps maps, const LrGemmArgs p) {
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_slot;
 
+  // Tile hand-out.  The producer thread decides the it-th tile of this CTA (its fixed share, or
+  // the next number of the device counter) and posts it in a small ring; -1 ends the kernel.
+  auto post_tile = [&](int it) -> int {
+    const int slot = it & (kRing - 1);
+    const uint32_t ph = (static_cast<uint32_t>(it) / kRing) & 1u;
+    int t = -1;
+    if (mbar_wait_bounded(&ring_empty[slot], ph ^ 1u)) {
+      t = p.sched ? atomicAdd(p.sched, 1) : static_cast<int>(blockIdx.x + it * gridDim.x);
+      if (t >= p.total_tiles) t = -1;
+    } else {
+      atomicExch(p.status, kStatusTimeoutEmpty);
+    }
+    tile_ring[slot] = t;
+    mbar_arrive(&ring_full[slot]);
+    return t;
+  };
+  // The other roles read it: the MMA thread alone (`whole_warp` false), or the 32 lanes of an
+  // epilogue warp together, of which one (`arrive`) hands the slot back once all have read.
+  auto take_tile = [&](int it, bool arrive, bool whole_warp) -> int {
+    const int slot = it & (kRing - 1);
+    const uint32_t ph = (static_cast<uint32_t>(it) / kRing) & 1u;
+    if (!mbar_wait_bounded(&ring_full[slot], ph)) {
+      if (arrive) atomicExch(p.status, kStatusTimeoutFull);
+      return -1;
+    }
+    const int t = tile_ring[slot];
+    if (whole_warp) __syncwarp();
+    if (arrive) mbar_arrive(&ring_empty[slot]);
+    return t;
+  };
+
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
     if (lane == 0) {
       uint32_t stage = 0, phase = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
+      for (int it = 0; ok; ++it) {
+        const int t = post_tile(it);
+        if (t < 0) break;
         const int b = t / p.tiles_per_mat;
         const int rem = t - b * p.tiles_per_mat;
         const int tm = rem / p.tiles_n, tn = rem - tm * p.tiles_n;
@@ -233,7 +279,8 @@ lr_gemm_kernel(const __grid_constant__ LrMaps maps, const LrGemmArgs p) {
       uint32_t aslot = 0, aphase = 0;
       bool ok = true;
       const int total_kb = num_kb * p.nseg;
-      for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
+      for (int it = 0; ok; ++it) {
+        if (take_tile(it, true, false) < 0) break;
         if (!mbar_wait_bounded(&tempty_bar[aslot], aphase ^ 1)) {
           atomicExch(p.status, kStatusTimeoutTmemEmpty);
           break;
@@ -275,7 +322,9 @@ lr_gemm_kernel(const __grid_constant__ LrMaps maps, const LrGemmArgs p) {
     const int epi_grp = (warp - 2) >> 2;
     const int row_in_tile = lane_grp * 32 + lane;
     uint32_t aslot = 0, aphase = 0;
-    for (int t = blockIdx.x; t < p.total_tiles; t += gridDim.x) {
+    for (int it = 0;; ++it) {
+      const int t = take_tile(it, lane == 0, true);
+      if (t < 0) break;
       const int b = t / p.tiles_per_mat;
       const int rem = t - b * p.tiles_per_mat;
       const int tm = rem / p.tiles_n, tn = rem - tm * p.tiles_n;
@@ -564,6 +613,15 @@ lr_gemm_kernel(const __grid_constant__ LrMaps maps, const LrGemmArgs p) {
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
   }
+  if (threadIdx.x == 0 && p.sched != nullptr) {
+    // Every CTA has drawn its last number by now; the last one to get here rewinds the pair.
+    __threadfence();
+    if (atomicAdd(p.sched + 1, 1) == static_cast<int>(gridDim.x) - 1) {
+      p.sched[0] = 0;
+      __threadfence();
+      p.sched[1] = 0;
+    }
+  }
 }
 
 // lo = x - tf32_part(x): what a tf32 instruction does not see of x (it reads sign, exponent and
@@ -692,6 +750,7 @@ struct DionLrExtra {
   int n_targets;
   int slot0;                  // mode 2: matrix b goes to slot slot0 + b
   float* colsq;               // [batch, N] column sums of squares of the result
+  int* sched;                 // optional: two zeroed ints for the dynamic tile order (see LrGemmArgs)
 };
 
 // C[b] = alpha * sum_s A_s[b] op(B_s[b]) + beta * D[b].
@@ -750,6 +809,7 @@ DION_EXPORT int dion_lr_gemm(int elem_bytes, int nseg, const DionLrOperand* A,
     g.slot0 = ex->slot0;
     for (int i = 0; i < 8; ++i) g.targets[i] = ex->targets[i];
     g.colsq = ex->colsq;
+    g.sched = ex->sched;
     if (g.out_mode < 0 || g.out_mode > 2 || g.n_targets < 0 || g.n_targets > 8) return -15;
     if (g.out_mode != 0 && c_dt != 0) return -15;
     if (g.out_mode == 2 && g.n_targets == 0) return -15;

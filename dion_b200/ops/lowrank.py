@@ -36,7 +36,27 @@ class _LrExtra(ctypes.Structure):
     _fields_ = [("c_table", ctypes.c_void_p), ("d_table", ctypes.c_void_p),
                 ("out_mode", ctypes.c_int), ("targets", ctypes.c_longlong * 8),
                 ("n_targets", ctypes.c_int), ("slot0", ctypes.c_int),
-                ("colsq", ctypes.c_void_p)]
+                ("colsq", ctypes.c_void_p), ("sched", ctypes.c_void_p)]
+
+
+_sched_pairs: dict = {}
+
+
+def dynamic_tiles_enabled() -> bool:
+    """``DION_B200_DYNAMIC_TILES`` (default on): the low-rank GEMM's CTAs draw tile numbers from a
+    device counter instead of taking a fixed share, so a launch that shares the GPU with another
+    stream's kernels is not held up by the CTAs that start late."""
+    return os.environ.get("DION_B200_DYNAMIC_TILES", "1") != "0"
+
+
+def _sched_pair(device: torch.device) -> Tensor:
+    """Two zeroed ints per (device, stream): launches on one stream follow one another, and the
+    kernel rewinds the pair when its last CTA leaves."""
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    t = _sched_pairs.get(key)
+    if t is None:
+        t = _sched_pairs[key] = torch.zeros(2, dtype=torch.int32, device=device)
+    return t
 
 
 _pointer_tables: dict = {}
@@ -197,6 +217,9 @@ def lr_gemm(A: Tensor, B: Tensor, *, a_mn: bool = False, b_mn: bool = False,
         use_ex = True
     if bn is None:
         bn = 256 if N > 128 else 128
+    if dynamic_tiles_enabled() and not torch.cuda.is_current_stream_capturing():
+        ex.sched = _sched_pair(dev).data_ptr()
+        use_ex = True
     st = gemm.status_tensor(dev)
     rc = _backend.lib("lowrank_gemm_sm100").dion_lr_gemm(
         eb, len(segs), a_ops, b_ops, int(a_mn), int(b_mn),
