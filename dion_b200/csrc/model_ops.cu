@@ -202,7 +202,7 @@ rope_qknorm_bwd_kernel(const __nv_bfloat16* Q, const __nv_bfloat16* K, long long
                        const __nv_bfloat16* COS, const __nv_bfloat16* SIN,
                        const __nv_bfloat16* DQO, const __nv_bfloat16* DKO, const float* rstd,
                        __nv_bfloat16* DQ, __nv_bfloat16* DK, long long out_row_stride,
-                       const __nv_bfloat16* DVI, __nv_bfloat16* DVO,
+                       const __nv_bfloat16* DVI, long long dvi_row_stride, __nv_bfloat16* DVO,
                        long long n_vec, int T, int H) {
   constexpr int HALF = D / 2, TPV = D / 16;
   const long long gid = (long long)blockIdx.x * 256 + threadIdx.x;
@@ -241,7 +241,7 @@ rope_qknorm_bwd_kernel(const __nv_bfloat16* Q, const __nv_bfloat16* K, long long
     const long long vv = w_raw - 2 * n_vec;
     const long long vbt = vv / H;
     const int vh = (int)(vv - vbt * H);
-    const uint4* src = reinterpret_cast<const uint4*>(DVI + vv * D);
+    const uint4* src = reinterpret_cast<const uint4*>(DVI + vbt * dvi_row_stride + (long long)vh * D);
     uint4* dst = reinterpret_cast<uint4*>(DVO + vbt * out_row_stride + (long long)vh * D);
     dst[sub] = src[sub];
     dst[HALF / 8 + sub] = src[HALF / 8 + sub];
@@ -471,11 +471,13 @@ DION_EXPORT int dion_rope_qknorm_fwd(const void* Q, const void* K, long long in_
 DION_EXPORT int dion_rope_qknorm_bwd(const void* Q, const void* K, long long in_row_stride,
                                      const void* COS, const void* SIN, const void* DQO,
                                      const void* DKO, const float* rstd, void* DQ, void* DK,
-                                     long long out_row_stride, const void* DVI, void* DVO,
-                                     int B, int T, int H, int D, void* stream) {
+                                     long long out_row_stride, const void* DVI,
+                                     long long dvi_row_stride, void* DVO, int B, int T, int H,
+                                     int D, void* stream) {
   const long long n_vec = (long long)B * T * H;
   if (n_vec <= 0) return 0;
   if (in_row_stride % 8 || out_row_stride % 8) return -2;
+  if (DVI != nullptr && (dvi_row_stride % 8 || dvi_row_stride < (long long)H * D)) return -2;
   if (DVI != nullptr && ((reinterpret_cast<uintptr_t>(DVI) | reinterpret_cast<uintptr_t>(DVO)) & 15))
     return -2;
   const long long threads = (DVI != nullptr ? 3 : 2) * n_vec * (D / 16);
@@ -484,7 +486,8 @@ DION_EXPORT int dion_rope_qknorm_bwd(const void* Q, const void* K, long long in_
   typedef __nv_bfloat16* P;
   DION_ROPE_DISPATCH(D, (rope_qknorm_bwd_kernel<DD><<<grid, 256, 0, S(stream)>>>(
                             (CP)Q, (CP)K, in_row_stride, (CP)COS, (CP)SIN, (CP)DQO, (CP)DKO, rstd,
-                            (P)DQ, (P)DK, out_row_stride, (CP)DVI, (P)DVO, n_vec, T, H)))
+                            (P)DQ, (P)DK, out_row_stride, (CP)DVI, dvi_row_stride, (P)DVO, n_vec,
+                            T, H)))
   return rc();
 }
 

@@ -214,7 +214,8 @@ class _RopeQKNorm(torch.autograd.Function):
         dk = torch.empty_like(dq)
         _check(_lib().dion_rope_qknorm_bwd(_c(q), _c(k), ctypes.c_longlong(ctx.rs), _c(cos),
                                            _c(sin), _c(dqo), _c(dko), _c(rstd), _c(dq), _c(dk),
-                                           ctypes.c_longlong(H * D), _c(None), _c(None),
+                                           ctypes.c_longlong(H * D), _c(None),
+                                           ctypes.c_longlong(0), _c(None),
                                            B, T, H, D, _stream(q.device)), "dion_rope_qknorm_bwd")
         return dq, dk, None, None, None
 
@@ -271,13 +272,22 @@ class _QKVRope(torch.autograd.Function):
         h2, W, qkv, cos, sin, rstd = ctx.saved_tensors
         B, T, C, H, D = ctx.dims
         dqkv = torch.empty_like(qkv)
-        dqo, dko, dv = dqo.contiguous(), dko.contiguous(), dv.contiguous()
+        dqo, dko = dqo.contiguous(), dko.contiguous()
+        # The attention backward lays dv out like v itself (rows 3C apart): the kernel reads it
+        # through its row pitch instead of a compacting copy first.
+        if (dv.dim() == 4 and dv.stride(3) == 1 and dv.stride(2) == D and dv.stride(1) % 8 == 0
+                and dv.stride(1) >= C and dv.stride(0) == T * dv.stride(1)
+                and dv.data_ptr() % 16 == 0):
+            dv_pitch = dv.stride(1)
+        else:
+            dv, dv_pitch = dv.contiguous(), C
         # One kernel: RoPE/QK-norm backward into the q and k columns, dv copied into the v columns.
         _check(_lib().dion_rope_qknorm_bwd(_c(qkv[:, :C]), _c(qkv[:, C:2 * C]),
                                            ctypes.c_longlong(3 * C), _c(cos), _c(sin), _c(dqo),
                                            _c(dko), _c(rstd), _c(dqkv[:, :C]),
                                            _c(dqkv[:, C:2 * C]), ctypes.c_longlong(3 * C),
-                                           _c(dv), _c(dqkv[:, 2 * C:]),
+                                           _c(dv), ctypes.c_longlong(dv_pitch),
+                                           _c(dqkv[:, 2 * C:]),
                                            B, T, H, D, _stream(h2.device)),
                "dion_rope_qknorm_bwd")
         dh = torch.mm(dqkv, W).view(B, T, C)
