@@ -107,6 +107,31 @@ def test_fused_exchange_eligibility_uses_only_rank_independent_facts(monkeypatch
     assert not FX.eligible(**ok)
 
 
+def test_fused_exchange_eligibility_of_column_shards(monkeypatch):
+    """Column shards are taken only by callers that ask (``allow_columns``), only when every
+    rank holds the same whole number of 32-column chunks and nothing else shards that dimension;
+    the fused low-rank synchronisation of legacy Dion is opt-in."""
+    from dion_b200.ops import newton_schulz as NS
+    from dion_b200.parallel import fused_exchange as FX
+    from dion_b200.parallel import lowrank_sync as LS
+    monkeypatch.setattr(FX.symm, "symmetric_memory_available", lambda pg: True)
+    monkeypatch.delenv("DION_B200_FUSED_EXCHANGE", raising=False)
+    ok = dict(local_shape=(512, 256), comm_dim=-1, global_rows=1024, world=4, pg=object(),
+              ns_func=NS.newton_schulz_quintic, flatten=False, split_sizes=None)
+    assert not FX.eligible(**ok)
+    assert FX.eligible(**ok, allow_columns=True)
+    for change in (dict(global_rows=1028, local_shape=(512, 257)),   # ragged blocks
+                   dict(global_rows=960, local_shape=(512, 240)),    # 240 is no multiple of 32
+                   dict(local_shape=(512, 128)),                     # also sharded elsewhere
+                   dict(local_shape=(516, 256)),                     # rows: Gram is a TMA operand
+                   dict(flatten=True)):
+        assert not FX.eligible(**{**ok, **change}, allow_columns=True), change
+    monkeypatch.delenv("DION_B200_FUSED_LOWRANK", raising=False)
+    assert not LS.fused_lowrank_enabled()
+    monkeypatch.setenv("DION_B200_FUSED_LOWRANK", "1")
+    assert LS.fused_lowrank_enabled()
+
+
 def test_megabatch_plan_modes_padding_and_argument_errors():
     """Layout decisions of one megabatch round, without communication: mode, per-rank counts,
     padded shard sizes, where each input is written, and the argument errors (the reference checks
