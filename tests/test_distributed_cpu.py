@@ -101,6 +101,31 @@ def test_replicated_matches_single_process(tmp_path):
             assert (a - b).abs().max().item() <= 1e-6, name
 
 
+def _eight_rank_worker(rank, world):
+    shapes = ((24, 16),) * 3 + ((16, 40),) * 11      # fewer and more matrices than ranks
+    a = _sharded_worker(rank, world, "Muon", dict(nesterov=True), shapes, 2, 0)
+    b = _sharded_worker(rank, world, "Muon", dict(nesterov=True), shapes, 2, 1)
+    wide = ((8, 24),) * 3 + ((16, 40),) * 11      # Dion2 by rows: sharded and single agree if wide
+    c = _sharded_worker(rank, world, "Dion2", dict(selection_scope="global"), wide, 2, 0)
+    d = _replicated_worker(rank, world, "Dion2", {}, shapes, 2)
+    return (a, b, c, d) if rank == 0 else None
+
+
+def test_eight_ranks_match_single_process(tmp_path):
+    """World size 8 (one node of B200s): buckets with fewer and with more matrices than ranks,
+    rows (24, 16) and columns (16, 40) that leave 3-, 2- or 5-wide shards, sharded by either
+    dimension or replicated with the work dealt out."""
+    shapes = ((24, 16),) * 3 + ((16, 40),) * 11
+    wide = ((8, 24),) * 3 + ((16, 40),) * 11
+    a, b, c, d = run_ranks(_eight_rank_worker, 8, "gloo", (), str(tmp_path))[0]
+    for ref, out, tol in ((_single("Muon", dict(nesterov=True), shapes), a, 1e-6),
+                          (_single("Muon", dict(nesterov=True), shapes), b, 1e-6),
+                          (_single("Dion2", dict(selection_scope="global"), wide), c, 5e-4),
+                          (_single("Dion2", {}, shapes), d, 1e-6)):
+        for x, y in zip(ref, out):
+            assert x.shape == y.shape and (x - y).abs().max().item() <= tol
+
+
 def _uneven_worker(rank, world):
     shapes = ((3, 8), (3, 8), (3, 8))  # 3 rows over 4 ranks: one rank holds nothing
     a = _sharded_worker(rank, world, "Muon", {}, shapes, 2, 0)
