@@ -378,6 +378,7 @@ def embedding(idx: Tensor, weight: Tensor) -> Tensor:
     idx = materialize(idx)
     if (is_plain_tensor(idx) and is_plain_tensor(weight) and weight.is_cuda
             and weight.dtype == torch.float32 and weight.size(1) % 8 == 0
+            and weight.size(1) <= 7168 and idx.numel() < 2 ** 31 - 256
             and idx.dtype == torch.int64 and weight.requires_grad and torch.is_grad_enabled()):
         return _Embedding.apply(idx, weight)
     return tF.embedding(idx, weight)
