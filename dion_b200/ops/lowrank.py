@@ -136,15 +136,16 @@ def lr_gemm(A: Tensor, B: Tensor, *, a_mn: bool = False, b_mn: bool = False,
             reduce_into: Optional[Tensor] = None, reduce_ld: int = 0,
             broadcast_to: Optional[List[int]] = None, slot0: int = 0, out_ld: int = 0,
             out_stride: int = 0, bn: Optional[int] = None,
-            a_lo: Optional[Tensor] = None) -> Optional[Tensor]:
+            a_lo: Optional[Tensor] = None, b_lo: Optional[Tensor] = None) -> Optional[Tensor]:
     """``out[b] = alpha * A[b] @ op(B[b]) + beta * D[b]`` on the tensor cores (tf32 for fp32
     operands, bf16 otherwise; fp32 accumulation), see csrc/lowrank_gemm_sm100.cu.
 
     ``A`` is ``[batch, M, K]`` (``a_mn``: ``[batch, K, M]``), ``B`` is ``[batch, N, K]``
     (``b_mn``: ``[batch, K, N]``).  ``out`` / ``D`` are strided batches, ``out_list`` / ``d_list``
     lists of per-matrix tensors (separately allocated weights); ``D`` may be ``out``.
-    ``precise`` (fp32 operands): three tf32 products recover fp32-level accuracy (``a_lo``: the
-    tf32 remainder of ``A`` if the caller has it already).
+    ``precise`` (fp32 operands): three tf32 products recover fp32-level accuracy (``a_lo``,
+    ``b_lo``: the tf32 remainders of ``A`` / ``B`` if the caller has them already; computed once
+    when ``B`` is ``A``).
     ``colsq [batch, N]`` (fp32, zeroed by the caller) receives the column sums of squares of the
     result.
 
@@ -166,7 +167,13 @@ def lr_gemm(A: Tensor, B: Tensor, *, a_mn: bool = False, b_mn: bool = False,
     eb = A.element_size()
     segs = [(A, B)]
     if precise and eb == 4:
-        segs = [(A, B), (a_lo if a_lo is not None else split_lo(A), B), (A, split_lo(B))]
+        if a_lo is None:
+            a_lo = split_lo(A)
+        if b_lo is None:
+            same = (B.data_ptr() == A.data_ptr() and B.shape == A.shape
+                    and B.stride() == A.stride())
+            b_lo = a_lo if same else split_lo(B)
+        segs = [(A, B), (a_lo, B), (A, b_lo)]
     a_ops = (_LrOperand * 3)()
     b_ops = (_LrOperand * 3)()
     for i, (a, b) in enumerate(segs):
@@ -373,20 +380,28 @@ def cholesky_upper(G: Tensor) -> Tensor:
     return torch.linalg.cholesky_ex(G, upper=True)[0]
 
 
-def right_solve_upper(R: Tensor, P: Tensor) -> Tensor:
+def _solve_on_kernel(R: Tensor, P: Tensor) -> bool:
+    return (P.is_cuda and P.dtype == torch.float32 and R.dtype == torch.float32 and P.ndim == 3
+            and R.size(-1) <= _MAX_FACTOR_DIM and lr_gemm_ok(P, R.contiguous()))
+
+
+def right_solve_upper(R: Tensor, P: Tensor, p_lo: Optional[Tensor] = None,
+                      out_dtype: Optional[torch.dtype] = None) -> Tensor:
     """``P @ R^-1`` for upper-triangular ``R`` (``[B, r, r]`` fp32) and ``P [B, m, r]`` fp32.  On
     a GPU: ``R^-1`` from the batched inversion kernel, then a tensor-core product with split
-    operands (fp32-level accuracy); elsewhere a triangular solve."""
-    if (P.is_cuda and P.dtype == torch.float32 and R.dtype == torch.float32 and P.ndim == 3
-            and R.size(-1) <= _MAX_FACTOR_DIM and lr_gemm_ok(P, R.contiguous())):
-        return lr_gemm(P, triu_inverse(R), b_mn=True, precise=True)
-    return torch.linalg.solve_triangular(R, P, upper=True, left=False)
+    operands (fp32-level accuracy; ``p_lo``: the tf32 remainder of ``P`` if already known; the
+    epilogue rounds to ``out_dtype``); elsewhere a triangular solve."""
+    if _solve_on_kernel(R, P):
+        return lr_gemm(P, triu_inverse(R), b_mn=True, precise=True, a_lo=p_lo,
+                       out_dtype=out_dtype)
+    X = torch.linalg.solve_triangular(R, P, upper=True, left=False)
+    return X if out_dtype is None else X.to(out_dtype)
 
 
-def gram(P: Tensor) -> Tensor:
+def gram(P: Tensor, p_lo: Optional[Tensor] = None) -> Tensor:
     """``P^T P`` in fp32 for ``P [B, m, r]`` fp32 (tensor cores with split operands on a GPU)."""
     if P.is_cuda and P.dtype == torch.float32 and P.ndim == 3 and lr_gemm_ok(P):
-        return lr_gemm(P, P, a_mn=True, b_mn=True, precise=True)
+        return lr_gemm(P, P, a_mn=True, b_mn=True, precise=True, a_lo=p_lo, b_lo=p_lo)
     return P.mT @ P
 
 
@@ -416,8 +431,10 @@ def orthogonalize(P: Tensor, oversample: float = 1.25,
         sketch = random_sketch(P.size(0), sketch_rows(r, oversample), m, dtype, P.device, generator)
     R1 = qr_r_factor(sketch_product(sketch, P), overwrite=True)
     P32 = right_solve_upper(R1, P.to(torch.float32))
-    R2 = cholesky_upper(gram(P32))
-    return right_solve_upper(R2, P32).to(dtype).contiguous()
+    # the tf32 remainder of the preconditioned P serves the Gram product and the second solve
+    lo = split_lo(P32) if (P32.is_cuda and lr_gemm_ok(P32)) else None
+    R2 = cholesky_upper(gram(P32, lo))
+    return right_solve_upper(R2, P32, lo, out_dtype=dtype).contiguous()
 
 
 def fix_all_zero_or_nan(P: Tensor, R: Tensor, Q_init: Tensor, B: Optional[Tensor],
