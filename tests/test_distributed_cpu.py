@@ -429,9 +429,15 @@ def _dion_layout_worker(rank, world, mode, steps, cls="Dion"):
         mesh = init_device_mesh("cpu", (world,), mesh_dim_names=("tp",))
         kw = dict(inner_shard_mesh=mesh["tp"])
         place = lambda i: [Shard(0)] if i < 2 else [Shard(1)]  # noqa: E731
-    else:
+    elif mode == "fsdp_tp":
         mesh = init_device_mesh("cpu", (2, 2), mesh_dim_names=("fs", "tp"))
         kw = dict(outer_shard_mesh=mesh["fs"], inner_shard_mesh=mesh["tp"])
+        place = lambda i: [Shard(1), Shard(0)] if i < 2 else [Shard(0), Shard(1)]  # noqa: E731
+    else:   # dp x fs x tp on eight ranks: replicas synchronize the low-rank factors
+        full_mesh = init_device_mesh("cpu", (2, 2, 2), mesh_dim_names=("dp", "fs", "tp"))
+        mesh = full_mesh["fs", "tp"]
+        kw = dict(replicate_mesh=full_mesh["dp"], outer_shard_mesh=full_mesh["fs"],
+                  inner_shard_mesh=full_mesh["tp"], replicate_mesh_grad_sync=True)
         place = lambda i: [Shard(1), Shard(0)] if i < 2 else [Shard(0), Shard(1)]  # noqa: E731
     ps = [torch.nn.Parameter(distribute_tensor(w, mesh, place(i)))
           for i, w in enumerate(_weights(DION_SHAPES))]
@@ -447,7 +453,8 @@ def _dion_layout_worker(rank, world, mode, steps, cls="Dion"):
 
 
 @pytest.mark.parametrize("cls", ["Dion", "DionReference"])
-@pytest.mark.parametrize("mode,world", [("fsdp", 2), ("tp", 2), ("fsdp_tp", 4)])
+@pytest.mark.parametrize("mode,world", [("fsdp", 2), ("tp", 2), ("fsdp_tp", 4),
+                                        ("dp_fsdp_tp", 8)])
 def test_dion_sharded_layouts_equal_the_single_process_run(tmp_path, mode, world, cls):
     """Legacy Dion on FSDP, tensor-parallel and FSDP x TP shards follows the single-process
     trajectory when both start from the same ``Q`` and iterate on the same side of the matrix
