@@ -137,6 +137,23 @@ def test_trainer_hybrid_meshes():
         assert len(ls) == 3 and ls[-1] < ls[0], (extra, ls)
 
 
+def test_trainer_on_eight_ranks_in_the_benchmark_layouts():
+    """The two eight-GPU layouts named as benchmark configurations, as eight gloo processes on a
+    small model: Muon with every parameter sharded eight ways (64 rows over 8 ranks), and legacy
+    Dion on a dp2 x fs2 x tp2 mesh with compressed data-parallel synchronisation.  Three steps on
+    random tokens say nothing about convergence (the optimizer-level tests compare eight ranks
+    with a single process); here the meshes, the sharded model and the step have to work."""
+    def losses(out):
+        return [float(tok.split("=")[1].rstrip(",")) for tok in out.split()
+                if tok.startswith("train_loss=")]
+    big = ["--batch_size", "32", "--num_iterations", "3"]
+    for extra in (["--optimizer", "muon", "--fs_size", "8"],
+                  ["--optimizer", "dion", "--dp_size", "2", "--fs_size", "2", "--tp_size", "2",
+                   "--replicate_mesh_grad_sync"]):
+        ls = losses(_torchrun(extra + big, nproc=8, timeout=1500))
+        assert len(ls) == 3 and all(10.0 < v < 12.5 for v in ls), (extra, ls)
+
+
 def test_trace_spans_and_profile_helper():
     from dion_b200.utils import trace
     with trace.span("idle"):          # disabled (or no GPU): nothing happens
